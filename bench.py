@@ -1,0 +1,564 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse FlashAttention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference] [--path auto|gather|tiled]
+
+One "step" = one forward of one mask family over one batch of seeded synthetic input. The default
+workload is the Local (sliding-window) configuration: L=65536, d=64, fp32 Q/K/V ~ N(0,1), window
+|i-j| <= 256. Other workloads (--workload csr|l1d|gnl|l2d|coo) are the remaining benchmark shapes.
+
+Multi-GPU (launched by torch.distributed.run, one rank per GPU): weak scaling over query-row ranges.
+The sequence has N*L rows; rank r owns rows [r*L, (r+1)*L) and K/V of the whole sequence are
+replicated on every rank (no reduction, no softmax-state exchange). `value` is measured with K/V
+already replicated; `e2e` includes the host->device copy of the rank's Q/K/V rows, the NCCL all-gather
+that replicates K/V, the state initialisation, the forward and the device->host copy of O.
+
+Prints ONE JSON line (rank 0). Timing: CUDA events on the launching stream around each step, L2
+flushed (256 MiB memset) and the (m, l, O) state re-initialised before each step outside the timed
+span; per-rank total = sum of step times; reported time = max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+WORKLOADS = {
+    # name: kind, L, d, p0, p1, description
+    "local": dict(kind="local", L=65536, d=64, p0=256, p1=0,
+                  desc="Local sliding window, L=65536, d=64, fp32, |i-j|<=256 (width 513)"),
+    "csr": dict(kind="csr", L=4096, d=64, p0=0, p1=0,
+                desc="CSR explicit mask, L=4096, d=64, fp32, diagonal + Bernoulli(0.01)"),
+    "l1d": dict(kind="local_1d_dilated", L=131072, d=128, p0=512, p1=1,
+                desc="Local 1D dilated, L=131072, d=128, fp32, 512 each side, every 2nd key (1025 keys/row)"),
+    "gnl": dict(kind="global_no_local", L=131072, d=128, p0=256, p1=0,
+                desc="Global-no-local, L=131072, d=128, fp32, 64 global tokens, local window 256 excluded"),
+    "l2d": dict(kind="local_2d_dilated", L=262144, d=64, p0=256, p1=4,
+                desc="Local 2D dilated (reference semantics), L=262144, d=64, fp32, block 256, dil_factor 4, use_nan"),
+    "coo": dict(kind="coo", L=1048576, d=64, p0=64, p1=0,
+                desc="COO explicit graph mask, L=1048576, d=64, fp32, Zipf(2.1) mean-32 max-8192 random cols + band 64"),
+}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# mask sizes (closed forms) and algorithmic bytes
+# ---------------------------------------------------------------------------------------------------------
+def implicit_nnz(kind, L, p0, p1, G, rb, re):
+    i = torch.arange(rb, re, dtype=torch.int64)
+    if kind == "local":
+        return int((torch.clamp(i + p0 + 1, max=L) - torch.clamp(i - p0, min=0)).sum())
+    if kind == "local_1d_dilated":
+        s = p1 + 1
+        lo = torch.maximum(i - p0 * s, i % s)
+        hi = torch.clamp(i + p0 * s, max=L - 1)
+        return int(((hi - lo) // s + 1).sum())
+    if kind == "local_2d_dilated":
+        s, B = p1 + 1, p0
+        live = ((i % B) % s == 0).sum()
+        return int(live) * min(B, (B - 1) // s + 1)
+    if kind == "global_no_local":
+        g = torch.as_tensor(G, dtype=torch.int64)
+        isg = torch.zeros(L, dtype=torch.bool)
+        isg[g] = True
+        lo, hi = torch.clamp(i - p0, min=0), torch.clamp(i + p0 + 1, max=L)
+        n_glob_rows = L - (hi - lo)
+        gs = torch.sort(g).values
+        inside = torch.searchsorted(gs, hi) - torch.searchsorted(gs, lo)
+        n_other = g.numel() - inside
+        return int(torch.where(isg[rb:re], n_glob_rows, n_other).sum())
+    raise ValueError(kind)
+
+
+def algorithmic_bytes(kind, L_keys, n_rows, d, nnz, n_live_rows):
+    """Explicit masks: gather-counted nnz*(2*d*4+4) + rows*(2*d*4+16) + 8*(rows+1).
+    Implicit masks: compulsory traffic (Q read, K and V read once, O written) + 16 B/row of (m, l)."""
+    if kind in ("csr", "coo"):
+        extra = 8 * nnz if kind == "coo" else 0
+        return nnz * (2 * d * 4 + 4) + n_live_rows * (2 * d * 4 + 16) + 8 * (n_rows + 1) + extra
+    return (2 * n_rows * d + 2 * L_keys * d) * 4 + 16 * n_live_rows
+
+
+# ---------------------------------------------------------------------------------------------------------
+# synthetic inputs
+# ---------------------------------------------------------------------------------------------------------
+def make_qkv(L, d, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    return tuple(torch.randn(L, d, device=dev, generator=g, dtype=torch.float32) for _ in range(3))
+
+
+def make_csr_mask(L, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    mask = torch.rand(L, L, device=dev, generator=g) < 0.01
+    mask |= torch.eye(L, dtype=torch.bool, device=dev)
+    counts = mask.sum(1)
+    row_off = torch.zeros(L + 1, dtype=torch.int64, device=dev)
+    row_off[1:] = torch.cumsum(counts, 0)
+    col = mask.nonzero()[:, 1].to(torch.int32).contiguous()
+    return row_off, col
+
+
+def make_coo_graph(L, band, seed, dev, mean_deg=32, max_deg=8192, alpha=2.1):
+    """Row-sorted COO: power-law out-degrees (Zipf alpha, rescaled to the mean, clipped) with uniform random
+    columns, united with the band |i-j| <= band; duplicates removed."""
+    rng = np.random.default_rng(seed)
+    z = rng.zipf(alpha, L).astype(np.float64)
+    deg = np.minimum(max_deg, np.maximum(0, np.rint(z * (mean_deg / z.mean())))).astype(np.int64)
+    deg_t = torch.from_numpy(deg).to(dev)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    r_rows = torch.repeat_interleave(torch.arange(L, device=dev), deg_t)
+    r_cols = torch.randint(0, L, (int(deg.sum()),), device=dev, generator=g)
+    key_r = r_rows * L + r_cols
+    del r_rows, r_cols
+    i = torch.arange(L, device=dev).unsqueeze(1)
+    j = i + torch.arange(-band, band + 1, device=dev).unsqueeze(0)
+    ok = (j >= 0) & (j < L)
+    key_b = (i * L + j)[ok]
+    del i, j, ok
+    keys = torch.unique(torch.cat([key_r, key_b]))  # sorted ascending = (row, col) order
+    del key_r, key_b
+    rows = (keys // L).contiguous()
+    cols = (keys % L).to(torch.int32).contiguous()
+    return rows, cols
+
+
+# ---------------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        try:  # address the GPU by UUID: nvidia-smi's numbering ignores CUDA_VISIBLE_DEVICES
+            self.gpu = "GPU-" + str(torch.cuda.get_device_properties(gpu_index).uuid)
+        except Exception:
+            self.gpu = str(gpu_index)
+        self.proc, self.lines, self.thread = None, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: [self.lines.append(x) for x in self.proc.stdout], daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val == "Active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "sm_mhz_max_seen": max(sm) if sm else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def recorded_traffic(kernel_key):
+    """DRAM bytes per launch from the committed ncu summary (profiles/dram_traffic.json), or None."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        return json.load(f).get(kernel_key)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="local", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="auto", choices=["auto", "gather", "tiled"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
+    return ap.parse_args()
+
+
+class Job:
+    """One rank's share of the workload, resident on its GPU."""
+
+    def __init__(self, workload, rank, world, dev, whole_on_one_gpu=False):
+        w = WORKLOADS[workload]
+        self.w, self.kind, self.d = w, w["kind"], w["d"]
+        self.L = w["L"] * world  # weak scaling: N*L rows in the sequence
+        if whole_on_one_gpu:  # a single-GPU implementation given the whole N*L-row job
+            self.L_local, self.rb, self.re = self.L, 0, self.L
+        else:
+            self.L_local = w["L"]
+            self.rb, self.re = rank * self.L_local, (rank + 1) * self.L_local
+        self.rank, self.world, self.dev = rank, world, dev
+        self.p0, self.p1 = w["p0"], w["p1"]
+        seed = 1000 + sorted(WORKLOADS).index(workload)
+        Q, self.K, self.V = make_qkv(self.L, self.d, seed, dev)
+        self.Q = Q[self.rb:self.re].contiguous()
+        del Q
+        self.G = None
+        self.mask = None
+        n_live = self.L_local
+        if self.kind == "global_no_local":
+            g = torch.Generator().manual_seed(seed)
+            Gc = torch.sort(torch.randperm(self.L, generator=g)[:64]).values.to(torch.int32)
+            self.G_cpu, self.G = Gc, Gc.to(dev)
+            self.nnz = implicit_nnz(self.kind, self.L, self.p0, self.p1, Gc, self.rb, self.re)
+        elif self.kind == "csr":
+            row_off, col = make_csr_mask(self.L, seed, dev)
+            lo, hi = int(row_off[self.rb]), int(row_off[self.re])
+            self.mask = ((row_off[self.rb:self.re + 1] - lo).contiguous(), col[lo:hi].contiguous())
+            self.nnz = hi - lo
+        elif self.kind == "coo":
+            rows, cols = make_coo_graph(self.L, self.p0, seed, dev)
+            edges = torch.searchsorted(rows, torch.tensor([self.rb, self.re], device=dev))
+            lo, hi = int(edges[0]), int(edges[1])
+            self.mask = (rows[lo:hi].contiguous(), cols[lo:hi].contiguous())
+            self.nnz = hi - lo
+        else:
+            self.nnz = implicit_nnz(self.kind, self.L, self.p0, self.p1, None, self.rb, self.re)
+            if self.kind == "local_2d_dilated":
+                n_live = self.L_local // (self.p1 + 1) if self.p0 % (self.p1 + 1) == 0 else None
+                if n_live is None:
+                    i = torch.arange(self.rb, self.re)
+                    n_live = int(((i % self.p0) % (self.p1 + 1) == 0).sum())
+        self.n_live = n_live
+        self.flops = 4.0 * self.nnz * self.d
+        self.bytes = algorithmic_bytes(self.kind, self.L, self.L_local, self.d, self.nnz, n_live)
+        self.m = torch.empty(self.L_local, device=dev)
+        self.l = torch.empty(self.L_local, device=dev)
+        self.O = torch.empty(self.L_local, self.d, device=dev)
+        self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def reset_state(self):
+        self.m.fill_(float("-inf"))
+        self.l.zero_()
+        self.O.zero_()
+
+    def flush_l2(self):
+        self.flush_buf.zero_()
+
+    def forward(self, capi, Q=None, K=None, V=None):
+        Q = self.Q if Q is None else Q
+        K = self.K if K is None else K
+        V = self.V if V is None else V
+        k, st = self.kind, (self.m, self.l, self.O)
+        if k == "local":
+            capi.local_forward(Q, K, V, *st, self.p0, self.rb, self.re)
+        elif k == "local_1d_dilated":
+            capi.local_1d_dilated_forward(Q, K, V, *st, self.p0, self.p1, self.rb, self.re)
+        elif k == "local_2d_dilated":
+            capi.local_2d_dilated_forward(Q, K, V, *st, self.p0, self.p1, True, self.rb, self.re)
+        elif k == "global_no_local":
+            capi.global_no_local_forward(Q, K, V, *st, self.G, self.p0, self.rb, self.re)
+        elif k == "csr":
+            capi.csr_forward(Q, K, V, self.mask[0], self.mask[1], *st, use_nan=False)
+        else:
+            capi.coo_forward(Q, K, V, self.mask[0], self.mask[1], *st, use_nan=False, row_begin=self.rb)
+
+
+def dist_max(x: float, world: int, dev) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def dist_sum(x: float, world: int, dev) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def barrier(world):
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        torch.cuda.synchronize()
+
+
+def timed_steps(job, fn, steps, warmup, world, counter=None):
+    """warmup untimed calls, then `steps` calls each bracketed by CUDA events (flush + reset outside).
+    Returns (per-step ms, kernels launched by the library inside the timed loop)."""
+    for _ in range(warmup):
+        job.reset_state()
+        fn()
+    barrier(world)
+    n0 = counter() if counter else 0
+    evs = []
+    for _ in range(steps):
+        job.reset_state()
+        job.flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        evs.append((a, b))
+    barrier(world)
+    n1 = counter() if counter else 0
+    return [a.elapsed_time(b) for a, b in evs], n1 - n0
+
+
+def run_ours(args, rank, world, dev):
+    pkg = entry.load()
+    capi = pkg.capi
+    capi.lib()
+    capi.set_path({"auto": capi.PATH_AUTO, "gather": capi.PATH_GATHER, "tiled": capi.PATH_TILED}[args.path])
+    job = Job(args.workload, rank, world, dev)
+    peaks, peak_src = load_peaks()
+
+    # ---- kernel-only: inputs resident in HBM ----
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    times, launches = timed_steps(job, lambda: job.forward(capi), args.steps, args.warmup, world, capi.launch_count)
+    tiled = capi.last_path() == capi.PATH_TILED
+    clocks = sampler.stop() if sampler else None
+    total_ms = dist_max(sum(times), world, dev)
+    total_flops = dist_sum(job.flops, world, dev)
+    total_nnz = dist_sum(float(job.nnz), world, dev)
+    value = total_flops * args.steps / (total_ms * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers -> device -> (all-gather K/V) -> forward -> host ----
+    hQ = job.Q.cpu().pin_memory()
+    hK = job.K[job.rb:job.re].cpu().pin_memory()
+    hV = job.V[job.rb:job.re].cpu().pin_memory()
+    hO = torch.empty_like(job.O, device="cpu").pin_memory()
+    dQ, dKs, dVs = torch.empty_like(job.Q), torch.empty_like(job.Q), torch.empty_like(job.Q)
+    ranges = [(r * job.L_local, (r + 1) * job.L_local) for r in range(world)]
+    binding = pkg.binding("spfa_" + job.kind) if world == 1 else None
+    w_val = torch.ones(1, device=dev)
+
+    def e2e_step():
+        dQ.copy_(hQ, non_blocking=True)
+        dKs.copy_(hK, non_blocking=True)
+        dVs.copy_(hV, non_blocking=True)
+        job.reset_state()
+        if world > 1:
+            Kf, Vf = pkg.sharding.replicate_kv(dKs, dVs, ranges)
+            job.forward(capi, dQ, Kf, Vf)
+        else:
+            st = (job.m, job.l, job.O)
+            k = job.kind
+            if k == "local":
+                binding.forward(dQ, dKs, dVs, *st, job.p0)
+            elif k == "local_1d_dilated":
+                binding.forward(dQ, dKs, dVs, *st, job.p0, job.p1)
+            elif k == "local_2d_dilated":
+                binding.forward(dQ, dKs, dVs, *st, job.p0, job.p1, True)
+            elif k == "global_no_local":
+                binding.forward(dQ, dKs, dVs, *st, job.G, job.p0)
+            elif k == "csr":
+                binding.forward(dQ, dKs, dVs, job.mask[0], job.mask[1], w_val, *st, False)
+            else:
+                binding.forward(dQ, dKs, dVs, job.mask[0], job.mask[1], w_val, *st, False)
+        hO.copy_(job.O, non_blocking=True)
+
+    e2e_times, _ = timed_steps(job, e2e_step, args.steps, args.warmup, world)
+    e2e_ms = dist_max(sum(e2e_times), world, dev)
+    e2e_value = total_flops * args.steps / (e2e_ms * 1e-3) / 1e12
+    h2d = 3 * job.L_local * job.d * 4 * world
+    d2h = job.L_local * job.d * 4 * world
+
+    if rank != 0:
+        return None
+
+    # ---- roofline of the dominant kernel (this rank's launch) ----
+    kernel_ms = statistics.mean(times)
+    if tiled:
+        peak = peaks["bf16_tflops"] / 2.0
+        achieved = job.flops / (kernel_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": recorded_traffic(f"tiled_{args.workload}"),
+                "note": f"useful flops 4*nnz*d per launch / mean launch time; peak = {peak_src} bf16 matmul / 2 taken as TF32"}
+    else:
+        peak = peaks["hbm_gbs"]
+        achieved = job.bytes / (kernel_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": recorded_traffic(f"gather_{args.workload}"),
+                "note": f"algorithmic bytes per launch / mean launch time; peak = {peak_src} copy bandwidth"}
+
+    line = {
+        "metric": "effective_nnz_tflops_fwd", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "tf32" if tiled else "f32", "data": "synthetic",
+        "config": {"workload": job.w["desc"] + (f"; sequence of {world}x{job.L_local} rows, one row range per GPU" if world > 1 else ""),
+                   "mask": job.kind, "L": job.L, "rows_per_gpu": job.L_local, "d": job.d, "nnz": int(total_nnz),
+                   "flops_per_step": total_flops, "path": args.path, "l2": "flushed (256 MiB memset) before every timed step",
+                   "state": "m=-inf,l=0,O=0 re-initialised before every step outside the timed span"},
+        "fwd_ms": total_ms / args.steps,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h,
+                "api": "spfa_%s.forward (torch extension)" % job.kind if world == 1 else "capi.*_forward(row range) + sharding.replicate_kv (NCCL all-gather)"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roof,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline(job, args.cpu_budget)
+    return line
+
+
+def cpu_baseline(job, budget):
+    """The reference's dense PyTorch CPU path (SDPA-MATH on a boolean mask), row-chunked, bounded sample."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("spfa_dense_sdpa", os.path.join(ROOT, "oracle", "dense_sdpa.py"))
+    ds = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ds)
+    if job.kind in ("csr", "coo"):
+        return {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                "sample": "not timed for explicit masks in this run"}
+    q, k, v = job.Q.cpu(), job.K.cpu(), job.V.cpu()
+    G = job.G_cpu if job.kind == "global_no_local" else None
+    chunk = 1024 if job.L <= 65536 else 512
+    r = ds.time_dense_cpu(job.kind, q, k, v, job.p0, job.p1, G, chunk_rows=chunk, budget_s=budget, max_chunks=64)
+    val = 4.0 * r["nnz"] * job.d / r["seconds"] / 1e12
+    return {"value": val, "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
+            "sample": f"{r['chunks']} evenly spaced chunks of {chunk} rows x all {job.L} keys ({r['rows']} of {job.L} rows), "
+                      f"dense scaled_dot_product_attention under SDPBackend.MATH on CPU, {r['seconds']:.1f} s, "
+                      f"{r['threads']} torch threads on {r['cores']} logical cores; useful flops 4*nnz*d of the sampled rows"}
+
+
+def run_reference(args, rank, world, dev):
+    """The reference's own CUDA kernels (compiled unmodified into oracle/_ref/) on the same workload, one GPU."""
+    if rank != 0:
+        return None
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("spfa_build_ref", os.path.join(ROOT, "oracle", "build_ref.py"))
+    br = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(br)
+    job = Job(args.workload, 0, world, dev, whole_on_one_gpu=True)  # the reference is single-GPU
+    mod = br.load(job.kind)
+    base = {"impl": "reference", "metric": "effective_nnz_tflops_fwd", "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": job.w["desc"], "mask": job.kind, "L": job.L, "d": job.d, "nnz": int(job.nnz)}}
+    if job.kind == "coo" and job.L > 65536:
+        base.update({"unavailable": "reference COO kernel scans the whole row-index array per row (O(L*nnz)); does not complete at this size"})
+        return base
+    if mod is None:
+        # no rebuilt reference kernels on this box: time the reference's dense CPU path instead
+        cb = cpu_baseline(job, max(args.cpu_budget, 10.0))
+        base.update({"value": cb["value"], "ms_per_step": None, "cpu_baseline": cb,
+                     "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                     "gpu_launches": 0, "config": {**base["config"], "arm": "dense SDPA-MATH on CPU (oracle/_ref not built)"}})
+        return base
+    w_val = torch.ones(1, device=dev)
+    st = (job.m, job.l, job.O)
+
+    def step():
+        k = job.kind
+        if k == "local":
+            mod.forward(job.Q, job.K, job.V, *st, job.p0)
+        elif k == "local_1d_dilated":
+            mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1)
+        elif k == "local_2d_dilated":
+            mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1, True)
+        elif k == "global_no_local":
+            mod.forward(job.Q, job.K, job.V, *st, job.G, job.p0)
+        else:
+            mod.forward(job.Q, job.K, job.V, job.mask[0].view(torch.uint64), job.mask[1].view(torch.uint32), w_val, *st, False)
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    # the reference launches on the legacy default stream; events are recorded there too
+    with torch.cuda.stream(torch.cuda.default_stream(dev)):
+        times, _ = timed_steps(job, step, args.steps, args.warmup, 1)
+    clocks = sampler.stop()
+    total_ms = sum(times)
+    value = job.flops * args.steps / (total_ms * 1e-3) / 1e12
+    cb = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "reference",
+          "sample": "this arm runs the reference's CUDA kernels on the GPU (the reference has no CPU implementation); "
+                    "the dense CPU path is timed in the other arm's cpu_baseline"}
+    base.update({"value": value, "ms_per_step": total_ms / args.steps, "fwd_ms": total_ms / args.steps, "clocks": clocks,
+                 "cpu_baseline": cb, "gpu_launches": args.steps,
+                 "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 "config": {**base["config"], "arm": "reference CUDA kernels compiled unmodified for sm_100a (oracle/_ref), "
+                                                      "device-resident inputs, legacy default stream",
+                            "l2": "flushed (256 MiB memset) before every timed step"}})
+    return base
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    if args.impl == "reference" and rank != 0:
+        return 0
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device: this benchmark has no CPU path"}))
+        return 1
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    try:
+        line = run_ours(args, rank, world, dev) if args.impl == "ours" else run_reference(args, rank, world, dev)
+        if line is not None:
+            print(json.dumps(line))
+    finally:
+        if world > 1 and args.impl == "ours":
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

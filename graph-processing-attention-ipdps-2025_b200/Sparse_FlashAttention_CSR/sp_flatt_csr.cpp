@@ -1,0 +1,44 @@
+// Torch-extension binding `spfa_csr` -- same module name, function name, argument order and tensor
+// layouts as the reference (Sparse_FlashAttention_CSR/sp_flatt_csr.cpp:28-59); the reference's
+// sp_flatt_csr_kernel.cu is replaced by the sm_100a library behind spfa_csr_forward_f32().
+#include "binding_common.h"
+
+// Host dispatch: stands in for spfa_csr_cuda_forward (sp_flatt_csr_kernel.cu:224-288).
+torch::Tensor spfa_csr_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor W_row_off,
+                                    torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
+                                    torch::Tensor O, bool use_nan) {
+  using namespace spfa_binding;
+  check_qkv_state(Q, K, V, m, l, O);
+  // W_val is dtype-checked by the reference's accessor (sp_flatt_csr_kernel.cu:277) and never read.
+  TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
+  TORCH_CHECK(W_row_off.dim() == 1 && W_row_off.size(0) == Q.size(0) + 1, "W_row_off must have L+1 entries");
+  TORCH_CHECK(W_col_ind.dim() == 1, "W_col_ind must be 1-D");
+  c10::cuda::CUDAGuard guard(Q.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  Workspace ws(spfa_csr_workspace_bytes(Q.size(0), (int)Q.size(1)), Q.device());
+  raise_for_status(spfa_csr_forward_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
+                                        u64_ptr(W_row_off, "W_row_off"), u32_ptr(W_col_ind, "W_col_ind"),
+                                        m.data_ptr<float>(), l.data_ptr<float>(), O.data_ptr<float>(), Q.size(0),
+                                        K.size(0), (int)Q.size(1), use_nan ? 1 : 0, ws.ptr, ws.bytes, stream.stream()));
+  return O;
+}
+
+// C++ interface for PyTorch inputs (sp_flatt_csr.cpp:28-53).
+torch::Tensor spfa_csr_forward(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor W_row_off,
+                               torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
+                               torch::Tensor O, bool use_nan) {
+  CHECK_INPUT(Q);
+  CHECK_INPUT(K);
+  CHECK_INPUT(V);
+  CHECK_INPUT(W_row_off);
+  CHECK_INPUT(W_col_ind);
+  CHECK_INPUT(W_val);
+  CHECK_INPUT(m);
+  CHECK_INPUT(l);
+  CHECK_INPUT(O);
+  return spfa_csr_cuda_forward(Q, K, V, W_row_off, W_col_ind, W_val, m, l, O, use_nan);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
+  mod.def("forward", &spfa_csr_forward, "Sparse-FlashAttention forward (CUDA)");
+}

@@ -1,0 +1,268 @@
+"""ctypes view of the C ABI (include/spfa_b200.h) for callers that hold torch CUDA tensors.
+
+Every function here is a thin argument marshaller: it checks dtype/device/contiguity, allocates the
+workspace the entry point asks for with torch's caching allocator, passes raw device pointers and the
+current torch stream, and raises on a non-zero status. No arithmetic happens in Python and there is no
+CPU path: if ``lib/libspfa_b200.so`` is missing, loading raises.
+
+Row-range arguments (``row_begin``/``row_end``) select the query rows one GPU works on; Q/m/l/O then
+hold only those rows while K/V hold all L rows. The reference API is single-GPU and has no such
+argument (README.md:10); with the defaults these calls behave exactly like its ``forward`` functions.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libspfa_b200.so")
+
+OK = 0
+PATH_AUTO, PATH_GATHER, PATH_TILED = 0, 1, 2
+MASK_KIND = {"local": 0, "local_1d_dilated": 1, "local_2d_dilated": 2, "global_no_local": 3}
+
+# every symbol include/spfa_b200.h declares (checked by the CPU test-suite)
+EXPORTS = (
+    "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count",
+    "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
+    "spfa_coo_workspace_bytes", "spfa_coo_forward_f32",
+    "spfa_local_workspace_bytes", "spfa_local_forward_f32",
+    "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
+    "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
+    "spfa_global_no_local_workspace_bytes", "spfa_global_no_local_forward_f32",
+    "spfa_mask_count", "spfa_mask_fill",
+)
+
+_lib = None
+
+
+class SpfaError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"spfa_b200 status {status}: {text}")
+        self.status = status
+
+
+def lib() -> ctypes.CDLL:
+    """Load the C-ABI library (once) and declare its signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is not built; run `python {os.path.join(_HERE, 'build.py')}`. "
+                          "There is no CPU fallback.")
+    L = ctypes.CDLL(LIB_PATH)
+    i64, i32, vp, sz = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+    L.spfa_status_string.restype = ctypes.c_char_p
+    L.spfa_status_string.argtypes = [i32]
+    L.spfa_abi_version.restype = i32
+    L.spfa_set_path.restype = None
+    L.spfa_set_path.argtypes = [i32]
+    L.spfa_get_path.restype = i32
+    L.spfa_last_path.restype = i32
+    L.spfa_launch_count.restype = i64
+    L.spfa_csr_workspace_bytes.restype = sz
+    L.spfa_csr_workspace_bytes.argtypes = [i64, i32]
+    L.spfa_csr_forward_f32.restype = i32
+    L.spfa_csr_forward_f32.argtypes = [vp] * 8 + [i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_coo_workspace_bytes.restype = sz
+    L.spfa_coo_workspace_bytes.argtypes = [i64, i32]
+    L.spfa_coo_forward_f32.restype = i32
+    L.spfa_coo_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    for name in ("spfa_local", "spfa_local_1d_dilated", "spfa_local_2d_dilated"):
+        f = getattr(L, name + "_workspace_bytes")
+        f.restype = sz
+        f.argtypes = [i64, i64, i32]
+    L.spfa_local_forward_f32.restype = i32
+    L.spfa_local_forward_f32.argtypes = [vp] * 6 + [i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_local_1d_dilated_forward_f32.restype = i32
+    L.spfa_local_1d_dilated_forward_f32.argtypes = [vp] * 6 + [i64, i32, i64, i64, i64, i64, vp, sz, vp]
+    L.spfa_local_2d_dilated_forward_f32.restype = i32
+    L.spfa_local_2d_dilated_forward_f32.argtypes = [vp] * 6 + [i64, i32, i64, i64, i32, i64, i64, vp, sz, vp]
+    L.spfa_global_no_local_workspace_bytes.restype = sz
+    L.spfa_global_no_local_workspace_bytes.argtypes = [i64, i64, i32, i64]
+    L.spfa_global_no_local_forward_f32.restype = i32
+    L.spfa_global_no_local_forward_f32.argtypes = [vp] * 7 + [i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_mask_count.restype = i32
+    L.spfa_mask_count.argtypes = [i32, i64, i64, i64, vp, i64, i64, i64, vp, vp]
+    L.spfa_mask_fill.restype = i32
+    L.spfa_mask_fill.argtypes = [i32, i64, i64, i64, vp, i64, i64, i64, vp, vp, vp]
+    _lib = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return lib().spfa_status_string(status).decode()
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise SpfaError(status, status_string(status))
+
+
+def set_path(path: int) -> None:
+    lib().spfa_set_path(path)
+
+
+def get_path() -> int:
+    return lib().spfa_get_path()
+
+
+def last_path() -> int:
+    return lib().spfa_last_path()
+
+
+def launch_count() -> int:
+    return int(lib().spfa_launch_count())
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _f32(*ts):
+    dev = ts[0].device
+    for t in ts:
+        if not t.is_cuda:
+            raise SpfaError(-1, "tensors must be CUDA tensors (there is no CPU path)")
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.device != dev:
+            raise SpfaError(-1, "floating tensors must be contiguous float32 on one device")
+    return dev
+
+
+def workspace(nbytes: int, dev) -> tuple[torch.Tensor | None, ctypes.c_void_p | None, int]:
+    """A 256-byte aligned scratch buffer from torch's caching allocator (kept alive by the caller)."""
+    if nbytes == 0:
+        return None, None, 0
+    buf = torch.empty(nbytes + 256, dtype=torch.uint8, device=dev)
+    p = (buf.data_ptr() + 255) & ~255
+    return buf, ctypes.c_void_p(p), nbytes
+
+
+def _as_u64(t):
+    if t.dtype not in (torch.uint64, torch.int64) or not t.is_contiguous():
+        raise SpfaError(-1, "row offsets/indices must be contiguous torch.uint64 (or int64)")
+    return t
+
+
+def _as_u32(t):
+    if t.dtype not in (torch.uint32, torch.int32) or not t.is_contiguous():
+        raise SpfaError(-1, "column indices must be contiguous torch.uint32 (or int32)")
+    return t
+
+
+def csr_forward(Q, K, V, row_off, col_ind, m, l, O, use_nan=False):
+    """Rows of Q attend to K/V rows col_ind[row_off[r]:row_off[r+1]]. Q may be a row shard; row_off then
+    holds that shard's n_rows+1 offsets (indexing col_ind as passed)."""
+    dev = _f32(Q, K, V, m, l, O)
+    with torch.cuda.device(dev):
+        n_rows, d = Q.shape
+        buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, d), dev)
+        check(lib().spfa_csr_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)),
+                                         _ptr(m), _ptr(l), _ptr(O), n_rows, K.shape[0], d, int(use_nan), wp, wb,
+                                         _stream(dev)))
+    return O
+
+
+def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):
+    """Row-sorted COO mask. Q holds rows [row_begin, row_begin+Q.shape[0]); (row_ind, col_ind) must contain
+    every entry of those rows (entries of other rows are ignored)."""
+    dev = _f32(Q, K, V, m, l, O)
+    with torch.cuda.device(dev):
+        n_rows, d = Q.shape
+        buf, wp, wb = workspace(lib().spfa_coo_workspace_bytes(n_rows, d), dev)
+        check(lib().spfa_coo_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)),
+                                         row_ind.shape[0], _ptr(m), _ptr(l), _ptr(O), row_begin, n_rows, K.shape[0],
+                                         d, int(use_nan), wp, wb, _stream(dev)))
+    return O
+
+
+def _rows(Q, K, row_begin, row_end):
+    L = K.shape[0]
+    row_end = L if row_end is None else row_end
+    if Q.shape[0] != row_end - row_begin:
+        raise SpfaError(-1, f"Q must hold rows [row_begin, row_end): {Q.shape[0]} != {row_end - row_begin}")
+    return L, row_end
+
+
+def local_forward(Q, K, V, m, l, O, local_size_each_dir, row_begin=0, row_end=None):
+    dev = _f32(Q, K, V, m, l, O)
+    L, row_end = _rows(Q, K, row_begin, row_end)
+    with torch.cuda.device(dev):
+        d = Q.shape[1]
+        buf, wp, wb = workspace(lib().spfa_local_workspace_bytes(L, Q.shape[0], d), dev)
+        check(lib().spfa_local_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), L, d,
+                                           int(local_size_each_dir), row_begin, row_end, wp, wb, _stream(dev)))
+    return O
+
+
+def local_1d_dilated_forward(Q, K, V, m, l, O, local_size_each_dir, dil_factor, row_begin=0, row_end=None):
+    dev = _f32(Q, K, V, m, l, O)
+    L, row_end = _rows(Q, K, row_begin, row_end)
+    with torch.cuda.device(dev):
+        d = Q.shape[1]
+        buf, wp, wb = workspace(lib().spfa_local_1d_dilated_workspace_bytes(L, Q.shape[0], d), dev)
+        check(lib().spfa_local_1d_dilated_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), L, d,
+                                                      int(local_size_each_dir), int(dil_factor), row_begin, row_end,
+                                                      wp, wb, _stream(dev)))
+    return O
+
+
+def local_2d_dilated_forward(Q, K, V, m, l, O, block_size, dil_factor, use_nan=False, row_begin=0, row_end=None):
+    dev = _f32(Q, K, V, m, l, O)
+    L, row_end = _rows(Q, K, row_begin, row_end)
+    with torch.cuda.device(dev):
+        d = Q.shape[1]
+        buf, wp, wb = workspace(lib().spfa_local_2d_dilated_workspace_bytes(L, Q.shape[0], d), dev)
+        check(lib().spfa_local_2d_dilated_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), L, d,
+                                                      int(block_size), int(dil_factor), int(use_nan), row_begin,
+                                                      row_end, wp, wb, _stream(dev)))
+    return O
+
+
+def global_no_local_forward(Q, K, V, m, l, O, global_inds, local_size_each_dir, row_begin=0, row_end=None):
+    dev = _f32(Q, K, V, m, l, O)
+    L, row_end = _rows(Q, K, row_begin, row_end)
+    if global_inds.dtype != torch.int32 or not global_inds.is_contiguous() or global_inds.device != dev:
+        raise SpfaError(-1, "global_inds must be a contiguous torch.int32 tensor on Q's device")
+    with torch.cuda.device(dev):
+        d, nG = Q.shape[1], global_inds.shape[0]
+        buf, wp, wb = workspace(lib().spfa_global_no_local_workspace_bytes(L, Q.shape[0], d, nG), dev)
+        check(lib().spfa_global_no_local_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O),
+                                                     _ptr(global_inds) if nG else None, nG, L, d,
+                                                     int(local_size_each_dir), row_begin, row_end, wp, wb,
+                                                     _stream(dev)))
+    return O
+
+
+def visited_pairs(kind: str, L: int, p0: int, p1: int = 0, global_inds=None, row_begin=0, row_end=None,
+                  device="cuda"):
+    """(row_off int64[n_rows+1], col uint32[nnz]) of the (row, key) pairs an implicit mask visits, in
+    visiting order, produced on the GPU by the kernels' own column generators."""
+    row_end = L if row_end is None else row_end
+    n_rows = row_end - row_begin
+    dev = torch.device(device)
+    with torch.cuda.device(dev):
+        counts = torch.zeros(max(n_rows, 1), dtype=torch.int64, device=dev)
+        nG = 0 if global_inds is None else global_inds.shape[0]
+        check(lib().spfa_mask_count(MASK_KIND[kind], L, int(p0), int(p1), _ptr(global_inds), nG, row_begin, row_end,
+                                    _ptr(counts), _stream(dev)))
+        row_off = torch.zeros(n_rows + 1, dtype=torch.int64, device=dev)
+        row_off[1:] = torch.cumsum(counts[:n_rows], 0)
+        nnz = int(row_off[-1].item())
+        col = torch.zeros(max(nnz, 1), dtype=torch.uint32, device=dev)
+        check(lib().spfa_mask_fill(MASK_KIND[kind], L, int(p0), int(p1), _ptr(global_inds), nG, row_begin, row_end,
+                                   _ptr(row_off), _ptr(col), _stream(dev)))
+    return row_off, col[:nnz]
+
+
+def new_state(n_rows: int, d: int, device="cuda"):
+    """Initial softmax state the operators expect: m = -inf, l = 0, O = 0."""
+    return (torch.full((n_rows,), float("-inf"), dtype=torch.float32, device=device),
+            torch.zeros(n_rows, dtype=torch.float32, device=device),
+            torch.zeros(n_rows, d, dtype=torch.float32, device=device))

@@ -1,0 +1,313 @@
+// FP32 gather path: one warp per query row, K/V rows fetched with 128-bit loads.
+//
+// Layout of a warp: a key row of D floats is D/4 float4s, so LPK = D/4 lanes cover one key and the
+// warp works on KPS = 32/LPK keys at once ("key groups"). Each group keeps its own online-softmax
+// state (m, l, acc) over the slots it owns; the groups are merged once at the end of the row, then
+// merged with the caller's (m, l, O) state. All arithmetic is fp32 FMA; exponentials are ex2.approx.
+//
+// Replaces the per-row CTA loop of the reference (sp_flatt_csr_kernel.cu:104-205 and its five copies):
+// same key visiting order, same state recurrence, no shared memory, no block barriers.
+#pragma once
+#include "spfa_common.cuh"
+
+namespace spfa {
+
+constexpr int kGatherWarps = 4;  // warps (rows) per CTA
+constexpr int kGatherUnroll = 4; // keys in flight per group per step
+
+template <int D>
+struct RowAcc {
+  float m, l;
+  float4 acc;
+};
+
+// Online-softmax accumulation of slots [t0, t1) of one row into the calling lane's group state.
+template <int D, class Cols>
+__device__ __forceinline__ void accumulate_slots(const Cols& cols, const typename Cols::Row& row,
+                                                 int64_t t0, int64_t t1, const float4 q,
+                                                 const float* __restrict__ K, const float* __restrict__ V,
+                                                 float scale, int lane, RowAcc<D>& st) {
+  constexpr int LPK = D / 4;
+  constexpr int KPS = 32 / LPK;
+  constexpr int U = (LPK < kGatherUnroll) ? LPK : kGatherUnroll;
+  const int grp = lane / LPK, sub = lane % LPK;
+
+  for (int64_t base = t0; base < t1; base += 32) {
+    const int64_t tl = base + lane;
+    const int32_t c_lane = (tl < t1) ? cols.slot(row, tl) : -1;
+    const int nb = (t1 - base < 32) ? (int)(t1 - base) : 32;
+#pragma unroll 1
+    for (int j0 = 0; j0 < LPK; j0 += U) {
+      if (j0 * KPS >= nb) break;  // warp-uniform
+      int32_t c[U];
+      float4 k4[U], v4[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        c[u] = __shfl_sync(kFullMask, c_lane, grp + (j0 + u) * KPS);
+        if (c[u] >= 0) {
+          const size_t off = (size_t)c[u] * D + sub * 4;
+          k4[u] = ldg4(K + off);
+          v4[u] = ldg4(V + off);
+        } else {
+          k4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          v4[u] = k4[u];
+        }
+      }
+      float s[U];
+      float mc = neg_inf();
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float p = q.x * k4[u].x;
+        p = fmaf(q.y, k4[u].y, p);
+        p = fmaf(q.z, k4[u].z, p);
+        p = fmaf(q.w, k4[u].w, p);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) p += __shfl_xor_sync(kFullMask, p, o);
+        s[u] = (c[u] >= 0) ? p * scale : neg_inf();
+        mc = fmaxf(mc, s[u]);
+      }
+      const float m_new = fmaxf(st.m, mc);
+      const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
+      const float corr = fast_exp2((st.m - m_safe) * kLog2e);
+      float lsum = 0.f;
+      float4 a = make_float4(st.acc.x * corr, st.acc.y * corr, st.acc.z * corr, st.acc.w * corr);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float p = fast_exp2((s[u] - m_safe) * kLog2e);
+        lsum += p;
+        a.x = fmaf(p, v4[u].x, a.x);
+        a.y = fmaf(p, v4[u].y, a.y);
+        a.z = fmaf(p, v4[u].z, a.z);
+        a.w = fmaf(p, v4[u].w, a.w);
+      }
+      st.acc = a;
+      st.l = fmaf(st.l, corr, lsum);
+      st.m = m_new;
+    }
+  }
+}
+
+// Merge the KPS key-group states of a warp; afterwards every lane holds the whole-row (m, l) and the
+// un-normalised accumulator slice for dims [4*sub, 4*sub+4).
+template <int D>
+__device__ __forceinline__ void merge_groups(RowAcc<D>& st) {
+  constexpr int LPK = D / 4;
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+    const float mo = __shfl_xor_sync(kFullMask, st.m, o);
+    const float lo = __shfl_xor_sync(kFullMask, st.l, o);
+    float4 ao;
+    ao.x = __shfl_xor_sync(kFullMask, st.acc.x, o);
+    ao.y = __shfl_xor_sync(kFullMask, st.acc.y, o);
+    ao.z = __shfl_xor_sync(kFullMask, st.acc.z, o);
+    ao.w = __shfl_xor_sync(kFullMask, st.acc.w, o);
+    const float mn = fmaxf(st.m, mo);
+    const float ms = (mn == neg_inf()) ? 0.f : mn;
+    const float c1 = fast_exp2((st.m - ms) * kLog2e);
+    const float c2 = fast_exp2((mo - ms) * kLog2e);
+    st.l = st.l * c1 + lo * c2;
+    st.acc.x = st.acc.x * c1 + ao.x * c2;
+    st.acc.y = st.acc.y * c1 + ao.y * c2;
+    st.acc.z = st.acc.z * c1 + ao.z * c2;
+    st.acc.w = st.acc.w * c1 + ao.w * c2;
+    st.m = mn;
+  }
+}
+
+// Fold a finished row (m_loc, l_loc, un-normalised acc) into the caller's state and store it.
+// O_out = (l_in e^{m_in-m_out} O_in + e^{m_loc-m_out} acc) / l_out -- the recurrence of
+// sp_flatt_csr_kernel.cu:162-194 applied once to the whole row. No guard on 0*NaN: a row a previous
+// call NaN-filled stays NaN, as it does in the reference.
+template <int D>
+__device__ __forceinline__ void store_row(const RowAcc<D>& st, float* __restrict__ m, float* __restrict__ l,
+                                          float* __restrict__ O, int64_t r, int lane) {
+  constexpr int LPK = D / 4;
+  const float m_in = m[r], l_in = l[r];
+  const float m_out = fmaxf(m_in, st.m);
+  const float a = l_in * fast_exp2((m_in - m_out) * kLog2e);
+  const float b = fast_exp2((st.m - m_out) * kLog2e);
+  const float l_out = fmaf(st.l, b, a);
+  const float inv = 1.0f / l_out;
+  if (lane < LPK) {
+    float4* op = reinterpret_cast<float4*>(O + (size_t)r * D) + lane;
+    float4 o = *op;
+    o.x = (a * o.x + b * st.acc.x) * inv;
+    o.y = (a * o.y + b * st.acc.y) * inv;
+    o.z = (a * o.z + b * st.acc.z) * inv;
+    o.w = (a * o.w + b * st.acc.w) * inv;
+    *op = o;
+  }
+  if (lane == 0) {
+    m[r] = m_out;
+    l[r] = l_out;
+  }
+}
+
+template <int D>
+__device__ __forceinline__ void nan_fill_row(float* __restrict__ O, int64_t r, int lane) {
+  constexpr int LPK = D / 4;
+  if (lane < LPK) {
+    const float n = __int_as_float(0x7fc00000);
+    reinterpret_cast<float4*>(O + (size_t)r * D)[lane] = make_float4(n, n, n, n);
+  }
+}
+
+// One warp per row of the shard. Q/m/l/O are indexed by shard-local row; the generator sees the
+// absolute row (row_begin + r).
+template <int D, class Cols>
+__global__ void __launch_bounds__(kGatherWarps * 32)
+gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                   float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
+                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale) {
+  constexpr int LPK = D / 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t r = (int64_t)blockIdx.x * kGatherWarps + warp;
+  if (r >= n_rows) return;
+  const typename Cols::Row row = cols.open(r, row_begin + r);
+  if (row.n <= 0) {
+    if (Cols::kNanFillEmpty && use_nan) nan_fill_row<D>(O, r, lane);
+    return;
+  }
+  const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
+  RowAcc<D> st;
+  st.m = neg_inf();
+  st.l = 0.f;
+  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  accumulate_slots<D, Cols>(cols, row, 0, row.n, q, K, V, scale, lane, st);
+  merge_groups<D>(st);
+  if (st.l > 0.f) store_row<D>(st, m, l, O, r, lane);
+}
+
+// Split-row variant for very long rows: entry e of row_list is processed by n_split warps, each
+// over a contiguous slot range; partial states go to `partials` ((D+4) floats per (entry, split):
+// acc[D], m, l, pad, pad) and are folded into the caller's state by combine_partials_kernel.
+template <int D, class Cols>
+__global__ void __launch_bounds__(kGatherWarps * 32)
+gather_split_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                         const Cols cols, const int32_t* __restrict__ row_list,
+                         const uint8_t* __restrict__ entry_live, int64_t row_begin, int64_t row_end,
+                         int n_split, int64_t slots_per_split, float* __restrict__ partials, float scale) {
+  constexpr int LPK = D / 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.y;
+  const int split = blockIdx.x * kGatherWarps + warp;
+  if (split >= n_split) return;
+  float* part = partials + ((size_t)e * n_split + split) * (D + 4);
+  RowAcc<D> st;
+  st.m = neg_inf();
+  st.l = 0.f;
+  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int64_t i = row_list[e];
+  const bool live = entry_live[e] && i >= row_begin && i < row_end;
+  if (live) {
+    const int64_t r = i - row_begin;
+    const typename Cols::Row row = cols.open(r, i);
+    const int64_t t0 = (int64_t)split * slots_per_split;
+    int64_t t1 = t0 + slots_per_split;
+    if (t1 > row.n) t1 = row.n;
+    if (t0 < t1) {
+      const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
+      accumulate_slots<D, Cols>(cols, row, t0, t1, q, K, V, scale, lane, st);
+      merge_groups<D>(st);
+    }
+  }
+  if (lane < LPK) reinterpret_cast<float4*>(part)[lane] = st.acc;
+  if (lane == 0) {
+    part[D] = st.m;
+    part[D + 1] = st.l;
+  }
+}
+
+// One warp per list entry: merges that entry's n_split partial states in split order, then folds the
+// result into (m, l, O).
+template <int D>
+__global__ void __launch_bounds__(kGatherWarps * 32)
+combine_partials_kernel(const float* __restrict__ partials, const int32_t* __restrict__ row_list,
+                        const uint8_t* __restrict__ entry_live, int n_entries, int64_t row_begin,
+                        int64_t row_end, int n_split, float* __restrict__ m, float* __restrict__ l,
+                        float* __restrict__ O) {
+  constexpr int LPK = D / 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.x * kGatherWarps + warp;
+  if (e >= n_entries) return;
+  const int64_t i = row_list[e];
+  if (!entry_live[e] || i < row_begin || i >= row_end) return;
+  RowAcc<D> st;
+  st.m = neg_inf();
+  st.l = 0.f;
+  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int sub = lane % LPK;
+  for (int sp = 0; sp < n_split; ++sp) {
+    const float* part = partials + ((size_t)e * n_split + sp) * (D + 4);
+    const float mo = part[D], lo = part[D + 1];
+    const float4 ao = reinterpret_cast<const float4*>(part)[sub];
+    const float mn = fmaxf(st.m, mo);
+    const float ms = (mn == neg_inf()) ? 0.f : mn;
+    const float c1 = fast_exp2((st.m - ms) * kLog2e);
+    const float c2 = fast_exp2((mo - ms) * kLog2e);
+    st.l = st.l * c1 + lo * c2;
+    st.acc.x = st.acc.x * c1 + ao.x * c2;
+    st.acc.y = st.acc.y * c1 + ao.y * c2;
+    st.acc.z = st.acc.z * c1 + ao.z * c2;
+    st.acc.w = st.acc.w * c1 + ao.w * c2;
+    st.m = mn;
+  }
+  if (st.l > 0.f) store_row<D>(st, m, l, O, i - row_begin, lane);
+}
+
+// ---- COO row pointers --------------------------------------------------------------------------
+// ptr[r] = first k with row_ind[k] >= row_begin + r, for r in [0, n_rows]. One pass over the sorted
+// row array: position k writes the pointers of all rows in (row_ind[k-1], row_ind[k]].
+__global__ void coo_row_pointers_kernel(const uint64_t* __restrict__ row_ind, int64_t nnz,
+                                        int64_t row_begin, int64_t n_rows, uint64_t* __restrict__ ptr) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k <= nnz; k += stride) {
+    // rows strictly above `prev` and up to `cur` start at k
+    int64_t prev = (k == 0) ? (row_begin - 1) : (int64_t)row_ind[k - 1];
+    int64_t cur = (k == nnz) ? (row_begin + n_rows) : (int64_t)row_ind[k];
+    if (cur == prev) continue;
+    int64_t a = prev + 1 - row_begin, b = cur - row_begin;
+    if (a < 0) a = 0;
+    if (b > n_rows) b = n_rows;
+    for (int64_t r = a; r <= b; ++r) ptr[r] = (uint64_t)k;
+  }
+}
+
+// ---- Global-no-local: mark the listed rows -------------------------------------------------------
+// bits must be zero on entry. entry_live[t] = 1 for the first list position naming a row.
+__global__ void gnl_mark_globals_kernel(const int32_t* __restrict__ G, int64_t nG, int64_t L,
+                                        uint32_t* __restrict__ bits, uint8_t* __restrict__ entry_live) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nG) return;
+  const int64_t g = G[t];
+  if (g < 0 || g >= L) { entry_live[t] = 0; return; }
+  const uint32_t bit = 1u << (g & 31);
+  const uint32_t old = atomicOr(bits + (g >> 5), bit);
+  entry_live[t] = (old & bit) ? 0 : 1;
+}
+
+// ---- visited-pair dump ----------------------------------------------------------------------------
+template <class Cols>
+__global__ void mask_count_kernel(const Cols cols, int64_t row_begin, int64_t n_rows, int64_t* __restrict__ counts) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const typename Cols::Row row = cols.open(r, row_begin + r);
+  int64_t n = 0;
+  for (int64_t t = 0; t < row.n; ++t) n += (cols.slot(row, t) >= 0);
+  counts[r] = n;
+}
+
+template <class Cols>
+__global__ void mask_fill_kernel(const Cols cols, int64_t row_begin, int64_t n_rows,
+                                 const int64_t* __restrict__ row_off, uint32_t* __restrict__ col_out) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const typename Cols::Row row = cols.open(r, row_begin + r);
+  int64_t w = row_off[r];
+  for (int64_t t = 0; t < row.n; ++t) {
+    const int32_t c = cols.slot(row, t);
+    if (c >= 0) col_out[w++] = (uint32_t)c;
+  }
+}
+
+}  // namespace spfa

@@ -1,0 +1,345 @@
+// C ABI of the library (declared in include/spfa_b200.h): argument validation, workspace carving and
+// kernel dispatch. No torch types, no exceptions, no allocation.
+#include "../../include/spfa_b200.h"
+
+#include <atomic>
+#include <cmath>
+
+#include "gather_kernels.cuh"
+#include "tile_dispatch.cuh"
+
+namespace spfa {
+
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_path{SPFA_PATH_AUTO};
+std::atomic<int> g_last_path{SPFA_PATH_GATHER};
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool supported_d(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+
+inline int launch_status() {
+  return cudaGetLastError() == cudaSuccess ? SPFA_OK : SPFA_ERR_LAUNCH;
+}
+
+template <int D, class Cols>
+int launch_gather(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                  const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
+  if (n_rows <= 0) return SPFA_OK;
+  const int64_t blocks = (n_rows + kGatherWarps - 1) / kGatherWarps;
+  if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  const float scale = 1.0f / sqrtf((float)D);
+  gather_rows_kernel<D, Cols><<<(unsigned)blocks, kGatherWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, row_begin,
+                                                                             n_rows, use_nan, scale);
+  g_launches.fetch_add(1);
+  g_last_path.store(SPFA_PATH_GATHER);
+  return launch_status();
+}
+
+template <class Cols>
+int dispatch_gather(int d, const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                    const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
+  switch (d) {
+    case 16: return launch_gather<16, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+    case 32: return launch_gather<32, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+    case 64: return launch_gather<64, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+    case 128: return launch_gather<128, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
+}
+
+inline int check_common(const void* Q, const void* K, const void* V, const void* m, const void* l, const void* O,
+                        int d) {
+  if (!supported_d(d)) return SPFA_ERR_EMBED_DIM;
+  if (!Q || !K || !V || !m || !l || !O) return SPFA_ERR_BAD_ARG;
+  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return SPFA_ERR_BAD_ARG;
+  return SPFA_OK;
+}
+
+inline int check_rows(int64_t L, int64_t row_begin, int64_t row_end) {
+  if (L <= 0 || L >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (row_begin < 0 || row_end < row_begin || row_end > L) return SPFA_ERR_BAD_ARG;
+  return SPFA_OK;
+}
+
+inline int check_workspace(const void* ws, size_t have, size_t need) {
+  if (need == 0) return SPFA_OK;
+  if (!ws || have < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return SPFA_ERR_WORKSPACE;
+  return SPFA_OK;
+}
+
+// Split of the global rows' key range: enough warps for a few waves over 148 SMs, ranges a multiple
+// of 32 slots.
+struct GnlPlan {
+  int n_split;
+  int64_t slots_per_split;
+  size_t off_bits, off_live, off_part, total;
+};
+
+inline GnlPlan gnl_plan(int64_t L, int d, int64_t nG) {
+  GnlPlan p;
+  int64_t want = (148 * 32 + nG - 1) / (nG > 0 ? nG : 1);
+  int64_t max_split = (L + 255) / 256;
+  if (want < 1) want = 1;
+  if (want > max_split) want = max_split;
+  if (want > 1024) want = 1024;
+  int64_t sps = (L + want - 1) / want;
+  sps = (sps + 31) / 32 * 32;
+  p.slots_per_split = sps;
+  p.n_split = (int)((L + sps - 1) / sps);
+  p.off_bits = 0;
+  p.off_live = align_up((size_t)((L + 31) / 32) * 4);
+  p.off_part = p.off_live + align_up((size_t)nG);
+  p.total = p.off_part + align_up((size_t)nG * p.n_split * (d + 4) * sizeof(float));
+  return p;
+}
+
+template <int D>
+int launch_gnl_global_rows(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                           const int32_t* G, int64_t nG, int64_t L, int64_t w, int64_t row_begin, int64_t row_end,
+                           const GnlPlan& plan, const uint8_t* live, float* partials, cudaStream_t st) {
+  GnlGlobalRowCols cols{L, w};
+  const float scale = 1.0f / sqrtf((float)D);
+  dim3 grid((plan.n_split + kGatherWarps - 1) / kGatherWarps, (unsigned)nG);
+  gather_split_rows_kernel<D, GnlGlobalRowCols><<<grid, kGatherWarps * 32, 0, st>>>(
+      Q, K, V, cols, G, live, row_begin, row_end, plan.n_split, plan.slots_per_split, partials, scale);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  combine_partials_kernel<D><<<(unsigned)((nG + kGatherWarps - 1) / kGatherWarps), kGatherWarps * 32, 0, st>>>(
+      partials, G, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
+  g_launches.fetch_add(1);
+  return launch_status();
+}
+
+template <class F>
+inline int with_mask_cols(int kind, int64_t L, int64_t p0, int64_t p1, const int32_t* G, int64_t nG, F&& f) {
+  switch (kind) {
+    case 0: return f(LocalCols{L, p0});
+    case 1: return f(Local1dCols{L, p0, p1 + 1});
+    case 2: return f(Local2dCols{L, p0, p1 + 1});
+    case 3: {
+      if (!G || nG <= 0) return SPFA_ERR_GLOBAL_COUNT;
+      GnlDumpCols c;
+      c.list = GnlCols{G, nG, L, p0, nullptr};
+      c.strip = GnlGlobalRowCols{L, p0};
+      return f(c);
+    }
+  }
+  return SPFA_ERR_BAD_ARG;
+}
+
+}  // namespace spfa
+
+using namespace spfa;
+
+extern "C" {
+
+const char* spfa_status_string(int s) {
+  switch (s) {
+    case SPFA_OK: return "ok";
+    case SPFA_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, negative size, or row range outside [0, L])";
+    case SPFA_ERR_EMBED_DIM: return "The embedded dimension is not supported (must be 16, 32, 64 or 128).";
+    case SPFA_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
+    case SPFA_ERR_LAUNCH: return "CUDA reported an error while enqueueing a kernel";
+    case SPFA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    case SPFA_ERR_LOCAL_SIZE: return "The local size specified is either negative or greater than/equal to (1 - Sequence Length).";
+    case SPFA_ERR_DILATION_NEG: return "The dilation factor must be atleast 0.";
+    case SPFA_ERR_BLOCK_DIVISOR: return "The block/window size must be a divisor of the whole tensor's size.";
+    case SPFA_ERR_DILATION_BLOCK: return "The dilation factor must be less than the block/window size.";
+    case SPFA_ERR_GLOBAL_COUNT: return "There are either no global tokens provided or there are more than the sequence length given.";
+    case SPFA_ERR_TOO_LARGE: return "size beyond a fixed maximum";
+  }
+  return "unknown status";
+}
+
+int spfa_abi_version(void) { return 1000; }
+
+void spfa_set_path(int path) {
+  if (path == SPFA_PATH_AUTO || path == SPFA_PATH_GATHER || path == SPFA_PATH_TILED) g_path.store(path);
+}
+int spfa_get_path(void) { return g_path.load(); }
+int spfa_last_path(void) { return g_last_path.load(); }
+
+int64_t spfa_launch_count(void) { return g_launches.load(); }
+
+// ---- CSR -----------------------------------------------------------------------------------------
+size_t spfa_csr_workspace_bytes(int64_t, int) { return 0; }
+
+int spfa_csr_forward_f32(const float* Q, const float* K, const float* V, const uint64_t* row_off,
+                         const uint32_t* col_ind, float* m, float* l, float* O, int64_t n_rows, int64_t Lk, int d,
+                         int use_nan, void*, size_t, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (!row_off || n_rows < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0) return SPFA_OK;
+  if (!col_ind) return SPFA_ERR_BAD_ARG;
+  CsrCols cols{row_off, col_ind, Lk};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, 0, n_rows, use_nan, (cudaStream_t)stream);
+}
+
+// ---- COO -----------------------------------------------------------------------------------------
+size_t spfa_coo_workspace_bytes(int64_t n_rows, int) {
+  return n_rows < 0 ? 0 : align_up((size_t)(n_rows + 1) * sizeof(uint64_t));
+}
+
+int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const uint64_t* row_ind,
+                         const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t row_begin,
+                         int64_t n_rows, int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (nnz < 0 || n_rows < 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0) return SPFA_OK;
+  rc = check_workspace(workspace, workspace_bytes, spfa_coo_workspace_bytes(n_rows, d));
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
+  int64_t blocks = (nnz + 1 + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  CsrCols cols{ptr, col_ind, Lk};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+}
+
+// ---- Local ---------------------------------------------------------------------------------------
+size_t spfa_local_workspace_bytes(int64_t, int64_t, int) { return 0; }
+
+int spfa_local_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L,
+                           int d, int64_t w, int64_t row_begin, int64_t row_end, void*, size_t, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  rc = check_rows(L, row_begin, row_end);
+  if (rc) return rc;
+  if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int path = g_path.load();
+  if (path != SPFA_PATH_GATHER) {
+    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, /*stride=*/1, row_begin, row_end, path == SPFA_PATH_TILED, st);
+    if (rc != SPFA_TILE_NOT_TAKEN) {
+      if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
+      return rc;
+    }
+  }
+  LocalCols cols{L, w};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);
+}
+
+// ---- Local 1D dilated ------------------------------------------------------------------------------
+size_t spfa_local_1d_dilated_workspace_bytes(int64_t, int64_t, int) { return 0; }
+
+int spfa_local_1d_dilated_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                      int64_t L, int d, int64_t w, int64_t dil, int64_t row_begin, int64_t row_end,
+                                      void*, size_t, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  rc = check_rows(L, row_begin, row_end);
+  if (rc) return rc;
+  if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
+  if (dil < 0) return SPFA_ERR_DILATION_NEG;
+  if (dil >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int path = g_path.load();
+  if (path != SPFA_PATH_GATHER) {
+    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, dil + 1, row_begin, row_end, path == SPFA_PATH_TILED, st);
+    if (rc != SPFA_TILE_NOT_TAKEN) {
+      if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
+      return rc;
+    }
+  }
+  Local1dCols cols{L, w, dil + 1};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);
+}
+
+// ---- Local 2D dilated ------------------------------------------------------------------------------
+size_t spfa_local_2d_dilated_workspace_bytes(int64_t, int64_t, int) { return 0; }
+
+int spfa_local_2d_dilated_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                      int64_t L, int d, int64_t B, int64_t dil, int use_nan, int64_t row_begin,
+                                      int64_t row_end, void*, size_t, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  rc = check_rows(L, row_begin, row_end);
+  if (rc) return rc;
+  if (B <= 0 || L % B != 0) return SPFA_ERR_BLOCK_DIVISOR;
+  if (dil < 0) return SPFA_ERR_DILATION_NEG;
+  if (dil >= (1LL << 31) || B / (dil + 1) < 1) return SPFA_ERR_DILATION_BLOCK;
+  Local2dCols cols{L, B, dil + 1};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, use_nan, (cudaStream_t)stream);
+}
+
+// ---- Global-no-local -------------------------------------------------------------------------------
+size_t spfa_global_no_local_workspace_bytes(int64_t L, int64_t, int d, int64_t n_global) {
+  if (L <= 0 || n_global <= 0 || !supported_d(d)) return 0;
+  return gnl_plan(L, d, n_global).total;
+}
+
+int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                     const int32_t* G, int64_t nG, int64_t L, int d, int64_t w, int64_t row_begin,
+                                     int64_t row_end, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  rc = check_rows(L, row_begin, row_end);
+  if (rc) return rc;
+  if (nG == 0 || nG > L || nG < 0) return SPFA_ERR_GLOBAL_COUNT;
+  if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
+  if (!G) return SPFA_ERR_BAD_ARG;
+  if (nG > 65535) return SPFA_ERR_TOO_LARGE;  // grid.y of the global-row kernel
+  const GnlPlan plan = gnl_plan(L, d, nG);
+  rc = check_workspace(workspace, workspace_bytes, plan.total);
+  if (rc) return rc;
+  if (row_end == row_begin) return SPFA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = reinterpret_cast<char*>(workspace);
+  uint32_t* bits = reinterpret_cast<uint32_t*>(ws + plan.off_bits);
+  uint8_t* live = reinterpret_cast<uint8_t*>(ws + plan.off_live);
+  float* partials = reinterpret_cast<float*>(ws + plan.off_part);
+  if (cudaMemsetAsync(bits, 0, (size_t)((L + 31) / 32) * 4, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  gnl_mark_globals_kernel<<<(unsigned)((nG + 255) / 256), 256, 0, st>>>(G, nG, L, bits, live);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  // rows outside the list: listed keys outside the window
+  GnlCols cols{G, nG, L, w, bits};
+  rc = dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);
+  if (rc) return rc;
+  // rows in the list: all keys outside the window, key range split across warps
+  switch (d) {
+    case 16: return launch_gnl_global_rows<16>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
+    case 32: return launch_gnl_global_rows<32>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
+    case 64: return launch_gnl_global_rows<64>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
+    case 128: return launch_gnl_global_rows<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
+}
+
+// ---- visited-pair dump -----------------------------------------------------------------------------
+int spfa_mask_count(int kind, int64_t L, int64_t p0, int64_t p1, const int32_t* G, int64_t nG, int64_t row_begin,
+                    int64_t row_end, int64_t* counts, void* stream) {
+  int rc = check_rows(L, row_begin, row_end);
+  if (rc || !counts) return SPFA_ERR_BAD_ARG;
+  const int64_t n_rows = row_end - row_begin;
+  if (n_rows == 0) return SPFA_OK;
+  return with_mask_cols(kind, L, p0, p1, G, nG, [&](auto cols) {
+    mask_count_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, (cudaStream_t)stream>>>(cols, row_begin, n_rows, counts);
+    g_launches.fetch_add(1);
+    return launch_status();
+  });
+}
+
+int spfa_mask_fill(int kind, int64_t L, int64_t p0, int64_t p1, const int32_t* G, int64_t nG, int64_t row_begin,
+                   int64_t row_end, const int64_t* row_off, uint32_t* col_out, void* stream) {
+  int rc = check_rows(L, row_begin, row_end);
+  if (rc || !row_off || !col_out) return SPFA_ERR_BAD_ARG;
+  const int64_t n_rows = row_end - row_begin;
+  if (n_rows == 0) return SPFA_OK;
+  return with_mask_cols(kind, L, p0, p1, G, nG, [&](auto cols) {
+    mask_fill_kernel<<<(unsigned)((n_rows + 127) / 128), 128, 0, (cudaStream_t)stream>>>(cols, row_begin, n_rows, row_off,
+                                                                                       col_out);
+    g_launches.fetch_add(1);
+    return launch_status();
+  });
+}
+
+}  // extern "C"

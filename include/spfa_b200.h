@@ -1,0 +1,167 @@
+/*
+ * spfa_b200.h -- C ABI of the B200 (sm_100a) sparse FlashAttention forward library.
+ *
+ * One entry point per attention-mask family of KLab-AI3/Graph-Processing-Attention-IPDPS-2025.
+ * Each replaces the host dispatch function + CUDA kernel of one reference folder; the reference
+ * interface every function stands in for is cited beside it (paths relative to the reference tree).
+ *
+ * Conventions shared by all entry points
+ *   - All pointers are DEVICE pointers on the current CUDA device. Nothing is allocated or freed
+ *     by the library: scratch memory comes in through (workspace, workspace_bytes).
+ *   - Q, K, V, O are row-major [rows, d] float32; m, l are float32 vectors. K and V hold all
+ *     Lk key rows. Q, m, l, O address ONLY the query rows this call works on: element 0 is the
+ *     first row of the shard (absolute row `row_begin` for the implicit masks). A single-GPU
+ *     caller passes the full tensors with row_begin = 0, row_end = L.
+ *   - (m, l, O) are read-modify-write softmax state, exactly as in the reference
+ *     (Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:79-92 load, :208-218 store):
+ *       m_out = max(m_in, max_j s_ij)               s_ij = q_i . k_j / sqrt(d)
+ *       l_out = l_in e^{m_in-m_out} + sum_j e^{s_ij-m_out}
+ *       O_out = (l_in e^{m_in-m_out} O_in + sum_j e^{s_ij-m_out} v_j) / l_out
+ *     Initial state is m = -inf, l = 0, O = 0. Rows whose key set is empty are left untouched
+ *     (or O is NaN-filled where the family has a use_nan flag and it is non-zero).
+ *   - `stream` is a cudaStream_t passed as void*. Calls are asynchronous; they return after
+ *     enqueueing. The return value is SPFA_OK or a negative spfa_status.
+ *   - d must be one of 16, 32, 64, 128.
+ */
+#ifndef SPFA_B200_H_
+#define SPFA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum spfa_status {
+  SPFA_OK = 0,
+  SPFA_ERR_BAD_ARG = -1,        /* null pointer, negative size, row range outside [0, L] */
+  SPFA_ERR_EMBED_DIM = -2,      /* d not supported (reference: "embedded dimension is too large", sp_flatt_csr_kernel.cu:264-266) */
+  SPFA_ERR_WORKSPACE = -3,      /* workspace missing, misaligned (256 B) or smaller than *_workspace_bytes() */
+  SPFA_ERR_LAUNCH = -4,         /* CUDA reported an error when enqueueing */
+  SPFA_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (reported by spfa_last_device_error) */
+  SPFA_ERR_LOCAL_SIZE = -6,     /* local_size_each_dir < 0 or > L-1 (sp_flatt_local_kernel.cu:252-254) */
+  SPFA_ERR_DILATION_NEG = -7,   /* dil_factor < 0 (sp_flatt_local_1d_dilated_kernel.cu:259-261) */
+  SPFA_ERR_BLOCK_DIVISOR = -8,  /* L % block_size != 0 (sp_flatt_local_2d_dilated_kernel.cu:274-276) */
+  SPFA_ERR_DILATION_BLOCK = -9, /* block_size / (dil_factor+1) < 1 (sp_flatt_local_2d_dilated_kernel.cu:284-286) */
+  SPFA_ERR_GLOBAL_COUNT = -10,  /* n_global == 0 or > L (sp_flatt_global_no_local_kernel.cu:325-327) */
+  SPFA_ERR_TOO_LARGE = -11      /* size beyond a stated fixed maximum */
+} spfa_status;
+
+/* Human-readable text for a status code (static storage). */
+const char* spfa_status_string(int status);
+
+/* Library/ABI version: major*1000 + minor. */
+int spfa_abi_version(void);
+
+/* Execution path selector for the implicit-mask entry points.
+ *   SPFA_PATH_AUTO   library picks (tiled tensor-core path when the window is wide enough, else gather)
+ *   SPFA_PATH_GATHER FP32 warp-per-row gather path (max-abs error ~1e-6 vs fp64)
+ *   SPFA_PATH_TILED  tcgen05 TF32 tiled path (max-abs error <= 2e-3 vs fp64); falls back to
+ *                    SPFA_ERR_BAD_ARG if the shape is not supported by that path
+ * The choice is process-wide state for testing and benchmarking; default AUTO. */
+enum { SPFA_PATH_AUTO = 0, SPFA_PATH_GATHER = 1, SPFA_PATH_TILED = 2 };
+void spfa_set_path(int path);
+int spfa_get_path(void);
+/* Path the most recent forward call of this process actually took (SPFA_PATH_GATHER or SPFA_PATH_TILED). */
+int spfa_last_path(void);
+
+/* ---- explicit CSR mask ------------------------------------------------------------------------
+ * Replaces spfa_csr_cuda_forward + spfa_csr_cuda_forward_kernel
+ * (Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:224-288, :14-220).
+ * Row r of the shard attends to K/V rows col_ind[row_off[r] .. row_off[r+1]) in storage order.
+ * row_off has n_rows+1 entries that index col_ind directly. Column values >= Lk are skipped.
+ * The reference's W_val argument is never read by the reference kernel and is not part of the ABI. */
+size_t spfa_csr_workspace_bytes(int64_t n_rows, int d);
+int spfa_csr_forward_f32(const float* Q, const float* K, const float* V,
+                         const uint64_t* row_off, const uint32_t* col_ind,
+                         float* m, float* l, float* O,
+                         int64_t n_rows, int64_t Lk, int d, int use_nan,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- explicit COO mask ------------------------------------------------------------------------
+ * Replaces spfa_coo_cuda_forward + spfa_coo_cuda_forward_kernel
+ * (Sparse_FlashAttention_COO/sp_flatt_coo_kernel.cu:263-327, :14-259).
+ * row_ind (ascending, absolute row numbers) / col_ind hold nnz entries that include every entry of
+ * rows [row_begin, row_begin + n_rows); entries of other rows are ignored. The per-row linear scan
+ * of the reference (:47-79) is replaced by one pass that writes n_rows+1 row pointers into the
+ * workspace, followed by the CSR kernel. */
+size_t spfa_coo_workspace_bytes(int64_t n_rows, int d);
+int spfa_coo_forward_f32(const float* Q, const float* K, const float* V,
+                         const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                         float* m, float* l, float* O,
+                         int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- implicit Local (sliding window) mask -------------------------------------------------------
+ * Replaces spfa_local_cuda_forward + kernel (Sparse_FlashAttention_Local/sp_flatt_local_kernel.cu:208-272, :12-204).
+ * Row i attends to j in [max(0, i-w), min(L, i+w+1)).  (:24-28) */
+size_t spfa_local_workspace_bytes(int64_t L, int64_t n_rows, int d);
+int spfa_local_forward_f32(const float* Q, const float* K, const float* V,
+                           float* m, float* l, float* O,
+                           int64_t L, int d, int64_t local_size_each_dir,
+                           int64_t row_begin, int64_t row_end,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- implicit Local 1D dilated mask -------------------------------------------------------------
+ * Replaces spfa_local_1d_dilated_cuda_forward + kernel
+ * (Sparse_FlashAttention_Local_1D_Dilated/sp_flatt_local_1d_dilated_kernel.cu:209-280, :12-205).
+ * s = dil_factor+1; lo = max(i - w s, i mod s); hi = min(i + w s, L-1); n = (hi-lo)/s + 1;
+ * row i attends to lo + t s, 0 <= t < n.  (:25-29, :102) */
+size_t spfa_local_1d_dilated_workspace_bytes(int64_t L, int64_t n_rows, int d);
+int spfa_local_1d_dilated_forward_f32(const float* Q, const float* K, const float* V,
+                                      float* m, float* l, float* O,
+                                      int64_t L, int d, int64_t local_size_each_dir, int64_t dil_factor,
+                                      int64_t row_begin, int64_t row_end,
+                                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- implicit Local 2D dilated (block-diagonal, intra-block dilation) mask -----------------------
+ * Replaces spfa_local_2d_dilated_cuda_forward + kernel
+ * (Sparse_FlashAttention_Local_2D_Dilated/sp_flatt_local_2d_dilated_kernel.cu:230-306, :12-226).
+ * s = dil_factor+1; start = (i / B) B; rows with (i-start) mod s != 0 have no keys (NaN-filled O if
+ * use_nan, else untouched); other rows attend to start + t s, 0 <= t < min(B, (B-1)/s + 1).  (:26-39, :123) */
+size_t spfa_local_2d_dilated_workspace_bytes(int64_t L, int64_t n_rows, int d);
+int spfa_local_2d_dilated_forward_f32(const float* Q, const float* K, const float* V,
+                                      float* m, float* l, float* O,
+                                      int64_t L, int d, int64_t block_size, int64_t dil_factor, int use_nan,
+                                      int64_t row_begin, int64_t row_end,
+                                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- implicit Global-no-local mask --------------------------------------------------------------
+ * Replaces spfa_global_no_local_cuda_forward + kernel
+ * (Sparse_FlashAttention_Global_No_Local/sp_flatt_global_no_local_kernel.cu:280-353, :12-276).
+ * W(i) = [max(0,i-w), min(L,i+w+1)). A row i listed in global_inds attends to every j outside W(i)
+ * (:54-57, :135-145); any other row attends to the listed g outside W(i), in list order (:58-60, :146-162).
+ * global_inds is int32[n_global]; entries outside [0, L) are ignored. Rows with no key are untouched. */
+size_t spfa_global_no_local_workspace_bytes(int64_t L, int64_t n_rows, int d, int64_t n_global);
+int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float* V,
+                                     float* m, float* l, float* O,
+                                     const int32_t* global_inds, int64_t n_global,
+                                     int64_t L, int d, int64_t local_size_each_dir,
+                                     int64_t row_begin, int64_t row_end,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- visited-pair dump (test support) -----------------------------------------------------------
+ * Emits the (row, key) set an implicit mask visits, produced by the same device-side column
+ * generators the gather kernels use. No counterpart in the reference (its index arithmetic is inlined
+ * in each kernel); exists so mask indexing can be compared bit-for-bit with the closed forms.
+ *   kind: 0 local(p0=w)  1 local_1d_dilated(p0=w,p1=dil)  2 local_2d_dilated(p0=B,p1=dil)
+ *         3 global_no_local(p0=w, global_inds/n_global)
+ * Pass 1: spfa_mask_count writes counts[n_rows] (int64). The caller prefix-sums them into
+ * row_off[n_rows+1]. Pass 2: spfa_mask_fill writes col_out[row_off[r] ...] in visiting order. */
+int spfa_mask_count(int kind, int64_t L, int64_t p0, int64_t p1,
+                    const int32_t* global_inds, int64_t n_global,
+                    int64_t row_begin, int64_t row_end, int64_t* counts, void* stream);
+int spfa_mask_fill(int kind, int64_t L, int64_t p0, int64_t p1,
+                   const int32_t* global_inds, int64_t n_global,
+                   int64_t row_begin, int64_t row_end, const int64_t* row_off, uint32_t* col_out,
+                   void* stream);
+
+/* Number of kernels this library has launched in the calling process since load (monotonic).
+ * Benchmarks subtract two readings to report how many launches a timed region contained. */
+int64_t spfa_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPFA_B200_H_ */

@@ -1,0 +1,407 @@
+"""GPU: the CUDA library, called through the C ABI and through the drop-in torch extensions, against
+the CPU oracle and the fixtures recorded from the reference's verification script.
+
+Tolerances (max-abs, fp32 I/O): FP32 gather path 1e-5; tensor-core (TF32) tiled path 2e-3; (m, l)
+are compared relatively. Index sets must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_calls, random_csr, seeded_qkv, unpack_mask
+
+pytestmark = pytest.mark.gpu
+
+TOL_GATHER = 1e-5
+TOL_TILED = 2e-3
+
+
+@pytest.fixture(scope="module")
+def capi(pkg):
+    assert torch.cuda.is_available()
+    c = pkg.capi
+    c.lib()
+    yield c
+    c.set_path(c.PATH_AUTO)
+
+
+def dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def to_np(state):
+    torch.cuda.synchronize()
+    return tuple(t.detach().cpu().double().numpy() for t in state)
+
+
+def state_to_dev(state):
+    return tuple(torch.from_numpy(s).float().cuda() for s in state)
+
+
+def assert_state_close(got, want, tol, msg=""):
+    gm, gl, gO = got
+    wm, wl, wO = want
+    assert np.array_equal(np.isnan(gO), np.isnan(wO)), f"{msg}: NaN pattern of O differs"
+    fin = np.isfinite(wm)
+    assert np.array_equal(np.isfinite(gm), fin), f"{msg}: -inf pattern of m differs"
+    np.testing.assert_allclose(gm[fin], wm[fin], rtol=1e-5 if tol <= 1e-4 else 2e-3, atol=tol, err_msg=f"{msg}: m")
+    np.testing.assert_allclose(gl, wl, rtol=10 * tol if tol <= 1e-4 else 4e-3, atol=tol, err_msg=f"{msg}: l")
+    err = np.nanmax(np.abs(gO - wO)) if gO.size else 0.0
+    assert err <= tol, f"{msg}: max-abs O error {err:.3e} > {tol}"
+
+
+# ------------------------------------------------------------------------------------------------------
+# fixtures recorded from the reference's verification script (L=256, d=32)
+# ------------------------------------------------------------------------------------------------------
+EXPECT = ["g_torch_out", "g_torch_out", "g_torch_out", "V", "g_torch_out", "g_torch_out", None, None, "g_torch_out",
+          "g_torch_out_1d", "g_torch_out_2d", "g_torch_out_2d"]
+
+
+def _replay_on_gpu(golden, fwd):
+    q, k, v = (dev(golden[n]) for n in "qkv")
+    L, d = q.shape
+    state, outs = None, []
+    for c in golden_calls(golden):
+        if int(c["fresh"]):
+            state = (torch.full((L,), float("-inf"), device="cuda"), torch.zeros(L, device="cuda"),
+                     torch.zeros(L, d, device="cuda"))
+        fwd(c, q, k, v, state)
+        outs.append((c, to_np(state)))
+    return outs
+
+
+def _check_replay(golden, outs, tol):
+    L = golden["q"].shape[0]
+    for i, (c, (m, l, O)) in enumerate(outs):
+        key = EXPECT[i]
+        if key is None:
+            continue
+        want = golden["v"] if key == "V" else c[key]
+        live = ~np.isnan(O).any(axis=1)
+        if i == 11:
+            dead = ~unpack_mask(c["g_mask_2d"], L).any(axis=1)
+            assert np.array_equal(~live, dead)
+        else:
+            assert live.all(), f"call {i}: unexpected NaN rows"
+        err = np.abs(O[live] - want[live]).max()
+        assert err <= tol, f"scenario call {i} ({c['op']}): max-abs {err:.3e}"
+
+
+@pytest.mark.parametrize("path", ["gather", "auto"])
+def test_reference_script_scenarios_through_c_abi(capi, golden, path):
+    capi.set_path(capi.PATH_GATHER if path == "gather" else capi.PATH_AUTO)
+
+    def fwd(c, q, k, v, st):
+        op = c["op"]
+        if op == "csr":
+            capi.csr_forward(q, k, v, dev(c["row_off"].astype(np.int64)), dev(c["col"].astype(np.int32)), *st,
+                             use_nan=bool(c["use_nan"]))
+        elif op == "coo":
+            capi.coo_forward(q, k, v, dev(c["row"].astype(np.int64)), dev(c["col"].astype(np.int32)), *st,
+                             use_nan=bool(c["use_nan"]))
+        elif op == "local":
+            capi.local_forward(q, k, v, *st, int(c["p0"]))
+        elif op == "local_1d_dilated":
+            capi.local_1d_dilated_forward(q, k, v, *st, int(c["p0"]), int(c["p1"]))
+        elif op == "local_2d_dilated":
+            capi.local_2d_dilated_forward(q, k, v, *st, int(c["p0"]), int(c["p1"]), use_nan=bool(c["use_nan"]))
+        else:
+            capi.global_no_local_forward(q, k, v, *st, dev(c["G"]), int(c["p0"]))
+
+    _check_replay(golden, _replay_on_gpu(golden, fwd), TOL_GATHER if path == "gather" else TOL_TILED)
+
+
+def test_reference_script_scenarios_through_torch_extensions(pkg, capi, golden):
+    """Same scenarios through `import spfa_csr` ... with the reference's dtypes (uint64/uint32/int32)."""
+    capi.set_path(capi.PATH_AUTO)
+    mods = {n: pkg.binding(n) for n in pkg.MODULES}
+
+    def fwd(c, q, k, v, st):
+        op = c["op"]
+        m, l, O = st
+        if op == "csr":
+            w_val = torch.ones(1, device="cuda")
+            out = mods["spfa_csr"].forward(q, k, v, dev(c["row_off"].astype(np.int64)).view(torch.uint64),
+                                           dev(c["col"].astype(np.int32)).view(torch.uint32), w_val, m, l, O,
+                                           bool(c["use_nan"]))
+        elif op == "coo":
+            w_val = torch.ones(1, device="cuda")
+            out = mods["spfa_coo"].forward(q, k, v, dev(c["row"].astype(np.int64)).view(torch.uint64),
+                                           dev(c["col"].astype(np.int32)).view(torch.uint32), w_val, m, l, O,
+                                           bool(c["use_nan"]))
+        elif op == "local":
+            out = mods["spfa_local"].forward(q, k, v, m, l, O, int(c["p0"]))
+        elif op == "local_1d_dilated":
+            out = mods["spfa_local_1d_dilated"].forward(q, k, v, m, l, O, int(c["p0"]), int(c["p1"]))
+        elif op == "local_2d_dilated":
+            out = mods["spfa_local_2d_dilated"].forward(q, k, v, m, l, O, int(c["p0"]), int(c["p1"]), bool(c["use_nan"]))
+        else:
+            out = mods["spfa_global_no_local"].forward(q, k, v, m, l, O, dev(c["G"]), int(c["p0"]))
+        assert out.data_ptr() == O.data_ptr(), "forward must return the same O tensor"
+
+    _check_replay(golden, _replay_on_gpu(golden, fwd), TOL_TILED)
+
+
+def test_torch_extension_errors_match_reference_types(pkg, capi):
+    q = torch.randn(64, 32, device="cuda")
+    m, l, O = capi.new_state(64, 32)
+    loc = pkg.binding("spfa_local")
+    with pytest.raises(ValueError, match="local size specified"):
+        loc.forward(q, q, q, m, l, O, 64)
+    with pytest.raises(ValueError, match="local size specified"):
+        loc.forward(q, q, q, m, l, O, -1)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        loc.forward(q.cpu(), q, q, m, l, O, 1)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        loc.forward(q.t().contiguous().t(), q, q, m, l, O, 1)
+    l1d = pkg.binding("spfa_local_1d_dilated")
+    with pytest.raises(ValueError, match="dilation factor must be atleast 0"):
+        l1d.forward(q, q, q, m, l, O, 3, -1)
+    l2d = pkg.binding("spfa_local_2d_dilated")
+    with pytest.raises(ValueError, match="divisor"):
+        l2d.forward(q, q, q, m, l, O, 48, 0, True)
+    with pytest.raises(ValueError, match="less than the block"):
+        l2d.forward(q, q, q, m, l, O, 16, 16, True)
+    gnl = pkg.binding("spfa_global_no_local")
+    with pytest.raises(ValueError, match="no global tokens"):
+        gnl.forward(q, q, q, m, l, O, torch.zeros(0, dtype=torch.int32, device="cuda"), 3)
+    q48 = torch.randn(64, 48, device="cuda")
+    with pytest.raises(ValueError, match="embedded dimension"):
+        loc.forward(q48, q48, q48, m, l, torch.zeros(64, 48, device="cuda"), 1)
+    csr = pkg.binding("spfa_csr")
+    with pytest.raises(RuntimeError):
+        csr.forward(q, q, q, torch.zeros(65, dtype=torch.float32, device="cuda"),
+                    torch.zeros(1, dtype=torch.uint32, device="cuda"), torch.ones(1, device="cuda"), m, l, O, True)
+
+
+# ------------------------------------------------------------------------------------------------------
+# index sets: visited pairs emitted by the kernels' own column generators == oracle closed forms
+# ------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind,L,p0,p1", [
+    ("local", 1, 0, 0), ("local", 2, 1, 0), ("local", 127, 3, 0), ("local", 129, 128, 0), ("local", 1000, 37, 0),
+    ("local_1d_dilated", 128, 4, 0), ("local_1d_dilated", 257, 10, 2), ("local_1d_dilated", 1000, 100, 6),
+    ("local_1d_dilated", 50, 49, 49), ("local_2d_dilated", 256, 16, 0), ("local_2d_dilated", 256, 16, 1),
+    ("local_2d_dilated", 1024, 256, 4), ("local_2d_dilated", 90, 30, 29), ("global_no_local", 256, 10, 0),
+    ("global_no_local", 1000, 0, 0), ("global_no_local", 333, 332, 0)])
+def test_visited_pairs_bit_exact(capi, orc, kind, L, p0, p1):
+    G = None
+    if kind == "global_no_local":
+        G = np.random.default_rng(L).permutation(L)[: min(7, L)].astype(np.int32)
+    row_off, col = capi.visited_pairs(kind, L, p0, p1, None if G is None else dev(G))
+    w_off, w_col = orc.implicit_csr(kind, L, p0, p1, G=G)
+    assert np.array_equal(row_off.cpu().numpy(), w_off.astype(np.int64))
+    assert np.array_equal(col.cpu().view(torch.int32).numpy().astype(np.uint32), w_col)
+
+
+def test_visited_pairs_row_shard_at_full_size(capi, orc):
+    """Config-sized masks, a row window each (edges + interior), still bit-exact."""
+    for kind, L, p0, p1 in (("local", 65536, 256, 0), ("local_1d_dilated", 131072, 512, 1),
+                            ("local_2d_dilated", 262144, 256, 4)):
+        for rb, re in ((0, 700), (L // 2 - 100, L // 2 + 100), (L - 700, L)):
+            row_off, col = capi.visited_pairs(kind, L, p0, p1, None, rb, re)
+            w_off, w_col = orc.implicit_csr(kind, L, p0, p1, row_begin=rb, row_end=re)
+            assert np.array_equal(row_off.cpu().numpy(), w_off.astype(np.int64))
+            assert np.array_equal(col.cpu().view(torch.int32).numpy().astype(np.uint32), w_col)
+
+
+# ------------------------------------------------------------------------------------------------------
+# numerics vs the oracle, every mask family, both paths, d in {16, 32, 64, 128}, ragged sizes
+# ------------------------------------------------------------------------------------------------------
+def _run_implicit(capi, kind, Q, K, V, st, p0, p1, G, use_nan, rb, re):
+    if kind == "local":
+        capi.local_forward(Q, K, V, *st, p0, rb, re)
+    elif kind == "local_1d_dilated":
+        capi.local_1d_dilated_forward(Q, K, V, *st, p0, p1, rb, re)
+    elif kind == "local_2d_dilated":
+        capi.local_2d_dilated_forward(Q, K, V, *st, p0, p1, use_nan, rb, re)
+    else:
+        capi.global_no_local_forward(Q, K, V, *st, G, p0, rb, re)
+
+
+IMPLICIT_CASES = [
+    ("local", 257, 64, 0, 0), ("local", 257, 64, 1, 0), ("local", 1000, 64, 45, 0), ("local", 1000, 32, 999, 0),
+    ("local", 640, 128, 130, 0), ("local", 77, 16, 5, 0), ("local", 2048, 64, 256, 0), ("local", 1, 64, 0, 0),
+    ("local_1d_dilated", 1000, 64, 20, 1), ("local_1d_dilated", 1000, 128, 64, 2), ("local_1d_dilated", 513, 32, 7, 6),
+    ("local_1d_dilated", 300, 64, 299, 0), ("local_1d_dilated", 2048, 128, 200, 1),
+    ("local_2d_dilated", 1024, 64, 256, 4), ("local_2d_dilated", 768, 32, 16, 0), ("local_2d_dilated", 512, 128, 64, 1),
+    ("local_2d_dilated", 600, 64, 200, 7),
+    ("global_no_local", 1000, 64, 10, 0), ("global_no_local", 513, 128, 100, 0), ("global_no_local", 256, 32, 255, 0),
+    ("global_no_local", 2000, 64, 0, 0)]
+
+
+@pytest.mark.parametrize("path", ["gather", "auto"])
+@pytest.mark.parametrize("kind,L,d,p0,p1", IMPLICIT_CASES)
+def test_implicit_masks_vs_oracle(capi, orc, path, kind, L, d, p0, p1):
+    capi.set_path(capi.PATH_GATHER if path == "gather" else capi.PATH_AUTO)
+    tol = TOL_GATHER if (path == "gather" or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+    Q, K, V = seeded_qkv(L, d, 1000 + L + d)
+    G = None
+    if kind == "global_no_local":
+        G = np.random.default_rng(L + 1).permutation(L)[: min(9, L)].astype(np.int32)
+    want = orc.implicit_forward(kind, Q, K, V, p0, p1, G=G, use_nan=True)
+    st = capi.new_state(L, d)
+    _run_implicit(capi, kind, dev(Q), dev(K), dev(V), st, p0, p1, None if G is None else dev(G), True, 0, L)
+    assert_state_close(to_np(st), want, tol, f"{kind} L={L} d={d} p=({p0},{p1}) {path}")
+
+
+@pytest.mark.parametrize("path", ["gather", "auto"])
+@pytest.mark.parametrize("kind,L,d,p0,p1", [("local", 1500, 64, 100, 0), ("local_1d_dilated", 1500, 64, 50, 2),
+                                             ("local_2d_dilated", 1536, 64, 128, 1), ("global_no_local", 1500, 64, 30, 0)])
+def test_row_shards_and_incoming_state(capi, orc, path, kind, L, d, p0, p1):
+    """Row ranges (as a second GPU would own them) on top of a non-trivial incoming (m, l, O)."""
+    capi.set_path(capi.PATH_GATHER if path == "gather" else capi.PATH_AUTO)
+    tol = TOL_GATHER if (path == "gather" or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+    Q, K, V = seeded_qkv(L, d, 31)
+    G = np.array([0, 700, 701, 1499, 33], dtype=np.int32) if kind == "global_no_local" else None
+    rng = np.random.default_rng(8)
+    for rb, re in ((0, 333), (333, 1100), (1100, L), (640, 641)):
+        n = re - rb
+        st0 = (rng.standard_normal(n) * 2, rng.random(n) + 0.5, rng.standard_normal((n, d)))
+        st0 = tuple(s.astype(np.float32).astype(np.float64) for s in st0)
+        want = orc.implicit_forward(kind, Q[rb:re], K, V, p0, p1, G=G, state=tuple(s.copy() for s in st0),
+                                    use_nan=False, row_begin=rb, row_end=re)
+        st = state_to_dev(st0)
+        _run_implicit(capi, kind, dev(Q[rb:re]), dev(K), dev(V), st, p0, p1, None if G is None else dev(G), False, rb, re)
+        assert_state_close(to_np(st), want, tol, f"{kind} rows [{rb},{re}) {path}")
+
+
+@pytest.mark.parametrize("L,Lk,d,density", [(512, 512, 64, 0.02), (300, 700, 32, 0.1), (257, 129, 128, 0.5),
+                                             (64, 64, 16, 1.0), (2000, 2000, 64, 0.004)])
+def test_csr_and_coo_vs_oracle(capi, orc, L, Lk, d, density):
+    Q, K, V = seeded_qkv(L, d, 5 + L, Lk)
+    empty = (0, L // 2, L - 1) if density < 1.0 else ()
+    mask, row_off, col = random_csr(L, Lk, density, 17, empty_rows=empty)
+    rows = np.repeat(np.arange(L, dtype=np.int64), np.diff(row_off.astype(np.int64)))
+    for use_nan in (True, False):
+        want = orc.csr_forward(Q, K, V, row_off, col, use_nan=use_nan)
+        st = capi.new_state(L, d)
+        capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off.astype(np.int64)), dev(col.astype(np.int32)), *st,
+                         use_nan=use_nan)
+        assert_state_close(to_np(st), want, TOL_GATHER, f"csr use_nan={use_nan}")
+        st2 = capi.new_state(L, d)
+        capi.coo_forward(dev(Q), dev(K), dev(V), dev(rows), dev(col.astype(np.int32)), *st2, use_nan=use_nan)
+        got, got2 = to_np(st), to_np(st2)
+        for a, b in zip(got, got2):
+            assert np.array_equal(a, b, equal_nan=True), "COO must equal CSR bit for bit"
+    # COO row shard given the whole list, and given only its own slice
+    rb, re = L // 3, 2 * L // 3
+    want = orc.coo_forward(Q[rb:re], K, V, rows.astype(np.uint64), col, row_begin=rb)
+    for lo, hi in ((0, len(rows)), (np.searchsorted(rows, rb), np.searchsorted(rows, re))):
+        st = capi.new_state(re - rb, d)
+        capi.coo_forward(dev(Q[rb:re]), dev(K), dev(V), dev(rows[lo:hi]), dev(col[lo:hi].astype(np.int32)), *st,
+                         row_begin=rb)
+        assert_state_close(to_np(st), want, TOL_GATHER, "coo shard")
+
+
+def test_coo_trailing_and_leading_empty_rows(capi, orc):
+    """Rows after the last stored row / before the first are empty rows (the reference's scan leaves
+    them undefined); an all-empty mask touches nothing."""
+    L, d = 100, 32
+    Q, K, V = seeded_qkv(L, d, 2)
+    rows = np.array([10, 10, 11, 50], dtype=np.int64)
+    col = np.array([3, 99, 0, 50], dtype=np.int32)
+    want = orc.coo_forward(Q, K, V, rows.astype(np.uint64), col.astype(np.uint32), use_nan=True)
+    st = capi.new_state(L, d)
+    capi.coo_forward(dev(Q), dev(K), dev(V), dev(rows), dev(col), *st, use_nan=True)
+    assert_state_close(to_np(st), want, TOL_GATHER, "coo sparse rows")
+    st = capi.new_state(L, d)
+    capi.coo_forward(dev(Q), dev(K), dev(V), dev(rows[:0]), dev(col[:0]), *st, use_nan=False)
+    m, l, O = to_np(st)
+    assert np.all(np.isinf(m)) and not l.any() and not O.any()
+
+
+def test_chained_bigbird_equals_union(capi, orc):
+    """Local -> Global-no-local -> CSR(random minus the others) on one (m, l, O) == the union mask."""
+    L, d, w = 512, 64, 12
+    Q, K, V = seeded_qkv(L, d, 404)
+    G = np.array([7, 100, 101, 400, 511], dtype=np.int32)
+    band = orc.dense_mask("local", L, w)
+    glob = orc.dense_mask("global_no_local", L, w, G=G)
+    rnd = (np.random.default_rng(1).random((L, L)) < 0.05) & ~band & ~glob
+    row_off = np.concatenate([[0], np.cumsum(rnd.sum(1))]).astype(np.int64)
+    col = np.nonzero(rnd)[1].astype(np.int32)
+    want = orc.dense_forward(Q, K, V, band | glob | rnd)
+    for path, tol in ((capi.PATH_GATHER, TOL_GATHER), (capi.PATH_AUTO, TOL_TILED)):
+        capi.set_path(path)
+        q, k, v = dev(Q), dev(K), dev(V)
+        st = capi.new_state(L, d)
+        capi.local_forward(q, k, v, *st, w)
+        capi.global_no_local_forward(q, k, v, *st, dev(G), w)
+        capi.csr_forward(q, k, v, dev(row_off), dev(col), *st, use_nan=False)
+        assert_state_close(to_np(st), want, tol, "chained bigbird")
+
+
+def test_nan_rows_propagate_like_the_reference(capi):
+    """A row NaN-filled by a use_nan call stays NaN when a later call adds keys to it (0*NaN in the
+    reference's update, sp_flatt_csr_kernel.cu:191)."""
+    L, d = 64, 32
+    Q, K, V = seeded_qkv(L, d, 9)
+    st = capi.new_state(L, d)
+    capi.local_2d_dilated_forward(dev(Q), dev(K), dev(V), *st, 16, 1, use_nan=True)
+    capi.local_forward(dev(Q), dev(K), dev(V), *st, 2)
+    m, l, O = to_np(st)
+    dead = (np.arange(L) % 16) % 2 == 1
+    assert np.isnan(O[dead]).all() and np.isfinite(O[~dead]).all() and np.isfinite(l).all()
+
+
+def test_duplicate_and_out_of_range_global_indices(capi, orc):
+    L, d, w = 300, 64, 4
+    Q, K, V = seeded_qkv(L, d, 12)
+    G = np.array([5, 200, 5, 299], dtype=np.int32)  # row 5 listed twice: other rows see key 5 twice
+    want = orc.implicit_forward("global_no_local", Q, K, V, w, G=G)
+    st = capi.new_state(L, d)
+    capi.global_no_local_forward(dev(Q), dev(K), dev(V), *st, dev(G), w)
+    assert_state_close(to_np(st), want, TOL_GATHER, "duplicate globals")
+
+
+def test_full_size_properties_local(capi):
+    """Config-sized Local (L=65536, d=64, w=256): size-independent properties instead of a full oracle run.
+    (1) constant V rows -> every output equals that constant; (2) l counts keys when Q = 0; (3) a row
+    shard equals the same rows of the full run bit for bit."""
+    L, d, w = 65536, 64, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Q = torch.randn(L, d, device="cuda", generator=g)
+    K = torch.randn(L, d, device="cuda", generator=g)
+    V = torch.ones(L, d, device="cuda") * 0.375
+    for path, tol in ((capi.PATH_GATHER, TOL_GATHER), (capi.PATH_AUTO, TOL_TILED)):
+        capi.set_path(path)
+        st = capi.new_state(L, d)
+        capi.local_forward(Q, K, V, *st, w)
+        assert (st[2] - 0.375).abs().max().item() <= tol
+        st0 = capi.new_state(L, d)
+        capi.local_forward(torch.zeros_like(Q), K, V, *st0, w)
+        i = torch.arange(L, device="cuda")
+        n = torch.minimum(i + w + 1, torch.tensor(L, device="cuda")) - torch.clamp(i - w, min=0)
+        assert torch.allclose(st0[1], n.float(), rtol=tol, atol=0) and (st0[0] == 0).all()
+        rb, re = 30000, 34000
+        sh = capi.new_state(re - rb, d)
+        capi.local_forward(Q[rb:re].contiguous(), K, V, *sh, w, rb, re)
+        assert torch.equal(sh[1], st[1][rb:re]) and torch.equal(sh[2], st[2][rb:re])
+
+
+def test_full_size_sampled_rows_vs_oracle(capi, orc):
+    """Config-sized masks; oracle evaluated on sampled row windows only (edges + interior)."""
+    cases = [("local", 65536, 64, 256, 0, None), ("local_1d_dilated", 131072, 128, 512, 1, None),
+             ("local_2d_dilated", 262144, 64, 256, 4, None),
+             ("global_no_local", 131072, 128, 256, 0,
+              np.sort(np.random.default_rng(1003).choice(131072, 64, replace=False)).astype(np.int32))]
+    for kind, L, d, p0, p1, G in cases:
+        g = torch.Generator().manual_seed(1000 + L)
+        Q, K, V = (torch.randn(L, d, generator=g) for _ in range(3))
+        Qd, Kd, Vd = Q.cuda(), K.cuda(), V.cuda()
+        Gd = None if G is None else dev(G)
+        for path in (capi.PATH_GATHER, capi.PATH_AUTO):
+            capi.set_path(path)
+            tol = TOL_GATHER if (path == capi.PATH_GATHER or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+            st = capi.new_state(L, d)
+            _run_implicit(capi, kind, Qd, Kd, Vd, st, p0, p1, Gd, True, 0, L)
+            m, l, O = to_np(st)
+            windows = [(0, 300), (L // 2 - 150, L // 2 + 150), (L - 300, L)]
+            if G is not None:
+                windows.append((int(G[10]), int(G[10]) + 1))  # one global row: L-513 keys
+            for rb, re in windows:
+                want = orc.implicit_forward(kind, Q[rb:re].numpy(), K.numpy(), V.numpy(), p0, p1, G=G, use_nan=True,
+                                            row_begin=rb, row_end=re)
+                assert_state_close((m[rb:re], l[rb:re], O[rb:re]), want, tol, f"{kind} rows [{rb},{re})")
