@@ -25,7 +25,7 @@ MASK_KIND = {"local": 0, "local_1d_dilated": 1, "local_2d_dilated": 2, "global_n
 
 # every symbol include/spfa_b200.h declares (checked by the CPU test-suite)
 EXPORTS = (
-    "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count",
+    "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
     "spfa_coo_workspace_bytes", "spfa_coo_forward_f32",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
@@ -62,6 +62,7 @@ def lib() -> ctypes.CDLL:
     L.spfa_get_path.restype = i32
     L.spfa_last_path.restype = i32
     L.spfa_launch_count.restype = i64
+    L.spfa_last_device_error.restype = i32
     L.spfa_csr_workspace_bytes.restype = sz
     L.spfa_csr_workspace_bytes.argtypes = [i64, i32]
     L.spfa_csr_forward_f32.restype = i32
@@ -111,6 +112,11 @@ def get_path() -> int:
 
 def last_path() -> int:
     return lib().spfa_last_path()
+
+
+def last_device_error() -> int:
+    """Synchronise and return (then clear) the tiled kernels' error word; 0 means no bounded wait gave up."""
+    return int(lib().spfa_last_device_error())
 
 
 def launch_count() -> int:

@@ -162,6 +162,8 @@ int spfa_last_path(void) { return g_last_path.load(); }
 
 int64_t spfa_launch_count(void) { return g_launches.load(); }
 
+int spfa_last_device_error(void) { return read_and_clear_tile_error(); }
+
 // ---- CSR -----------------------------------------------------------------------------------------
 size_t spfa_csr_workspace_bytes(int64_t, int) { return 0; }
 

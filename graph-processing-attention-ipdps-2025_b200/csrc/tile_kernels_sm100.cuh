@@ -1,0 +1,533 @@
+// Tiled tensor-core path for banded masks on sm_100a: TMA-staged K/V tiles, tcgen05 TF32 MMAs with
+// TMEM accumulators, online softmax in registers.
+//
+// One CTA owns 256 consecutive query rows of a (strided) row sequence, as two 128-row sub-tiles A and
+// B, and walks the key tiles that intersect the band |u_q - u_k| <= w. Roles (320 threads):
+//   warps 0-3  softmax group A   thread t <-> query row t of sub-tile A  <-> TMEM lane t
+//   warps 4-7  softmax group B
+//   warp  8    TMA producer (one elected lane) + TMEM allocation
+//   warp  9    MMA issuer (one elected lane)
+// Per key tile j and sub-tile X:
+//   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM
+//   P_X = exp2(S_X*c - m) written back over S_X in TMEM by the softmax group (row max / row sum in
+//                         registers, no shuffles: one thread owns one row)
+//   O_X = P_X V_j        tcgen05.mma kind::tf32, A = P_X (TMEM), B = V_j (smem, MN-major), fresh D
+//   acc = acc*corr + O_X in the softmax group's registers (so TMEM never needs rescaling)
+// The MMA thread interleaves the two sub-tiles (PV_A(j), S_A(j+1), PV_B(j), S_B(j+1), ...) so the
+// tensor pipe works on one sub-tile while the other is in its exponentials.
+//
+// Strided sequences: the rows a CTA sees are  abs_row = r + u*s  (s = dilation stride, r = residue),
+// addressed through tensor maps whose row pitch is s*d*4 bytes; the 1D-dilated mask is exactly a band
+// in u on every residue class, Local is s = 1.
+//
+// Every wait is bounded: on timeout the waiter records a code in *err, raises an abort flag the other
+// roles poll, and the CTA falls through to the common exit where TMEM is released.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "spfa_common.cuh"
+
+namespace spfa {
+namespace tile {
+
+constexpr int kThreads = 320;
+constexpr int kQRows = 256;        // query rows per CTA (two 128-row sub-tiles)
+constexpr uint64_t kWaitNs = 200ull * 1000 * 1000;  // 0.2 s per wait before giving up
+
+struct BandParams {
+  int64_t n_keys;     // n_r: rows of this residue's key sequence
+  int64_t u_q_first;  // first query u of the shard for this residue
+  int64_t n_q;        // number of query rows (u_q_first .. u_q_first + n_q)
+  int64_t w;          // band half-width in u
+  int64_t s, r;       // stride and residue: abs_row = r + u*s
+  int64_t row_begin;  // first absolute row of the shard (Q/m/l/O are indexed by abs_row - row_begin)
+  float scale_log2e;  // (1/sqrt(d)) * log2(e)
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait. Returns false on timeout or when another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = globaltimer();
+  uint32_t spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > kWaitNs) {
+        *abort_flag = 1;
+        atomicCAS(err, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int32_t x, int32_t y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t y;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
+  return y;
+}
+
+// ---- descriptors ------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor, sm_100 format:
+//   [0,14) start address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
+//   [46,48) version = 1         [61,64) layout type
+// Layout types used here: 2 = 128-byte swizzle on 16-byte units (K-major operands: Q and K tiles);
+// 1 = 128-byte swizzle on 32-byte units, the only layout the hardware accepts for an MN-major 32-bit
+// operand (the V tile, whose rows are keys = the contraction dimension of P V).
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= 1ull << 46;
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32, fp32 accumulate:
+//   [4,6) D format (1 = f32)  [7,10) A format (2 = tf32)  [10,13) B format (2 = tf32)
+//   [15] A major (0 = K)  [16] B major (0 = K, 1 = MN)  [17,23) N >> 3  [24,29) M >> 4
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int b_mn_major) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- shared-memory plan --------------------------------------------------------------------------------
+template <int D, int BN, int NS>
+struct Plan {
+  static constexpr int kChunks = D / 32;                    // 32-float (128 B) column chunks per row
+  static constexpr int kQChunkBytes = 128 * 128;            // 128 rows x 128 B
+  static constexpr int kKVChunkBytes = BN * 128;            // BN rows x 128 B
+  static constexpr int kQBytes = 2 * kChunks * kQChunkBytes;  // two sub-tiles
+  static constexpr int kKVStageBytes = kChunks * kKVChunkBytes;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffK = kOffQ + kQBytes;
+  static constexpr int kOffV = kOffK + NS * kKVStageBytes;
+  static constexpr int kOffBar = kOffV + NS * kKVStageBytes;
+  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[2], p_ready[2], o_ready[2]
+  static constexpr int kNumBars = 1 + 4 * NS + 6;
+  static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
+  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
+  // TMEM columns: S_A, S_B (BN each, at 0 and 128), O_A, O_B (D each, at 256 and 256 + D)
+  static constexpr int kTmemCols = 512;
+  static constexpr int kColS = 0, kColO = 256;
+};
+
+template <int D, int BN, int NS>
+__global__ void __launch_bounds__(kThreads, 1)
+band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, float* __restrict__ m_out, float* __restrict__ l_out,
+                    float* __restrict__ O_out, const BandParams prm, int* __restrict__ err) {
+  using P = Plan<D, BN, NS>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + P::kOffBar;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 1 + NS, B_VFULL = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
+            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + 2, B_OREADY = B_SREADY + 4;
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + P::kOffMisc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- tile geometry (uniform across the CTA) ----
+  const int64_t uq0 = prm.u_q_first + (int64_t)blockIdx.x * kQRows;  // first query u of this CTA
+  const int64_t uq_end = prm.u_q_first + prm.n_q;                    // one past the last valid query u
+  const int64_t rows_here = (uq_end - uq0 < kQRows) ? (uq_end - uq0) : kQRows;
+  const int64_t kv_lo = (uq0 - prm.w > 0) ? (uq0 - prm.w) : 0;
+  int64_t kv_hi = uq0 + rows_here - 1 + prm.w + 1;
+  if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
+  const int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
+  // active key-tile range [j0, j1) of each sub-tile
+  int j0[2], j1[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int64_t ux0 = uq0 + 128 * x;
+    int64_t ux_last = ux0 + 127;
+    if (ux_last > uq_end - 1) ux_last = uq_end - 1;
+    if (ux0 >= uq_end) {
+      j0[x] = 0;
+      j1[x] = 0;
+    } else {
+      const int64_t lo = (ux0 - prm.w > 0) ? (ux0 - prm.w) : 0;
+      int64_t hi = ux_last + prm.w + 1;
+      if (hi > prm.n_keys) hi = prm.n_keys;
+      j0[x] = (int)((lo - kv_lo) / BN);
+      j1[x] = (int)((hi - kv_lo + BN - 1) / BN);
+    }
+  }
+
+  // ---- setup ----
+  if (threadIdx.x == 0) {
+    mbar_init(bar(B_QFULL), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar(B_SREADY + x), 1);
+      mbar_init(bar(B_PREADY + x), 128);
+      mbar_init(bar(B_OREADY + x), 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + P::kOffMisc),
+                 "r"(P::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_base_slot;
+
+  if (warp == 8) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      // Q: both sub-tiles, coordinates relative to the first query u of the shard (rows past the end read zeros)
+      mbar_expect_tx(bar(B_QFULL), P::kQBytes);
+      const int32_t yq = (int32_t)(uq0 - prm.u_q_first);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < P::kChunks; ++c)
+          tma_load_2d(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes, &tmQ, c * 32, yq + 128 * x,
+                      bar(B_QFULL));
+      bool ok = true;
+      for (int j = 0; j < nT && ok; ++j) {
+        const int st = j % NS;
+        const uint32_t ph = (uint32_t)((j / NS) & 1);
+        const int32_t yk = (int32_t)(kv_lo + (int64_t)j * BN);
+        ok = mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, err, 101);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_KFULL + st), P::kKVStageBytes);
+#pragma unroll
+        for (int c = 0; c < P::kChunks; ++c)
+          tma_load_2d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmK, c * 32, yk,
+                      bar(B_KFULL + st));
+        ok = mbar_wait(bar(B_VEMPTY + st), ph ^ 1u, abort_flag, err, 102);
+        if (!ok) break;
+        mbar_expect_tx(bar(B_VFULL + st), P::kKVStageBytes);
+#pragma unroll
+        for (int c = 0; c < P::kChunks; ++c)
+          tma_load_2d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmV, c * 32, yk,
+                      bar(B_VFULL + st));
+      }
+    }
+  } else if (warp == 9) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      constexpr uint32_t kIdescS = idesc_tf32(128, BN, 0);
+      constexpr uint32_t kIdescO = idesc_tf32(128, D, 1);
+      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
+      int n_s[2] = {0, 0};  // S tiles issued per sub-tile (for nothing but symmetry with the consumers)
+      auto issue_S = [&](int x, int j) {
+        const int st = j % NS;
+        const uint32_t qa = sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
+        const uint32_t ka = sbase + P::kOffK + st * P::kKVStageBytes;
+        const uint32_t d_t = tmem + P::kColS + 128 * x;
+        int k = 0;
+#pragma unroll
+        for (int c = 0; c < P::kChunks; ++c)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk, ++k)
+            mma_ss(d_t, smem_desc(qa + c * P::kQChunkBytes + kk * 32, 16, 1024, kLayoutSw128),
+                   smem_desc(ka + c * P::kKVChunkBytes + kk * 32, 16, 1024, kLayoutSw128), kIdescS, k > 0 ? 1u : 0u);
+        tc_commit(bar(B_SREADY + x));
+        ++n_s[x];
+      };
+      auto issue_PV = [&](int x, int j) {
+        const int st = j % NS;
+        const uint32_t va = sbase + P::kOffV + st * P::kKVStageBytes;
+        const uint32_t a_t = tmem + P::kColS + 128 * x;
+        const uint32_t d_t = tmem + P::kColO + D * x;
+#pragma unroll
+        for (int kk = 0; kk < BN / 8; ++kk)
+          // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
+          mma_ts(d_t, a_t + kk * 8, smem_desc(va + kk * 1024, P::kKVChunkBytes, 512, kLayoutSw128Base32), kIdescO,
+                 kk > 0 ? 1u : 0u);
+        tc_commit(bar(B_OREADY + x));
+      };
+      auto active = [&](int x, int j) { return j >= j0[x] && j < j1[x]; };
+      auto last_active = [&](int x, int j) {  // is x the last sub-tile (in issue order A, B) using tile j?
+        return x == 1 || !active(1, j);
+      };
+      // prologue: S of tile 0
+      if (ok && nT > 0) {
+        ok = mbar_wait(bar(B_KFULL + 0), 0, abort_flag, err, 202);
+        if (ok) {
+          tc_fence_after();
+          for (int x = 0; x < 2; ++x)
+            if (active(x, 0)) {
+              issue_S(x, 0);
+              if (last_active(x, 0)) tc_commit(bar(B_KEMPTY + 0));
+            }
+        }
+      }
+      for (int j = 0; j < nT && ok; ++j) {
+        const int st = j % NS, stn = (j + 1) % NS;
+        const uint32_t ph = (uint32_t)((j / NS) & 1), phn = (uint32_t)(((j + 1) / NS) & 1);
+        bool have_v = false, have_kn = false;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (active(x, j)) {
+            ok = mbar_wait(bar(B_PREADY + x), (uint32_t)((j - j0[x]) & 1), abort_flag, err, 203);
+            if (!ok) break;
+            if (!have_v) {
+              ok = mbar_wait(bar(B_VFULL + st), ph, abort_flag, err, 204);
+              if (!ok) break;
+              have_v = true;
+            }
+            tc_fence_after();
+            issue_PV(x, j);
+            if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
+          }
+          if (j + 1 < nT && active(x, j + 1)) {
+            if (!have_kn) {
+              ok = mbar_wait(bar(B_KFULL + stn), phn, abort_flag, err, 205);
+              if (!ok) break;
+              have_kn = true;
+            }
+            tc_fence_after();
+            issue_S(x, j + 1);
+            if (last_active(x, j + 1)) tc_commit(bar(B_KEMPTY + stn));
+          }
+        }
+      }
+    }
+  } else {
+    // =============================== softmax groups ===============================
+    const int x = warp >> 2;                 // sub-tile
+    const int row = threadIdx.x & 127;       // row within the sub-tile == TMEM lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + P::kColS + 128 * x;
+    const uint32_t tO = tmem + lane_base + P::kColO + D * x;
+    const int64_t uq = uq0 + 128 * x + row;
+    const bool row_valid = uq < uq_end;
+    const int64_t lo_q = (uq - prm.w > 0) ? (uq - prm.w) : 0;
+    const int64_t hi_q = (uq + prm.w < prm.n_keys - 1) ? (uq + prm.w) : (prm.n_keys - 1);
+    float m_run = neg_inf(), l_run = 0.f, corr_prev = 0.f;
+    float acc[D];
+#pragma unroll
+    for (int e = 0; e < D; ++e) acc[e] = 0.f;
+    bool ok = true;
+    uint32_t r[32];
+    const int nx = j1[x] - j0[x];
+    for (int it = 0; it < nx && ok; ++it) {
+      const int j = j0[x] + it;
+      const int64_t k0 = kv_lo + (int64_t)j * BN;
+      // columns of this tile that are inside the band for this row: [c_lo, c_hi]
+      const int c_lo = (lo_q > k0) ? (int)(lo_q - k0) : 0;
+      const int c_hi = (hi_q - k0 < BN - 1) ? (int)(hi_q - k0) : (BN - 1);
+      const bool full = (c_lo == 0) && (c_hi == BN - 1);
+      ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + x), (uint32_t)(it & 1), abort_flag, err, 301));
+      if (!ok) break;
+      tc_fence_after();
+      // pass 1: row maximum (log2 domain)
+      float mx = neg_inf();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        tmem_ld32(tS + c * 32, r);
+        tc_wait_ld();
+        if (full) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int cc = c * 32 + e;
+            if (cc >= c_lo && cc <= c_hi) mx = fmaxf(mx, __uint_as_float(r[e]));
+          }
+        }
+      }
+      mx *= prm.scale_log2e;  // scale > 0: max commutes with the scaling
+      const float m_new = fmaxf(m_run, mx);
+      const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
+      const float corr = fast_exp2(m_run - m_safe);
+      // fold in the previous tile's P V (the tensor pipe finished it before it produced this S)
+      if (it > 0) {
+        ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((it - 1) & 1), abort_flag, err, 302));
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld32(tO + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(r[e]));
+        }
+      }
+      // pass 2: P = exp2(S*c - m), row sum, P (rounded to tf32) back over S
+      float lsum = 0.f;
+      const float neg_m = -m_safe;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        tmem_ld32(tS + c * 32, r);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int cc = c * 32 + e;
+          float p = fast_exp2(fmaf(__uint_as_float(r[e]), prm.scale_log2e, neg_m));
+          if (!full && (cc < c_lo || cc > c_hi)) p = 0.f;
+          lsum += p;
+          r[e] = to_tf32(p);
+        }
+        tmem_st32(tS + c * 32, r);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(B_PREADY + x));
+      l_run = fmaf(l_run, corr, lsum);
+      m_run = m_new;
+      corr_prev = corr;
+    }
+    if (ok && nx > 0) {
+      ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((nx - 1) & 1), abort_flag, err, 303));
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          tmem_ld32(tO + c * 32, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(r[e]));
+        }
+      }
+    }
+    // ---- epilogue: merge with the caller's (m, l, O) and store (same recurrence as the gather path) ----
+    if (ok && row_valid && l_run > 0.f) {
+      const int64_t rl = prm.r + uq * prm.s - prm.row_begin;  // shard-local row
+      const float m_loc = m_run * 0.6931471805599453f;        // back to natural-log units
+      const float m_in = m_out[rl], l_in = l_out[rl];
+      const float m_o = fmaxf(m_in, m_loc);
+      const float a = l_in * fast_exp2((m_in - m_o) * kLog2e);
+      const float b = fast_exp2((m_loc - m_o) * kLog2e);
+      const float l_o = fmaf(l_run, b, a);
+      const float inv = 1.0f / l_o;
+      float4* op = reinterpret_cast<float4*>(O_out + (size_t)rl * D);
+#pragma unroll
+      for (int e = 0; e < D / 4; ++e) {
+        float4 o = op[e];
+        o.x = (a * o.x + b * acc[4 * e + 0]) * inv;
+        o.y = (a * o.y + b * acc[4 * e + 1]) * inv;
+        o.z = (a * o.z + b * acc[4 * e + 2]) * inv;
+        o.w = (a * o.w + b * acc[4 * e + 3]) * inv;
+        op[e] = o;
+      }
+      m_out[rl] = m_o;
+      l_out[rl] = l_o;
+    }
+  }
+
+  // ---- common exit: everyone is done with TMEM before it is released ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    if (*abort_flag && lane == 0) {
+      // give copies that may still be in flight time to land before the CTA's shared memory is reused
+      const uint64_t t0 = globaltimer();
+      while (globaltimer() - t0 < 2000000ull) {
+      }
+    }
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P::kTmemCols) : "memory");
+  }
+}
+
+}  // namespace tile
+}  // namespace spfa

@@ -157,6 +157,12 @@ int spfa_mask_fill(int kind, int64_t L, int64_t p0, int64_t p1,
                    int64_t row_begin, int64_t row_end, const int64_t* row_off, uint32_t* col_out,
                    void* stream);
 
+/* Reads and clears the error word of the tiled kernels on the current device. Synchronises the device.
+ * 0 = no error; a positive code names the bounded wait that gave up (1xx TMA producer, 2xx MMA issuer,
+ * 3xx softmax group); -1 = the CUDA runtime reported an error. No counterpart in the reference, whose
+ * launches are never checked (sp_flatt_csr_kernel.cu:271). */
+int spfa_last_device_error(void);
+
 /* Number of kernels this library has launched in the calling process since load (monotonic).
  * Benchmarks subtract two readings to report how many launches a timed region contained. */
 int64_t spfa_launch_count(void);

@@ -24,6 +24,13 @@ def capi(pkg):
     c.set_path(c.PATH_AUTO)
 
 
+@pytest.fixture(autouse=True)
+def no_device_timeouts(capi):
+    """Every bounded device-side wait must have completed: the kernels' error word stays 0."""
+    yield
+    assert capi.last_device_error() == 0, "a tiled kernel reported a timed-out wait"
+
+
 def dev(x, dtype=None):
     t = torch.from_numpy(np.ascontiguousarray(x))
     if dtype is not None:
@@ -405,3 +412,20 @@ def test_full_size_sampled_rows_vs_oracle(capi, orc):
                 want = orc.implicit_forward(kind, Q[rb:re].numpy(), K.numpy(), V.numpy(), p0, p1, G=G, use_nan=True,
                                             row_begin=rb, row_end=re)
                 assert_state_close((m[rb:re], l[rb:re], O[rb:re]), want, tol, f"{kind} rows [{rb},{re})")
+
+
+def test_auto_routes_wide_bands_to_the_tensor_core_path(capi):
+    L, d = 1024, 64
+    Q, K, V = (dev(x) for x in seeded_qkv(L, d, 3))
+    capi.set_path(capi.PATH_AUTO)
+    st = capi.new_state(L, d)
+    capi.local_forward(Q, K, V, *st, 200)
+    assert capi.last_path() == capi.PATH_TILED
+    capi.local_forward(Q, K, V, *st, 3)      # narrow window: exact FP32 gather path
+    assert capi.last_path() == capi.PATH_GATHER
+    capi.local_1d_dilated_forward(Q, K, V, *st, 100, 1)
+    assert capi.last_path() == capi.PATH_TILED
+    capi.set_path(capi.PATH_GATHER)
+    capi.local_forward(Q, K, V, *st, 200)
+    assert capi.last_path() == capi.PATH_GATHER
+    capi.set_path(capi.PATH_AUTO)
