@@ -63,6 +63,11 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
   auto kern = tile::band_forward_kernel<D, BN, NS>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
+  // The kernel re-balances registers with setmaxnreg, which blocks without timeout if the budgets exceed
+  // what the launch allocated: refuse to launch unless the compiled register count covers them.
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, kern) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  if (attr.numRegs * tile::kThreads < tile::kRegsSoftmax * 256 + tile::kRegsAux * 128) return SPFA_ERR_LAUNCH;
   int* err = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
   for (int64_t r = 0; r < s && r < L; ++r) {

@@ -7,6 +7,8 @@
 //   warps 4-7  softmax group B
 //   warp  8    TMA producer (one elected lane) + TMEM allocation
 //   warp  9    MMA issuer (one elected lane)
+//   warps 10-11 idle (they complete the third warpgroup so registers can be re-balanced:
+//              setmaxnreg gives the softmax groups 216 registers/thread and leaves 72 to this group)
 // Per key tile j and sub-tile X:
 //   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM
 //   P_X = exp2(S_X*c - m) written back over S_X in TMEM by the softmax group (row max / row sum in
@@ -28,12 +30,36 @@
 #include <stdint.h>
 
 #include "spfa_common.cuh"
+#if defined(SPFA_TILE_TIMING) || defined(SPFA_TILE_TRACE)
+#include <cstdio>
+#endif
 
 namespace spfa {
 namespace tile {
 
-constexpr int kThreads = 320;
+#ifdef SPFA_TILE_TRACE  // probe build only: per-event cycle stamps of one CTA, printed at its exit
+__device__ long long g_trace[4096];
+__device__ int g_trace_n;
+#define SPFA_TRACE(tag, a, b)                                                                   \
+  do {                                                                                            \
+    if (blockIdx.x == 1) {                                                                        \
+      int i_ = atomicAdd(&g_trace_n, 1);                                                          \
+      if (i_ < 4096) g_trace[i_] = ((long long)(tag) << 56) | ((long long)(a) << 52) | ((long long)(b) << 44) | (clock64() & 0xfffffffffffLL); \
+    }                                                                                             \
+  } while (0)
+#else
+#define SPFA_TRACE(tag, a, b) do {} while (0)
+#endif
+
+constexpr int kThreads = 384;      // three warpgroups: softmax A, softmax B, {TMA, MMA, 2 idle warps}
 constexpr int kQRows = 256;        // query rows per CTA (two 128-row sub-tiles)
+// Register re-balancing. The CTA is launched with kRegsLaunch registers per thread (what the compiler
+// assigns to a 384-thread, 1-CTA/SM kernel: 3 warps per scheduler share 512 registers per lane). setmaxnreg.inc
+// BLOCKS until the CTA's pool can satisfy it and has no timeout, so the two budgets must fit in the
+// pool the launch allocated -- otherwise the softmax groups would wait forever.
+constexpr int kRegsLaunch = 168, kRegsSoftmax = 216, kRegsAux = 72;
+static_assert(kRegsSoftmax * 256 + kRegsAux * 128 <= kRegsLaunch * kThreads, "setmaxnreg budgets exceed the launch pool");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsAux % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr uint64_t kWaitNs = 200ull * 1000 * 1000;  // 0.2 s per wait before giving up
 
 struct BandParams {
@@ -276,6 +302,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *tmem_base_slot;
 
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsAux));
   if (warp == 8) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
@@ -315,13 +343,16 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t kIdescS = idesc_tf32(128, BN, 0);
       constexpr uint32_t kIdescO = idesc_tf32(128, D, 1);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
-      int n_s[2] = {0, 0};  // S tiles issued per sub-tile (for nothing but symmetry with the consumers)
+      int n_s[2] = {0, 0}, n_pv[2] = {0, 0};  // S / PV tiles issued per sub-tile (phase of their barriers)
       auto issue_S = [&](int x, int j) {
         const int st = j % NS;
         const uint32_t qa = sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
         const uint32_t ka = sbase + P::kOffK + st * P::kKVStageBytes;
         const uint32_t d_t = tmem + P::kColS + 128 * x;
         int k = 0;
+#ifdef SPFA_TILE_TIMING
+        const long long t_s0 = clock64();
+#endif
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
 #pragma unroll
@@ -329,6 +360,13 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mma_ss(d_t, smem_desc(qa + c * P::kQChunkBytes + kk * 32, 16, 1024, kLayoutSw128),
                    smem_desc(ka + c * P::kKVChunkBytes + kk * 32, 16, 1024, kLayoutSw128), kIdescS, k > 0 ? 1u : 0u);
         tc_commit(bar(B_SREADY + x));
+#ifdef SPFA_TILE_TIMING  // probe build only: serialise on the MMA's completion and report its latency
+        if (blockIdx.x == 1) {
+          const long long t_s1 = clock64();
+          mbar_wait(bar(B_SREADY + x), (uint32_t)(n_s[x] & 1), abort_flag, err, 901);
+          printf("S  x=%d j=%d issue=%lld done=%lld cycles\n", x, j, t_s1 - t_s0, clock64() - t_s0);
+        }
+#endif
         ++n_s[x];
       };
       auto issue_PV = [&](int x, int j) {
@@ -336,12 +374,23 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t va = sbase + P::kOffV + st * P::kKVStageBytes;
         const uint32_t a_t = tmem + P::kColS + 128 * x;
         const uint32_t d_t = tmem + P::kColO + D * x;
+#ifdef SPFA_TILE_TIMING
+        const long long t_p0 = clock64();
+#endif
 #pragma unroll
         for (int kk = 0; kk < BN / 8; ++kk)
           // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
           mma_ts(d_t, a_t + kk * 8, smem_desc(va + kk * 1024, P::kKVChunkBytes, 512, kLayoutSw128Base32), kIdescO,
                  kk > 0 ? 1u : 0u);
         tc_commit(bar(B_OREADY + x));
+#ifdef SPFA_TILE_TIMING
+        if (blockIdx.x == 1) {
+          const long long t_p1 = clock64();
+          mbar_wait(bar(B_OREADY + x), (uint32_t)(n_pv[x] & 1), abort_flag, err, 902);
+          printf("PV x=%d j=%d issue=%lld done=%lld cycles\n", x, j, t_p1 - t_p0, clock64() - t_p0);
+        }
+#endif
+        ++n_pv[x];
       };
       auto active = [&](int x, int j) { return j >= j0[x] && j < j1[x]; };
       auto last_active = [&](int x, int j) {  // is x the last sub-tile (in issue order A, B) using tile j?
@@ -373,7 +422,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               have_v = true;
             }
             tc_fence_after();
+            SPFA_TRACE(1, x, j);
             issue_PV(x, j);
+            SPFA_TRACE(2, x, j);
             if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
           }
           if (j + 1 < nT && active(x, j + 1)) {
@@ -383,14 +434,20 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               have_kn = true;
             }
             tc_fence_after();
+            SPFA_TRACE(3, x, j + 1);
             issue_S(x, j + 1);
+            SPFA_TRACE(4, x, j + 1);
             if (last_active(x, j + 1)) tc_commit(bar(B_KEMPTY + stn));
           }
         }
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     // =============================== softmax groups ===============================
+    constexpr int NC = BN / 32;              // 32-column chunks per key tile
+    constexpr bool PIPE = (D <= 64);         // double-buffer TMEM loads (needs 32 more registers)
     const int x = warp >> 2;                 // sub-tile
     const int row = threadIdx.x & 127;       // row within the sub-tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -398,80 +455,126 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tO = tmem + lane_base + P::kColO + D * x;
     const int64_t uq = uq0 + 128 * x + row;
     const bool row_valid = uq < uq_end;
+    const int64_t n1 = prm.n_keys - 1;
+    // band of this row, and of the first / last row of this warp (warp-uniform bounds for chunk classes)
     const int64_t lo_q = (uq - prm.w > 0) ? (uq - prm.w) : 0;
-    const int64_t hi_q = (uq + prm.w < prm.n_keys - 1) ? (uq + prm.w) : (prm.n_keys - 1);
+    const int64_t hi_q = (uq + prm.w < n1) ? (uq + prm.w) : n1;
+    const int64_t uq_a = uq - lane, uq_b = uq - lane + 31;
+    const int64_t lo_a = (uq_a - prm.w > 0) ? (uq_a - prm.w) : 0, lo_b = (uq_b - prm.w > 0) ? (uq_b - prm.w) : 0;
+    const int64_t hi_a = (uq_a + prm.w < n1) ? (uq_a + prm.w) : n1, hi_b = (uq_b + prm.w < n1) ? (uq_b + prm.w) : n1;
     float m_run = neg_inf(), l_run = 0.f, corr_prev = 0.f;
     float acc[D];
 #pragma unroll
     for (int e = 0; e < D; ++e) acc[e] = 0.f;
     bool ok = true;
-    uint32_t r[32];
+    uint32_t ra[32], rb[32];
     const int nx = j1[x] - j0[x];
+    const float sc = prm.scale_log2e;
     for (int it = 0; it < nx && ok; ++it) {
       const int j = j0[x] + it;
       const int64_t k0 = kv_lo + (int64_t)j * BN;
-      // columns of this tile that are inside the band for this row: [c_lo, c_hi]
-      const int c_lo = (lo_q > k0) ? (int)(lo_q - k0) : 0;
-      const int c_hi = (hi_q - k0 < BN - 1) ? (int)(hi_q - k0) : (BN - 1);
-      const bool full = (c_lo == 0) && (c_hi == BN - 1);
+      // columns of this tile inside the band: this row [c_lo, c_hi]; every row of the warp [w_lo, w_hi];
+      // some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
+      const int c_lo = (int)(lo_q - k0), c_hi = (int)(hi_q - k0);
+      const int w_lo = (int)(lo_b - k0), w_hi = (int)(hi_a - k0);
+      const int v_lo = (int)(lo_a - k0), v_hi = (int)(hi_b - k0);
       ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + x), (uint32_t)(it & 1), abort_flag, err, 301));
       if (!ok) break;
       tc_fence_after();
-      // pass 1: row maximum (log2 domain)
-      float mx = neg_inf();
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tmem_ld32(tS + c * 32, r);
+      if (row == 0) SPFA_TRACE(5, x, j);
+      // Chunk classes (warp-uniform): 2 = every (row, column) valid, 0 = none valid, 1 = mixed.
+      // Mixed chunks use a per-row bit mask of valid columns.
+      int cls[NC];
+      uint32_t vmask[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int cb = c * 32;
+        cls[c] = (cb >= w_lo && cb + 31 <= w_hi) ? 2 : ((cb + 31 < v_lo || cb > v_hi) ? 0 : 1);
+        const int a = c_lo - cb, b = c_hi - cb;  // valid columns of this chunk: [a, b] clipped to [0, 31]
+        const uint32_t m_lo = (a <= 0) ? 0xffffffffu : (a >= 32 ? 0u : (0xffffffffu << a));
+        const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
+        vmask[c] = m_lo & m_hi;
+      }
+      // ---- pass 1: row maximum of the raw scores (TMEM loads double-buffered against the max tree) ----
+      float mx[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
+      if (PIPE) tmem_ld32(tS, ra);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
+        uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
+        if (!PIPE) tmem_ld32(tS + c * 32, ra);
         tc_wait_ld();
-        if (full) {
+        if (PIPE && c + 1 < NC) tmem_ld32(tS + (c + 1) * 32, nxt);
+        if (cls[c] == 2) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
+          for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(cur[e]));
+        } else if (cls[c] == 1) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int cc = c * 32 + e;
-            if (cc >= c_lo && cc <= c_hi) mx = fmaxf(mx, __uint_as_float(r[e]));
-          }
+          for (int e = 0; e < 32; ++e)
+            mx[e & 3] = fmaxf(mx[e & 3], ((vmask[c] >> e) & 1u) ? __uint_as_float(cur[e]) : neg_inf());
         }
       }
-      mx *= prm.scale_log2e;  // scale > 0: max commutes with the scaling
-      const float m_new = fmaxf(m_run, mx);
+      if (row == 0) SPFA_TRACE(6, x, j);
+      const float mraw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_new = fmaxf(m_run, mraw * sc);  // sc > 0: max commutes with the scaling
       const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
       const float corr = fast_exp2(m_run - m_safe);
-      // fold in the previous tile's P V (the tensor pipe finished it before it produced this S)
+      // ---- fold in the previous tile's P V (the tensor pipe finished it before it produced this S) ----
       if (it > 0) {
         ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((it - 1) & 1), abort_flag, err, 302));
         if (!ok) break;
         tc_fence_after();
+        if (PIPE) tmem_ld32(tO, ra);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          tmem_ld32(tO + c * 32, r);
+          uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
+          uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
+          if (!PIPE) tmem_ld32(tO + c * 32, ra);
           tc_wait_ld();
+          if (PIPE && c + 1 < D / 32) tmem_ld32(tO + (c + 1) * 32, nxt);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(cur[e]));
         }
       }
-      // pass 2: P = exp2(S*c - m), row sum, P (rounded to tf32) back over S
-      float lsum = 0.f;
+      // ---- pass 2: P = exp2(S*sc - m) truncated to tf32 (the bits the MMA reads), row sum of the
+      //      truncated values (so P/l stays exactly normalised), P written back over S ----
+      if (row == 0) SPFA_TRACE(7, x, j);
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_safe;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        tmem_ld32(tS + c * 32, r);
-        tc_wait_ld();
+      if (PIPE) tmem_ld32(tS, ra);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int cc = c * 32 + e;
-          float p = fast_exp2(fmaf(__uint_as_float(r[e]), prm.scale_log2e, neg_m));
-          if (!full && (cc < c_lo || cc > c_hi)) p = 0.f;
-          lsum += p;
-          r[e] = to_tf32(p);
+      for (int c = 0; c < NC; ++c) {
+        uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
+        uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
+        if (!PIPE) tmem_ld32(tS + c * 32, ra);
+        tc_wait_ld();
+        if (PIPE && c + 1 < NC) tmem_ld32(tS + (c + 1) * 32, nxt);
+        if (cls[c] == 2) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(cur[e]), sc, neg_m))) & 0xffffe000u;
+            ls[e & 3] += __uint_as_float(pb);
+            cur[e] = pb;
+          }
+        } else if (cls[c] == 1) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(cur[e]), sc, neg_m))) & 0xffffe000u;
+            pb = ((vmask[c] >> e) & 1u) ? pb : 0u;
+            ls[e & 3] += __uint_as_float(pb);
+            cur[e] = pb;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) cur[e] = 0u;
         }
-        tmem_st32(tS + c * 32, r);
+        tmem_st32(tS + c * 32, cur);
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_PREADY + x));
-      l_run = fmaf(l_run, corr, lsum);
+      if (row == 0) SPFA_TRACE(8, x, j);
+      l_run = fmaf(l_run, corr, (ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
       corr_prev = corr;
     }
@@ -481,10 +584,10 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          tmem_ld32(tO + c * 32, r);
+          tmem_ld32(tO + c * 32, ra);
           tc_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(r[e]));
+          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(ra[e]));
         }
       }
     }
@@ -516,6 +619,15 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // ---- common exit: everyone is done with TMEM before it is released ----
   tc_fence_before();
   __syncthreads();
+#ifdef SPFA_TILE_TRACE
+  if (blockIdx.x == 1 && threadIdx.x == 0) {
+    const int n = g_trace_n < 4096 ? g_trace_n : 4096;
+    for (int i = 0; i < n; ++i) {
+      const long long v = g_trace[i];
+      printf("T %d %d %d %lld\n", (int)(v >> 56), (int)((v >> 52) & 15), (int)((v >> 44) & 255), v & 0xfffffffffffLL);
+    }
+  }
+#endif
   if (warp == 8) {
     tc_fence_after();
     if (*abort_flag && lane == 0) {

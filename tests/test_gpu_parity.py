@@ -385,7 +385,10 @@ def test_full_size_properties_local(capi):
         rb, re = 30000, 34000
         sh = capi.new_state(re - rb, d)
         capi.local_forward(Q[rb:re].contiguous(), K, V, *sh, w, rb, re)
-        assert torch.equal(sh[1], st[1][rb:re]) and torch.equal(sh[2], st[2][rb:re])
+        if path == capi.PATH_GATHER:  # one warp per row: a shard repeats the full run's arithmetic exactly
+            assert torch.equal(sh[1], st[1][rb:re]) and torch.equal(sh[2], st[2][rb:re])
+        else:  # tile boundaries move with the shard, so the summation order differs
+            assert torch.allclose(sh[1], st[1][rb:re], rtol=4e-3) and (sh[2] - st[2][rb:re]).abs().max().item() <= tol
 
 
 def test_full_size_sampled_rows_vs_oracle(capi, orc):
