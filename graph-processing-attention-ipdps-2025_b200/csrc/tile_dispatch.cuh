@@ -7,6 +7,8 @@
 
 #include <atomic>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 
 #include "../../include/spfa_b200.h"
 #include "tile_kernels_sm100.cuh"
@@ -56,18 +58,34 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, int BN, int NS>
+template <int D, int BN, int NS, int NSUB>
 int launch_band(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t w,
                 int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
-  using P = tile::Plan<D, BN, NS>;
-  auto kern = tile::band_forward_kernel<D, BN, NS>;
+  using P = tile::Plan<D, BN, NS, NSUB>;
+  using G = tile::Geo<NSUB>;
+  auto kern = tile::band_forward_kernel<D, BN, NS, NSUB>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
+  // ask for the largest shared-memory carve-out so that kCtasPerSm CTAs are co-resident
+  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (const char* dbg = getenv("SPFA_DEBUG_OCCUPANCY")) {
+    int nb = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, G::kThreads, P::kDynSmem);
+    cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, kern);
+    int nb_small = 0, smem_sm = 0, regs_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb_small, kern, G::kThreads, 1024);
+    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, 0);
+    cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, 0);
+    fprintf(stderr, "spfa: band kernel D=%d BN=%d NS=%d NSUB=%d dyn smem=%d B static=%d B regs=%d threads=%d -> %d CTA/SM "
+            "(%d with 1 KB smem); SM has %d B smem, %d regs (%s)\n", D, BN, NS, NSUB, (int)P::kDynSmem,
+            (int)fa.sharedSizeBytes, fa.numRegs, G::kThreads, nb, nb_small, smem_sm, regs_sm, dbg);
+  }
   // The kernel re-balances registers with setmaxnreg, which blocks without timeout if the budgets exceed
   // what the launch allocated: refuse to launch unless the compiled register count covers them.
   cudaFuncAttributes attr;
   if (cudaFuncGetAttributes(&attr, kern) != cudaSuccess) return SPFA_ERR_LAUNCH;
-  if (attr.numRegs * tile::kThreads < tile::kRegsSoftmax * 256 + tile::kRegsAux * 128) return SPFA_ERR_LAUNCH;
+  if (attr.numRegs * G::kThreads < G::kRegsSoftmax * 128 * NSUB + G::kRegsAux * 128) return SPFA_ERR_LAUNCH;
   int* err = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
   for (int64_t r = 0; r < s && r < L; ++r) {
@@ -89,9 +107,9 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
     if (!make_row_map(&tmQ, Q + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128) ||
         !make_row_map(&tmK, K + r * D, D, prm.n_keys, pitch, BN) || !make_row_map(&tmV, V + r * D, D, prm.n_keys, pitch, BN, /*mn_major=*/true))
       return SPFA_ERR_LAUNCH;
-    const int64_t grid = (prm.n_q + tile::kQRows - 1) / tile::kQRows;
+    const int64_t grid = (prm.n_q + G::kQRows - 1) / G::kQRows;
     if (grid > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
-    kern<<<(unsigned)grid, tile::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
+    kern<<<(unsigned)grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
     g_launches.fetch_add(1);
     if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
   }
@@ -106,9 +124,9 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
   if (!shape_ok) return forced ? (int)SPFA_ERR_BAD_ARG : SPFA_TILE_NOT_TAKEN;
   if (!forced && w < kTileMinHalfWidth) return SPFA_TILE_NOT_TAKEN;
   switch (d) {
-    case 32: return launch_band<32, 128, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 64: return launch_band<64, 128, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 128: return launch_band<128, 64, 1>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 32: return launch_band<32, 128, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 64: return launch_band<64, 128, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 128: return launch_band<128, 64, 1, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
   }
   return SPFA_TILE_NOT_TAKEN;
 }

@@ -2,7 +2,8 @@
 // TMEM accumulators, online softmax in registers.
 //
 // One CTA owns 256 consecutive query rows of a (strided) row sequence, as two 128-row sub-tiles A and
-// B, and walks the key tiles that intersect the band |u_q - u_k| <= w. Roles (320 threads):
+// B (or, with NSUB = 1, a single 128-row tile and two CTAs per SM), and walks the key tiles that
+// intersect the band |u_q - u_k| <= w. Roles for NSUB = 2 (384 threads; NSUB = 1 drops group B):
 //   warps 0-3  softmax group A   thread t <-> query row t of sub-tile A  <-> TMEM lane t
 //   warps 4-7  softmax group B
 //   warp  8    TMA producer (one elected lane) + TMEM allocation
@@ -11,10 +12,11 @@
 //              setmaxnreg gives the softmax groups 216 registers/thread and leaves 72 to this group)
 // Per key tile j and sub-tile X:
 //   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM
-//   P_X = exp2(S_X*c - m) written back over S_X in TMEM by the softmax group (row max / row sum in
-//                         registers, no shuffles: one thread owns one row)
-//   O_X = P_X V_j        tcgen05.mma kind::tf32, A = P_X (TMEM), B = V_j (smem, MN-major), fresh D
-//   acc = acc*corr + O_X in the softmax group's registers (so TMEM never needs rescaling)
+//   P_X = exp2(S_X*c - shift) written back over S_X in TMEM by the softmax group (row max / row sum in
+//                         registers, no shuffles: one thread owns one row; `shift` is a lazy per-row
+//                         reference that moves only when the row maximum outgrows it by 2^8)
+//   O_X += P_X V_j       tcgen05.mma kind::tf32, A = P_X (TMEM), B = V_j (smem, MN-major), D stays in TMEM
+//                         for the whole CTA; a row whose reference moves rescales its own O row in TMEM
 // The MMA thread interleaves the two sub-tiles (PV_A(j), S_A(j+1), PV_B(j), S_B(j+1), ...) so the
 // tensor pipe works on one sub-tile while the other is in its exponentials.
 //
@@ -37,29 +39,44 @@
 namespace spfa {
 namespace tile {
 
-#ifdef SPFA_TILE_TRACE  // probe build only: per-event cycle stamps of one CTA, printed at its exit
-__device__ long long g_trace[4096];
-__device__ int g_trace_n;
-#define SPFA_TRACE(tag, a, b)                                                                   \
-  do {                                                                                            \
-    if (blockIdx.x == 1) {                                                                        \
-      int i_ = atomicAdd(&g_trace_n, 1);                                                          \
-      if (i_ < 4096) g_trace[i_] = ((long long)(tag) << 56) | ((long long)(a) << 52) | ((long long)(b) << 44) | (clock64() & 0xfffffffffffLL); \
-    }                                                                                             \
+#ifdef SPFA_TILE_TRACE  // probe build only: per-event cycle stamps of one CTA, kept in shared memory
+// (a global atomic per event would perturb the timeline) and printed at the CTA's exit.
+constexpr int kTraceSlots = 3, kTraceCap = 400;  // slot 0: MMA thread, 1: softmax A row 0, 2: softmax B row 0
+#define SPFA_TRACE_AT(slot, tag, a, b)                                                                       \
+  do {                                                                                                       \
+    if (blockIdx.x == 1) {                                                                                   \
+      int& n_ = trace_n[slot];                                                                               \
+      if (n_ < kTraceCap)                                                                                    \
+        trace_buf[(slot) * kTraceCap + n_++] =                                                               \
+            ((long long)(tag) << 56) | ((long long)(a) << 52) | ((long long)(b) << 44) | (clock64() & 0xfffffffffffLL); \
+    }                                                                                                        \
   } while (0)
 #else
-#define SPFA_TRACE(tag, a, b) do {} while (0)
+#define SPFA_TRACE_AT(slot, tag, a, b) do {} while (0)
 #endif
 
-constexpr int kThreads = 384;      // three warpgroups: softmax A, softmax B, {TMA, MMA, 2 idle warps}
-constexpr int kQRows = 256;        // query rows per CTA (two 128-row sub-tiles)
-// Register re-balancing. The CTA is launched with kRegsLaunch registers per thread (what the compiler
-// assigns to a 384-thread, 1-CTA/SM kernel: 3 warps per scheduler share 512 registers per lane). setmaxnreg.inc
-// BLOCKS until the CTA's pool can satisfy it and has no timeout, so the two budgets must fit in the
-// pool the launch allocated -- otherwise the softmax groups would wait forever.
-constexpr int kRegsLaunch = 168, kRegsSoftmax = 216, kRegsAux = 72;
-static_assert(kRegsSoftmax * 256 + kRegsAux * 128 <= kRegsLaunch * kThreads, "setmaxnreg budgets exceed the launch pool");
-static_assert(kRegsSoftmax % 8 == 0 && kRegsAux % 8 == 0, "setmaxnreg takes multiples of 8");
+// Geometry of a CTA with NSUB 128-row sub-tiles: NSUB softmax warpgroups + one warpgroup holding the
+// TMA warp, the MMA warp and two idle warps. NSUB = 2 runs one CTA per SM (sub-tiles interleave on the
+// tensor pipe inside the CTA); NSUB = 1 runs two CTAs per SM, which also hides each CTA's prologue and
+// epilogue latency behind the other CTA.
+//
+// Register re-balancing. A CTA is launched with Geo::kRegsLaunch registers per thread (what the compiler
+// assigns under __launch_bounds__(kThreads, kCtasPerSm)). setmaxnreg.inc BLOCKS until the CTA's pool can
+// satisfy it and has no timeout, so the two budgets must fit in the pool the launch allocated -- otherwise
+// the softmax groups would wait forever. The host re-checks this against cudaFuncGetAttributes.
+template <int NSUB>
+struct Geo {
+  static constexpr int kThreads = 128 * NSUB + 128;
+  static constexpr int kQRows = 128 * NSUB;
+  static constexpr int kCtasPerSm = (NSUB == 1) ? 2 : 1;
+  static constexpr int kRegsLaunch = (NSUB == 1) ? 128 : 168;
+  static constexpr int kRegsSoftmax = (NSUB == 1) ? 208 : 216;
+  static constexpr int kRegsAux = (NSUB == 1) ? 48 : 72;
+  static constexpr int kSoftmaxWarps = 4 * NSUB;
+  static_assert(kRegsSoftmax * 128 * NSUB + kRegsAux * 128 <= kRegsLaunch * kThreads,
+                "setmaxnreg budgets exceed the launch pool");
+  static_assert(kRegsSoftmax % 8 == 0 && kRegsAux % 8 == 0, "setmaxnreg takes multiples of 8");
+};
 constexpr uint64_t kWaitNs = 200ull * 1000 * 1000;  // 0.2 s per wait before giving up
 
 struct BandParams {
@@ -175,6 +192,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ uint32_t to_tf32(float x) {
   uint32_t y;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(y) : "f"(x));
@@ -208,42 +237,50 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int b_mn_major) 
 }
 
 // ---- shared-memory plan --------------------------------------------------------------------------------
-template <int D, int BN, int NS>
+template <int D, int BN, int NS, int NSUB>
 struct Plan {
   static constexpr int kChunks = D / 32;                    // 32-float (128 B) column chunks per row
   static constexpr int kQChunkBytes = 128 * 128;            // 128 rows x 128 B
   static constexpr int kKVChunkBytes = BN * 128;            // BN rows x 128 B
-  static constexpr int kQBytes = 2 * kChunks * kQChunkBytes;  // two sub-tiles
+  static constexpr int kQBytes = NSUB * kChunks * kQChunkBytes;  // all sub-tiles
   static constexpr int kKVStageBytes = kChunks * kKVChunkBytes;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + NS * kKVStageBytes;
   static constexpr int kOffBar = kOffV + NS * kKVStageBytes;
-  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[2], p_ready[2], o_ready[2]
-  static constexpr int kNumBars = 1 + 4 * NS + 6;
+  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[NSUB], p_ready[NSUB], o_ready[NSUB]
+  static constexpr int kNumBars = 1 + 4 * NS + 3 * NSUB;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
   static constexpr int kBytes = kOffMisc + 16;
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
-  // TMEM columns: S_A, S_B (BN each, at 0 and 128), O_A, O_B (D each, at 256 and 256 + D)
-  static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0, kColO = 256;
+  // TMEM columns: S_x (BN each, at 128 x), then O_x (D each, at 128 NSUB + D x); 256 columns per sub-tile
+  static constexpr int kTmemCols = 256 * NSUB;
+  static constexpr int kColS = 0, kColO = 128 * NSUB;
 };
 
-template <int D, int BN, int NS>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int D, int BN, int NS, int NSUB>
+__global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, float* __restrict__ m_out, float* __restrict__ l_out,
                     float* __restrict__ O_out, const BandParams prm, int* __restrict__ err) {
-  using P = Plan<D, BN, NS>;
+  using P = Plan<D, BN, NS, NSUB>;
+  using G = Geo<NSUB>;
+  constexpr int kQRows = G::kQRows;
+  constexpr int W_TMA = G::kSoftmaxWarps, W_MMA = G::kSoftmaxWarps + 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + P::kOffBar;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 1 + NS, B_VFULL = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
-            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + 2, B_OREADY = B_SREADY + 4;
+            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + NSUB, B_OREADY = B_SREADY + 2 * NSUB;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + P::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
+#ifdef SPFA_TILE_TRACE
+  __shared__ long long trace_buf[kTraceSlots * kTraceCap];
+  __shared__ int trace_n[kTraceSlots];
+  if (threadIdx.x < kTraceSlots) trace_n[threadIdx.x] = 0;
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -256,9 +293,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
   const int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
   // active key-tile range [j0, j1) of each sub-tile
-  int j0[2], j1[2];
+  int j0[NSUB], j1[NSUB];
 #pragma unroll
-  for (int x = 0; x < 2; ++x) {
+  for (int x = 0; x < NSUB; ++x) {
     const int64_t ux0 = uq0 + 128 * x;
     int64_t ux_last = ux0 + 127;
     if (ux_last > uq_end - 1) ux_last = uq_end - 1;
@@ -283,7 +320,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(bar(B_VFULL + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
     }
-    for (int x = 0; x < 2; ++x) {
+    for (int x = 0; x < NSUB; ++x) {
       mbar_init(bar(B_SREADY + x), 1);
       mbar_init(bar(B_PREADY + x), 128);
       mbar_init(bar(B_OREADY + x), 1);
@@ -291,7 +328,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == W_TMA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + P::kOffMisc),
                  "r"(P::kTmemCols)
                  : "memory");
@@ -302,16 +339,16 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = *tmem_base_slot;
 
-  if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsAux));
-  if (warp == 8) {
+  if (warp >= W_TMA) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(G::kRegsAux));
+  if (warp == W_TMA) {
     // =============================== TMA producer ===============================
     if (lane == 0) {
       // Q: both sub-tiles, coordinates relative to the first query u of the shard (rows past the end read zeros)
       mbar_expect_tx(bar(B_QFULL), P::kQBytes);
       const int32_t yq = (int32_t)(uq0 - prm.u_q_first);
 #pragma unroll
-      for (int x = 0; x < 2; ++x)
+      for (int x = 0; x < NSUB; ++x)
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
           tma_load_2d(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes, &tmQ, c * 32, yq + 128 * x,
@@ -337,28 +374,33 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                       bar(B_VFULL + st));
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == W_MMA) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t kIdescS = idesc_tf32(128, BN, 0);
       constexpr uint32_t kIdescO = idesc_tf32(128, D, 1);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
-      int n_s[2] = {0, 0}, n_pv[2] = {0, 0};  // S / PV tiles issued per sub-tile (phase of their barriers)
+      int n_s[NSUB] = {}, n_pv[NSUB] = {};  // S / PV tiles issued per sub-tile (phase of their barriers)
+      // Descriptors are built once per operand tile; each MMA only adds a compile-time offset to the
+      // 14-bit start-address field (shared memory is < 256 KB, so the field cannot carry out).
       auto issue_S = [&](int x, int j) {
         const int st = j % NS;
-        const uint32_t qa = sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
-        const uint32_t ka = sbase + P::kOffK + st * P::kKVStageBytes;
+        const uint64_t qd = smem_desc(sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes, 16, 1024, kLayoutSw128);
+        const uint64_t kd = smem_desc(sbase + P::kOffK + st * P::kKVStageBytes, 16, 1024, kLayoutSw128);
         const uint32_t d_t = tmem + P::kColS + 128 * x;
-        int k = 0;
 #ifdef SPFA_TILE_TIMING
         const long long t_s0 = clock64();
 #endif
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk, ++k)
-            mma_ss(d_t, smem_desc(qa + c * P::kQChunkBytes + kk * 32, 16, 1024, kLayoutSw128),
-                   smem_desc(ka + c * P::kKVChunkBytes + kk * 32, 16, 1024, kLayoutSw128), kIdescS, k > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk)
+#ifndef SPFA_X_NO_S
+            mma_ss(d_t, qd + (uint64_t)((c * P::kQChunkBytes + kk * 32) >> 4),
+                   kd + (uint64_t)((c * P::kKVChunkBytes + kk * 32) >> 4), kIdescS, (c | kk) ? 1u : 0u);
+#else
+            ;
+#endif
         tc_commit(bar(B_SREADY + x));
 #ifdef SPFA_TILE_TIMING  // probe build only: serialise on the MMA's completion and report its latency
         if (blockIdx.x == 1) {
@@ -371,17 +413,20 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       auto issue_PV = [&](int x, int j) {
         const int st = j % NS;
-        const uint32_t va = sbase + P::kOffV + st * P::kKVStageBytes;
+        // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
+        const uint64_t vd = smem_desc(sbase + P::kOffV + st * P::kKVStageBytes, P::kKVChunkBytes, 512, kLayoutSw128Base32);
         const uint32_t a_t = tmem + P::kColS + 128 * x;
         const uint32_t d_t = tmem + P::kColO + D * x;
+        const uint32_t first = (j > j0[x]) ? 1u : 0u;  // O accumulates in TMEM across the key tiles of a sub-tile
 #ifdef SPFA_TILE_TIMING
         const long long t_p0 = clock64();
 #endif
 #pragma unroll
-        for (int kk = 0; kk < BN / 8; ++kk)
-          // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
-          mma_ts(d_t, a_t + kk * 8, smem_desc(va + kk * 1024, P::kKVChunkBytes, 512, kLayoutSw128Base32), kIdescO,
-                 kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < BN / 8; ++kk) {
+#ifndef SPFA_X_NO_PV
+          mma_ts(d_t, a_t + kk * 8, vd + (uint64_t)((kk * 1024) >> 4), kIdescO, kk > 0 ? 1u : first);
+#endif
+        }
         tc_commit(bar(B_OREADY + x));
 #ifdef SPFA_TILE_TIMING
         if (blockIdx.x == 1) {
@@ -394,14 +439,14 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       auto active = [&](int x, int j) { return j >= j0[x] && j < j1[x]; };
       auto last_active = [&](int x, int j) {  // is x the last sub-tile (in issue order A, B) using tile j?
-        return x == 1 || !active(1, j);
+        return x == NSUB - 1 || !active(NSUB - 1, j);
       };
       // prologue: S of tile 0
       if (ok && nT > 0) {
         ok = mbar_wait(bar(B_KFULL + 0), 0, abort_flag, err, 202);
         if (ok) {
           tc_fence_after();
-          for (int x = 0; x < 2; ++x)
+          for (int x = 0; x < NSUB; ++x)
             if (active(x, 0)) {
               issue_S(x, 0);
               if (last_active(x, 0)) tc_commit(bar(B_KEMPTY + 0));
@@ -412,7 +457,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int st = j % NS, stn = (j + 1) % NS;
         const uint32_t ph = (uint32_t)((j / NS) & 1), phn = (uint32_t)(((j + 1) / NS) & 1);
         bool have_v = false, have_kn = false;
-        for (int x = 0; x < 2 && ok; ++x) {
+        for (int x = 0; x < NSUB && ok; ++x) {
           if (active(x, j)) {
             ok = mbar_wait(bar(B_PREADY + x), (uint32_t)((j - j0[x]) & 1), abort_flag, err, 203);
             if (!ok) break;
@@ -422,9 +467,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               have_v = true;
             }
             tc_fence_after();
-            SPFA_TRACE(1, x, j);
+            SPFA_TRACE_AT(0, 1, x, j);
             issue_PV(x, j);
-            SPFA_TRACE(2, x, j);
+            SPFA_TRACE_AT(0, 2, x, j);
             if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
           }
           if (j + 1 < nT && active(x, j + 1)) {
@@ -434,9 +479,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               have_kn = true;
             }
             tc_fence_after();
-            SPFA_TRACE(3, x, j + 1);
+            SPFA_TRACE_AT(0, 3, x, j + 1);
             issue_S(x, j + 1);
-            SPFA_TRACE(4, x, j + 1);
+            SPFA_TRACE_AT(0, 4, x, j + 1);
             if (last_active(x, j + 1)) tc_commit(bar(B_KEMPTY + stn));
           }
         }
@@ -444,10 +489,16 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(G::kRegsSoftmax));
     // =============================== softmax groups ===============================
+    // One thread owns one query row. Per key tile the row of S is read from TMEM ONCE (all chunk loads
+    // issued back to back), exponentiated against a per-row reference `shift`, and written back as P.
+    // O accumulates in TMEM across tiles (the PV MMAs add into it), so nothing is read back per tile.
+    // `shift` is lazy: it only moves when the row maximum exceeds it by more than kShiftSlack (log2
+    // units), in which case this thread rescales its own O row and row sum. The true running maximum is
+    // tracked separately for the (m, l) state the caller gets back.
     constexpr int NC = BN / 32;              // 32-column chunks per key tile
-    constexpr bool PIPE = (D <= 64);         // double-buffer TMEM loads (needs 32 more registers)
+    constexpr float kShiftSlack = 8.0f;      // P values stay below 2^8 relative to the reference
     const int x = warp >> 2;                 // sub-tile
     const int row = threadIdx.x & 127;       // row within the sub-tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -455,33 +506,42 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tO = tmem + lane_base + P::kColO + D * x;
     const int64_t uq = uq0 + 128 * x + row;
     const bool row_valid = uq < uq_end;
-    const int64_t n1 = prm.n_keys - 1;
-    // band of this row, and of the first / last row of this warp (warp-uniform bounds for chunk classes)
-    const int64_t lo_q = (uq - prm.w > 0) ? (uq - prm.w) : 0;
-    const int64_t hi_q = (uq + prm.w < n1) ? (uq + prm.w) : n1;
-    const int64_t uq_a = uq - lane, uq_b = uq - lane + 31;
-    const int64_t lo_a = (uq_a - prm.w > 0) ? (uq_a - prm.w) : 0, lo_b = (uq_b - prm.w > 0) ? (uq_b - prm.w) : 0;
-    const int64_t hi_a = (uq_a + prm.w < n1) ? (uq_a + prm.w) : n1, hi_b = (uq_b + prm.w < n1) ? (uq_b + prm.w) : n1;
-    float m_run = neg_inf(), l_run = 0.f, corr_prev = 0.f;
-    float acc[D];
+    // band of this row, and of the first / last row of this warp (warp-uniform bounds for chunk classes),
+    // as 32-bit offsets from the CTA's first key tile
+    int lo_q, hi_q, lo_a, lo_b, hi_a, hi_b;
+    {
+      const int64_t n1 = prm.n_keys - 1, uq_a = uq - lane, uq_b = uq - lane + 31;
+      auto lo_of = [&](int64_t u) { return (int)(((u - prm.w > 0) ? (u - prm.w) : 0) - kv_lo); };
+      auto hi_of = [&](int64_t u) { return (int)(((u + prm.w < n1) ? (u + prm.w) : n1) - kv_lo); };
+      lo_q = lo_of(uq); hi_q = hi_of(uq);
+      lo_a = lo_of(uq_a); lo_b = lo_of(uq_b);
+      hi_a = hi_of(uq_a); hi_b = hi_of(uq_b);
+    }
+    // The caller's state row is needed only in the epilogue; asking L2 for it now takes its DRAM latency
+    // off the end of the CTA.
+    if (row_valid) {
+      const int64_t rl0 = prm.r + uq * prm.s - prm.row_begin;
+      const char* orow = reinterpret_cast<const char*>(O_out + (size_t)rl0 * D);
 #pragma unroll
-    for (int e = 0; e < D; ++e) acc[e] = 0.f;
+      for (int b = 0; b < D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + b));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(m_out + rl0));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(l_out + rl0));
+    }
+    float m_true = neg_inf();   // running maximum of the scaled scores (log2 units)
+    float shift = neg_inf();    // reference the exponentials and O are currently expressed against
+    float l_run = 0.f;          // row sum relative to `shift`
     bool ok = true;
-    uint32_t ra[32], rb[32];
+    uint32_t sr[NC][32];
     const int nx = j1[x] - j0[x];
     const float sc = prm.scale_log2e;
     for (int it = 0; it < nx && ok; ++it) {
       const int j = j0[x] + it;
-      const int64_t k0 = kv_lo + (int64_t)j * BN;
+      const int k0 = j * BN;
       // columns of this tile inside the band: this row [c_lo, c_hi]; every row of the warp [w_lo, w_hi];
       // some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
-      const int c_lo = (int)(lo_q - k0), c_hi = (int)(hi_q - k0);
-      const int w_lo = (int)(lo_b - k0), w_hi = (int)(hi_a - k0);
-      const int v_lo = (int)(lo_a - k0), v_hi = (int)(hi_b - k0);
-      ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + x), (uint32_t)(it & 1), abort_flag, err, 301));
-      if (!ok) break;
-      tc_fence_after();
-      if (row == 0) SPFA_TRACE(5, x, j);
+      const int c_lo = lo_q - k0, c_hi = hi_q - k0;
+      const int w_lo = lo_b - k0, w_hi = hi_a - k0;
+      const int v_lo = lo_a - k0, v_hi = hi_b - k0;
       // Chunk classes (warp-uniform): 2 = every (row, column) valid, 0 = none valid, 1 = mixed.
       // Mixed chunks use a per-row bit mask of valid columns.
       int cls[NC];
@@ -495,124 +555,145 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
         vmask[c] = m_lo & m_hi;
       }
-      // ---- pass 1: row maximum of the raw scores (TMEM loads double-buffered against the max tree) ----
+      ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + x), (uint32_t)(it & 1), abort_flag, err, 301));
+      if (!ok) break;
+      tc_fence_after();
+      if (row == 0) SPFA_TRACE_AT(1 + x, 5, x, j);
+      // ---- the whole S row, one TMEM latency ----
+#ifndef SPFA_X_NO_SOFTMAX
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+        if (cls[c] != 0) tmem_ld32(tS + c * 32, sr[c]);
+      tc_wait_ld();
+#else
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sr[c][e] = 0x3f800000u;
+#endif
+      // ---- row maximum over the valid columns ----
       float mx[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
-      if (PIPE) tmem_ld32(tS, ra);
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
-        uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
-        uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
-        if (!PIPE) tmem_ld32(tS + c * 32, ra);
-        tc_wait_ld();
-        if (PIPE && c + 1 < NC) tmem_ld32(tS + (c + 1) * 32, nxt);
         if (cls[c] == 2) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(cur[e]));
+          for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(sr[c][e]));
         } else if (cls[c] == 1) {
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            mx[e & 3] = fmaxf(mx[e & 3], ((vmask[c] >> e) & 1u) ? __uint_as_float(cur[e]) : neg_inf());
+            mx[e & 3] = fmaxf(mx[e & 3], ((vmask[c] >> e) & 1u) ? __uint_as_float(sr[c][e]) : neg_inf());
         }
       }
-      if (row == 0) SPFA_TRACE(6, x, j);
-      const float mraw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_run, mraw * sc);  // sc > 0: max commutes with the scaling
-      const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
-      const float corr = fast_exp2(m_run - m_safe);
-      // ---- fold in the previous tile's P V (the tensor pipe finished it before it produced this S) ----
-      if (it > 0) {
-        ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((it - 1) & 1), abort_flag, err, 302));
-        if (!ok) break;
-        tc_fence_after();
-        if (PIPE) tmem_ld32(tO, ra);
+      const float t_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
+      m_true = fmaxf(m_true, t_max);
+      if (row == 0) SPFA_TRACE_AT(1 + x, 6, x, j);
+      // ---- move the reference if this row outgrew it (always on the row's first valid tile) ----
+      const bool move = t_max > shift + kShiftSlack;  // shift = -inf: true as soon as the row has a valid column
+      if (__any_sync(kFullMask, move)) {
+        const float new_shift = move ? t_max : shift;
+        const float f = move ? ((shift == neg_inf()) ? 0.f : fast_exp2(shift - new_shift)) : 1.0f;
+        l_run *= f;
+        if (it > 0) {
+          // O of this row is final up to the previous tile: its PV finished before this S was produced
+          // (the tensor pipe runs one thread's MMAs in order), and the next PV waits for our P.
+          uint32_t ob[8];  // small pieces: the S row (sr) stays live in registers across this
+#pragma unroll 1
+          for (int c = 0; c < D / 8; ++c) {
+            tmem_ld8(tO + c * 8, ob);
+            tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
-          uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
-          if (!PIPE) tmem_ld32(tO + c * 32, ra);
-          tc_wait_ld();
-          if (PIPE && c + 1 < D / 32) tmem_ld32(tO + (c + 1) * 32, nxt);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(cur[e]));
+            for (int e = 0; e < 8; ++e) ob[e] = __float_as_uint(__uint_as_float(ob[e]) * f);
+            tmem_st8(tO + c * 8, ob);
+          }
         }
+        shift = new_shift;
       }
-      // ---- pass 2: P = exp2(S*sc - m) truncated to tf32 (the bits the MMA reads), row sum of the
-      //      truncated values (so P/l stays exactly normalised), P written back over S ----
-      if (row == 0) SPFA_TRACE(7, x, j);
+      const float neg_shift = (shift == neg_inf()) ? 0.f : -shift;
+      // ---- P = exp2(S*sc - shift) truncated to tf32 (the bits the MMA reads); the row sum adds the
+      //      truncated values so that P / l stays exactly normalised; P goes back over S ----
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_safe;
-      if (PIPE) tmem_ld32(tS, ra);
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
-        uint32_t(&cur)[32] = (PIPE && (c & 1)) ? rb : ra;
-        uint32_t(&nxt)[32] = (PIPE && (c & 1)) ? ra : rb;
-        if (!PIPE) tmem_ld32(tS + c * 32, ra);
-        tc_wait_ld();
-        if (PIPE && c + 1 < NC) tmem_ld32(tS + (c + 1) * 32, nxt);
         if (cls[c] == 2) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(cur[e]), sc, neg_m))) & 0xffffe000u;
+#ifndef SPFA_X_NO_EXP
+            const uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[c][e]), sc, neg_shift))) & 0xffffe000u;
+#else
+            const uint32_t pb = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc, neg_shift)) & 0xffffe000u;
+#endif
             ls[e & 3] += __uint_as_float(pb);
-            cur[e] = pb;
+            sr[c][e] = pb;
           }
         } else if (cls[c] == 1) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(cur[e]), sc, neg_m))) & 0xffffe000u;
+            uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[c][e]), sc, neg_shift))) & 0xffffe000u;
             pb = ((vmask[c] >> e) & 1u) ? pb : 0u;
             ls[e & 3] += __uint_as_float(pb);
-            cur[e] = pb;
+            sr[c][e] = pb;
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) cur[e] = 0u;
+          for (int e = 0; e < 32; ++e) sr[c][e] = 0u;
         }
-        tmem_st32(tS + c * 32, cur);
+#ifndef SPFA_X_NO_SOFTMAX
+        tmem_st32(tS + c * 32, sr[c]);
+#endif
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_PREADY + x));
-      if (row == 0) SPFA_TRACE(8, x, j);
-      l_run = fmaf(l_run, corr, (ls[0] + ls[1]) + (ls[2] + ls[3]));
-      m_run = m_new;
-      corr_prev = corr;
+      if (row == 0) SPFA_TRACE_AT(1 + x, 8, x, j);
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
+    // ---- epilogue: O row from TMEM, normalised and merged with the caller's (m, l, O) ----
     if (ok && nx > 0) {
       ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((nx - 1) & 1), abort_flag, err, 303));
       if (ok) {
         tc_fence_after();
+#ifdef SPFA_X_NO_EPI
+        const bool store = false;
+#else
+        const bool store = row_valid && l_run > 0.f;
+#endif
+        const int64_t rl = store ? (prm.r + uq * prm.s - prm.row_begin) : 0;  // shard-local row
+        float a = 0.f, b = 0.f, inv = 0.f, m_o = 0.f, l_o = 0.f;
+        if (store) {
+          // state in natural-log units, as the gather path: l is re-expressed against the true maximum
+          const float l_loc = l_run * fast_exp2(shift - m_true);
+          const float m_loc = m_true * 0.6931471805599453f;
+          const float m_in = m_out[rl], l_in = l_out[rl];
+          m_o = fmaxf(m_in, m_loc);
+          a = l_in * fast_exp2((m_in - m_o) * kLog2e);
+          const float bt = fast_exp2((m_loc - m_o) * kLog2e);
+          l_o = fmaf(l_loc, bt, a);
+          inv = 1.0f / l_o;
+          b = bt * fast_exp2(shift - m_true);  // O in TMEM is relative to `shift`
+        }
+        float4* op = reinterpret_cast<float4*>(O_out + (size_t)rl * D);
+        uint32_t ob[32];
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          tmem_ld32(tO + c * 32, ra);
+          tmem_ld32(tO + c * 32, ob);
           tc_wait_ld();
+          if (store) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], corr_prev, __uint_as_float(ra[e]));
+            for (int e = 0; e < 8; ++e) {
+              float4 o = op[c * 8 + e];
+              o.x = (a * o.x + b * __uint_as_float(ob[4 * e + 0])) * inv;
+              o.y = (a * o.y + b * __uint_as_float(ob[4 * e + 1])) * inv;
+              o.z = (a * o.z + b * __uint_as_float(ob[4 * e + 2])) * inv;
+              o.w = (a * o.w + b * __uint_as_float(ob[4 * e + 3])) * inv;
+              op[c * 8 + e] = o;
+            }
+          }
+        }
+        if (store) {
+          m_out[rl] = m_o;
+          l_out[rl] = l_o;
         }
       }
-    }
-    // ---- epilogue: merge with the caller's (m, l, O) and store (same recurrence as the gather path) ----
-    if (ok && row_valid && l_run > 0.f) {
-      const int64_t rl = prm.r + uq * prm.s - prm.row_begin;  // shard-local row
-      const float m_loc = m_run * 0.6931471805599453f;        // back to natural-log units
-      const float m_in = m_out[rl], l_in = l_out[rl];
-      const float m_o = fmaxf(m_in, m_loc);
-      const float a = l_in * fast_exp2((m_in - m_o) * kLog2e);
-      const float b = fast_exp2((m_loc - m_o) * kLog2e);
-      const float l_o = fmaf(l_run, b, a);
-      const float inv = 1.0f / l_o;
-      float4* op = reinterpret_cast<float4*>(O_out + (size_t)rl * D);
-#pragma unroll
-      for (int e = 0; e < D / 4; ++e) {
-        float4 o = op[e];
-        o.x = (a * o.x + b * acc[4 * e + 0]) * inv;
-        o.y = (a * o.y + b * acc[4 * e + 1]) * inv;
-        o.z = (a * o.z + b * acc[4 * e + 2]) * inv;
-        o.w = (a * o.w + b * acc[4 * e + 3]) * inv;
-        op[e] = o;
-      }
-      m_out[rl] = m_o;
-      l_out[rl] = l_o;
     }
   }
 
@@ -621,14 +702,14 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
 #ifdef SPFA_TILE_TRACE
   if (blockIdx.x == 1 && threadIdx.x == 0) {
-    const int n = g_trace_n < 4096 ? g_trace_n : 4096;
-    for (int i = 0; i < n; ++i) {
-      const long long v = g_trace[i];
-      printf("T %d %d %d %lld\n", (int)(v >> 56), (int)((v >> 52) & 15), (int)((v >> 44) & 255), v & 0xfffffffffffLL);
-    }
+    for (int sl = 0; sl < kTraceSlots; ++sl)
+      for (int i = 0; i < trace_n[sl]; ++i) {
+        const long long v = trace_buf[sl * kTraceCap + i];
+        printf("T %d %d %d %lld\n", (int)(v >> 56), (int)((v >> 52) & 15), (int)((v >> 44) & 255), v & 0xfffffffffffLL);
+      }
   }
 #endif
-  if (warp == 8) {
+  if (warp == W_TMA) {
     tc_fence_after();
     if (*abort_flag && lane == 0) {
       // give copies that may still be in flight time to land before the CTA's shared memory is reused
