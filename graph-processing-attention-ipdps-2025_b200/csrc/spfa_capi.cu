@@ -164,6 +164,13 @@ int64_t spfa_launch_count(void) { return g_launches.load(); }
 
 int spfa_last_device_error(void) { return read_and_clear_tile_error(); }
 
+#ifdef SPFA_TILE_TRACE
+int spfa_debug_cta_times(unsigned long long* host, int n) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(host, tile::g_cta_times, sizeof(unsigned long long) * 3 * n);
+}
+#endif
+
 // ---- CSR -----------------------------------------------------------------------------------------
 size_t spfa_csr_workspace_bytes(int64_t, int) { return 0; }
 

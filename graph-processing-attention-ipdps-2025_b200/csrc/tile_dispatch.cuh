@@ -124,8 +124,8 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
   if (!shape_ok) return forced ? (int)SPFA_ERR_BAD_ARG : SPFA_TILE_NOT_TAKEN;
   if (!forced && w < kTileMinHalfWidth) return SPFA_TILE_NOT_TAKEN;
   switch (d) {
-    case 32: return launch_band<32, 128, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 64: return launch_band<64, 128, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 32: return launch_band<32, 96, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 64: return launch_band<64, 96, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
     case 128: return launch_band<128, 64, 1, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
   }
   return SPFA_TILE_NOT_TAKEN;

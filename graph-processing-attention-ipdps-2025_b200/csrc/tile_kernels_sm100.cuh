@@ -2,23 +2,27 @@
 // TMEM accumulators, online softmax in registers.
 //
 // One CTA owns 256 consecutive query rows of a (strided) row sequence, as two 128-row sub-tiles A and
-// B (or, with NSUB = 1, a single 128-row tile and two CTAs per SM), and walks the key tiles that
-// intersect the band |u_q - u_k| <= w. Roles for NSUB = 2 (384 threads; NSUB = 1 drops group B):
+// B, and walks the key tiles (BN keys each) that intersect the band |u_q - u_k| <= w. A kernel that
+// allocates TMEM runs one CTA per SM on this toolchain (the occupancy API reports 1 for any kernel
+// containing tcgen05.alloc), so all overlap is arranged inside the CTA. Roles (384 threads):
 //   warps 0-3  softmax group A   thread t <-> query row t of sub-tile A  <-> TMEM lane t
 //   warps 4-7  softmax group B
 //   warp  8    TMA producer (one elected lane) + TMEM allocation
 //   warp  9    MMA issuer (one elected lane)
 //   warps 10-11 idle (they complete the third warpgroup so registers can be re-balanced:
 //              setmaxnreg gives the softmax groups 216 registers/thread and leaves 72 to this group)
-// Per key tile j and sub-tile X:
-//   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM
+// Per key tile j and sub-tile X (S has two TMEM buffers per sub-tile, used alternately):
+//   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM;
+//                         issued TWO tiles ahead of the softmax group, so that group never waits for it
 //   P_X = exp2(S_X*c - shift) written back over S_X in TMEM by the softmax group (row max / row sum in
 //                         registers, no shuffles: one thread owns one row; `shift` is a lazy per-row
 //                         reference that moves only when the row maximum outgrows it by 2^8)
 //   O_X += P_X V_j       tcgen05.mma kind::tf32, A = P_X (TMEM), B = V_j (smem, MN-major), D stays in TMEM
 //                         for the whole CTA; a row whose reference moves rescales its own O row in TMEM
-// The MMA thread interleaves the two sub-tiles (PV_A(j), S_A(j+1), PV_B(j), S_B(j+1), ...) so the
-// tensor pipe works on one sub-tile while the other is in its exponentials.
+// MMA issue order per key tile j: PV_A(j), PV_B(j), S_A(j+2), S_B(j+2). TMEM: 4 S buffers of BN columns +
+// 2 O accumulators of d columns <= 512 columns (BN = 96 for d <= 64, BN = 64 for d = 128).
+// Epilogue: O rows leave TMEM through shared memory (the dead Q tile) so that the read-modify-write of
+// the caller's O is coalesced.
 //
 // Strided sequences: the rows a CTA sees are  abs_row = r + u*s  (s = dilation stride, r = residue),
 // addressed through tensor maps whose row pitch is s*d*4 bytes; the 1D-dilated mask is exactly a band
@@ -32,13 +36,16 @@
 #include <stdint.h>
 
 #include "spfa_common.cuh"
-#if defined(SPFA_TILE_TIMING) || defined(SPFA_TILE_TRACE)
+#ifdef SPFA_TILE_TRACE
 #include <cstdio>
 #endif
 
 namespace spfa {
 namespace tile {
 
+#ifdef SPFA_TILE_TRACE
+__device__ unsigned long long g_cta_times[8192][3];  // probe build only: start, end (globaltimer ns), SM id
+#endif
 #ifdef SPFA_TILE_TRACE  // probe build only: per-event cycle stamps of one CTA, kept in shared memory
 // (a global atomic per event would perturb the timeline) and printed at the CTA's exit.
 constexpr int kTraceSlots = 3, kTraceCap = 400;  // slot 0: MMA thread, 1: softmax A row 0, 2: softmax B row 0
@@ -56,9 +63,8 @@ constexpr int kTraceSlots = 3, kTraceCap = 400;  // slot 0: MMA thread, 1: softm
 #endif
 
 // Geometry of a CTA with NSUB 128-row sub-tiles: NSUB softmax warpgroups + one warpgroup holding the
-// TMA warp, the MMA warp and two idle warps. NSUB = 2 runs one CTA per SM (sub-tiles interleave on the
-// tensor pipe inside the CTA); NSUB = 1 runs two CTAs per SM, which also hides each CTA's prologue and
-// epilogue latency behind the other CTA.
+// TMA warp, the MMA warp and two idle warps. NSUB = 2 is what the dispatcher launches (the sub-tiles
+// interleave on the tensor pipe inside the CTA); NSUB = 1 is kept as a smaller variant of the same code.
 //
 // Register re-balancing. A CTA is launched with Geo::kRegsLaunch registers per thread (what the compiler
 // assigns under __launch_bounds__(kThreads, kCtasPerSm)). setmaxnreg.inc BLOCKS until the CTA's pool can
@@ -248,14 +254,16 @@ struct Plan {
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + NS * kKVStageBytes;
   static constexpr int kOffBar = kOffV + NS * kKVStageBytes;
-  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[NSUB], p_ready[NSUB], o_ready[NSUB]
-  static constexpr int kNumBars = 1 + 4 * NS + 3 * NSUB;
+  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[2 NSUB], p_ready[2 NSUB], o_ready[2 NSUB] (one per S buffer / tile parity)
+  static constexpr int kNumBars = 1 + 4 * NS + 6 * NSUB;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
-  static constexpr int kBytes = kOffMisc + 16;
+  static constexpr int kOffCoef = (kOffMisc + 16 + 15) / 16 * 16;  // epilogue: 256 floats per sub-tile
+  static constexpr int kBytes = kOffCoef + NSUB * 256 * 4;
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
-  // TMEM columns: S_x (BN each, at 128 x), then O_x (D each, at 128 NSUB + D x); 256 columns per sub-tile
+  // TMEM columns: two S buffers per sub-tile (BN each, at BN (2x + b)), then O_x (D each, at 2 BN NSUB + D x)
   static constexpr int kTmemCols = 256 * NSUB;
-  static constexpr int kColS = 0, kColO = 128 * NSUB;
+  static constexpr int kColS = 0, kColO = 2 * BN * NSUB;
+  static_assert(kColO + NSUB * D <= kTmemCols, "S buffers and O accumulators exceed the TMEM allocation");
 };
 
 template <int D, int BN, int NS, int NSUB>
@@ -273,7 +281,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t bar0 = sbase + P::kOffBar;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   const int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 1 + NS, B_VFULL = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
-            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + NSUB, B_OREADY = B_SREADY + 2 * NSUB;
+            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + 2 * NSUB, B_OREADY = B_SREADY + 4 * NSUB;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + P::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
 #ifdef SPFA_TILE_TRACE
@@ -283,6 +291,14 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SPFA_TILE_TRACE
+  if (threadIdx.x == 0 && blockIdx.x < 8192) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_cta_times[blockIdx.x][0] = globaltimer();
+    g_cta_times[blockIdx.x][2] = smid;
+  }
+#endif
 
   // ---- tile geometry (uniform across the CTA) ----
   const int64_t uq0 = prm.u_q_first + (int64_t)blockIdx.x * kQRows;  // first query u of this CTA
@@ -320,7 +336,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(bar(B_VFULL + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
     }
-    for (int x = 0; x < NSUB; ++x) {
+    for (int x = 0; x < 2 * NSUB; ++x) {
       mbar_init(bar(B_SREADY + x), 1);
       mbar_init(bar(B_PREADY + x), 128);
       mbar_init(bar(B_OREADY + x), 1);
@@ -380,111 +396,80 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t kIdescS = idesc_tf32(128, BN, 0);
       constexpr uint32_t kIdescO = idesc_tf32(128, D, 1);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
-      int n_s[NSUB] = {}, n_pv[NSUB] = {};  // S / PV tiles issued per sub-tile (phase of their barriers)
       // Descriptors are built once per operand tile; each MMA only adds a compile-time offset to the
       // 14-bit start-address field (shared memory is < 256 KB, so the field cannot carry out).
+      // S of key tile j goes to S buffer (j - j0[x]) & 1 of its sub-tile; it is issued two tiles ahead of the
+      // softmax group so that group never waits for the tensor pipe.
       auto issue_S = [&](int x, int j) {
         const int st = j % NS;
+        const int sb = x * 2 + ((j - j0[x]) & 1);
         const uint64_t qd = smem_desc(sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes, 16, 1024, kLayoutSw128);
         const uint64_t kd = smem_desc(sbase + P::kOffK + st * P::kKVStageBytes, 16, 1024, kLayoutSw128);
-        const uint32_t d_t = tmem + P::kColS + 128 * x;
-#ifdef SPFA_TILE_TIMING
-        const long long t_s0 = clock64();
-#endif
+        const uint32_t d_t = tmem + P::kColS + BN * sb;
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-#ifndef SPFA_X_NO_S
             mma_ss(d_t, qd + (uint64_t)((c * P::kQChunkBytes + kk * 32) >> 4),
                    kd + (uint64_t)((c * P::kKVChunkBytes + kk * 32) >> 4), kIdescS, (c | kk) ? 1u : 0u);
-#else
-            ;
-#endif
-        tc_commit(bar(B_SREADY + x));
-#ifdef SPFA_TILE_TIMING  // probe build only: serialise on the MMA's completion and report its latency
-        if (blockIdx.x == 1) {
-          const long long t_s1 = clock64();
-          mbar_wait(bar(B_SREADY + x), (uint32_t)(n_s[x] & 1), abort_flag, err, 901);
-          printf("S  x=%d j=%d issue=%lld done=%lld cycles\n", x, j, t_s1 - t_s0, clock64() - t_s0);
-        }
-#endif
-        ++n_s[x];
+        tc_commit(bar(B_SREADY + sb));
       };
       auto issue_PV = [&](int x, int j) {
         const int st = j % NS;
+        const int sb = x * 2 + ((j - j0[x]) & 1);
         // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
         const uint64_t vd = smem_desc(sbase + P::kOffV + st * P::kKVStageBytes, P::kKVChunkBytes, 512, kLayoutSw128Base32);
-        const uint32_t a_t = tmem + P::kColS + 128 * x;
+        const uint32_t a_t = tmem + P::kColS + BN * sb;
         const uint32_t d_t = tmem + P::kColO + D * x;
         const uint32_t first = (j > j0[x]) ? 1u : 0u;  // O accumulates in TMEM across the key tiles of a sub-tile
-#ifdef SPFA_TILE_TIMING
-        const long long t_p0 = clock64();
-#endif
 #pragma unroll
-        for (int kk = 0; kk < BN / 8; ++kk) {
-#ifndef SPFA_X_NO_PV
+        for (int kk = 0; kk < BN / 8; ++kk)
           mma_ts(d_t, a_t + kk * 8, vd + (uint64_t)((kk * 1024) >> 4), kIdescO, kk > 0 ? 1u : first);
-#endif
-        }
-        tc_commit(bar(B_OREADY + x));
-#ifdef SPFA_TILE_TIMING
-        if (blockIdx.x == 1) {
-          const long long t_p1 = clock64();
-          mbar_wait(bar(B_OREADY + x), (uint32_t)(n_pv[x] & 1), abort_flag, err, 902);
-          printf("PV x=%d j=%d issue=%lld done=%lld cycles\n", x, j, t_p1 - t_p0, clock64() - t_p0);
-        }
-#endif
-        ++n_pv[x];
+        tc_commit(bar(B_OREADY + sb));  // tiles alternate between two barriers, like the S buffers
       };
       auto active = [&](int x, int j) { return j >= j0[x] && j < j1[x]; };
       auto last_active = [&](int x, int j) {  // is x the last sub-tile (in issue order A, B) using tile j?
         return x == NSUB - 1 || !active(NSUB - 1, j);
       };
-      // prologue: S of tile 0
-      if (ok && nT > 0) {
-        ok = mbar_wait(bar(B_KFULL + 0), 0, abort_flag, err, 202);
-        if (ok) {
-          tc_fence_after();
-          for (int x = 0; x < NSUB; ++x)
-            if (active(x, 0)) {
-              issue_S(x, 0);
-              if (last_active(x, 0)) tc_commit(bar(B_KEMPTY + 0));
-            }
-        }
-      }
+      // S of key tile jj for every sub-tile that uses it, then release the K stage
+      auto issue_S_tile = [&](int jj) -> bool {
+        if (jj >= nT) return true;
+        if (!mbar_wait(bar(B_KFULL + jj % NS), (uint32_t)((jj / NS) & 1), abort_flag, err, 202)) return false;
+        tc_fence_after();
+        for (int x = 0; x < NSUB; ++x)
+          if (active(x, jj)) {
+            SPFA_TRACE_AT(0, 3, x, jj);
+            issue_S(x, jj);
+            SPFA_TRACE_AT(0, 4, x, jj);
+            if (last_active(x, jj)) tc_commit(bar(B_KEMPTY + jj % NS));
+          }
+        return true;
+      };
+      // prologue: S of key tiles 0 and 1
+      ok = ok && issue_S_tile(0);
+      ok = ok && issue_S_tile(1);
       for (int j = 0; j < nT && ok; ++j) {
-        const int st = j % NS, stn = (j + 1) % NS;
-        const uint32_t ph = (uint32_t)((j / NS) & 1), phn = (uint32_t)(((j + 1) / NS) & 1);
-        bool have_v = false, have_kn = false;
+        const int st = j % NS;
+        const uint32_t ph = (uint32_t)((j / NS) & 1);
+        bool have_v = false;
         for (int x = 0; x < NSUB && ok; ++x) {
-          if (active(x, j)) {
-            ok = mbar_wait(bar(B_PREADY + x), (uint32_t)((j - j0[x]) & 1), abort_flag, err, 203);
+          if (!active(x, j)) continue;
+          const int it = j - j0[x];
+          ok = mbar_wait(bar(B_PREADY + x * 2 + (it & 1)), (uint32_t)((it >> 1) & 1), abort_flag, err, 203);
+          if (!ok) break;
+          if (!have_v) {
+            ok = mbar_wait(bar(B_VFULL + st), ph, abort_flag, err, 204);
             if (!ok) break;
-            if (!have_v) {
-              ok = mbar_wait(bar(B_VFULL + st), ph, abort_flag, err, 204);
-              if (!ok) break;
-              have_v = true;
-            }
-            tc_fence_after();
-            SPFA_TRACE_AT(0, 1, x, j);
-            issue_PV(x, j);
-            SPFA_TRACE_AT(0, 2, x, j);
-            if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
+            have_v = true;
           }
-          if (j + 1 < nT && active(x, j + 1)) {
-            if (!have_kn) {
-              ok = mbar_wait(bar(B_KFULL + stn), phn, abort_flag, err, 205);
-              if (!ok) break;
-              have_kn = true;
-            }
-            tc_fence_after();
-            SPFA_TRACE_AT(0, 3, x, j + 1);
-            issue_S(x, j + 1);
-            SPFA_TRACE_AT(0, 4, x, j + 1);
-            if (last_active(x, j + 1)) tc_commit(bar(B_KEMPTY + stn));
-          }
+          tc_fence_after();
+          SPFA_TRACE_AT(0, 1, x, j);
+          issue_PV(x, j);
+          SPFA_TRACE_AT(0, 2, x, j);
+          if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
         }
+        // the S buffers of tile j are free again once its PVs are queued (the pipe runs them in order)
+        ok = ok && issue_S_tile(j + 2);
       }
     }
   }
@@ -502,7 +487,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int x = warp >> 2;                 // sub-tile
     const int row = threadIdx.x & 127;       // row within the sub-tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_base + P::kColS + 128 * x;
+    const uint32_t tS0 = tmem + lane_base + P::kColS + 2 * BN * x;
     const uint32_t tO = tmem + lane_base + P::kColO + D * x;
     const int64_t uq = uq0 + 128 * x + row;
     const bool row_valid = uq < uq_end;
@@ -527,6 +512,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       asm volatile("prefetch.global.L2 [%0];" ::"l"(m_out + rl0));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(l_out + rl0));
     }
+    if (row == 0) SPFA_TRACE_AT(1 + x, 14, x, 0);
     float m_true = neg_inf();   // running maximum of the scaled scores (log2 units)
     float shift = neg_inf();    // reference the exponentials and O are currently expressed against
     float l_run = 0.f;          // row sum relative to `shift`
@@ -555,22 +541,17 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
         vmask[c] = m_lo & m_hi;
       }
-      ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + x), (uint32_t)(it & 1), abort_flag, err, 301));
+      const int sb = x * 2 + (it & 1);                  // S buffer of this tile
+      const uint32_t tS = tS0 + BN * (it & 1);
+      ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + sb), (uint32_t)((it >> 1) & 1), abort_flag, err, 301));
       if (!ok) break;
       tc_fence_after();
       if (row == 0) SPFA_TRACE_AT(1 + x, 5, x, j);
       // ---- the whole S row, one TMEM latency ----
-#ifndef SPFA_X_NO_SOFTMAX
 #pragma unroll
       for (int c = 0; c < NC; ++c)
         if (cls[c] != 0) tmem_ld32(tS + c * 32, sr[c]);
       tc_wait_ld();
-#else
-#pragma unroll
-      for (int c = 0; c < NC; ++c)
-#pragma unroll
-        for (int e = 0; e < 32; ++e) sr[c][e] = 0x3f800000u;
-#endif
       // ---- row maximum over the valid columns ----
       float mx[4] = {neg_inf(), neg_inf(), neg_inf(), neg_inf()};
 #pragma unroll
@@ -594,8 +575,15 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float f = move ? ((shift == neg_inf()) ? 0.f : fast_exp2(shift - new_shift)) : 1.0f;
         l_run *= f;
         if (it > 0) {
-          // O of this row is final up to the previous tile: its PV finished before this S was produced
-          // (the tensor pipe runs one thread's MMAs in order), and the next PV waits for our P.
+          // O of this row must be final up to the previous tile before it is rescaled: wait for that PV
+          // (the PV of this tile cannot start before our P is ready). PV completions alternate between
+          // two barriers per sub-tile, so this parity wait is unambiguous: the barrier of tile it-1 can be
+          // neither two phases behind (S of this tile was queued after the PV of tile it-3 on it) nor
+          // ahead (tile it+1 needs a P this group has not produced).
+          ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x * 2 + ((it - 1) & 1)), (uint32_t)(((it - 1) >> 1) & 1),
+                                               abort_flag, err, 302));
+          if (!ok) break;
+          tc_fence_after();
           uint32_t ob[8];  // small pieces: the S row (sr) stays live in registers across this
 #pragma unroll 1
           for (int c = 0; c < D / 8; ++c) {
@@ -617,11 +605,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (cls[c] == 2) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-#ifndef SPFA_X_NO_EXP
             const uint32_t pb = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sr[c][e]), sc, neg_shift))) & 0xffffe000u;
-#else
-            const uint32_t pb = __float_as_uint(fmaf(__uint_as_float(sr[c][e]), sc, neg_shift)) & 0xffffe000u;
-#endif
             ls[e & 3] += __uint_as_float(pb);
             sr[c][e] = pb;
           }
@@ -637,62 +621,112 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 32; ++e) sr[c][e] = 0u;
         }
-#ifndef SPFA_X_NO_SOFTMAX
         tmem_st32(tS + c * 32, sr[c]);
-#endif
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(B_PREADY + x));
+      mbar_arrive(bar(B_PREADY + sb));
       if (row == 0) SPFA_TRACE_AT(1 + x, 8, x, j);
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
     // ---- epilogue: O row from TMEM, normalised and merged with the caller's (m, l, O) ----
-    if (ok && nx > 0) {
-      ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x), (uint32_t)((nx - 1) & 1), abort_flag, err, 303));
+    if (row == 0) SPFA_TRACE_AT(1 + x, 10, x, 0);
+    if (nx > 0) {  // uniform over the softmax group, so the group barriers below are safe
+      // both tile parities: the PVs of the last two tiles
+      if (ok && nx > 1)
+        ok = __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x * 2 + ((nx - 2) & 1)), (uint32_t)(((nx - 2) >> 1) & 1),
+                                             abort_flag, err, 304));
+      ok = ok && __all_sync(kFullMask, mbar_wait(bar(B_OREADY + x * 2 + ((nx - 1) & 1)), (uint32_t)(((nx - 1) >> 1) & 1),
+                                                 abort_flag, err, 303));
+      // The epilogue uses a group barrier, which has no timeout: agree first (barrier + AND-reduction that
+      // every thread of the group executes) that no warp of the group gave up on a wait.
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, %2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(all_ok)
+            : "r"((uint32_t)ok), "r"(1 + x)
+            : "memory");
+        ok = all_ok != 0;
+      }
       if (ok) {
         tc_fence_after();
-#ifdef SPFA_X_NO_EPI
-        const bool store = false;
-#else
         const bool store = row_valid && l_run > 0.f;
-#endif
-        const int64_t rl = store ? (prm.r + uq * prm.s - prm.row_begin) : 0;  // shard-local row
-        float a = 0.f, b = 0.f, inv = 0.f, m_o = 0.f, l_o = 0.f;
+        if (row == 0) SPFA_TRACE_AT(1 + x, 11, x, 0);
+        // Per-row coefficients of  O_out = ca * O_in + cb * O_tmem  (state in natural-log units, as the
+        // gather path; l is re-expressed against the true maximum, O in TMEM is relative to `shift`).
+        float ca = 0.f, cb = 0.f;
         if (store) {
-          // state in natural-log units, as the gather path: l is re-expressed against the true maximum
-          const float l_loc = l_run * fast_exp2(shift - m_true);
+          const int64_t rl = prm.r + uq * prm.s - prm.row_begin;  // shard-local row
+          const float rel = fast_exp2(shift - m_true);
+          const float l_loc = l_run * rel;
           const float m_loc = m_true * 0.6931471805599453f;
           const float m_in = m_out[rl], l_in = l_out[rl];
-          m_o = fmaxf(m_in, m_loc);
-          a = l_in * fast_exp2((m_in - m_o) * kLog2e);
+          const float m_o = fmaxf(m_in, m_loc);
+          const float a = l_in * fast_exp2((m_in - m_o) * kLog2e);
           const float bt = fast_exp2((m_loc - m_o) * kLog2e);
-          l_o = fmaf(l_loc, bt, a);
-          inv = 1.0f / l_o;
-          b = bt * fast_exp2(shift - m_true);  // O in TMEM is relative to `shift`
-        }
-        float4* op = reinterpret_cast<float4*>(O_out + (size_t)rl * D);
-        uint32_t ob[32];
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          tmem_ld32(tO + c * 32, ob);
-          tc_wait_ld();
-          if (store) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float4 o = op[c * 8 + e];
-              o.x = (a * o.x + b * __uint_as_float(ob[4 * e + 0])) * inv;
-              o.y = (a * o.y + b * __uint_as_float(ob[4 * e + 1])) * inv;
-              o.z = (a * o.z + b * __uint_as_float(ob[4 * e + 2])) * inv;
-              o.w = (a * o.w + b * __uint_as_float(ob[4 * e + 3])) * inv;
-              op[c * 8 + e] = o;
-            }
-          }
-        }
-        if (store) {
+          const float l_o = fmaf(l_loc, bt, a);
+          const float inv = 1.0f / l_o;
+          ca = a * inv;
+          cb = bt * rel * inv;
           m_out[rl] = m_o;
           l_out[rl] = l_o;
         }
+        // Stage cb * O_tmem in shared memory (this sub-tile's Q region is dead: all its S MMAs completed
+        // before the last PV), 16-byte chunks XOR-swizzled by the row so that both the row-per-thread
+        // writes here and the row-per-lane-group reads below spread over the banks.
+        constexpr int LPR = D / 4;  // float4 chunks (= lanes) per row
+        uint8_t* stage = smem + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
+        float* coef = reinterpret_cast<float*>(smem + P::kOffCoef) + x * 256;  // [0,128): ca, [128,256): store flag
+        coef[row] = ca;
+        coef[128 + row] = store ? 1.f : 0.f;
+        {
+          uint32_t ob[32];
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld32(tO + c * 32, ob);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int ch = c * 8 + e;
+              float4 v4 = make_float4(cb * __uint_as_float(ob[4 * e + 0]), cb * __uint_as_float(ob[4 * e + 1]),
+                                      cb * __uint_as_float(ob[4 * e + 2]), cb * __uint_as_float(ob[4 * e + 3]));
+              *reinterpret_cast<float4*>(stage + (size_t)row * (D * 4) + ((ch ^ (row & (LPR - 1))) << 4)) = v4;
+            }
+          }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");  // this softmax group only
+        if (row == 0) SPFA_TRACE_AT(1 + x, 12, x, 0);
+        // Coalesced read-modify-write of the caller's O rows: LPR lanes cover one row (D*4 contiguous bytes).
+        constexpr int RPI = 32 / LPR;    // rows per warp instruction
+        constexpr int NIT = 32 / RPI;    // instructions for this warp's 32 rows
+        const int wrow0 = (warp & 3) * 32, sub = lane % LPR;
+        float4 oin[NIT];
+#pragma unroll
+        for (int i = 0; i < NIT; ++i) {
+          const int r = wrow0 + i * RPI + lane / LPR;
+          oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (coef[128 + r] != 0.f) {
+            const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+            oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < NIT; ++i) {
+          const int r = wrow0 + i * RPI + lane / LPR;
+          if (coef[128 + r] != 0.f) {
+            const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+            const float car = coef[r];
+            const float4 t = *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
+            float4 o;
+            o.x = fmaf(car, oin[i].x, t.x);
+            o.y = fmaf(car, oin[i].y, t.y);
+            o.z = fmaf(car, oin[i].z, t.z);
+            o.w = fmaf(car, oin[i].w, t.w);
+            *reinterpret_cast<float4*>(O_out + (size_t)rl * D + sub * 4) = o;
+          }
+        }
+        if (row == 0) SPFA_TRACE_AT(1 + x, 13, x, 0);
       }
     }
   }
@@ -701,7 +735,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_before();
   __syncthreads();
 #ifdef SPFA_TILE_TRACE
-  if (blockIdx.x == 1 && threadIdx.x == 0) {
+  if (threadIdx.x == 0 && blockIdx.x < 8192) g_cta_times[blockIdx.x][1] = globaltimer();
+  if (blockIdx.x == 1 && threadIdx.x == 0 && gridDim.x < 64) {
     for (int sl = 0; sl < kTraceSlots; ++sl)
       for (int i = 0; i < trace_n[sl]; ++i) {
         const long long v = trace_buf[sl * kTraceCap + i];
