@@ -213,6 +213,7 @@ def parse_args():
     ap.add_argument("--workload", default="local", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "gather", "tiled"])
+    ap.add_argument("--rows", type=int, default=0, help="override the workload's L (smaller cases for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
     return ap.parse_args()
@@ -532,6 +533,11 @@ def run_reference(args, rank, world, dev):
 
 def main():
     args = parse_args()
+    if args.rows > 0:
+        w = dict(WORKLOADS[args.workload])
+        w["desc"] = w["desc"].replace(f"L={w['L']}", f"L={args.rows}") + " [reduced size]"
+        w["L"] = args.rows
+        WORKLOADS[args.workload] = w
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

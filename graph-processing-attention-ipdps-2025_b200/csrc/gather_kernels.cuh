@@ -4,6 +4,9 @@
 // warp works on KPS = 32/LPK keys at once ("key groups"). Each group keeps its own online-softmax
 // state (m, l, acc) over the slots it owns; the groups are merged once at the end of the row, then
 // merged with the caller's (m, l, O) state. All arithmetic is fp32 FMA; exponentials are ex2.approx.
+// The kernel is instruction-issue bound, not bandwidth bound, on cache-friendly masks, so the inner step is
+// written to minimise shuffles and special-function work: four keys per lane group are reduced with a
+// transposed butterfly and each lane exponentiates one key only.
 //
 // Replaces the per-row CTA loop of the reference (sp_flatt_csr_kernel.cu:104-205 and its five copies):
 // same key visiting order, same state recurrence, no shared memory, no block barriers.
@@ -21,7 +24,66 @@ struct RowAcc {
   float4 acc;
 };
 
+// Sum of four per-lane partial dot products over the LPK lanes of a key group, "transposed": instead of
+// four full butterflies (4 log2(LPK) shuffles) the first two exchange steps halve the number of live values,
+// so each lane ends with the complete sum of ONE of the four keys:
+//   key index owned by a lane = 2 * bit(sub, LPK/2) + bit(sub, LPK/4)
+// 2 + 1 + (log2(LPK) - 2) shuffles in total.
+template <int LPK>
+__device__ __forceinline__ float reduce4_transposed(float p0, float p1, float p2, float p3, int sub) {
+  static_assert(LPK >= 4, "needs at least four lanes per key");
+  const bool hi = (sub & (LPK / 2)) != 0;
+  float a0 = hi ? p2 : p0, a1 = hi ? p3 : p1;
+  const float b0 = hi ? p0 : p2, b1 = hi ? p1 : p3;
+  a0 += __shfl_xor_sync(kFullMask, b0, LPK / 2);
+  a1 += __shfl_xor_sync(kFullMask, b1, LPK / 2);
+  const bool hi2 = (sub & (LPK / 4)) != 0;
+  float c0 = hi2 ? a1 : a0;
+  const float d0 = hi2 ? a0 : a1;
+  c0 += __shfl_xor_sync(kFullMask, d0, LPK / 4);
+#pragma unroll
+  for (int o = LPK / 8; o > 0; o >>= 1) c0 += __shfl_xor_sync(kFullMask, c0, o);
+  return c0;
+}
+
+// One step of the online softmax for the four keys a lane group has in flight. `mine` is the score
+// (natural-log units, -inf if masked) of the key this lane owns after reduce4_transposed; the group
+// maximum takes two shuffles, each lane exponentiates only its own key, and the four probabilities are
+// then broadcast inside the group.
+template <int D>
+__device__ __forceinline__ void softmax_step4(float mine, int grp, const float4 (&v4)[4], RowAcc<D>& st) {
+  constexpr int LPK = D / 4;
+  float mc = fmaxf(mine, __shfl_xor_sync(kFullMask, mine, LPK / 2));
+  mc = fmaxf(mc, __shfl_xor_sync(kFullMask, mc, LPK / 4));
+  const float m_new = fmaxf(st.m, mc);
+  const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
+  const float corr = fast_exp2((st.m - m_safe) * kLog2e);
+  const float pm = fast_exp2((mine - m_safe) * kLog2e);
+  const int base = grp * LPK;
+  const float p0 = __shfl_sync(kFullMask, pm, base);
+  const float p1 = __shfl_sync(kFullMask, pm, base + LPK / 4);
+  const float p2 = __shfl_sync(kFullMask, pm, base + LPK / 2);
+  const float p3 = __shfl_sync(kFullMask, pm, base + LPK / 2 + LPK / 4);
+  float4 a = make_float4(st.acc.x * corr, st.acc.y * corr, st.acc.z * corr, st.acc.w * corr);
+  a.x = fmaf(p0, v4[0].x, a.x); a.y = fmaf(p0, v4[0].y, a.y); a.z = fmaf(p0, v4[0].z, a.z); a.w = fmaf(p0, v4[0].w, a.w);
+  a.x = fmaf(p1, v4[1].x, a.x); a.y = fmaf(p1, v4[1].y, a.y); a.z = fmaf(p1, v4[1].z, a.z); a.w = fmaf(p1, v4[1].w, a.w);
+  a.x = fmaf(p2, v4[2].x, a.x); a.y = fmaf(p2, v4[2].y, a.y); a.z = fmaf(p2, v4[2].z, a.z); a.w = fmaf(p2, v4[2].w, a.w);
+  a.x = fmaf(p3, v4[3].x, a.x); a.y = fmaf(p3, v4[3].y, a.y); a.z = fmaf(p3, v4[3].z, a.z); a.w = fmaf(p3, v4[3].w, a.w);
+  st.acc = a;
+  st.l = fmaf(st.l, corr, (p0 + p1) + (p2 + p3));
+  st.m = m_new;
+}
+
+__device__ __forceinline__ float dot4(const float4 q, const float4 k) {
+  float p = q.x * k.x;
+  p = fmaf(q.y, k.y, p);
+  p = fmaf(q.z, k.z, p);
+  return fmaf(q.w, k.w, p);
+}
+
 // Online-softmax accumulation of slots [t0, t1) of one row into the calling lane's group state.
+// Slots are taken 32 at a time (one per lane, so explicit column lists are read coalesced); a batch whose
+// 32 slots are all valid takes a predicate-free body, ragged or partly masked batches a predicated one.
 template <int D, class Cols>
 __device__ __forceinline__ void accumulate_slots(const Cols& cols, const typename Cols::Row& row,
                                                  int64_t t0, int64_t t1, const float4 q,
@@ -29,60 +91,53 @@ __device__ __forceinline__ void accumulate_slots(const Cols& cols, const typenam
                                                  float scale, int lane, RowAcc<D>& st) {
   constexpr int LPK = D / 4;
   constexpr int KPS = 32 / LPK;
-  constexpr int U = (LPK < kGatherUnroll) ? LPK : kGatherUnroll;
+  static_assert(LPK >= 4 && kGatherUnroll == 4, "the step below handles four keys per lane group");
   const int grp = lane / LPK, sub = lane % LPK;
+  // which of the four in-flight keys this lane owns after the transposed reduction
+  const int own = (((sub & (LPK / 2)) != 0) ? 2 : 0) + (((sub & (LPK / 4)) != 0) ? 1 : 0);
+  const float* Kl = K + sub * 4;
+  const float* Vl = V + sub * 4;
 
   for (int64_t base = t0; base < t1; base += 32) {
     const int64_t tl = base + lane;
     const int32_t c_lane = (tl < t1) ? cols.slot(row, tl) : -1;
-    const int nb = (t1 - base < 32) ? (int)(t1 - base) : 32;
+    const bool full = __all_sync(kFullMask, c_lane >= 0);
+    if (full) {
 #pragma unroll 1
-    for (int j0 = 0; j0 < LPK; j0 += U) {
-      if (j0 * KPS >= nb) break;  // warp-uniform
-      int32_t c[U];
-      float4 k4[U], v4[U];
+      for (int j0 = 0; j0 < LPK; j0 += 4) {
+        float4 k4[4], v4[4];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        c[u] = __shfl_sync(kFullMask, c_lane, grp + (j0 + u) * KPS);
-        if (c[u] >= 0) {
-          const size_t off = (size_t)c[u] * D + sub * 4;
-          k4[u] = ldg4(K + off);
-          v4[u] = ldg4(V + off);
-        } else {
-          k4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-          v4[u] = k4[u];
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t c = (uint32_t)__shfl_sync(kFullMask, c_lane, grp + (j0 + u) * KPS);
+          k4[u] = ldg4(Kl + (size_t)c * D);
+          v4[u] = ldg4(Vl + (size_t)c * D);
         }
+        const float mine = reduce4_transposed<LPK>(dot4(q, k4[0]), dot4(q, k4[1]), dot4(q, k4[2]), dot4(q, k4[3]), sub) * scale;
+        softmax_step4<D>(mine, grp, v4, st);
       }
-      float s[U];
-      float mc = neg_inf();
+    } else {
+      const int nb = (t1 - base < 32) ? (int)(t1 - base) : 32;
+#pragma unroll 1
+      for (int j0 = 0; j0 < LPK; j0 += 4) {
+        if (j0 * KPS >= nb) break;  // warp-uniform
+        float4 k4[4], v4[4];
+        int32_t c_own = -1;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float p = q.x * k4[u].x;
-        p = fmaf(q.y, k4[u].y, p);
-        p = fmaf(q.z, k4[u].z, p);
-        p = fmaf(q.w, k4[u].w, p);
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) p += __shfl_xor_sync(kFullMask, p, o);
-        s[u] = (c[u] >= 0) ? p * scale : neg_inf();
-        mc = fmaxf(mc, s[u]);
+        for (int u = 0; u < 4; ++u) {
+          const int32_t c = __shfl_sync(kFullMask, c_lane, grp + (j0 + u) * KPS);
+          if (c >= 0) {
+            k4[u] = ldg4(Kl + (size_t)c * D);
+            v4[u] = ldg4(Vl + (size_t)c * D);
+          } else {  // a masked key contributes probability 0; zero V keeps 0 * V finite
+            k4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            v4[u] = k4[u];
+          }
+          if (u == own) c_own = c;
+        }
+        float mine = reduce4_transposed<LPK>(dot4(q, k4[0]), dot4(q, k4[1]), dot4(q, k4[2]), dot4(q, k4[3]), sub) * scale;
+        if (c_own < 0) mine = neg_inf();
+        softmax_step4<D>(mine, grp, v4, st);
       }
-      const float m_new = fmaxf(st.m, mc);
-      const float m_safe = (m_new == neg_inf()) ? 0.f : m_new;
-      const float corr = fast_exp2((st.m - m_safe) * kLog2e);
-      float lsum = 0.f;
-      float4 a = make_float4(st.acc.x * corr, st.acc.y * corr, st.acc.z * corr, st.acc.w * corr);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const float p = fast_exp2((s[u] - m_safe) * kLog2e);
-        lsum += p;
-        a.x = fmaf(p, v4[u].x, a.x);
-        a.y = fmaf(p, v4[u].y, a.y);
-        a.z = fmaf(p, v4[u].z, a.z);
-        a.w = fmaf(p, v4[u].w, a.w);
-      }
-      st.acc = a;
-      st.l = fmaf(st.l, corr, lsum);
-      st.m = m_new;
     }
   }
 }
