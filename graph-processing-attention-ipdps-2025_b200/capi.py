@@ -27,7 +27,7 @@ MASK_KIND = {"local": 0, "local_1d_dilated": 1, "local_2d_dilated": 2, "global_n
 EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
-    "spfa_coo_workspace_bytes", "spfa_coo_forward_f32",
+    "spfa_coo_workspace_bytes", "spfa_coo_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -71,6 +71,9 @@ def lib() -> ctypes.CDLL:
     L.spfa_coo_workspace_bytes.argtypes = [i64, i32]
     L.spfa_coo_forward_f32.restype = i32
     L.spfa_coo_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_coo_static_max_rows.restype = i64
+    L.spfa_coo_forward_f32_static.restype = i32
+    L.spfa_coo_forward_f32_static.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp]
     for name in ("spfa_local", "spfa_local_1d_dilated", "spfa_local_2d_dilated"):
         f = getattr(L, name + "_workspace_bytes")
         f.restype = sz

@@ -128,6 +128,29 @@ inline int with_mask_cols(int kind, int64_t L, int64_t p0, int64_t p1, const int
   return SPFA_ERR_BAD_ARG;
 }
 
+// ---- scratch for the allocation-free COO entry point ---------------------------------------------------
+// Row pointers for up to kStaticCooMaxRows query rows, resident in every GPU context that loads this
+// library (2 MiB + 8 B) until the process exits. In host code the array's name is only a handle: the
+// device address is obtained once per device with cudaGetSymbolAddress and cached here.
+constexpr int64_t kStaticCooMaxRows = 1 << 18;
+static __device__ __align__(256) unsigned long long g_static_coo_row_ptr[kStaticCooMaxRows + 1];
+constexpr int kMaxDevices = 64;
+static std::atomic<unsigned long long*> g_static_coo_ptr[kMaxDevices];
+
+inline int static_coo_scratch(unsigned long long** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SPFA_ERR_LAUNCH;
+  unsigned long long* p = g_static_coo_ptr[dev].load(std::memory_order_acquire);
+  if (!p) {  // first call on this device: resolve the symbol in the current device's context
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_static_coo_row_ptr) != cudaSuccess || !addr) return SPFA_ERR_LAUNCH;
+    p = static_cast<unsigned long long*>(addr);
+    g_static_coo_ptr[dev].store(p, std::memory_order_release);  // racing first calls resolve the same address
+  }
+  *out = p;
+  return SPFA_OK;
+}
+
 }  // namespace spfa
 
 using namespace spfa;
@@ -206,6 +229,34 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const u
   uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
   int64_t blocks = (nnz + 1 + 255) / 256;
   if (blocks > 148 * 64) blocks = 148 * 64;
+  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  CsrCols cols{ptr, col_ind, Lk};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+}
+
+int64_t spfa_coo_static_max_rows(void) { return kStaticCooMaxRows; }
+
+// COO forward for callers that may not allocate: same arithmetic and kernels as spfa_coo_forward_f32, with
+// the row-pointer scratch taken from the library's own static device array instead of a caller workspace.
+int spfa_coo_forward_f32_static(const float* Q, const float* K, const float* V, const uint64_t* row_ind,
+                                const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O,
+                                int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (nnz < 0 || n_rows < 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
+  if (n_rows > kStaticCooMaxRows) return SPFA_ERR_TOO_LARGE;  // more rows than the static scratch holds
+  if (n_rows == 0) return SPFA_OK;
+  unsigned long long* scratch = nullptr;
+  rc = static_coo_scratch(&scratch);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* ptr = reinterpret_cast<uint64_t*>(scratch);
+  int64_t blocks = (nnz + 1 + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  // every entry ptr[0 .. n_rows] is written by this pass, so nothing left by an earlier call is read
   coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;

@@ -93,6 +93,33 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V,
                          int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- explicit COO mask, allocation-free variant ---------------------------------------------------
+ * No counterpart in the reference (its COO kernel needs no scratch because it re-scans the row array
+ * for every row, sp_flatt_coo_kernel.cu:47-79).
+ *
+ * For callers that cannot hand this library a workspace because they are not allowed to allocate
+ * device memory at the point of the call: for example a serving process that gave its whole device
+ * budget to its own pool at start-up and forbids plug-ins from touching the CUDA allocator, or a
+ * latency-critical section in which the implicit device-wide synchronisation of cudaMalloc/cudaFree
+ * is not acceptable. Identical to spfa_coo_forward_f32 except that the n_rows+1 row pointers live in a
+ * static device array inside the library (2 MiB per GPU that loads the library, held until exit).
+ *
+ *   - n_rows may not exceed spfa_coo_static_max_rows() (262144); larger shards return
+ *     SPFA_ERR_TOO_LARGE and launch nothing. Shard the rows or use the workspace variant.
+ *   - Neither this function nor anything it calls uses cudaMalloc, cudaFree or another allocating
+ *     routine. The first call on a device resolves the array's device address
+ *     (cudaGetSymbolAddress with that device current) and caches it; make that first call on each
+ *     device during set-up, before any stream capture is begun.
+ *   - All calls on a device share the one array. Its previous contents never matter (each call
+ *     rewrites every entry it reads), but two calls whose kernels may overlap on the GPU -- different
+ *     streams, or different host threads on different streams -- race on it: serialise them. */
+int64_t spfa_coo_static_max_rows(void);
+int spfa_coo_forward_f32_static(const float* Q, const float* K, const float* V,
+                                const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                                float* m, float* l, float* O,
+                                int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
+                                void* stream);
+
 /* ---- implicit Local (sliding window) mask -------------------------------------------------------
  * Replaces spfa_local_cuda_forward + kernel (Sparse_FlashAttention_Local/sp_flatt_local_kernel.cu:208-272, :12-204).
  * Row i attends to j in [max(0, i-w), min(L, i+w+1)).  (:24-28) */
