@@ -214,6 +214,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "gather", "tiled"])
     ap.add_argument("--rows", type=int, default=0, help="override the workload's L (smaller cases for profiling)")
+    ap.add_argument("--strong", action="store_true", help="N>1: split the workload's L rows over the GPUs (default: L rows per GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
     return ap.parse_args()
@@ -222,18 +223,34 @@ def parse_args():
 class Job:
     """One rank's share of the workload, resident on its GPU."""
 
-    def __init__(self, workload, rank, world, dev, whole_on_one_gpu=False):
+    def __init__(self, workload, rank, world, dev, whole_on_one_gpu=False, strong=False):
         w = WORKLOADS[workload]
         self.w, self.kind, self.d = w, w["kind"], w["d"]
-        self.L = w["L"] * world  # weak scaling: N*L rows in the sequence
-        if whole_on_one_gpu:  # a single-GPU implementation given the whole N*L-row job
-            self.L_local, self.rb, self.re = self.L, 0, self.L
-        else:
-            self.L_local = w["L"]
-            self.rb, self.re = rank * self.L_local, (rank + 1) * self.L_local
+        # weak scaling: N*L rows in the sequence, L per GPU; strong scaling: L rows split over the GPUs
+        self.L = w["L"] if strong else w["L"] * world
         self.rank, self.world, self.dev = rank, world, dev
         self.p0, self.p1 = w["p0"], w["p1"]
         seed = 1000 + sorted(WORKLOADS).index(workload)
+        full_mask = None
+        if self.kind == "csr":
+            full_mask = make_csr_mask(self.L, seed, dev)
+        elif self.kind == "coo":
+            full_mask = make_coo_graph(self.L, self.p0, seed, dev)
+        if whole_on_one_gpu:  # a single-GPU implementation given the whole job
+            self.ranges = [(0, self.L)]
+            rank = 0
+        elif not strong:
+            self.ranges = [(r * w["L"], (r + 1) * w["L"]) for r in range(world)]
+        else:
+            sh = entry.load().sharding
+            if self.kind == "csr":
+                self.ranges = sh.nnz_balanced_row_ranges(full_mask[0], world)
+            elif self.kind == "coo":
+                self.ranges = sh.coo_nnz_balanced_row_ranges(full_mask[0], self.L, world)
+            else:
+                self.ranges = sh.equal_row_ranges(self.L, world, multiple=256)
+        self.rb, self.re = self.ranges[rank]
+        self.L_local = self.re - self.rb
         Q, self.K, self.V = make_qkv(self.L, self.d, seed, dev)
         self.Q = Q[self.rb:self.re].contiguous()
         del Q
@@ -246,12 +263,12 @@ class Job:
             self.G_cpu, self.G = Gc, Gc.to(dev)
             self.nnz = implicit_nnz(self.kind, self.L, self.p0, self.p1, Gc, self.rb, self.re)
         elif self.kind == "csr":
-            row_off, col = make_csr_mask(self.L, seed, dev)
+            row_off, col = full_mask
             lo, hi = int(row_off[self.rb]), int(row_off[self.re])
             self.mask = ((row_off[self.rb:self.re + 1] - lo).contiguous(), col[lo:hi].contiguous())
             self.nnz = hi - lo
         elif self.kind == "coo":
-            rows, cols = make_coo_graph(self.L, self.p0, seed, dev)
+            rows, cols = full_mask
             edges = torch.searchsorted(rows, torch.tensor([self.rb, self.re], device=dev))
             lo, hi = int(edges[0]), int(edges[1])
             self.mask = (rows[lo:hi].contiguous(), cols[lo:hi].contiguous())
@@ -263,6 +280,7 @@ class Job:
                 if n_live is None:
                     i = torch.arange(self.rb, self.re)
                     n_live = int(((i % self.p0) % (self.p1 + 1) == 0).sum())
+        del full_mask
         self.n_live = n_live
         self.flops = 4.0 * self.nnz * self.d
         self.bytes = algorithmic_bytes(self.kind, self.L, self.L_local, self.d, self.nnz, n_live)
@@ -354,7 +372,7 @@ def run_ours(args, rank, world, dev):
     capi = pkg.capi
     capi.lib()
     capi.set_path({"auto": capi.PATH_AUTO, "gather": capi.PATH_GATHER, "tiled": capi.PATH_TILED}[args.path])
-    job = Job(args.workload, rank, world, dev)
+    job = Job(args.workload, rank, world, dev, strong=args.strong)
     peaks, peak_src = load_peaks()
 
     # ---- kernel-only: inputs resident in HBM ----
@@ -367,6 +385,7 @@ def run_ours(args, rank, world, dev):
     total_ms = dist_max(sum(times), world, dev)
     total_flops = dist_sum(job.flops, world, dev)
     total_nnz = dist_sum(float(job.nnz), world, dev)
+    nnz_imbalance = dist_max(float(job.nnz), world, dev) / max(total_nnz / world, 1.0)
     value = total_flops * args.steps / (total_ms * 1e-3) / 1e12
 
     # ---- end to end: pinned host buffers -> device -> (all-gather K/V) -> forward -> host ----
@@ -375,7 +394,7 @@ def run_ours(args, rank, world, dev):
     hV = job.V[job.rb:job.re].cpu().pin_memory()
     hO = torch.empty_like(job.O, device="cpu").pin_memory()
     dQ, dKs, dVs = torch.empty_like(job.Q), torch.empty_like(job.Q), torch.empty_like(job.Q)
-    ranges = [(r * job.L_local, (r + 1) * job.L_local) for r in range(world)]
+    ranges = job.ranges
     binding = pkg.binding("spfa_" + job.kind) if world == 1 else None
     w_val = torch.ones(1, device=dev)
 
@@ -407,8 +426,8 @@ def run_ours(args, rank, world, dev):
     e2e_times, _ = timed_steps(job, e2e_step, args.steps, args.warmup, world)
     e2e_ms = dist_max(sum(e2e_times), world, dev)
     e2e_value = total_flops * args.steps / (e2e_ms * 1e-3) / 1e12
-    h2d = 3 * job.L_local * job.d * 4 * world
-    d2h = job.L_local * job.d * 4 * world
+    h2d = 3 * job.L * job.d * 4
+    d2h = job.L * job.d * 4
 
     if rank != 0:
         return None
@@ -430,10 +449,14 @@ def run_ours(args, rank, world, dev):
 
     line = {
         "metric": "effective_nnz_tflops_fwd", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "strong" if args.strong else "weak",
         "vs_baseline": None, "dtype": "tf32" if tiled else "f32", "data": "synthetic",
-        "config": {"workload": job.w["desc"] + (f"; sequence of {world}x{job.L_local} rows, one row range per GPU" if world > 1 else ""),
+        "config": {"workload": job.w["desc"] + (("; %d rows split into %d %s row ranges" % (job.L, world, "nnz-balanced" if job.kind in ("csr", "coo") else "equal"))
+                                           if (world > 1 and args.strong) else
+                                           (f"; sequence of {world}x{job.L_local} rows, one row range per GPU" if world > 1 else "")),
                    "mask": job.kind, "L": job.L, "rows_per_gpu": job.L_local, "d": job.d, "nnz": int(total_nnz),
+                   "nnz_imbalance_max_over_mean": round(nnz_imbalance, 4),
                    "flops_per_step": total_flops, "path": args.path, "l2": "flushed (256 MiB memset) before every timed step",
                    "state": "m=-inf,l=0,O=0 re-initialised before every step outside the timed span"},
         "fwd_ms": total_ms / args.steps,
@@ -479,7 +502,7 @@ def run_reference(args, rank, world, dev):
     spec = importlib.util.spec_from_file_location("spfa_build_ref", os.path.join(ROOT, "oracle", "build_ref.py"))
     br = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(br)
-    job = Job(args.workload, 0, world, dev, whole_on_one_gpu=True)  # the reference is single-GPU
+    job = Job(args.workload, 0, world, dev, whole_on_one_gpu=True, strong=args.strong)  # the reference is single-GPU
     mod = br.load(job.kind)
     base = {"impl": "reference", "metric": "effective_nnz_tflops_fwd", "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
