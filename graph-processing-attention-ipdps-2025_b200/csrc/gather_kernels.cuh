@@ -240,13 +240,15 @@ template <int D, class Cols>
 __global__ void __launch_bounds__(kGatherWarps * 32)
 gather_split_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                          const Cols cols, const int32_t* __restrict__ row_list,
-                         const uint8_t* __restrict__ entry_live, int64_t row_begin, int64_t row_end,
+                         const uint8_t* __restrict__ entry_live, int n_entries, int64_t row_begin, int64_t row_end,
                          int n_split, int64_t slots_per_split, float* __restrict__ partials, float scale) {
   constexpr int LPK = D / 4;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int e = blockIdx.y;
-  const int split = blockIdx.x * kGatherWarps + warp;
-  if (split >= n_split) return;
+  // One key range (split) per blockIdx.y, four list entries per CTA: CTAs that are resident together
+  // walk the same K/V rows.
+  const int e = blockIdx.x * kGatherWarps + warp;
+  const int split = blockIdx.y;
+  if (e >= n_entries) return;
   float* part = partials + ((size_t)e * n_split + split) * (D + 4);
   RowAcc<D> st;
   st.m = neg_inf();

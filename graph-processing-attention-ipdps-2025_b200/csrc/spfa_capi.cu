@@ -78,7 +78,7 @@ struct GnlPlan {
 
 inline GnlPlan gnl_plan(int64_t L, int d, int64_t nG) {
   GnlPlan p;
-  int64_t want = (148 * 32 + nG - 1) / (nG > 0 ? nG : 1);
+  int64_t want = (148 * 64 + nG - 1) / (nG > 0 ? nG : 1);  // ~64 warps per SM in flight
   int64_t max_split = (L + 255) / 256;
   if (want < 1) want = 1;
   if (want > max_split) want = max_split;
@@ -100,9 +100,9 @@ int launch_gnl_global_rows(const float* Q, const float* K, const float* V, float
                            const GnlPlan& plan, const uint8_t* live, float* partials, cudaStream_t st) {
   GnlGlobalRowCols cols{L, w};
   const float scale = 1.0f / sqrtf((float)D);
-  dim3 grid((plan.n_split + kGatherWarps - 1) / kGatherWarps, (unsigned)nG);
+  dim3 grid((unsigned)((nG + kGatherWarps - 1) / kGatherWarps), (unsigned)plan.n_split);
   gather_split_rows_kernel<D, GnlGlobalRowCols><<<grid, kGatherWarps * 32, 0, st>>>(
-      Q, K, V, cols, G, live, row_begin, row_end, plan.n_split, plan.slots_per_split, partials, scale);
+      Q, K, V, cols, G, live, (int)nG, row_begin, row_end, plan.n_split, plan.slots_per_split, partials, scale);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
   combine_partials_kernel<D><<<(unsigned)((nG + kGatherWarps - 1) / kGatherWarps), kGatherWarps * 32, 0, st>>>(
@@ -346,7 +346,7 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
   if (nG == 0 || nG > L || nG < 0) return SPFA_ERR_GLOBAL_COUNT;
   if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
   if (!G) return SPFA_ERR_BAD_ARG;
-  if (nG > 65535) return SPFA_ERR_TOO_LARGE;  // grid.y of the global-row kernel
+  if (nG > (1LL << 30)) return SPFA_ERR_TOO_LARGE;
   const GnlPlan plan = gnl_plan(L, d, nG);
   rc = check_workspace(workspace, workspace_bytes, plan.total);
   if (rc) return rc;
