@@ -381,6 +381,7 @@ def run_ours(args, rank, world, dev):
         sampler.start()
     times, launches = timed_steps(job, lambda: job.forward(capi), args.steps, args.warmup, world, capi.launch_count)
     tiled = capi.last_path() == capi.PATH_TILED
+    tensor_bound = tiled and job.kind in ("local", "local_1d_dilated")  # Global-no-local stays HBM-bound on the tiles
     clocks = sampler.stop() if sampler else None
     total_ms = dist_max(sum(times), world, dev)
     total_flops = dist_sum(job.flops, world, dev)
@@ -434,7 +435,7 @@ def run_ours(args, rank, world, dev):
 
     # ---- roofline of the dominant kernel (this rank's launch) ----
     kernel_ms = statistics.mean(times)
-    if tiled:
+    if tensor_bound:
         peak = peaks["bf16_tflops"] / 2.0
         achieved = job.flops / (kernel_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,

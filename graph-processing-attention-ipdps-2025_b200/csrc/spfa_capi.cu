@@ -333,7 +333,9 @@ int spfa_local_2d_dilated_forward_f32(const float* Q, const float* K, const floa
 // ---- Global-no-local -------------------------------------------------------------------------------
 size_t spfa_global_no_local_workspace_bytes(int64_t L, int64_t, int d, int64_t n_global) {
   if (L <= 0 || n_global <= 0 || !supported_d(d)) return 0;
-  return gnl_plan(L, d, n_global).total;
+  size_t total = gnl_plan(L, d, n_global).total;  // gather path
+  if (gnl_tiled_shape_ok(d, n_global)) total += gnl_tiled_plan(L, d, n_global).total;  // + tiled path scratch
+  return total;
 }
 
 int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
@@ -348,11 +350,32 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
   if (!G) return SPFA_ERR_BAD_ARG;
   if (nG > (1LL << 30)) return SPFA_ERR_TOO_LARGE;
   const GnlPlan plan = gnl_plan(L, d, nG);
-  rc = check_workspace(workspace, workspace_bytes, plan.total);
+  rc = check_workspace(workspace, workspace_bytes, spfa_global_no_local_workspace_bytes(L, row_end - row_begin, d, nG));
   if (rc) return rc;
   if (row_end == row_begin) return SPFA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   char* ws = reinterpret_cast<char*>(workspace);
+  const int path = g_path.load();
+  if (path != SPFA_PATH_GATHER) {
+    if (gnl_tiled_shape_ok(d, nG)) {
+      const bool rows_tiled = (path == SPFA_PATH_TILED) || nG >= kGnlTiledMinGlobalsForRows;
+      if (!rows_tiled) {  // few listed keys: ordinary rows on the exact gather kernel, global rows on the tiles
+        uint32_t* bits0 = reinterpret_cast<uint32_t*>(ws + plan.off_bits);
+        uint8_t* live0 = reinterpret_cast<uint8_t*>(ws + plan.off_live);
+        if (cudaMemsetAsync(bits0, 0, (size_t)((L + 31) / 32) * 4, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
+        gnl_mark_globals_kernel<<<(unsigned)((nG + 255) / 256), 256, 0, st>>>(G, nG, L, bits0, live0);
+        g_launches.fetch_add(1);
+        if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+        GnlCols cols0{G, nG, L, w, bits0};
+        rc = dispatch_gather(d, Q, K, V, m, l, O, cols0, row_begin, row_end - row_begin, 0, st);
+        if (rc) return rc;
+      }
+      rc = tiled_gnl_forward(Q, K, V, m, l, O, G, nG, L, d, w, row_begin, row_end, ws + plan.total, rows_tiled, st);
+      if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
+      return rc;
+    }
+    if (path == SPFA_PATH_TILED) return SPFA_ERR_BAD_ARG;
+  }
   uint32_t* bits = reinterpret_cast<uint32_t*>(ws + plan.off_bits);
   uint8_t* live = reinterpret_cast<uint8_t*>(ws + plan.off_live);
   float* partials = reinterpret_cast<float*>(ws + plan.off_part);

@@ -11,6 +11,7 @@
 #include <cstdlib>
 
 #include "../../include/spfa_b200.h"
+#include "gather_kernels.cuh"
 #include "tile_kernels_sm100.cuh"
 
 namespace spfa {
@@ -58,38 +59,31 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Common launch steps of band_forward_kernel: shared-memory opt-in, register-budget guard, error word.
 template <int D, int BN, int NS, int NSUB>
-int launch_band(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t w,
-                int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
+int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
+                    const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
   using P = tile::Plan<D, BN, NS, NSUB>;
   using G = tile::Geo<NSUB>;
   auto kern = tile::band_forward_kernel<D, BN, NS, NSUB>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
-  // ask for the largest shared-memory carve-out so that kCtasPerSm CTAs are co-resident
-  cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (const char* dbg = getenv("SPFA_DEBUG_OCCUPANCY")) {
-    int nb = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, G::kThreads, P::kDynSmem);
-    cudaFuncAttributes fa;
-    cudaFuncGetAttributes(&fa, kern);
-    int nb_small = 0, smem_sm = 0, regs_sm = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb_small, kern, G::kThreads, 1024);
-    cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, 0);
-    cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, 0);
-    fprintf(stderr, "spfa: band kernel D=%d BN=%d NS=%d NSUB=%d dyn smem=%d B static=%d B regs=%d threads=%d -> %d CTA/SM "
-            "(%d with 1 KB smem); SM has %d B smem, %d regs (%s)\n", D, BN, NS, NSUB, (int)P::kDynSmem,
-            (int)fa.sharedSizeBytes, fa.numRegs, G::kThreads, nb, nb_small, smem_sm, regs_sm, dbg);
-  }
-  // The kernel re-balances registers with setmaxnreg, which blocks without timeout if the budgets exceed
-  // what the launch allocated: refuse to launch unless the compiled register count covers them.
   cudaFuncAttributes attr;
   if (cudaFuncGetAttributes(&attr, kern) != cudaSuccess) return SPFA_ERR_LAUNCH;
   if (attr.numRegs * G::kThreads < G::kRegsSoftmax * 128 * NSUB + G::kRegsAux * 128) return SPFA_ERR_LAUNCH;
   int* err = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
+}
+
+template <int D, int BN, int NS, int NSUB>
+int launch_band(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t w,
+                int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
+  using G = tile::Geo<NSUB>;
   for (int64_t r = 0; r < s && r < L; ++r) {
-    tile::BandParams prm;
+    tile::BandParams prm{};
     prm.n_keys = (L - r + s - 1) / s;
     int64_t u_first = (row_begin > r) ? (row_begin - r + s - 1) / s : 0;
     int64_t u_end = (row_end > r) ? (row_end - r + s - 1) / s : 0;
@@ -109,9 +103,8 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
       return SPFA_ERR_LAUNCH;
     const int64_t grid = (prm.n_q + G::kQRows - 1) / G::kQRows;
     if (grid > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
-    kern<<<(unsigned)grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
-    g_launches.fetch_add(1);
-    if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+    const int rc = launch_band_raw<D, BN, NS, NSUB>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid), st);
+    if (rc) return rc;
   }
   return SPFA_OK;
 }
@@ -129,6 +122,167 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
     case 128: return launch_band<128, 64, 1, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
   }
   return SPFA_TILE_NOT_TAKEN;
+}
+
+// ---- Global-no-local on the tiled path ---------------------------------------------------------------
+// The listed global rows are sorted once (<= 1024 of them: one CTA, rank sort) and their Q/K/V rows
+// gathered into contiguous scratch. Then two launches of band_forward_kernel in its "every key except an
+// interval" modes cover the mask: mode 1, every ordinary row against the gathered global keys; mode 2, the
+// gathered global rows against all keys, key range split over the grid, followed by the combine pass.
+constexpr int kGnlTiledMaxGlobals = 1024;
+// Ordinary rows see at most n_global keys; with very few keys per row the TF32 error of a tile is not
+// averaged down, so below this count they stay on the exact FP32 gather kernel (only the global rows, which
+// see ~L keys each, go through the tiles).
+constexpr int kGnlTiledMinGlobalsForRows = 32;
+
+__global__ void gnl_sort_globals_kernel(const int32_t* __restrict__ G, int nG, int64_t L, int32_t* __restrict__ sorted,
+                                        int32_t* __restrict__ n_valid) {
+  __shared__ int32_t g[kGnlTiledMaxGlobals];
+  __shared__ int cnt;
+  const int t = threadIdx.x;
+  if (t == 0) cnt = 0;
+  int32_t v = 0x7fffffff;
+  if (t < nG) {
+    const int32_t x = G[t];
+    if (x >= 0 && (int64_t)x < L) v = x;
+  }
+  g[t] = v;
+  __syncthreads();
+  if (t < nG) {
+    int rank = 0;
+    for (int u = 0; u < nG; ++u) rank += (g[u] < v) || (g[u] == v && u < t);
+    sorted[rank] = v;  // invalid entries (INT_MAX) end up last
+    if (v != 0x7fffffff) atomicAdd(&cnt, 1);
+  }
+  __syncthreads();
+  if (t == 0) *n_valid = cnt;
+}
+
+// One warp per sorted entry: copies the entry's K and V rows (always) and its Q row (if the row belongs to
+// this shard) into the contiguous scratch; entries that are invalid get zero rows. live[e] = 1 for the first
+// occurrence of a row that lies in the shard (the combine pass writes exactly those rows).
+__global__ void gnl_gather_globals_kernel(const int32_t* __restrict__ sorted, int nG, const float* __restrict__ Q,
+                                          const float* __restrict__ K, const float* __restrict__ V, int d,
+                                          int64_t row_begin, int64_t row_end, float* __restrict__ QG,
+                                          float* __restrict__ KG, float* __restrict__ VG, uint8_t* __restrict__ live) {
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (e >= nG) return;
+  const int32_t g = sorted[e];
+  const bool valid = g != 0x7fffffff;
+  const bool mine = valid && g >= row_begin && g < row_end;
+  const bool first = (e == 0) || (sorted[e - 1] != g);
+  for (int c = lane * 4; c < d; c += 128) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(KG + (size_t)e * d + c) = valid ? ldg4(K + (size_t)g * d + c) : z;
+    *reinterpret_cast<float4*>(VG + (size_t)e * d + c) = valid ? ldg4(V + (size_t)g * d + c) : z;
+    *reinterpret_cast<float4*>(QG + (size_t)e * d + c) = mine ? ldg4(Q + (size_t)(g - row_begin) * d + c) : z;
+  }
+  if (lane == 0) live[e] = (mine && first) ? 1 : 0;
+}
+
+struct GnlTiledPlan {
+  int bn, n_split;
+  int64_t kv_chunk;
+  size_t off_sorted, off_nvalid, off_live, off_qg, off_kg, off_vg, off_part, total;
+};
+
+inline GnlTiledPlan gnl_tiled_plan(int64_t L, int d, int64_t nG) {
+  auto up = [](size_t x) { return (x + 255) / 256 * 256; };
+  GnlTiledPlan p;
+  p.bn = (d == 128) ? 64 : 96;
+  const int64_t tiles = (L + p.bn - 1) / p.bn;
+  const int64_t q_tiles = (nG + 255) / 256;
+  int64_t ctas = 148 / q_tiles;
+  if (ctas < 1) ctas = 1;
+  int64_t chunk_tiles = (tiles + ctas - 1) / ctas;
+  if (chunk_tiles < 2) chunk_tiles = 2;
+  p.kv_chunk = chunk_tiles * p.bn;
+  p.n_split = (int)((L + p.kv_chunk - 1) / p.kv_chunk);
+  p.off_sorted = 0;
+  p.off_nvalid = up((size_t)nG * 4);
+  p.off_live = p.off_nvalid + 256;
+  p.off_qg = p.off_live + up((size_t)nG);
+  p.off_kg = p.off_qg + up((size_t)nG * d * 4);
+  p.off_vg = p.off_kg + up((size_t)nG * d * 4);
+  p.off_part = p.off_vg + up((size_t)nG * d * 4);
+  p.total = p.off_part + up((size_t)nG * p.n_split * (d + 4) * 4);
+  return p;
+}
+
+inline bool gnl_tiled_shape_ok(int d, int64_t nG) {
+  return (d == 32 || d == 64 || d == 128) && nG >= 1 && nG <= kGnlTiledMaxGlobals;
+}
+
+template <int D, int BN, int NS>
+int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, float* l, float* O, const int32_t* G,
+                     int64_t nG, int64_t L, int64_t w, int64_t row_begin, int64_t row_end, char* ws,
+                     const GnlTiledPlan& plan, bool ordinary_rows_too, cudaStream_t st) {
+  int32_t* sorted = reinterpret_cast<int32_t*>(ws + plan.off_sorted);
+  int32_t* n_valid = reinterpret_cast<int32_t*>(ws + plan.off_nvalid);
+  uint8_t* live = reinterpret_cast<uint8_t*>(ws + plan.off_live);
+  float* QG = reinterpret_cast<float*>(ws + plan.off_qg);
+  float* KG = reinterpret_cast<float*>(ws + plan.off_kg);
+  float* VG = reinterpret_cast<float*>(ws + plan.off_vg);
+  float* partials = reinterpret_cast<float*>(ws + plan.off_part);
+  gnl_sort_globals_kernel<<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid);
+  g_launches.fetch_add(1);
+  gnl_gather_globals_kernel<<<(unsigned)((nG + 3) / 4), 128, 0, st>>>(sorted, (int)nG, Q, K, V, D, row_begin, row_end, QG,
+                                                                      KG, VG, live);
+  g_launches.fetch_add(1);
+  if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+  const int64_t pitch = D * (int64_t)sizeof(float);
+  const int64_t n_rows = row_end - row_begin;
+  tile::BandParams prm{};
+  prm.w = w;
+  prm.s = 1;
+  prm.r = 0;
+  prm.row_begin = row_begin;
+  prm.scale_log2e = (1.0f / sqrtf((float)D)) * kLog2e;
+  prm.sorted = sorted;
+  prm.n_valid = n_valid;
+  CUtensorMap tmQ, tmK, tmV;
+  // mode 1: ordinary rows of the shard against the gathered global keys
+  prm.mode = 1;
+  prm.n_keys = nG;
+  prm.u_q_first = row_begin;
+  prm.n_q = n_rows;
+  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, KG, D, nG, pitch, BN) ||
+      !make_row_map(&tmV, VG, D, nG, pitch, BN, /*mn_major=*/true))
+    return SPFA_ERR_LAUNCH;
+  int rc = SPFA_OK;
+  if (ordinary_rows_too) rc = launch_band_raw<D, BN, NS, 2>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + 255) / 256)), st);
+  if (rc) return rc;
+  // mode 2: the gathered global rows against every key, key range split over grid.y
+  prm.mode = 2;
+  prm.n_keys = L;
+  prm.u_q_first = 0;
+  prm.n_q = nG;
+  prm.row_begin = 0;
+  prm.kv_chunk = plan.kv_chunk;
+  prm.partials = partials;
+  prm.n_split = plan.n_split;
+  if (!make_row_map(&tmQ, QG, D, nG, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, BN) ||
+      !make_row_map(&tmV, V, D, L, pitch, BN, /*mn_major=*/true))
+    return SPFA_ERR_LAUNCH;
+  rc = launch_band_raw<D, BN, NS, 2>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((nG + 255) / 256), (unsigned)plan.n_split),
+                                     st);
+  if (rc) return rc;
+  combine_partials_kernel<D><<<(unsigned)((nG + kGatherWarps - 1) / kGatherWarps), kGatherWarps * 32, 0, st>>>(
+      partials, sorted, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
+}
+
+inline int tiled_gnl_forward(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                             const int32_t* G, int64_t nG, int64_t L, int d, int64_t w, int64_t row_begin,
+                             int64_t row_end, char* ws, bool ordinary_rows_too, cudaStream_t st) {
+  const GnlTiledPlan plan = gnl_tiled_plan(L, d, nG);
+  switch (d) {
+    case 32: return launch_gnl_tiled<32, 96, 2>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+    case 64: return launch_gnl_tiled<64, 96, 2>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+    case 128: return launch_gnl_tiled<128, 64, 1>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
 }
 
 // Reads and clears the tiled kernels' error word (synchronises the device). 0 = no error.

@@ -93,6 +93,21 @@ struct BandParams {
   int64_t s, r;       // stride and residue: abs_row = r + u*s
   int64_t row_begin;  // first absolute row of the shard (Q/m/l/O are indexed by abs_row - row_begin)
   float scale_log2e;  // (1/sqrt(d)) * log2(e)
+  // ---- "every key EXCEPT an interval" masks (Global-no-local) ----
+  // mode 0: band, a row attends to keys [u-w, u+w] (Local, Local-1D-dilated).
+  // mode 1: the keys are the listed global rows, gathered in ascending order (`sorted`, n_keys of them, of
+  //         which *n_valid are real); query row i attends to every listed key outside [i-w, i+w]; rows
+  //         that are themselves listed are skipped (mode 2 handles them).
+  // mode 2: the QUERY rows are the listed global rows (gathered, sorted); row r = sorted[r] attends to
+  //         every key of the full sequence outside [sorted[r]-w, sorted[r]+w]. The key range is split
+  //         over blockIdx.y (kv_chunk keys per CTA) and each CTA writes a partial softmax state per
+  //         row ((d+4) floats: un-normalised O relative to m, then m, l) for a later combine pass.
+  int mode;
+  const int32_t* sorted;  // modes 1, 2: ascending global row numbers (invalid entries last, as INT_MAX)
+  const int32_t* n_valid; // modes 1, 2: number of real entries in `sorted`
+  int64_t kv_chunk;       // mode 2: keys per CTA along blockIdx.y
+  float* partials;        // mode 2: [n_keys_of_sorted][n_split][d+4]
+  int n_split;            // mode 2: gridDim.y
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -304,9 +319,23 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int64_t uq0 = prm.u_q_first + (int64_t)blockIdx.x * kQRows;  // first query u of this CTA
   const int64_t uq_end = prm.u_q_first + prm.n_q;                    // one past the last valid query u
   const int64_t rows_here = (uq_end - uq0 < kQRows) ? (uq_end - uq0) : kQRows;
-  const int64_t kv_lo = (uq0 - prm.w > 0) ? (uq0 - prm.w) : 0;
-  int64_t kv_hi = uq0 + rows_here - 1 + prm.w + 1;
-  if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
+  int64_t kv_lo, kv_hi;
+  int64_t uq_end_eff = uq_end;  // mode 2: only the real entries of the sorted list are query rows
+  if (prm.mode == 0) {
+    kv_lo = (uq0 - prm.w > 0) ? (uq0 - prm.w) : 0;
+    kv_hi = uq0 + rows_here - 1 + prm.w + 1;
+    if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
+  } else if (prm.mode == 1) {
+    kv_lo = 0;
+    kv_hi = *prm.n_valid;  // real listed keys
+    if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
+  } else {
+    kv_lo = (int64_t)blockIdx.y * prm.kv_chunk;
+    kv_hi = kv_lo + prm.kv_chunk;
+    if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
+    if (uq_end_eff > *prm.n_valid) uq_end_eff = *prm.n_valid;
+  }
+  if (kv_hi < kv_lo) kv_hi = kv_lo;
   const int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
   // active key-tile range [j0, j1) of each sub-tile
   int j0[NSUB], j1[NSUB];
@@ -314,10 +343,13 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   for (int x = 0; x < NSUB; ++x) {
     const int64_t ux0 = uq0 + 128 * x;
     int64_t ux_last = ux0 + 127;
-    if (ux_last > uq_end - 1) ux_last = uq_end - 1;
-    if (ux0 >= uq_end) {
+    if (ux_last > uq_end_eff - 1) ux_last = uq_end_eff - 1;
+    if (ux0 >= uq_end_eff) {
       j0[x] = 0;
       j1[x] = 0;
+    } else if (prm.mode != 0) {
+      j0[x] = 0;
+      j1[x] = nT;
     } else {
       const int64_t lo = (ux0 - prm.w > 0) ? (ux0 - prm.w) : 0;
       int64_t hi = ux_last + prm.w + 1;
@@ -359,7 +391,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(G::kRegsAux));
   if (warp == W_TMA) {
     // =============================== TMA producer ===============================
-    if (lane == 0) {
+    if (lane == 0 && nT > 0) {  // nothing is fetched for a CTA without key tiles (no listed key at all)
       // Q: both sub-tiles, coordinates relative to the first query u of the shard (rows past the end read zeros)
       mbar_expect_tx(bar(B_QFULL), P::kQBytes);
       const int32_t yq = (int32_t)(uq0 - prm.u_q_first);
@@ -395,7 +427,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t kIdescS = idesc_tf32(128, BN, 0);
       constexpr uint32_t kIdescO = idesc_tf32(128, D, 1);
-      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
+      bool ok = (nT > 0) && mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
       // Descriptors are built once per operand tile; each MMA only adds a compile-time offset to the
       // 14-bit start-address field (shared memory is < 256 KB, so the field cannot carry out).
       // S of key tile j goes to S buffer (j - j0[x]) & 1 of its sub-tile; it is issued two tiles ahead of the
@@ -490,21 +522,46 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tS0 = tmem + lane_base + P::kColS + 2 * BN * x;
     const uint32_t tO = tmem + lane_base + P::kColO + D * x;
     const int64_t uq = uq0 + 128 * x + row;
-    const bool row_valid = uq < uq_end;
-    // band of this row, and of the first / last row of this warp (warp-uniform bounds for chunk classes),
-    // as 32-bit offsets from the CTA's first key tile
-    int lo_q, hi_q, lo_a, lo_b, hi_a, hi_b;
-    {
-      const int64_t n1 = prm.n_keys - 1, uq_a = uq - lane, uq_b = uq - lane + 31;
-      auto lo_of = [&](int64_t u) { return (int)(((u - prm.w > 0) ? (u - prm.w) : 0) - kv_lo); };
-      auto hi_of = [&](int64_t u) { return (int)(((u + prm.w < n1) ? (u + prm.w) : n1) - kv_lo); };
-      lo_q = lo_of(uq); hi_q = hi_of(uq);
-      lo_a = lo_of(uq_a); lo_b = lo_of(uq_b);
-      hi_a = hi_of(uq_a); hi_b = hi_of(uq_b);
+    const bool row_valid = uq < uq_end_eff;
+    // Per-row key interval [lo_q, hi_q] as 32-bit offsets from the CTA's first key tile: the keys a row
+    // attends to (mode 0) or the keys it must skip (modes 1, 2). Both ends grow with the row, so the first
+    // and last row of a warp (lo_a/hi_a, lo_b/hi_b) bound every row of the warp: that makes the chunk
+    // classes below warp-uniform.
+    int lo_q, hi_q;
+    bool listed = false;  // mode 1: this query row is itself a global row (handled by the mode-2 launch)
+    if (prm.mode == 0) {
+      const int64_t n1 = prm.n_keys - 1;
+      lo_q = (int)(((uq - prm.w > 0) ? (uq - prm.w) : 0) - kv_lo);
+      hi_q = (int)(((uq + prm.w < n1) ? (uq + prm.w) : n1) - kv_lo);
+    } else if (prm.mode == 1) {
+      const int nv = (int)kv_hi;
+      const int64_t ic = (uq < uq_end - 1) ? uq : (uq_end - 1);  // clamp keeps the bounds monotone past the end
+      auto lower_bound = [&](int64_t v) {  // first t with sorted[t] >= v
+        int a = 0, b = nv;
+        while (a < b) {
+          const int mid = (a + b) >> 1;
+          if ((int64_t)__ldg(prm.sorted + mid) < v) a = mid + 1; else b = mid;
+        }
+        return a;
+      };
+      lo_q = lower_bound(ic - prm.w);
+      hi_q = lower_bound(ic + prm.w + 1) - 1;
+      const int t = lower_bound(ic);
+      listed = (t < nv) && ((int64_t)__ldg(prm.sorted + t) == ic);
+    } else {
+      const int nv = *prm.n_valid;
+      const int64_t rc = (uq < nv - 1) ? uq : (int64_t)(nv - 1);
+      const int64_t g = (nv > 0) ? (int64_t)__ldg(prm.sorted + (rc > 0 ? rc : 0)) : 0;
+      const int64_t a = g - prm.w - kv_lo, b = g + prm.w - kv_lo;
+      lo_q = (int)((a < -(1 << 30)) ? -(1 << 30) : ((a > (1 << 30)) ? (1 << 30) : a));
+      hi_q = (int)((b < -(1 << 30)) ? -(1 << 30) : ((b > (1 << 30)) ? (1 << 30) : b));
     }
+    const int lo_a = __shfl_sync(kFullMask, lo_q, 0), lo_b = __shfl_sync(kFullMask, lo_q, 31);
+    const int hi_a = __shfl_sync(kFullMask, hi_q, 0), hi_b = __shfl_sync(kFullMask, hi_q, 31);
+    const int n_cols = (int)(kv_hi - kv_lo);  // real keys of this CTA's range
     // The caller's state row is needed only in the epilogue; asking L2 for it now takes its DRAM latency
     // off the end of the CTA.
-    if (row_valid) {
+    if (row_valid && prm.mode != 2 && !listed) {
       const int64_t rl0 = prm.r + uq * prm.s - prm.row_begin;
       const char* orow = reinterpret_cast<const char*>(O_out + (size_t)rl0 * D);
 #pragma unroll
@@ -523,11 +580,12 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int it = 0; it < nx && ok; ++it) {
       const int j = j0[x] + it;
       const int k0 = j * BN;
-      // columns of this tile inside the band: this row [c_lo, c_hi]; every row of the warp [w_lo, w_hi];
-      // some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
+      // Interval of this tile's columns: this row [c_lo, c_hi]; common to every row of the warp [w_lo, w_hi];
+      // touched by some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
       const int c_lo = lo_q - k0, c_hi = hi_q - k0;
       const int w_lo = lo_b - k0, w_hi = hi_a - k0;
       const int v_lo = lo_a - k0, v_hi = hi_b - k0;
+      const int nvc = n_cols - k0;  // columns of this tile that are real keys
       // Chunk classes (warp-uniform): 2 = every (row, column) valid, 0 = none valid, 1 = mixed.
       // Mixed chunks use a per-row bit mask of valid columns.
       int cls[NC];
@@ -535,11 +593,21 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
         const int cb = c * 32;
-        cls[c] = (cb >= w_lo && cb + 31 <= w_hi) ? 2 : ((cb + 31 < v_lo || cb > v_hi) ? 0 : 1);
-        const int a = c_lo - cb, b = c_hi - cb;  // valid columns of this chunk: [a, b] clipped to [0, 31]
+        const int a = c_lo - cb, b = c_hi - cb;  // this row's interval within the chunk, clipped to [0, 31]
         const uint32_t m_lo = (a <= 0) ? 0xffffffffu : (a >= 32 ? 0u : (0xffffffffu << a));
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
-        vmask[c] = m_lo & m_hi;
+        const uint32_t m_in = m_lo & m_hi;
+        if (prm.mode == 0) {  // valid = inside the interval
+          cls[c] = (cb >= w_lo && cb + 31 <= w_hi) ? 2 : ((cb + 31 < v_lo || cb > v_hi) ? 0 : 1);
+          vmask[c] = m_in;
+        } else {              // valid = a real key outside the interval
+          const int r = nvc - cb;
+          const uint32_t m_rng = (r >= 32) ? 0xffffffffu : (r <= 0 ? 0u : ((1u << r) - 1u));
+          const bool all_valid = (r >= 32) && (cb + 31 < v_lo || cb > v_hi);
+          const bool none_valid = (r <= 0) || (cb >= w_lo && cb + 31 <= w_hi);
+          cls[c] = all_valid ? 2 : (none_valid ? 0 : 1);
+          vmask[c] = m_rng & ~m_in;
+        }
       }
       const int sb = x * 2 + (it & 1);                  // S buffer of this tile
       const uint32_t tS = tS0 + BN * (it & 1);
@@ -651,12 +719,15 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (ok) {
         tc_fence_after();
-        const bool store = row_valid && l_run > 0.f;
+        const bool partial_out = (prm.mode == 2);
+        // mode 2 writes a partial state for every real row (also rows with no key in this range);
+        // the other modes touch a row only if it attended to something and is theirs to write
+        const bool store = partial_out ? row_valid : (row_valid && l_run > 0.f && !listed);
         if (row == 0) SPFA_TRACE_AT(1 + x, 11, x, 0);
         // Per-row coefficients of  O_out = ca * O_in + cb * O_tmem  (state in natural-log units, as the
         // gather path; l is re-expressed against the true maximum, O in TMEM is relative to `shift`).
         float ca = 0.f, cb = 0.f;
-        if (store) {
+        if (store && !partial_out) {
           const int64_t rl = prm.r + uq * prm.s - prm.row_begin;  // shard-local row
           const float rel = fast_exp2(shift - m_true);
           const float l_loc = l_run * rel;
@@ -671,6 +742,18 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           cb = bt * rel * inv;
           m_out[rl] = m_o;
           l_out[rl] = l_o;
+        } else if (store) {
+          // partial state of this key range: un-normalised O relative to the range's own maximum, then m, l
+          float* part = prm.partials + ((size_t)uq * prm.n_split + blockIdx.y) * (D + 4);
+          if (l_run > 0.f) {
+            cb = fast_exp2(shift - m_true);
+            part[D] = m_true * 0.6931471805599453f;
+            part[D + 1] = l_run * cb;
+          } else {
+            cb = 0.f;
+            part[D] = neg_inf();
+            part[D + 1] = 0.f;
+          }
         }
         // Stage cb * O_tmem in shared memory (this sub-tile's Q region is dead: all its S MMAs completed
         // before the last PV), 16-byte chunks XOR-swizzled by the row so that both the row-per-thread
@@ -701,29 +784,41 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr int RPI = 32 / LPR;    // rows per warp instruction
         constexpr int NIT = 32 / RPI;    // instructions for this warp's 32 rows
         const int wrow0 = (warp & 3) * 32, sub = lane % LPR;
-        float4 oin[NIT];
+        if (partial_out) {
 #pragma unroll
-        for (int i = 0; i < NIT; ++i) {
-          const int r = wrow0 + i * RPI + lane / LPR;
-          oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (coef[128 + r] != 0.f) {
-            const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
-            oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
+          for (int i = 0; i < NIT; ++i) {
+            const int r = wrow0 + i * RPI + lane / LPR;
+            if (coef[128 + r] != 0.f) {
+              float* part = prm.partials + ((size_t)(uq0 + 128 * x + r) * prm.n_split + blockIdx.y) * (D + 4);
+              *reinterpret_cast<float4*>(part + sub * 4) =
+                  *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
+            }
           }
-        }
+        } else {
+          float4 oin[NIT];
 #pragma unroll
-        for (int i = 0; i < NIT; ++i) {
-          const int r = wrow0 + i * RPI + lane / LPR;
-          if (coef[128 + r] != 0.f) {
-            const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
-            const float car = coef[r];
-            const float4 t = *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
-            float4 o;
-            o.x = fmaf(car, oin[i].x, t.x);
-            o.y = fmaf(car, oin[i].y, t.y);
-            o.z = fmaf(car, oin[i].z, t.z);
-            o.w = fmaf(car, oin[i].w, t.w);
-            *reinterpret_cast<float4*>(O_out + (size_t)rl * D + sub * 4) = o;
+          for (int i = 0; i < NIT; ++i) {
+            const int r = wrow0 + i * RPI + lane / LPR;
+            oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (coef[128 + r] != 0.f) {
+              const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+              oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < NIT; ++i) {
+            const int r = wrow0 + i * RPI + lane / LPR;
+            if (coef[128 + r] != 0.f) {
+              const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+              const float car = coef[r];
+              const float4 t = *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
+              float4 o;
+              o.x = fmaf(car, oin[i].x, t.x);
+              o.y = fmaf(car, oin[i].y, t.y);
+              o.z = fmaf(car, oin[i].z, t.z);
+              o.w = fmaf(car, oin[i].w, t.w);
+              *reinterpret_cast<float4*>(O_out + (size_t)rl * D + sub * 4) = o;
+            }
           }
         }
         if (row == 0) SPFA_TRACE_AT(1 + x, 13, x, 0);

@@ -242,7 +242,7 @@ IMPLICIT_CASES = [
 @pytest.mark.parametrize("kind,L,d,p0,p1", IMPLICIT_CASES)
 def test_implicit_masks_vs_oracle(capi, orc, path, kind, L, d, p0, p1):
     capi.set_path(capi.PATH_GATHER if path == "gather" else capi.PATH_AUTO)
-    tol = TOL_GATHER if (path == "gather" or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+    tol = TOL_GATHER if (path == "gather" or kind == "local_2d_dilated") else TOL_TILED
     Q, K, V = seeded_qkv(L, d, 1000 + L + d)
     G = None
     if kind == "global_no_local":
@@ -259,7 +259,7 @@ def test_implicit_masks_vs_oracle(capi, orc, path, kind, L, d, p0, p1):
 def test_row_shards_and_incoming_state(capi, orc, path, kind, L, d, p0, p1):
     """Row ranges (as a second GPU would own them) on top of a non-trivial incoming (m, l, O)."""
     capi.set_path(capi.PATH_GATHER if path == "gather" else capi.PATH_AUTO)
-    tol = TOL_GATHER if (path == "gather" or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+    tol = TOL_GATHER if (path == "gather" or kind == "local_2d_dilated") else TOL_TILED
     Q, K, V = seeded_qkv(L, d, 31)
     G = np.array([0, 700, 701, 1499, 33], dtype=np.int32) if kind == "global_no_local" else None
     rng = np.random.default_rng(8)
@@ -358,9 +358,30 @@ def test_duplicate_and_out_of_range_global_indices(capi, orc):
     Q, K, V = seeded_qkv(L, d, 12)
     G = np.array([5, 200, 5, 299], dtype=np.int32)  # row 5 listed twice: other rows see key 5 twice
     want = orc.implicit_forward("global_no_local", Q, K, V, w, G=G)
-    st = capi.new_state(L, d)
-    capi.global_no_local_forward(dev(Q), dev(K), dev(V), *st, dev(G), w)
-    assert_state_close(to_np(st), want, TOL_GATHER, "duplicate globals")
+    for path, tol in ((capi.PATH_GATHER, TOL_GATHER), (capi.PATH_AUTO, TOL_TILED)):
+        capi.set_path(path)
+        st = capi.new_state(L, d)
+        capi.global_no_local_forward(dev(Q), dev(K), dev(V), *st, dev(G), w)
+        assert_state_close(to_np(st), want, tol, "duplicate globals")
+    capi.set_path(capi.PATH_AUTO)
+
+
+@pytest.mark.parametrize("L,d,w,nG,rb,re", [(4096, 64, 50, 300, 0, 4096), (3000, 128, 17, 64, 0, 3000),
+                                              (2500, 32, 0, 1024, 0, 2500), (5000, 64, 300, 100, 1234, 4321),
+                                              (700, 64, 699, 40, 0, 700)])
+def test_global_no_local_many_globals_tiled(capi, orc, L, d, w, nG, rb, re):
+    """Enough listed rows for both halves of the mask (ordinary rows against the gathered global keys, global
+    rows against every key) to run on the tensor cores; duplicates and a row shard included."""
+    Q, K, V = seeded_qkv(L, d, 77 + L)
+    rng = np.random.default_rng(L)
+    G = rng.permutation(L)[:nG].astype(np.int32)
+    G[nG // 2] = G[0]  # a duplicate entry
+    want = orc.implicit_forward("global_no_local", Q[rb:re], K, V, w, G=G, row_begin=rb, row_end=re)
+    capi.set_path(capi.PATH_AUTO)
+    st = capi.new_state(re - rb, d)
+    capi.global_no_local_forward(dev(Q[rb:re]), dev(K), dev(V), *st, dev(G), w, rb, re)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want, TOL_TILED, f"gnl tiled L={L} d={d} w={w} nG={nG}")
 
 
 def test_full_size_properties_local(capi):
@@ -404,7 +425,7 @@ def test_full_size_sampled_rows_vs_oracle(capi, orc):
         Gd = None if G is None else dev(G)
         for path in (capi.PATH_GATHER, capi.PATH_AUTO):
             capi.set_path(path)
-            tol = TOL_GATHER if (path == capi.PATH_GATHER or kind in ("local_2d_dilated", "global_no_local")) else TOL_TILED
+            tol = TOL_GATHER if (path == capi.PATH_GATHER or kind == "local_2d_dilated") else TOL_TILED
             st = capi.new_state(L, d)
             _run_implicit(capi, kind, Qd, Kd, Vd, st, p0, p1, Gd, True, 0, L)
             m, l, O = to_np(st)
