@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cmath>
 
+#include "block_kernels.cuh"
 #include "gather_kernels.cuh"
 #include "tile_dispatch.cuh"
 
@@ -109,6 +110,43 @@ int launch_gnl_global_rows(const float* Q, const float* K, const float* V, float
       partials, G, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
   g_launches.fetch_add(1);
   return launch_status();
+}
+
+// Local-2D-dilated: one CTA per mask block with the block's key rows staged in shared memory (FP32, exact).
+template <int D, int NK>
+int launch_local2d_block_nk(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L,
+                         int64_t B, int64_t s, int64_t n, int use_nan, int64_t row_begin, int64_t row_end,
+                         cudaStream_t st) {
+  const size_t smem = block2d_smem_bytes<D>(n);
+  auto kern = local2d_block_kernel<D, NK>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return SPFA_ERR_LAUNCH;
+  Block2dParams prm;
+  prm.L = L;
+  prm.B = B;
+  prm.s = s;
+  prm.n = n;
+  prm.row_begin = row_begin;
+  prm.row_end = row_end;
+  prm.first_block = row_begin / B;
+  prm.use_nan = use_nan;
+  prm.scale = 1.0f / sqrtf((float)D);
+  const int64_t blocks = (row_end - 1) / B - prm.first_block + 1;
+  if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  kern<<<(unsigned)blocks, kBlockWarps * 32, smem, st>>>(Q, K, V, m, l, O, prm);
+  g_launches.fetch_add(1);
+  g_last_path.store(SPFA_PATH_GATHER);  // an FP32 SIMT path, same accuracy class as the gather kernels
+  return launch_status();
+}
+
+template <int D>
+int launch_local2d_block(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L,
+                         int64_t B, int64_t s, int64_t n, int use_nan, int64_t row_begin, int64_t row_end,
+                         cudaStream_t st) {
+  if (n <= 32) return launch_local2d_block_nk<D, 1>(Q, K, V, m, l, O, L, B, s, n, use_nan, row_begin, row_end, st);
+  if (n <= 64) return launch_local2d_block_nk<D, 2>(Q, K, V, m, l, O, L, B, s, n, use_nan, row_begin, row_end, st);
+  if (n <= 128) return launch_local2d_block_nk<D, 4>(Q, K, V, m, l, O, L, B, s, n, use_nan, row_begin, row_end, st);
+  return launch_local2d_block_nk<D, 8>(Q, K, V, m, l, O, L, B, s, n, use_nan, row_begin, row_end, st);
 }
 
 template <class F>
@@ -326,6 +364,22 @@ int spfa_local_2d_dilated_forward_f32(const float* Q, const float* K, const floa
   if (B <= 0 || L % B != 0) return SPFA_ERR_BLOCK_DIVISOR;
   if (dil < 0) return SPFA_ERR_DILATION_NEG;
   if (dil >= (1LL << 31) || B / (dil + 1) < 1) return SPFA_ERR_DILATION_BLOCK;
+  if (row_end == row_begin) return SPFA_OK;
+  {
+    // block-staged kernel whenever a block's key rows fit in shared memory; else (and when the gather
+    // path is forced) one warp per row
+    const int64_t s1 = dil + 1;
+    const int64_t n = ((B - 1) / s1 + 1 < B) ? ((B - 1) / s1 + 1) : B;
+    if (g_path.load() != SPFA_PATH_GATHER && n <= 32 * kBlockMaxKeysPerLane) {
+      cudaStream_t st = (cudaStream_t)stream;
+      switch (d) {
+        case 16: if (block2d_smem_bytes<16>(n) <= 200 * 1024) return launch_local2d_block<16>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st); break;
+        case 32: if (block2d_smem_bytes<32>(n) <= 200 * 1024) return launch_local2d_block<32>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st); break;
+        case 64: if (block2d_smem_bytes<64>(n) <= 200 * 1024) return launch_local2d_block<64>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st); break;
+        case 128: if (block2d_smem_bytes<128>(n) <= 200 * 1024) return launch_local2d_block<128>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st); break;
+      }
+    }
+  }
   Local2dCols cols{L, B, dil + 1};
   return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, use_nan, (cudaStream_t)stream);
 }
