@@ -89,6 +89,10 @@ def algorithmic_bytes(kind, L_keys, n_rows, d, nnz, n_live_rows):
     if kind in ("csr", "coo"):
         extra = 8 * nnz if kind == "coo" else 0
         return nnz * (2 * d * 4 + 4) + n_live_rows * (2 * d * 4 + 16) + 8 * (n_rows + 1) + extra
+    if kind == "local_2d_dilated":
+        # only live rows are read (Q, incoming O) and only the live key rows of K, V (the same row set);
+        # every row is written once (result or NaN fill)
+        return (2 * n_live_rows * d + 2 * n_live_rows * d + n_rows * d) * 4 + 16 * n_live_rows
     return (2 * n_rows * d + 2 * L_keys * d) * 4 + 16 * n_live_rows
 
 

@@ -275,8 +275,10 @@ gather_split_rows_kernel(const float* __restrict__ Q, const float* __restrict__ 
   }
 }
 
-// One warp per list entry: merges that entry's n_split partial states in split order, then folds the
-// result into (m, l, O).
+// One CTA (four warps) per list entry: folds that entry's n_split partial states into (m, l, O).
+// The partial maxima are reduced first, so the accumulation over splits has no serial dependency: every
+// warp takes a quarter of the splits with several loads in flight, and the four warp results are merged
+// through shared memory.
 template <int D>
 __global__ void __launch_bounds__(kGatherWarps * 32)
 combine_partials_kernel(const float* __restrict__ partials, const int32_t* __restrict__ row_list,
@@ -284,32 +286,46 @@ combine_partials_kernel(const float* __restrict__ partials, const int32_t* __res
                         int64_t row_end, int n_split, float* __restrict__ m, float* __restrict__ l,
                         float* __restrict__ O) {
   constexpr int LPK = D / 4;
+  __shared__ float s_l[kGatherWarps];
+  __shared__ float4 s_acc[kGatherWarps][LPK];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int e = blockIdx.x * kGatherWarps + warp;
+  const int e = blockIdx.x;
   if (e >= n_entries) return;
   const int64_t i = row_list[e];
-  if (!entry_live[e] || i < row_begin || i >= row_end) return;
-  RowAcc<D> st;
-  st.m = neg_inf();
-  st.l = 0.f;
-  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!entry_live[e] || i < row_begin || i >= row_end) return;  // uniform over the CTA
+  const float* base = partials + (size_t)e * n_split * (D + 4);
+  // maximum of the partial maxima (all threads compute the same value)
+  float mx = neg_inf();
+  for (int sp = lane; sp < n_split; sp += 32) mx = fmaxf(mx, __ldg(base + (size_t)sp * (D + 4) + D));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(kFullMask, mx, o));
+  const float ms = (mx == neg_inf()) ? 0.f : mx;
   const int sub = lane % LPK;
-  for (int sp = 0; sp < n_split; ++sp) {
-    const float* part = partials + ((size_t)e * n_split + sp) * (D + 4);
-    const float mo = part[D], lo = part[D + 1];
-    const float4 ao = reinterpret_cast<const float4*>(part)[sub];
-    const float mn = fmaxf(st.m, mo);
-    const float ms = (mn == neg_inf()) ? 0.f : mn;
-    const float c1 = fast_exp2((st.m - ms) * kLog2e);
-    const float c2 = fast_exp2((mo - ms) * kLog2e);
-    st.l = st.l * c1 + lo * c2;
-    st.acc.x = st.acc.x * c1 + ao.x * c2;
-    st.acc.y = st.acc.y * c1 + ao.y * c2;
-    st.acc.z = st.acc.z * c1 + ao.z * c2;
-    st.acc.w = st.acc.w * c1 + ao.w * c2;
-    st.m = mn;
+  float lsum = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+  for (int sp = warp; sp < n_split; sp += kGatherWarps) {
+    const float* part = base + (size_t)sp * (D + 4);
+    const float w = fast_exp2((__ldg(part + D) - ms) * kLog2e);
+    const float4 a = ldg4(part + sub * 4);
+    lsum = fmaf(__ldg(part + D + 1), w, lsum);
+    acc.x = fmaf(a.x, w, acc.x);
+    acc.y = fmaf(a.y, w, acc.y);
+    acc.z = fmaf(a.z, w, acc.z);
+    acc.w = fmaf(a.w, w, acc.w);
   }
-  if (st.l > 0.f) store_row<D>(st, m, l, O, i - row_begin, lane);
+  if (lane < LPK) s_acc[warp][lane] = acc;
+  if (lane == 0) s_l[warp] = lsum;
+  __syncthreads();
+  if (warp == 0) {
+    RowAcc<D> st;
+    st.m = mx;
+    st.l = (s_l[0] + s_l[1]) + (s_l[2] + s_l[3]);
+    const float4 a0 = s_acc[0][sub], a1 = s_acc[1][sub], a2 = s_acc[2][sub], a3 = s_acc[3][sub];
+    st.acc = make_float4((a0.x + a1.x) + (a2.x + a3.x), (a0.y + a1.y) + (a2.y + a3.y), (a0.z + a1.z) + (a2.z + a3.z),
+                         (a0.w + a1.w) + (a2.w + a3.w));
+    if (st.l > 0.f) store_row<D>(st, m, l, O, i - row_begin, lane);
+  }
 }
 
 // ---- COO row pointers --------------------------------------------------------------------------
