@@ -207,30 +207,98 @@ __device__ __forceinline__ void nan_fill_row(float* __restrict__ O, int64_t r, i
   }
 }
 
-// One warp per row of the shard. Q/m/l/O are indexed by shard-local row; the generator sees the
-// absolute row (row_begin + r).
+// One warp per row of the shard, four rows per CTA. Q/m/l/O are indexed by shard-local row; the generator
+// sees the absolute row (row_begin + r).
+//
+// Long rows: a single warp walking thousands of scattered keys is latency bound (one DRAM round trip per
+// step of eight keys), so the longest row of a power-law graph would set the duration of the whole launch.
+// A row with more than kHeavyRowSlots slots is therefore postponed; once the CTA's ordinary rows are done,
+// all warps of the CTA take an equal share of its slots and their partial states are merged through shared
+// memory. No scratch memory and no extra launch are involved.
+constexpr int kRowWarps = 4;
+constexpr int kHeavyRowSlots = 1024;
+
 template <int D, class Cols>
-__global__ void __launch_bounds__(kGatherWarps * 32)
+__global__ void __launch_bounds__(kRowWarps * 32, 7)
 gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                    float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
                    const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale) {
   constexpr int LPK = D / 4;
+  __shared__ int s_heavy[kRowWarps];
+  __shared__ int s_n_heavy;
+  __shared__ float s_ml[kRowWarps][2];
+  __shared__ float4 s_acc[kRowWarps][LPK];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t r = (int64_t)blockIdx.x * kGatherWarps + warp;
-  if (r >= n_rows) return;
-  const typename Cols::Row row = cols.open(r, row_begin + r);
-  if (row.n <= 0) {
-    if (Cols::kNanFillEmpty && use_nan) nan_fill_row<D>(O, r, lane);
-    return;
+  if (threadIdx.x == 0) s_n_heavy = 0;
+  __syncthreads();
+  const int64_t r = (int64_t)blockIdx.x * kRowWarps + warp;
+  if (r < n_rows) {
+    const typename Cols::Row row = cols.open(r, row_begin + r);
+    if (row.n <= 0) {
+      if (Cols::kNanFillEmpty && use_nan) nan_fill_row<D>(O, r, lane);
+    } else if (row.n > kHeavyRowSlots) {
+      if (lane == 0) s_heavy[atomicAdd(&s_n_heavy, 1)] = warp;
+    } else {
+      const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
+      RowAcc<D> st;
+      st.m = neg_inf();
+      st.l = 0.f;
+      st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      accumulate_slots<D, Cols>(cols, row, 0, row.n, q, K, V, scale, lane, st);
+      merge_groups<D>(st);
+      if (st.l > 0.f) store_row<D>(st, m, l, O, r, lane);
+    }
   }
-  const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
-  RowAcc<D> st;
-  st.m = neg_inf();
-  st.l = 0.f;
-  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  accumulate_slots<D, Cols>(cols, row, 0, row.n, q, K, V, scale, lane, st);
-  merge_groups<D>(st);
-  if (st.l > 0.f) store_row<D>(st, m, l, O, r, lane);
+  __syncthreads();
+  const int n_heavy = s_n_heavy;  // uniform over the CTA
+  for (int h = 0; h < n_heavy; ++h) {
+    const int64_t rh = (int64_t)blockIdx.x * kRowWarps + s_heavy[h];
+    const typename Cols::Row row = cols.open(rh, row_begin + rh);
+    int64_t per = (row.n + kRowWarps - 1) / kRowWarps;
+    per = (per + 31) / 32 * 32;  // whole 32-slot batches per warp
+    const int64_t t0 = (int64_t)warp * per;
+    int64_t t1 = t0 + per;
+    if (t1 > row.n) t1 = row.n;
+    RowAcc<D> st;
+    st.m = neg_inf();
+    st.l = 0.f;
+    st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t0 < t1) {
+      const float4 q = ldg4(Q + (size_t)rh * D + (lane % LPK) * 4);
+      accumulate_slots<D, Cols>(cols, row, t0, t1, q, K, V, scale, lane, st);
+      merge_groups<D>(st);
+    }
+    if (lane < LPK) s_acc[warp][lane] = st.acc;
+    if (lane == 0) {
+      s_ml[warp][0] = st.m;
+      s_ml[warp][1] = st.l;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      RowAcc<D> tot;
+      tot.m = neg_inf();
+      tot.l = 0.f;
+      tot.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int sub = lane % LPK;
+#pragma unroll
+      for (int wv = 0; wv < kRowWarps; ++wv) {  // in slot order, like the single-warp walk
+        const float mo = s_ml[wv][0], lo = s_ml[wv][1];
+        const float4 ao = s_acc[wv][sub];
+        const float mn = fmaxf(tot.m, mo);
+        const float ms = (mn == neg_inf()) ? 0.f : mn;
+        const float c1 = fast_exp2((tot.m - ms) * kLog2e);
+        const float c2 = fast_exp2((mo - ms) * kLog2e);
+        tot.l = tot.l * c1 + lo * c2;
+        tot.acc.x = tot.acc.x * c1 + ao.x * c2;
+        tot.acc.y = tot.acc.y * c1 + ao.y * c2;
+        tot.acc.z = tot.acc.z * c1 + ao.z * c2;
+        tot.acc.w = tot.acc.w * c1 + ao.w * c2;
+        tot.m = mn;
+      }
+      if (tot.l > 0.f) store_row<D>(tot, m, l, O, rh, lane);
+    }
+    __syncthreads();
+  }
 }
 
 // Split-row variant for very long rows: entry e of row_list is processed by n_split warps, each

@@ -27,10 +27,10 @@ template <int D, class Cols>
 int launch_gather(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
                   const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
   if (n_rows <= 0) return SPFA_OK;
-  const int64_t blocks = (n_rows + kGatherWarps - 1) / kGatherWarps;
+  const int64_t blocks = (n_rows + kRowWarps - 1) / kRowWarps;
   if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
   const float scale = 1.0f / sqrtf((float)D);
-  gather_rows_kernel<D, Cols><<<(unsigned)blocks, kGatherWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, row_begin,
+  gather_rows_kernel<D, Cols><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, row_begin,
                                                                              n_rows, use_nan, scale);
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_GATHER);

@@ -275,7 +275,7 @@ def test_row_shards_and_incoming_state(capi, orc, path, kind, L, d, p0, p1):
 
 
 @pytest.mark.parametrize("L,Lk,d,density", [(512, 512, 64, 0.02), (300, 700, 32, 0.1), (257, 129, 128, 0.5),
-                                             (64, 64, 16, 1.0), (2000, 2000, 64, 0.004)])
+                                             (64, 64, 16, 1.0), (2000, 2000, 64, 0.004), (150, 6000, 64, 0.4), (90, 5000, 128, 0.6)])
 def test_csr_and_coo_vs_oracle(capi, orc, L, Lk, d, density):
     Q, K, V = seeded_qkv(L, d, 5 + L, Lk)
     empty = (0, L // 2, L - 1) if density < 1.0 else ()
@@ -453,3 +453,22 @@ def test_auto_routes_wide_bands_to_the_tensor_core_path(capi):
     capi.local_forward(Q, K, V, *st, 200)
     assert capi.last_path() == capi.PATH_GATHER
     capi.set_path(capi.PATH_AUTO)
+
+
+def test_mixed_light_and_very_long_rows(capi, orc):
+    """A power-law-like mask: most rows short, a few with thousands of keys (those are walked by all warps of
+    their CTA together); several long rows share a CTA, one is the last row."""
+    L, Lk, d = 333, 9000, 64
+    Q, K, V = seeded_qkv(L, d, 91, Lk)
+    rng = np.random.default_rng(5)
+    mask = rng.random((L, Lk)) < 0.002
+    for r, n in ((0, 8321), (1, 1025), (7, 3000), (100, 1024), (101, 5000), (332, 2048)):
+        mask[r] = False
+        mask[r, rng.permutation(Lk)[:n]] = True
+    mask[200] = False  # an empty row
+    row_off = np.concatenate([[0], np.cumsum(mask.sum(1))]).astype(np.int64)
+    col = np.nonzero(mask)[1].astype(np.int32)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st, use_nan=True)
+    assert_state_close(to_np(st), want, TOL_GATHER, "long rows")
