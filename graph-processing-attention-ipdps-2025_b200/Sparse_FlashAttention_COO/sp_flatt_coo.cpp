@@ -14,7 +14,7 @@ torch::Tensor spfa_coo_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
               "W_row_ind and W_col_ind must be 1-D with one entry per mask non-zero");
   c10::cuda::CUDAGuard guard(Q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
-  Workspace ws(spfa_coo_workspace_bytes(Q.size(0), (int)Q.size(1)), Q.device());
+  Workspace ws(spfa_coo_workspace_bytes(Q.size(0), W_row_ind.size(0), K.size(0), (int)Q.size(1)), Q.device());
   raise_for_status(spfa_coo_forward_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
                                         u64_ptr(W_row_ind, "W_row_ind"), u32_ptr(W_col_ind, "W_col_ind"),
                                         W_row_ind.size(0), m.data_ptr<float>(), l.data_ptr<float>(),

@@ -27,7 +27,7 @@ MASK_KIND = {"local": 0, "local_1d_dilated": 1, "local_2d_dilated": 2, "global_n
 EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
-    "spfa_coo_workspace_bytes", "spfa_coo_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
+    "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -64,11 +64,13 @@ def lib() -> ctypes.CDLL:
     L.spfa_launch_count.restype = i64
     L.spfa_last_device_error.restype = i32
     L.spfa_csr_workspace_bytes.restype = sz
-    L.spfa_csr_workspace_bytes.argtypes = [i64, i32]
+    L.spfa_csr_workspace_bytes.argtypes = [i64, i64, i64, i32]
     L.spfa_csr_forward_f32.restype = i32
-    L.spfa_csr_forward_f32.argtypes = [vp] * 8 + [i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_csr_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i32, i32, vp, sz, vp]
     L.spfa_coo_workspace_bytes.restype = sz
-    L.spfa_coo_workspace_bytes.argtypes = [i64, i32]
+    L.spfa_coo_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    L.spfa_coo_min_workspace_bytes.restype = sz
+    L.spfa_coo_min_workspace_bytes.argtypes = [i64]
     L.spfa_coo_forward_f32.restype = i32
     L.spfa_coo_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
     L.spfa_coo_static_max_rows.restype = i64
@@ -171,11 +173,28 @@ def csr_forward(Q, K, V, row_off, col_ind, m, l, O, use_nan=False):
     dev = _f32(Q, K, V, m, l, O)
     with torch.cuda.device(dev):
         n_rows, d = Q.shape
-        buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, d), dev)
+        nnz = col_ind.shape[0]
+        buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, nnz, K.shape[0], d), dev)
+        global _last_csr_workspace
+        _last_csr_workspace = (buf, wp.value if wp else 0, d)
         check(lib().spfa_csr_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)),
-                                         _ptr(m), _ptr(l), _ptr(O), n_rows, K.shape[0], d, int(use_nan), wp, wb,
-                                         _stream(dev)))
+                                         nnz, _ptr(m), _ptr(l), _ptr(O), n_rows, K.shape[0], d, int(use_nan), wp,
+                                         wb, _stream(dev)))
     return O
+
+
+_last_csr_workspace = None
+
+
+def last_csr_dense_tiles() -> int:
+    """Diagnostics: how many (row block, key tile) pairs the most recent csr_forward call of this process ran on
+    the tiled kernel (0 if it took the gather path). Synchronises."""
+    if not _last_csr_workspace or _last_csr_workspace[0] is None or last_path() != PATH_TILED:
+        return 0
+    buf, p, d = _last_csr_workspace
+    off = p - buf.data_ptr()
+    words = int(buf[off:off + 8].view(torch.int64).item())  # the plan's mask pool counter sits first
+    return words // ((2 if d == 128 else 3) * 128)
 
 
 def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):
@@ -184,7 +203,7 @@ def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):
     dev = _f32(Q, K, V, m, l, O)
     with torch.cuda.device(dev):
         n_rows, d = Q.shape
-        buf, wp, wb = workspace(lib().spfa_coo_workspace_bytes(n_rows, d), dev)
+        buf, wp, wb = workspace(lib().spfa_coo_workspace_bytes(n_rows, row_ind.shape[0], K.shape[0], d), dev)
         check(lib().spfa_coo_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)),
                                          row_ind.shape[0], _ptr(m), _ptr(l), _ptr(O), row_begin, n_rows, K.shape[0],
                                          d, int(use_nan), wp, wb, _stream(dev)))

@@ -1,0 +1,275 @@
+// Explicit masks (CSR, and COO after its row-pointer pass) as a hybrid of the two paths.
+//
+// The query rows are cut into 128-row blocks and the keys into tiles of BN consecutive rows. A (block, tile)
+// pair that holds many mask entries is a small dense problem: it goes to the tiled tensor-core kernel with a
+// bit mask of its valid (row, key) pairs. Every other entry stays on the FP32 gather path. Both passes merge
+// into the caller's (m, l, O) state, so their order does not matter and the result is the union.
+//
+// explicit_plan_kernel does the split, one CTA per 128-row block:
+//   1. histogram of the block's entries over ALL key tiles (shared memory, one counter per tile)
+//   2. the tiles with at least `min_entries` entries, ascending, at most kMaxDenseTiles, become "dense"
+//   3. bit masks of the dense tiles are built in shared memory; a tile in which some (row, key) pair occurs
+//      twice is demoted (a bit cannot say "twice", and the reference counts such a key twice)
+//   4. space for the masks is taken from a pool in the workspace (one atomicAdd per block); a block that does
+//      not get space keeps all its entries on the gather path
+//   5. the block's remaining entries are written, in storage order, to a residual column list that keeps the
+//      original row offsets (row r: res_col[row_off[r] .. row_off[r] + res_cnt[r])); columns >= Lk are dropped
+//      (the ABI skips them); rows without any entry are NaN-filled here when use_nan is set
+// Steps 3 and 5 share one walk over the block's entries; the walk of step 5 is repeated only for a block that
+// had a tile demoted in step 3 or 4. The passes are latency bound, hence 1024 threads and several independent
+// column loads per thread.
+// Runs of equal keys inside a warp are combined before they touch a shared-memory counter or mask word:
+// the entries of a row are normally sorted, so whole warps would otherwise hit one address.
+#pragma once
+#include "spfa_common.cuh"
+#include "tile_kernels_sm100.cuh"
+
+namespace spfa {
+
+constexpr int kPlanThreads = 1024;
+constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread (the passes are latency bound)
+constexpr int kPlanWarps = kPlanThreads / 32;
+constexpr int kPlanMaxSmem = 200 * 1024;
+
+struct ExplicitPlan {
+  // per 128-row block
+  int* rb_nt;                       // [n_blocks] dense tiles
+  int* rb_kt;                       // [n_blocks][kMaxDenseTiles] key-tile numbers, ascending
+  long long* rb_moff;               // [n_blocks] first mask word of the block
+  // mask pool
+  uint32_t* masks;                  // [cap_words]; tile t of a block: (t*(BN/32) + chunk)*128 + row
+  unsigned long long* pool_used;    // words handed out so far (zeroed before the kernel)
+  long long cap_words;
+  // residual entries for the gather path
+  uint32_t* res_cnt;                // [n_rows]
+  uint32_t* res_col;                // [nnz], row r at res_col + row_off[r]
+};
+
+// Residual rows of the hybrid (see above): same offsets as the caller's CSR, fewer entries, all < Lk.
+struct ResidualCols {
+  const uint64_t* row_off;
+  const uint32_t* cnt;
+  const uint32_t* col;
+  static constexpr bool kNanFillEmpty = false;  // the plan kernel has filled the rows that are really empty
+  struct Row { int64_t lo; int64_t n; };
+  __device__ __forceinline__ Row open(int64_t r_local, int64_t) const {
+    Row r;
+    r.lo = (int64_t)row_off[r_local];
+    r.n = (int64_t)cnt[r_local];
+    return r;
+  }
+  __device__ __forceinline__ int32_t slot(const Row& r, int64_t t) const { return (int32_t)__ldg(col + r.lo + t); }
+};
+
+inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
+  return (size_t)n_key_tiles * 4 + (size_t)tile::kMaxDenseTiles * (bn / 32) * 128 * 4;
+}
+
+// Runs of equal keys over the lanes of a warp. Returns the lane one past the end of the run this lane is in;
+// *lead says whether this lane starts its run (its length is then the return value minus the lane).
+// Inactive lanes pass a key no active lane has.
+__device__ __forceinline__ int run_end_of(uint32_t key, int lane, bool* lead) {
+  const uint32_t prev = __shfl_up_sync(kFullMask, key, 1);
+  *lead = (lane == 0) || (prev != key);
+  const uint32_t leaders = __ballot_sync(kFullMask, *lead);
+  const uint32_t later = (lane == 31) ? 0u : (leaders >> (lane + 1));
+  return later ? (lane + __ffs(later)) : 32;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kPlanThreads, 2)
+explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __restrict__ col, int64_t n_rows, int64_t Lk,
+                     int n_key_tiles, int min_entries, ExplicitPlan plan, int use_nan, float* __restrict__ O, int d) {
+  constexpr int NC = BN / 32;
+  constexpr int MAXT = tile::kMaxDenseTiles;
+  constexpr uint32_t kNoKey = 0xffffffffu;
+  extern __shared__ uint32_t plan_smem[];
+  uint32_t* hist = plan_smem;                    // [n_key_tiles]: entry count, later slot + 1 of dense tiles
+  uint32_t* masks = plan_smem + n_key_tiles;     // [MAXT][NC][128]
+  __shared__ int s_warp_cnt[kPlanWarps];
+  __shared__ int s_sel[MAXT];                    // key tile of slot t
+  __shared__ int s_dirty[MAXT];
+  __shared__ int s_map[MAXT];                    // slot -> position among the clean slots, or -1
+  __shared__ int s_nt, s_nclean, s_redo;
+  __shared__ long long s_moff;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t b = blockIdx.x;
+  const int64_t r0 = b * 128;
+  const int nr = (int)((n_rows - r0 < 128) ? (n_rows - r0) : 128);
+  const int64_t e0 = (int64_t)row_off[r0], e1 = (int64_t)row_off[r0 + nr];
+
+  // ---- 1. histogram over key tiles ----
+  for (int k = tid; k < n_key_tiles; k += kPlanThreads) hist[k] = 0;
+  if (tid < MAXT) s_dirty[tid] = 0;
+  __syncthreads();
+  for (int64_t base = e0; base < e1; base += kPlanThreads * kPlanUnroll) {  // every warp runs whole iterations
+    uint32_t cu[kPlanUnroll];
+#pragma unroll
+    for (int u = 0; u < kPlanUnroll; ++u) {
+      const int64_t e = base + u * kPlanThreads + tid;
+      cu[u] = (e < e1) ? __ldg(col + e) : kNoKey;
+    }
+#pragma unroll
+    for (int u = 0; u < kPlanUnroll; ++u) {
+      const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
+      bool lead;
+      const int end = run_end_of(kt, lane, &lead);
+      if (lead && kt != kNoKey) atomicAdd(&hist[kt], (uint32_t)(end - lane));
+    }
+  }
+  __syncthreads();
+
+  // ---- 2. dense tiles, ascending: each thread scans a contiguous range of tiles ----
+  const int per = (n_key_tiles + kPlanThreads - 1) / kPlanThreads;
+  const int k_lo = tid * per, k_hi = (k_lo + per < n_key_tiles) ? (k_lo + per) : n_key_tiles;
+  int mine = 0;
+  for (int k = k_lo; k < k_hi; ++k) mine += (hist[k] >= (uint32_t)min_entries);
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(kFullMask, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) s_warp_cnt[warp] = incl;
+  __syncthreads();
+  int before = incl - mine;
+  for (int wv = 0; wv < warp; ++wv) before += s_warp_cnt[wv];
+  if (tid == kPlanThreads - 1) s_nt = (before + mine < MAXT) ? (before + mine) : MAXT;
+  for (int k = k_lo; k < k_hi; ++k) {
+    const bool dense = hist[k] >= (uint32_t)min_entries;
+    uint32_t slot1 = 0;
+    if (dense) {
+      if (before < MAXT) {
+        s_sel[before] = k;
+        slot1 = (uint32_t)before + 1;
+      }
+      ++before;
+    }
+    hist[k] = slot1;
+  }
+  __syncthreads();
+  const int nt = s_nt;
+
+  // ---- 3. bit masks of the dense tiles; duplicates demote a tile ----
+  for (int i = tid; i < nt * NC * 128; i += kPlanThreads) masks[i] = 0;
+  __syncthreads();
+  // The same walk writes the entries outside the dense tiles to the residual list (step 5); if a tile is
+  // demoted afterwards (rare), the residual rows of the block are simply written again.
+  {
+    for (int rl = warp; rl < nr; rl += kPlanWarps) {
+      const int64_t a = (int64_t)row_off[r0 + rl], z = (int64_t)row_off[r0 + rl + 1];
+      uint32_t kept = 0;
+      for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
+        uint32_t cu[kPlanUnroll];
+#pragma unroll
+        for (int u = 0; u < kPlanUnroll; ++u) {
+          const int64_t e = base + u * 32 + lane;
+          cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+        }
+#pragma unroll
+        for (int u = 0; u < kPlanUnroll; ++u) {
+          if (base + u * 32 >= z) break;  // warp-uniform
+          const uint32_t c = cu[u];
+          uint32_t word = kNoKey, bit = 0;
+          bool keep = false;
+          if ((int64_t)c < Lk) {
+            const uint32_t kt = c / BN, slot1 = hist[kt];
+            if (slot1) {
+              const uint32_t kk = c - kt * BN;
+              word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl;
+              bit = 1u << (kk & 31);
+            } else {
+              keep = true;
+            }
+          }
+          const uint32_t bal = __ballot_sync(kFullMask, keep);
+          if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
+          kept += __popc(bal);
+          if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
+          // OR of the bits of each run of equal words, at the run's first lane (suffix scan by doubling)
+          bool lead;
+          const int end = run_end_of(word, lane, &lead);
+          uint32_t acc = bit;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_down_sync(kFullMask, acc, o);
+            if (lane + o < end) acc |= t;
+          }
+          if (lead && word != kNoKey) {
+            const uint32_t old = atomicOr(&masks[word], acc);
+            if ((old & acc) != 0u || __popc(acc) != end - lane) s_dirty[word / (NC * 128)] = 1;
+          }
+        }
+      }
+      if (lane == 0) plan.res_cnt[r0 + rl] = kept;
+      if (z <= a && use_nan) {  // a row without any entry
+        const float nn = __int_as_float(0x7fc00000);
+        for (int i = lane * 4; i < d; i += 128)
+          *reinterpret_cast<float4*>(O + (size_t)(r0 + rl) * d + i) = make_float4(nn, nn, nn, nn);
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- 4. drop the demoted tiles, take mask space from the pool, publish the block's tile list ----
+  if (tid == 0) {
+    int nc = 0;
+    for (int t = 0; t < nt; ++t) s_map[t] = s_dirty[t] ? -1 : nc++;
+    long long off = 0;
+    if (nc > 0) {
+      const long long need = (long long)nc * NC * 128;
+      off = (long long)atomicAdd(plan.pool_used, (unsigned long long)need);
+      if (off + need > plan.cap_words) {  // pool exhausted: this block stays on the gather path
+        for (int t = 0; t < nt; ++t) s_map[t] = -1;
+        nc = 0;
+        off = 0;
+      }
+    }
+    s_nclean = nc;
+    s_redo = (nc != nt);
+    s_moff = off;
+    plan.rb_nt[b] = nc;
+    plan.rb_moff[b] = off;
+  }
+  __syncthreads();
+  const int nclean = s_nclean;
+  if (tid < nt) {
+    const int to = s_map[tid];
+    if (to >= 0) plan.rb_kt[b * MAXT + to] = s_sel[tid];
+    else hist[s_sel[tid]] = 0;  // its entries go to the residual list
+  }
+  if (nclean > 0) {
+    uint32_t* dst = plan.masks + s_moff;
+    for (int i = tid; i < nt * NC * 128; i += kPlanThreads) {
+      const int to = s_map[i / (NC * 128)];
+      if (to >= 0) dst[(size_t)to * NC * 128 + i % (NC * 128)] = masks[i];
+    }
+  }
+  __syncthreads();
+
+  // ---- 5 again, only if a tile was demoted: its entries belong to the residual rows after all ----
+  if (!s_redo) return;
+  for (int rl = warp; rl < nr; rl += kPlanWarps) {
+    const int64_t a = (int64_t)row_off[r0 + rl], z = (int64_t)row_off[r0 + rl + 1];
+    uint32_t kept = 0;
+    for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
+      uint32_t cu[kPlanUnroll];
+#pragma unroll
+      for (int u = 0; u < kPlanUnroll; ++u) {
+        const int64_t e = base + u * 32 + lane;
+        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+      }
+#pragma unroll
+      for (int u = 0; u < kPlanUnroll; ++u) {
+        const uint32_t c = cu[u];
+        const bool keep = ((int64_t)c < Lk) && hist[c / BN] == 0;
+        const uint32_t bal = __ballot_sync(kFullMask, keep);
+        if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
+        kept += __popc(bal);
+      }
+    }
+    if (lane == 0) plan.res_cnt[r0 + rl] = kept;
+  }
+}
+
+}  // namespace spfa

@@ -6,6 +6,7 @@
 #include <cmath>
 
 #include "block_kernels.cuh"
+#include "explicit_plan.cuh"
 #include "gather_kernels.cuh"
 #include "tile_dispatch.cuh"
 
@@ -166,6 +167,116 @@ inline int with_mask_cols(int kind, int64_t L, int64_t p0, int64_t p1, const int
   return SPFA_ERR_BAD_ARG;
 }
 
+// ---- explicit masks: dense (row block, key tile) pairs on the tiled kernel, the rest on the gather kernel ----
+constexpr int64_t kHybridMinNnz = 1 << 20;  // AUTO: smaller masks are launch bound either way and stay exact FP32
+constexpr int kDenseDivisor = 24;           // a tile is dense from 128*BN/24 entries on (~4 % filled)
+
+struct HybridLayout {
+  int bn, n_key_tiles, min_entries;
+  int64_t n_blocks;
+  long long cap_words;
+  size_t smem;
+  size_t off_pool, off_nt, off_kt, off_moff, off_cnt, off_res, off_masks, total;
+};
+
+inline bool hybrid_shape_ok(int d, int64_t n_rows, int64_t nnz, int64_t Lk) {
+  if (!(d == 32 || d == 64 || d == 128) || n_rows <= 0 || nnz <= 0 || Lk <= 0) return false;
+  const int bn = (d == 128) ? 64 : 96;
+  return explicit_plan_smem_bytes((Lk + bn - 1) / bn, bn) <= (size_t)kPlanMaxSmem;
+}
+
+inline HybridLayout hybrid_layout(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
+  HybridLayout h;
+  h.bn = (d == 128) ? 64 : 96;
+  h.n_key_tiles = (int)((Lk + h.bn - 1) / h.bn);
+  h.min_entries = 128 * h.bn / kDenseDivisor;
+  h.n_blocks = (n_rows + 127) / 128;
+  h.smem = explicit_plan_smem_bytes(h.n_key_tiles, h.bn);
+  int64_t cap_tiles = nnz / h.min_entries + 1;  // a dense tile holds at least min_entries entries
+  if (cap_tiles > h.n_blocks * tile::kMaxDenseTiles) cap_tiles = h.n_blocks * tile::kMaxDenseTiles;
+  h.cap_words = (long long)cap_tiles * (h.bn / 32) * 128;
+  h.off_pool = 0;
+  h.off_nt = 256;
+  h.off_kt = h.off_nt + align_up((size_t)h.n_blocks * 4);
+  h.off_moff = h.off_kt + align_up((size_t)h.n_blocks * tile::kMaxDenseTiles * 4);
+  h.off_cnt = h.off_moff + align_up((size_t)h.n_blocks * 8);
+  h.off_res = h.off_cnt + align_up((size_t)n_rows * 4);
+  h.off_masks = h.off_res + align_up((size_t)nnz * 4);
+  h.total = h.off_masks + align_up((size_t)h.cap_words * 4);
+  return h;
+}
+
+// Does this call take the dense-tile split? 1 = yes, 0 = gather path, negative = status to return.
+inline int hybrid_decision(int d, int64_t n_rows, int64_t nnz, int64_t Lk, const void* ws, size_t ws_bytes) {
+  const int path = g_path.load();
+  if (path == SPFA_PATH_GATHER) return 0;
+  const bool shape = hybrid_shape_ok(d, n_rows, nnz, Lk);
+  if (path == SPFA_PATH_TILED && !shape) return SPFA_ERR_BAD_ARG;
+  if (!shape || (path == SPFA_PATH_AUTO && nnz < kHybridMinNnz)) return 0;
+  if (check_workspace(ws, ws_bytes, hybrid_layout(n_rows, nnz, Lk, d).total) != SPFA_OK)
+    return path == SPFA_PATH_TILED ? (int)SPFA_ERR_WORKSPACE : 0;
+  return 1;
+}
+
+template <int D, int BN, int NS>
+int launch_hybrid(const float* Q, const float* K, const float* V, const uint64_t* row_off, const uint32_t* col,
+                  float* m, float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, int use_nan, char* ws,
+                  cudaStream_t st) {
+  const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
+  ExplicitPlan plan;
+  plan.pool_used = reinterpret_cast<unsigned long long*>(ws + h.off_pool);
+  plan.rb_nt = reinterpret_cast<int*>(ws + h.off_nt);
+  plan.rb_kt = reinterpret_cast<int*>(ws + h.off_kt);
+  plan.rb_moff = reinterpret_cast<long long*>(ws + h.off_moff);
+  plan.res_cnt = reinterpret_cast<uint32_t*>(ws + h.off_cnt);
+  plan.res_col = reinterpret_cast<uint32_t*>(ws + h.off_res);
+  plan.masks = reinterpret_cast<uint32_t*>(ws + h.off_masks);
+  plan.cap_words = h.cap_words;
+  if (cudaMemsetAsync(plan.pool_used, 0, 8, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  auto plan_kern = explicit_plan_kernel<BN>;
+  if (cudaFuncSetAttribute(plan_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h.smem) != cudaSuccess)
+    return SPFA_ERR_LAUNCH;
+  plan_kern<<<(unsigned)h.n_blocks, kPlanThreads, h.smem, st>>>(row_off, col, n_rows, Lk, h.n_key_tiles, h.min_entries,
+                                                                plan, use_nan, O, D);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  // dense tiles
+  tile::BandParams prm{};
+  prm.mode = 3;
+  prm.n_keys = Lk;
+  prm.u_q_first = 0;
+  prm.n_q = n_rows;
+  prm.s = 1;
+  prm.scale_log2e = (1.0f / sqrtf((float)D)) * kLog2e;
+  prm.x_nt = plan.rb_nt;
+  prm.x_kt = plan.rb_kt;
+  prm.x_moff = plan.rb_moff;
+  prm.x_masks = plan.masks;
+  CUtensorMap tmQ, tmK, tmV;
+  const int64_t pitch = D * (int64_t)sizeof(float);
+  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, Lk, pitch, BN) ||
+      !make_row_map(&tmV, V, D, Lk, pitch, BN, /*mn_major=*/true))
+    return SPFA_ERR_LAUNCH;
+  int rc = launch_band_raw<D, BN, NS, 2, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + 255) / 256)), st);
+  if (rc) return rc;
+  // everything else
+  ResidualCols cols{row_off, plan.res_cnt, plan.res_col};
+  rc = launch_gather<D, ResidualCols>(Q, K, V, m, l, O, cols, 0, n_rows, 0, st);
+  g_last_path.store(SPFA_PATH_TILED);
+  return rc;
+}
+
+inline int hybrid_forward(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off,
+                          const uint32_t* col, float* m, float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk,
+                          int use_nan, char* ws, cudaStream_t st) {
+  switch (d) {
+    case 32: return launch_hybrid<32, 96, 2>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
+    case 64: return launch_hybrid<64, 96, 2>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
+    case 128: return launch_hybrid<128, 64, 1>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
+}
+
 // ---- scratch for the allocation-free COO entry point ---------------------------------------------------
 // Row pointers for up to kStaticCooMaxRows query rows, resident in every GPU context that loads this
 // library (2 MiB + 8 B) until the process exits. In host code the array's name is only a handle: the
@@ -213,7 +324,7 @@ const char* spfa_status_string(int s) {
   return "unknown status";
 }
 
-int spfa_abi_version(void) { return 1000; }
+int spfa_abi_version(void) { return 1100; }
 
 void spfa_set_path(int path) {
   if (path == SPFA_PATH_AUTO || path == SPFA_PATH_GATHER || path == SPFA_PATH_TILED) g_path.store(path);
@@ -233,23 +344,37 @@ int spfa_debug_cta_times(unsigned long long* host, int n) {
 #endif
 
 // ---- CSR -----------------------------------------------------------------------------------------
-size_t spfa_csr_workspace_bytes(int64_t, int) { return 0; }
+size_t spfa_csr_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
+  const int path = g_path.load();
+  if (path == SPFA_PATH_GATHER || !hybrid_shape_ok(d, n_rows, nnz, Lk)) return 0;
+  if (path == SPFA_PATH_AUTO && nnz < kHybridMinNnz) return 0;
+  return hybrid_layout(n_rows, nnz, Lk, d).total;
+}
 
 int spfa_csr_forward_f32(const float* Q, const float* K, const float* V, const uint64_t* row_off,
-                         const uint32_t* col_ind, float* m, float* l, float* O, int64_t n_rows, int64_t Lk, int d,
-                         int use_nan, void*, size_t, void* stream) {
+                         const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t n_rows,
+                         int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes, void* stream) {
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
-  if (!row_off || n_rows < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (!row_off || n_rows < 0 || nnz < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
   if (n_rows == 0) return SPFA_OK;
   if (!col_ind) return SPFA_ERR_BAD_ARG;
+  const int hy = hybrid_decision(d, n_rows, nnz, Lk, workspace, workspace_bytes);
+  if (hy < 0) return hy;
+  if (hy == 1)
+    return hybrid_forward(d, Q, K, V, row_off, col_ind, m, l, O, n_rows, nnz, Lk, use_nan,
+                          static_cast<char*>(workspace), (cudaStream_t)stream);
   CsrCols cols{row_off, col_ind, Lk};
   return dispatch_gather(d, Q, K, V, m, l, O, cols, 0, n_rows, use_nan, (cudaStream_t)stream);
 }
 
 // ---- COO -----------------------------------------------------------------------------------------
-size_t spfa_coo_workspace_bytes(int64_t n_rows, int) {
+size_t spfa_coo_min_workspace_bytes(int64_t n_rows) {
   return n_rows < 0 ? 0 : align_up((size_t)(n_rows + 1) * sizeof(uint64_t));
+}
+
+size_t spfa_coo_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
+  return spfa_coo_min_workspace_bytes(n_rows) + spfa_csr_workspace_bytes(n_rows, nnz, Lk, d);
 }
 
 int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const uint64_t* row_ind,
@@ -261,8 +386,12 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const u
   if (nnz < 0 || n_rows < 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
   if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
   if (n_rows == 0) return SPFA_OK;
-  rc = check_workspace(workspace, workspace_bytes, spfa_coo_workspace_bytes(n_rows, d));
+  const size_t ptr_bytes = spfa_coo_min_workspace_bytes(n_rows);
+  rc = check_workspace(workspace, workspace_bytes, ptr_bytes);
   if (rc) return rc;
+  char* rest = static_cast<char*>(workspace) + ptr_bytes;
+  const int hy = hybrid_decision(d, n_rows, nnz, Lk, rest, workspace_bytes - ptr_bytes);
+  if (hy < 0) return hy;
   cudaStream_t st = (cudaStream_t)stream;
   uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
   int64_t blocks = (nnz + 1 + 255) / 256;
@@ -270,6 +399,7 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const u
   coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  if (hy == 1) return hybrid_forward(d, Q, K, V, ptr, col_ind, m, l, O, n_rows, nnz, Lk, use_nan, rest, st);
   CsrCols cols{ptr, col_ind, Lk};
   return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
 }

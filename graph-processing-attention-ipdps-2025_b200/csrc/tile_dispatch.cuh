@@ -60,12 +60,12 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
 }
 
 // Common launch steps of band_forward_kernel: shared-memory opt-in, register-budget guard, error word.
-template <int D, int BN, int NS, int NSUB>
+template <int D, int BN, int NS, int NSUB, bool EXPL = false>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
                     const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
   using P = tile::Plan<D, BN, NS, NSUB>;
   using G = tile::Geo<NSUB>;
-  auto kern = tile::band_forward_kernel<D, BN, NS, NSUB>;
+  auto kern = tile::band_forward_kernel<D, BN, NS, NSUB, EXPL>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
   cudaFuncAttributes attr;

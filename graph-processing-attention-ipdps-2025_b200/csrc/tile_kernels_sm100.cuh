@@ -108,7 +108,16 @@ struct BandParams {
   int64_t kv_chunk;       // mode 2: keys per CTA along blockIdx.y
   float* partials;        // mode 2: [n_keys_of_sorted][n_split][d+4]
   int n_split;            // mode 2: gridDim.y
+  // ---- explicit masks (CSR/COO dense tiles; kernel instantiated with EXPL = true) ----
+  // The query rows are cut into 128-row blocks (= sub-tiles); block b has x_nt[b] <= kMaxDenseTiles dense key
+  // tiles, numbered x_kt[b*kMaxDenseTiles + t] (ascending; tile k covers keys [k*BN, (k+1)*BN)), and for its
+  // t-th tile a bit mask of valid (row, key) pairs at x_masks[x_moff[b] + (t*(BN/32) + chunk)*128 + row].
+  const int* x_nt;
+  const int* x_kt;
+  const long long* x_moff;
+  const uint32_t* x_masks;
 };
+constexpr int kMaxDenseTiles = 32;  // per 128-row block; a CTA (two blocks) walks at most 64 key tiles
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -273,7 +282,11 @@ struct Plan {
   static constexpr int kNumBars = 1 + 4 * NS + 6 * NSUB;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
   static constexpr int kOffCoef = (kOffMisc + 16 + 15) / 16 * 16;  // epilogue: 256 floats per sub-tile
-  static constexpr int kBytes = kOffCoef + NSUB * 256 * 4;
+  // explicit masks: merged key-tile list of the CTA: kt[64] (int), act[NSUB] (u64, bit j = sub-tile uses tile j;
+  // tile j is then the popcount(act & (2^j - 1))-th tile of the sub-tile's own list), nT (int)
+  static constexpr int kOffX = kOffCoef + NSUB * 256 * 4;
+  static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB;
+  static constexpr int kBytes = kOffX + (kXNt + 4 + 15) / 16 * 16;
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
   // TMEM columns: two S buffers per sub-tile (BN each, at BN (2x + b)), then O_x (D each, at 2 BN NSUB + D x)
   static constexpr int kTmemCols = 256 * NSUB;
@@ -281,7 +294,7 @@ struct Plan {
   static_assert(kColO + NSUB * D <= kTmemCols, "S buffers and O accumulators exceed the TMEM allocation");
 };
 
-template <int D, int BN, int NS, int NSUB>
+template <int D, int BN, int NS, int NSUB, bool EXPL = false>
 __global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, float* __restrict__ m_out, float* __restrict__ l_out,
@@ -321,7 +334,10 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int64_t rows_here = (uq_end - uq0 < kQRows) ? (uq_end - uq0) : kQRows;
   int64_t kv_lo, kv_hi;
   int64_t uq_end_eff = uq_end;  // mode 2: only the real entries of the sorted list are query rows
-  if (prm.mode == 0) {
+  if (EXPL) {
+    kv_lo = 0;
+    kv_hi = prm.n_keys;
+  } else if (prm.mode == 0) {
     kv_lo = (uq0 - prm.w > 0) ? (uq0 - prm.w) : 0;
     kv_hi = uq0 + rows_here - 1 + prm.w + 1;
     if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
@@ -336,11 +352,15 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (uq_end_eff > *prm.n_valid) uq_end_eff = *prm.n_valid;
   }
   if (kv_hi < kv_lo) kv_hi = kv_lo;
-  const int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
-  // active key-tile range [j0, j1) of each sub-tile
+  int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
+  // Key tiles of each sub-tile: a contiguous range [j0, j1) of the CTA's tiles (implicit masks), or the set
+  // bits of act[x] over the CTA's merged tile list (explicit masks, read from shared memory after set-up).
   int j0[NSUB], j1[NSUB];
+  uint64_t act[NSUB];
+  const int* s_kt = reinterpret_cast<const int*>(smem + P::kOffX + P::kXKt);
 #pragma unroll
   for (int x = 0; x < NSUB; ++x) {
+    act[x] = 0;
     const int64_t ux0 = uq0 + 128 * x;
     int64_t ux_last = ux0 + 127;
     if (ux_last > uq_end_eff - 1) ux_last = uq_end_eff - 1;
@@ -376,6 +396,46 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (EXPL && threadIdx.x == 32) {
+    // Merge the ascending dense-tile lists of the CTA's sub-tiles into one ascending list of key tiles.
+    int* kt = reinterpret_cast<int*>(smem + P::kOffX + P::kXKt);
+    uint64_t* s_act = reinterpret_cast<uint64_t*>(smem + P::kOffX + P::kXAct);
+    const int64_t n_blocks = (prm.n_q + 127) / 128;
+    int n[NSUB], pos[NSUB];
+    const int* list[NSUB];
+    uint64_t a[NSUB];
+#pragma unroll
+    for (int x = 0; x < NSUB; ++x) {
+      const int64_t b = (int64_t)blockIdx.x * NSUB + x;
+      n[x] = (b < n_blocks) ? prm.x_nt[b] : 0;
+      if (n[x] > kMaxDenseTiles) n[x] = kMaxDenseTiles;
+      list[x] = prm.x_kt + b * kMaxDenseTiles;
+      pos[x] = 0;
+      a[x] = 0;
+    }
+    int nt = 0;
+    while (nt < 64) {
+      int best = 0x7fffffff;
+#pragma unroll
+      for (int x = 0; x < NSUB; ++x)
+        if (pos[x] < n[x]) {
+          const int k = list[x][pos[x]];
+          best = (k < best) ? k : best;
+        }
+      if (best == 0x7fffffff) break;
+      kt[nt] = best;
+#pragma unroll
+      for (int x = 0; x < NSUB; ++x)
+        if (pos[x] < n[x] && list[x][pos[x]] == best) {
+          a[x] |= 1ull << nt;
+          ++pos[x];
+        }
+      ++nt;
+    }
+#pragma unroll
+    for (int x = 0; x < NSUB; ++x) s_act[x] = a[x];
+    *reinterpret_cast<int*>(smem + P::kOffX + P::kXNt) = nt;
+  }
   if (warp == W_TMA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + P::kOffMisc),
                  "r"(P::kTmemCols)
@@ -386,6 +446,21 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_base_slot;
+  if (EXPL) {
+    nT = *reinterpret_cast<const int*>(smem + P::kOffX + P::kXNt);
+#pragma unroll
+    for (int x = 0; x < NSUB; ++x) act[x] = reinterpret_cast<const uint64_t*>(smem + P::kOffX + P::kXAct)[x];
+  }
+  // helpers over both representations of "sub-tile x uses key tile j"
+  auto active = [&](int x, int j) -> bool {
+    return EXPL ? (((act[x] >> j) & 1ull) != 0) : (j >= j0[x] && j < j1[x]);
+  };
+  auto it_of = [&](int x, int j) -> int {  // how many of x's tiles come before tile j
+    return EXPL ? __popcll(act[x] & ((1ull << j) - 1ull)) : (j - j0[x]);
+  };
+  auto tile_key0 = [&](int j) -> int32_t {  // first key row of the CTA's tile j
+    return EXPL ? (int32_t)(s_kt[j] * BN) : (int32_t)(kv_lo + (int64_t)j * BN);
+  };
 
   if (warp >= W_TMA) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(G::kRegsAux));
@@ -405,7 +480,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = 0; j < nT && ok; ++j) {
         const int st = j % NS;
         const uint32_t ph = (uint32_t)((j / NS) & 1);
-        const int32_t yk = (int32_t)(kv_lo + (int64_t)j * BN);
+        const int32_t yk = tile_key0(j);
         ok = mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, err, 101);
         if (!ok) break;
         mbar_expect_tx(bar(B_KFULL + st), P::kKVStageBytes);
@@ -430,11 +505,11 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bool ok = (nT > 0) && mbar_wait(bar(B_QFULL), 0, abort_flag, err, 201);
       // Descriptors are built once per operand tile; each MMA only adds a compile-time offset to the
       // 14-bit start-address field (shared memory is < 256 KB, so the field cannot carry out).
-      // S of key tile j goes to S buffer (j - j0[x]) & 1 of its sub-tile; it is issued two tiles ahead of the
+      // S of a sub-tile's it-th key tile goes to its S buffer it & 1; it is issued two tiles ahead of the
       // softmax group so that group never waits for the tensor pipe.
       auto issue_S = [&](int x, int j) {
         const int st = j % NS;
-        const int sb = x * 2 + ((j - j0[x]) & 1);
+        const int sb = x * 2 + (it_of(x, j) & 1);
         const uint64_t qd = smem_desc(sbase + P::kOffQ + x * P::kChunks * P::kQChunkBytes, 16, 1024, kLayoutSw128);
         const uint64_t kd = smem_desc(sbase + P::kOffK + st * P::kKVStageBytes, 16, 1024, kLayoutSw128);
         const uint32_t d_t = tmem + P::kColS + BN * sb;
@@ -448,18 +523,18 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       auto issue_PV = [&](int x, int j) {
         const int st = j % NS;
-        const int sb = x * 2 + ((j - j0[x]) & 1);
+        const int it = it_of(x, j);
+        const int sb = x * 2 + (it & 1);
         // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
         const uint64_t vd = smem_desc(sbase + P::kOffV + st * P::kKVStageBytes, P::kKVChunkBytes, 512, kLayoutSw128Base32);
         const uint32_t a_t = tmem + P::kColS + BN * sb;
         const uint32_t d_t = tmem + P::kColO + D * x;
-        const uint32_t first = (j > j0[x]) ? 1u : 0u;  // O accumulates in TMEM across the key tiles of a sub-tile
+        const uint32_t first = (it > 0) ? 1u : 0u;  // O accumulates in TMEM across the key tiles of a sub-tile
 #pragma unroll
         for (int kk = 0; kk < BN / 8; ++kk)
           mma_ts(d_t, a_t + kk * 8, vd + (uint64_t)((kk * 1024) >> 4), kIdescO, kk > 0 ? 1u : first);
         tc_commit(bar(B_OREADY + sb));  // tiles alternate between two barriers, like the S buffers
       };
-      auto active = [&](int x, int j) { return j >= j0[x] && j < j1[x]; };
       auto last_active = [&](int x, int j) {  // is x the last sub-tile (in issue order A, B) using tile j?
         return x == NSUB - 1 || !active(NSUB - 1, j);
       };
@@ -486,7 +561,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bool have_v = false;
         for (int x = 0; x < NSUB && ok; ++x) {
           if (!active(x, j)) continue;
-          const int it = j - j0[x];
+          const int it = it_of(x, j);
           ok = mbar_wait(bar(B_PREADY + x * 2 + (it & 1)), (uint32_t)((it >> 1) & 1), abort_flag, err, 203);
           if (!ok) break;
           if (!have_v) {
@@ -529,7 +604,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // classes below warp-uniform.
     int lo_q, hi_q;
     bool listed = false;  // mode 1: this query row is itself a global row (handled by the mode-2 launch)
-    if (prm.mode == 0) {
+    if (EXPL) {
+      lo_q = hi_q = 0;  // validity comes from the plan's bit masks
+    } else if (prm.mode == 0) {
       const int64_t n1 = prm.n_keys - 1;
       lo_q = (int)(((uq - prm.w > 0) ? (uq - prm.w) : 0) - kv_lo);
       hi_q = (int)(((uq + prm.w < n1) ? (uq + prm.w) : n1) - kv_lo);
@@ -575,10 +652,19 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float l_run = 0.f;          // row sum relative to `shift`
     bool ok = true;
     uint32_t sr[NC][32];
-    const int nx = j1[x] - j0[x];
+    const int nx = EXPL ? __popcll(act[x]) : (j1[x] - j0[x]);
     const float sc = prm.scale_log2e;
+    uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
+    const uint32_t* xm = nullptr;
+    if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
     for (int it = 0; it < nx && ok; ++it) {
-      const int j = j0[x] + it;
+      int j;
+      if (EXPL) {
+        j = __ffsll((long long)rem) - 1;
+        rem &= rem - 1;
+      } else {
+        j = j0[x] + it;
+      }
       const int k0 = j * BN;
       // Interval of this tile's columns: this row [c_lo, c_hi]; common to every row of the warp [w_lo, w_hi];
       // touched by some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
@@ -597,7 +683,11 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t m_lo = (a <= 0) ? 0xffffffffu : (a >= 32 ? 0u : (0xffffffffu << a));
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
         const uint32_t m_in = m_lo & m_hi;
-        if (prm.mode == 0) {  // valid = inside the interval
+        if (EXPL) {  // valid = the pair's bit in the plan (the tile's position in this sub-tile's own list is `it`)
+          const uint32_t vm = __ldg(xm + (size_t)(it * NC + c) * 128);
+          vmask[c] = vm;
+          cls[c] = __all_sync(kFullMask, vm == 0xffffffffu) ? 2 : (__all_sync(kFullMask, vm == 0u) ? 0 : 1);
+        } else if (prm.mode == 0) {  // valid = inside the interval
           cls[c] = (cb >= w_lo && cb + 31 <= w_hi) ? 2 : ((cb + 31 < v_lo || cb > v_hi) ? 0 : 1);
           vmask[c] = m_in;
         } else {              // valid = a real key outside the interval

@@ -54,8 +54,9 @@ const char* spfa_status_string(int status);
 /* Library/ABI version: major*1000 + minor. */
 int spfa_abi_version(void);
 
-/* Execution path selector for the implicit-mask entry points.
- *   SPFA_PATH_AUTO   library picks (tiled tensor-core path when the window is wide enough, else gather)
+/* Execution path selector.
+ *   SPFA_PATH_AUTO   library picks (tiled tensor-core path when the window is wide enough or, for explicit
+ *                    masks, when the mask is large and the workspace allows the dense-tile split; else gather)
  *   SPFA_PATH_GATHER FP32 warp-per-row gather path (max-abs error ~1e-6 vs fp64)
  *   SPFA_PATH_TILED  tcgen05 TF32 tiled path (max-abs error <= 2e-3 vs fp64); falls back to
  *                    SPFA_ERR_BAD_ARG if the shape is not supported by that path
@@ -70,11 +71,19 @@ int spfa_last_path(void);
  * Replaces spfa_csr_cuda_forward + spfa_csr_cuda_forward_kernel
  * (Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:224-288, :14-220).
  * Row r of the shard attends to K/V rows col_ind[row_off[r] .. row_off[r+1]) in storage order.
- * row_off has n_rows+1 entries that index col_ind directly. Column values >= Lk are skipped.
- * The reference's W_val argument is never read by the reference kernel and is not part of the ABI. */
-size_t spfa_csr_workspace_bytes(int64_t n_rows, int d);
+ * row_off has n_rows+1 entries that index col_ind directly; nnz is the length of col_ind (every offset is
+ * <= nnz). Column values >= Lk are skipped.
+ * The reference's W_val argument is never read by the reference kernel and is not part of the ABI.
+ *
+ * Dense-tile split (north of ~1e6 entries under SPFA_PATH_AUTO, always under SPFA_PATH_TILED, d in
+ * {32, 64, 128}): the rows are cut into 128-row blocks and the keys into tiles of 96 (d = 128: 64) rows; a
+ * (block, tile) pair holding at least 1/24 of its possible entries runs on the tcgen05 tiled kernel under a
+ * bit mask (TF32 accuracy class), all other entries on the FP32 gather kernel. It is taken only if the
+ * workspace is at least spfa_csr_workspace_bytes(); with a smaller (or no) workspace every entry takes the
+ * gather path, which needs none. */
+size_t spfa_csr_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d);
 int spfa_csr_forward_f32(const float* Q, const float* K, const float* V,
-                         const uint64_t* row_off, const uint32_t* col_ind,
+                         const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
                          float* m, float* l, float* O,
                          int64_t n_rows, int64_t Lk, int d, int use_nan,
                          void* workspace, size_t workspace_bytes, void* stream);
@@ -85,8 +94,11 @@ int spfa_csr_forward_f32(const float* Q, const float* K, const float* V,
  * row_ind (ascending, absolute row numbers) / col_ind hold nnz entries that include every entry of
  * rows [row_begin, row_begin + n_rows); entries of other rows are ignored. The per-row linear scan
  * of the reference (:47-79) is replaced by one pass that writes n_rows+1 row pointers into the
- * workspace, followed by the CSR kernel. */
-size_t spfa_coo_workspace_bytes(int64_t n_rows, int d);
+ * workspace, followed by the CSR kernels (including the dense-tile split described above).
+ * spfa_coo_workspace_bytes() is the size that allows the split when the shape qualifies; the minimum the
+ * entry point accepts is spfa_coo_min_workspace_bytes() (the row pointers only: gather path). */
+size_t spfa_coo_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d);
+size_t spfa_coo_min_workspace_bytes(int64_t n_rows);
 int spfa_coo_forward_f32(const float* Q, const float* K, const float* V,
                          const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
                          float* m, float* l, float* O,

@@ -77,8 +77,12 @@ def test_argument_validation_without_gpu(pkg):
     assert lib.spfa_global_no_local_workspace_bytes(L, L, d, 4) > 0
     c = lib.spfa_coo_forward_f32
     assert c(p, p, p, p, p, 10, p, p, p, 0, L, L, d, 0, None, 0, None) == -3
-    assert lib.spfa_coo_workspace_bytes(L, d) >= 8 * (L + 1)
-    assert lib.spfa_csr_forward_f32(p, p, p, None, p, p, p, p, L, L, d, 0, None, 0, None) == -1
+    assert lib.spfa_coo_min_workspace_bytes(L) >= 8 * (L + 1)
+    assert lib.spfa_coo_workspace_bytes(L, 1000, L, d) == lib.spfa_coo_min_workspace_bytes(L)  # small mask: gather
+    big = lib.spfa_coo_workspace_bytes(1 << 20, 1 << 27, 1 << 20, d)   # large mask: room for the dense-tile split
+    assert big >= (1 << 27) * 4 + lib.spfa_coo_min_workspace_bytes(1 << 20)
+    assert lib.spfa_csr_workspace_bytes(1 << 20, 1 << 27, 1 << 20, 16) == 0          # d = 16 has no tiled path
+    assert lib.spfa_csr_forward_f32(p, p, p, None, p, 10, p, p, p, L, L, d, 0, None, 0, None) == -1
 
 
 def test_capi_refuses_cpu_tensors(pkg):

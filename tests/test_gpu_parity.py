@@ -472,3 +472,111 @@ def test_mixed_light_and_very_long_rows(capi, orc):
     st = capi.new_state(L, d)
     capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st, use_nan=True)
     assert_state_close(to_np(st), want, TOL_GATHER, "long rows")
+
+
+# ------------------------------------------------------------------------------------------------------
+# explicit masks split into dense tiles (tensor cores) + residual entries (gather)
+# ------------------------------------------------------------------------------------------------------
+def _band_plus_random(L, Lk, half, density, seed, empty_rows=()):
+    """Band |i-j| <= half union Bernoulli(density): dense tiles near the diagonal, stray entries elsewhere."""
+    rng = np.random.default_rng(seed)
+    mask = rng.random((L, Lk)) < density
+    i = np.arange(L)[:, None]
+    j = np.arange(Lk)[None, :]
+    mask |= np.abs(i - j) <= half
+    for r in empty_rows:
+        mask[r] = False
+    return mask
+
+
+def _csr_of(mask, shuffle_seed=None):
+    row_off = np.concatenate([[0], np.cumsum(mask.sum(1))]).astype(np.int64)
+    col = np.nonzero(mask)[1].astype(np.int32)
+    if shuffle_seed is not None:  # storage order inside a row is free
+        rng = np.random.default_rng(shuffle_seed)
+        for r in range(mask.shape[0]):
+            rng.shuffle(col[row_off[r]:row_off[r + 1]])
+    return row_off, col
+
+
+@pytest.mark.parametrize("L,Lk,d,half,density", [(700, 700, 64, 40, 0.003), (1000, 1300, 32, 70, 0.002),
+                                                 (515, 900, 128, 50, 0.004), (256, 256, 64, 255, 0.0)])
+def test_explicit_dense_tiles_vs_oracle(capi, orc, L, Lk, d, half, density):
+    Q, K, V = seeded_qkv(L, d, 300 + L, Lk)
+    mask = _band_plus_random(L, Lk, half, density, 17, empty_rows=(3, L - 1))
+    row_off, col = _csr_of(mask)
+    rows = np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    capi.set_path(capi.PATH_TILED)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st, use_nan=True)
+    assert capi.last_path() == capi.PATH_TILED
+    assert capi.last_csr_dense_tiles() >= (L + 127) // 128, "every row block has at least one dense tile here"
+    assert_state_close(to_np(st), want, TOL_TILED, "csr dense tiles")
+    st = capi.new_state(L, d)
+    capi.coo_forward(dev(Q), dev(K), dev(V), dev(rows), dev(col), *st, use_nan=True)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want, TOL_TILED, "coo dense tiles")
+    # the split must not lose or double an entry: against the exact path the difference is TF32 rounding only
+    capi.set_path(capi.PATH_GATHER)
+    sg = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *sg, use_nan=True)
+    assert_state_close(to_np(st), to_np(sg), TOL_TILED, "tiles vs gather")
+    capi.set_path(capi.PATH_AUTO)
+
+
+def test_explicit_dense_tiles_unsorted_duplicates_out_of_range_and_chaining(capi, orc):
+    L, Lk, d = 600, 800, 64
+    Q, K, V = seeded_qkv(L, d, 77, Lk)
+    mask = _band_plus_random(L, Lk, 60, 0.002, 5)
+    row_off, col = _csr_of(mask, shuffle_seed=9)
+    # duplicates inside a dense tile (row 130), and columns beyond Lk (skipped by contract) in rows 10 and 400
+    extra = {130: [130, 131, 131, 140], 10: [Lk, Lk + 5], 400: [4000000]}
+    pieces, offs = [], [0]
+    for r in range(L):
+        c = list(col[row_off[r]:row_off[r + 1]]) + extra.get(r, [])
+        pieces.append(np.asarray(c, dtype=np.int64))
+        offs.append(offs[-1] + len(c))
+    col2 = np.concatenate(pieces).astype(np.uint32)
+    off2 = np.asarray(offs, dtype=np.int64)
+    # chained on a state that another mask has already filled
+    _, off_a, col_a = random_csr(L, Lk, 0.01, 21, empty_rows=(5,))
+    first = orc.csr_forward(Q, K, V, off_a, col_a)
+    want = orc.csr_forward(Q, K, V, off2, col2, state=tuple(x.copy() for x in first), use_nan=False)
+    capi.set_path(capi.PATH_TILED)
+    st = state_to_dev(first)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(off2), dev(col2.astype(np.int32)), *st, use_nan=False)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want, TOL_TILED, "unsorted / duplicates / chained")
+    capi.set_path(capi.PATH_AUTO)
+
+
+def test_explicit_many_dense_tiles_per_block(capi, orc):
+    """A wide dense mask: more dense tiles per 128-row block than the tiled kernel takes (32); the rest must
+    arrive through the gather path."""
+    L, Lk, d = 200, 6000, 64
+    Q, K, V = seeded_qkv(L, d, 12, Lk)
+    _, row_off, col = random_csr(L, Lk, 0.3, 4)
+    want = orc.csr_forward(Q, K, V, row_off, col)
+    capi.set_path(capi.PATH_TILED)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off.astype(np.int64)), dev(col.astype(np.int32)), *st)
+    assert capi.last_csr_dense_tiles() == 2 * 32, "both row blocks are capped at 32 dense tiles"
+    assert_state_close(to_np(st), want, TOL_TILED, "wide dense mask")
+    capi.set_path(capi.PATH_AUTO)
+
+
+def test_explicit_auto_takes_dense_tiles_for_large_masks(capi, orc):
+    L, d, half = 8192, 64, 66
+    Q, K, V = seeded_qkv(L, d, 8, L)
+    i = np.arange(L)
+    lo, hi = np.maximum(i - half, 0), np.minimum(i + half + 1, L)
+    row_off = np.concatenate([[0], np.cumsum(hi - lo)]).astype(np.int64)
+    col = np.concatenate([np.arange(a, b) for a, b in zip(lo, hi)]).astype(np.int32)
+    assert col.size >= 1 << 20
+    want = orc.implicit_forward("local", Q, K, V, half)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st)
+    assert capi.last_path() == capi.PATH_TILED
+    assert capi.last_csr_dense_tiles() >= 2 * (L // 128)
+    assert_state_close(to_np(st), want, TOL_TILED, "auto dense tiles")
