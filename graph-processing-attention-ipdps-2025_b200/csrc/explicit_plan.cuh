@@ -16,17 +16,20 @@
 //      original row offsets (row r: res_col[row_off[r] .. row_off[r] + res_cnt[r])); columns >= Lk are dropped
 //      (the ABI skips them); rows without any entry are NaN-filled here when use_nan is set
 // Steps 3 and 5 share one walk over the block's entries; the walk of step 5 is repeated only for a block that
-// had a tile demoted in step 3 or 4. The passes are latency bound, hence 1024 threads and several independent
-// column loads per thread.
+// had a tile demoted in step 3 or 4. The passes are latency bound: several independent column loads per
+// thread, and shared memory kept small enough for four CTAs per SM (the histogram of step 1 and the masks of
+// step 3 share one region; from step 3 on "is this key tile dense, and which slot" is answered by a bit per
+// key tile plus a per-word count).
 // Runs of equal keys inside a warp are combined before they touch a shared-memory counter or mask word:
 // the entries of a row are normally sorted, so whole warps would otherwise hit one address.
 #pragma once
+#include "gather_kernels.cuh"
 #include "spfa_common.cuh"
 #include "tile_kernels_sm100.cuh"
 
 namespace spfa {
 
-constexpr int kPlanThreads = 1024;
+constexpr int kPlanThreads = 512;
 constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread (the passes are latency bound)
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kPlanMaxSmem = 200 * 1024;
@@ -43,6 +46,9 @@ struct ExplicitPlan {
   // residual entries for the gather path
   uint32_t* res_cnt;                // [n_rows]
   uint32_t* res_col;                // [nnz], row r at res_col + row_off[r]
+  // rows whose residual part is longer than kHeavyRowSlots get CTAs of their own (gather_rows_listed_first_kernel)
+  unsigned int* heavy_count;        // zeroed before the kernel
+  int* heavy_rows;                  // [n_rows]
 };
 
 // Residual rows of the hybrid (see above): same offsets as the caller's CSR, fewer entries, all < Lk.
@@ -50,19 +56,24 @@ struct ResidualCols {
   const uint64_t* row_off;
   const uint32_t* cnt;
   const uint32_t* col;
+  uint32_t skip_above;  // rows with more residual entries than this read as empty (they are on the heavy list)
   static constexpr bool kNanFillEmpty = false;  // the plan kernel has filled the rows that are really empty
   struct Row { int64_t lo; int64_t n; };
   __device__ __forceinline__ Row open(int64_t r_local, int64_t) const {
     Row r;
     r.lo = (int64_t)row_off[r_local];
-    r.n = (int64_t)cnt[r_local];
+    const uint32_t n = cnt[r_local];
+    r.n = (n > skip_above) ? 0 : (int64_t)n;
     return r;
   }
   __device__ __forceinline__ int32_t slot(const Row& r, int64_t t) const { return (int32_t)__ldg(col + r.lo + t); }
 };
 
 inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
-  return (size_t)n_key_tiles * 4 + (size_t)tile::kMaxDenseTiles * (bn / 32) * 128 * 4;
+  const size_t hist = (size_t)n_key_tiles * 4;
+  const size_t masks = (size_t)tile::kMaxDenseTiles * (bn / 32) * 128 * 4;
+  const size_t words = (size_t)(n_key_tiles + 31) / 32;
+  return (hist > masks ? hist : masks) + words * 4 + (words + 3) / 4 * 4;
 }
 
 // Runs of equal keys over the lanes of a warp. Returns the lane one past the end of the run this lane is in;
@@ -77,15 +88,20 @@ __device__ __forceinline__ int run_end_of(uint32_t key, int lane, bool* lead) {
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kPlanThreads, 2)
+__global__ void __launch_bounds__(kPlanThreads, 4)
 explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __restrict__ col, int64_t n_rows, int64_t Lk,
                      int n_key_tiles, int min_entries, ExplicitPlan plan, int use_nan, float* __restrict__ O, int d) {
   constexpr int NC = BN / 32;
   constexpr int MAXT = tile::kMaxDenseTiles;
   constexpr uint32_t kNoKey = 0xffffffffu;
   extern __shared__ uint32_t plan_smem[];
-  uint32_t* hist = plan_smem;                    // [n_key_tiles]: entry count, later slot + 1 of dense tiles
-  uint32_t* masks = plan_smem + n_key_tiles;     // [MAXT][NC][128]
+  const int n_words = (n_key_tiles + 31) / 32;
+  const int region = (n_key_tiles > MAXT * NC * 128) ? n_key_tiles : MAXT * NC * 128;
+  uint32_t* hist = plan_smem;                 // [n_key_tiles] entry counts            (steps 1-2)
+  uint32_t* masks = plan_smem;                // [MAXT][NC][128], same storage         (steps 3-4)
+  uint32_t* dense_bits = plan_smem + region;  // [n_words] bit k: key tile k is dense
+  uint8_t* dense_before = reinterpret_cast<uint8_t*>(dense_bits + n_words);  // [n_words] dense tiles in earlier words
+  __shared__ unsigned long long s_off[129];      // the block's row offsets
   __shared__ int s_warp_cnt[kPlanWarps];
   __shared__ int s_sel[MAXT];                    // key tile of slot t
   __shared__ int s_dirty[MAXT];
@@ -96,12 +112,14 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const int64_t b = blockIdx.x;
   const int64_t r0 = b * 128;
   const int nr = (int)((n_rows - r0 < 128) ? (n_rows - r0) : 128);
-  const int64_t e0 = (int64_t)row_off[r0], e1 = (int64_t)row_off[r0 + nr];
-
-  // ---- 1. histogram over key tiles ----
+  if (tid <= nr) s_off[tid] = row_off[r0 + tid];
   for (int k = tid; k < n_key_tiles; k += kPlanThreads) hist[k] = 0;
+  for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
   __syncthreads();
+  const int64_t e0 = (int64_t)s_off[0], e1 = (int64_t)s_off[nr];
+
+  // ---- 1. histogram over key tiles ----
   for (int64_t base = e0; base < e1; base += kPlanThreads * kPlanUnroll) {  // every warp runs whole iterations
     uint32_t cu[kPlanUnroll];
 #pragma unroll
@@ -135,78 +153,81 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   int before = incl - mine;
   for (int wv = 0; wv < warp; ++wv) before += s_warp_cnt[wv];
   if (tid == kPlanThreads - 1) s_nt = (before + mine < MAXT) ? (before + mine) : MAXT;
-  for (int k = k_lo; k < k_hi; ++k) {
-    const bool dense = hist[k] >= (uint32_t)min_entries;
-    uint32_t slot1 = 0;
-    if (dense) {
-      if (before < MAXT) {
-        s_sel[before] = k;
-        slot1 = (uint32_t)before + 1;
+  if (mine > 0)
+    for (int k = k_lo; k < k_hi && before < MAXT; ++k)
+      if (hist[k] >= (uint32_t)min_entries) {
+        s_sel[before++] = k;
+        atomicOr(&dense_bits[k >> 5], 1u << (k & 31));
       }
-      ++before;
-    }
-    hist[k] = slot1;
-  }
-  __syncthreads();
+  __syncthreads();  // the histogram is dead from here on: its storage becomes the masks
   const int nt = s_nt;
+  for (int w = tid; w < n_words; w += kPlanThreads) {
+    int c = 0;
+    for (int t = 0; t < nt; ++t) c += ((s_sel[t] >> 5) < w);
+    dense_before[w] = (uint8_t)c;
+  }
+  // slot + 1 of a dense key tile, 0 for any other
+  auto slot1_of = [&](uint32_t kt) -> uint32_t {
+    const uint32_t w = dense_bits[kt >> 5], bit = 1u << (kt & 31);
+    return (w & bit) ? (uint32_t)dense_before[kt >> 5] + __popc(w & (bit - 1u)) + 1u : 0u;
+  };
 
-  // ---- 3. bit masks of the dense tiles; duplicates demote a tile ----
+  // ---- 3. bit masks of the dense tiles (duplicates demote a tile) and, in the same walk, 5. the residual list ----
   for (int i = tid; i < nt * NC * 128; i += kPlanThreads) masks[i] = 0;
   __syncthreads();
-  // The same walk writes the entries outside the dense tiles to the residual list (step 5); if a tile is
-  // demoted afterwards (rare), the residual rows of the block are simply written again.
-  {
-    for (int rl = warp; rl < nr; rl += kPlanWarps) {
-      const int64_t a = (int64_t)row_off[r0 + rl], z = (int64_t)row_off[r0 + rl + 1];
-      uint32_t kept = 0;
-      for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
-        uint32_t cu[kPlanUnroll];
+  for (int rl = warp; rl < nr; rl += kPlanWarps) {
+    const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
+    uint32_t kept = 0;
+    for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
+      uint32_t cu[kPlanUnroll];
 #pragma unroll
-        for (int u = 0; u < kPlanUnroll; ++u) {
-          const int64_t e = base + u * 32 + lane;
-          cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
-        }
+      for (int u = 0; u < kPlanUnroll; ++u) {
+        const int64_t e = base + u * 32 + lane;
+        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+      }
 #pragma unroll
-        for (int u = 0; u < kPlanUnroll; ++u) {
-          if (base + u * 32 >= z) break;  // warp-uniform
-          const uint32_t c = cu[u];
-          uint32_t word = kNoKey, bit = 0;
-          bool keep = false;
-          if ((int64_t)c < Lk) {
-            const uint32_t kt = c / BN, slot1 = hist[kt];
-            if (slot1) {
-              const uint32_t kk = c - kt * BN;
-              word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl;
-              bit = 1u << (kk & 31);
-            } else {
-              keep = true;
-            }
-          }
-          const uint32_t bal = __ballot_sync(kFullMask, keep);
-          if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
-          kept += __popc(bal);
-          if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
-          // OR of the bits of each run of equal words, at the run's first lane (suffix scan by doubling)
-          bool lead;
-          const int end = run_end_of(word, lane, &lead);
-          uint32_t acc = bit;
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t t = __shfl_down_sync(kFullMask, acc, o);
-            if (lane + o < end) acc |= t;
-          }
-          if (lead && word != kNoKey) {
-            const uint32_t old = atomicOr(&masks[word], acc);
-            if ((old & acc) != 0u || __popc(acc) != end - lane) s_dirty[word / (NC * 128)] = 1;
+      for (int u = 0; u < kPlanUnroll; ++u) {
+        if (base + u * 32 >= z) break;  // warp-uniform
+        const uint32_t c = cu[u];
+        uint32_t word = kNoKey, bit = 0;
+        bool keep = false;
+        if ((int64_t)c < Lk) {
+          const uint32_t kt = c / BN, slot1 = slot1_of(kt);
+          if (slot1) {
+            const uint32_t kk = c - kt * BN;
+            word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl;
+            bit = 1u << (kk & 31);
+          } else {
+            keep = true;
           }
         }
+        const uint32_t bal = __ballot_sync(kFullMask, keep);
+        if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
+        kept += __popc(bal);
+        if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
+        // OR of the bits of each run of equal words, at the run's first lane (suffix scan by doubling)
+        bool lead;
+        const int end = run_end_of(word, lane, &lead);
+        uint32_t acc = bit;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t t = __shfl_down_sync(kFullMask, acc, o);
+          if (lane + o < end) acc |= t;
+        }
+        if (lead && word != kNoKey) {
+          const uint32_t old = atomicOr(&masks[word], acc);
+          if ((old & acc) != 0u || __popc(acc) != end - lane) s_dirty[word / (NC * 128)] = 1;
+        }
       }
-      if (lane == 0) plan.res_cnt[r0 + rl] = kept;
-      if (z <= a && use_nan) {  // a row without any entry
-        const float nn = __int_as_float(0x7fc00000);
-        for (int i = lane * 4; i < d; i += 128)
-          *reinterpret_cast<float4*>(O + (size_t)(r0 + rl) * d + i) = make_float4(nn, nn, nn, nn);
-      }
+    }
+    if (lane == 0) {
+      plan.res_cnt[r0 + rl] = kept;
+      if (kept > (uint32_t)kHeavyRowSlots) plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
+    }
+    if (z <= a && use_nan) {  // a row without any entry
+      const float nn = __int_as_float(0x7fc00000);
+      for (int i = lane * 4; i < d; i += 128)
+        *reinterpret_cast<float4*>(O + (size_t)(r0 + rl) * d + i) = make_float4(nn, nn, nn, nn);
     }
   }
   __syncthreads();
@@ -236,7 +257,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   if (tid < nt) {
     const int to = s_map[tid];
     if (to >= 0) plan.rb_kt[b * MAXT + to] = s_sel[tid];
-    else hist[s_sel[tid]] = 0;  // its entries go to the residual list
+    else atomicAnd(&dense_bits[s_sel[tid] >> 5], ~(1u << (s_sel[tid] & 31)));  // its entries are residual after all
   }
   if (nclean > 0) {
     uint32_t* dst = plan.masks + s_moff;
@@ -247,10 +268,10 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   }
   __syncthreads();
 
-  // ---- 5 again, only if a tile was demoted: its entries belong to the residual rows after all ----
+  // ---- 5 again, only if a tile was demoted: membership is all that is asked of the bits now ----
   if (!s_redo) return;
   for (int rl = warp; rl < nr; rl += kPlanWarps) {
-    const int64_t a = (int64_t)row_off[r0 + rl], z = (int64_t)row_off[r0 + rl + 1];
+    const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
     for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
       uint32_t cu[kPlanUnroll];
@@ -262,13 +283,22 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
 #pragma unroll
       for (int u = 0; u < kPlanUnroll; ++u) {
         const uint32_t c = cu[u];
-        const bool keep = ((int64_t)c < Lk) && hist[c / BN] == 0;
+        bool keep = false;
+        if ((int64_t)c < Lk) {
+          const uint32_t kt = c / BN;
+          keep = ((dense_bits[kt >> 5] >> (kt & 31)) & 1u) == 0u;
+        }
         const uint32_t bal = __ballot_sync(kFullMask, keep);
         if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
         kept += __popc(bal);
       }
     }
-    if (lane == 0) plan.res_cnt[r0 + rl] = kept;
+    if (lane == 0) {
+      const uint32_t before_cnt = plan.res_cnt[r0 + rl];  // listed already if it was long before the demotion
+      plan.res_cnt[r0 + rl] = kept;
+      if (kept > (uint32_t)kHeavyRowSlots && before_cnt <= (uint32_t)kHeavyRowSlots)
+        plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
+    }
   }
 }
 

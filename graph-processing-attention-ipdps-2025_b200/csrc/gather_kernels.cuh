@@ -218,20 +218,83 @@ __device__ __forceinline__ void nan_fill_row(float* __restrict__ O, int64_t r, i
 constexpr int kRowWarps = 4;
 constexpr int kHeavyRowSlots = 1024;
 
-template <int D, class Cols>
-__global__ void __launch_bounds__(kRowWarps * 32, 7)
-gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
-                   float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
-                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale) {
+// All NW warps of a CTA walk one row together: warp w takes the w-th share of the slots (whole 32-slot
+// batches), the partial states meet in shared memory and warp 0 folds them in slot order and stores the row.
+// Every thread of the CTA must call this (it contains block barriers).
+template <int D, class Cols, int NW>
+__device__ __forceinline__ void walk_row_with_cta(const Cols& cols, const typename Cols::Row& row, int64_t r,
+                                                  const float* __restrict__ Q, const float* __restrict__ K,
+                                                  const float* __restrict__ V, float* __restrict__ m,
+                                                  float* __restrict__ l, float* __restrict__ O, float scale, int warp,
+                                                  int lane, float (*s_ml)[2], float4 (*s_acc)[D / 4]) {
   constexpr int LPK = D / 4;
-  __shared__ int s_heavy[kRowWarps];
-  __shared__ int s_n_heavy;
-  __shared__ float s_ml[kRowWarps][2];
-  __shared__ float4 s_acc[kRowWarps][LPK];
+  int64_t per = (row.n + NW - 1) / NW;
+  per = (per + 31) / 32 * 32;  // whole 32-slot batches per warp
+  const int64_t t0 = (int64_t)warp * per;
+  int64_t t1 = t0 + per;
+  if (t1 > row.n) t1 = row.n;
+  RowAcc<D> st;
+  st.m = neg_inf();
+  st.l = 0.f;
+  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (t0 < t1) {
+    const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
+    accumulate_slots<D, Cols>(cols, row, t0, t1, q, K, V, scale, lane, st);
+    merge_groups<D>(st);
+  }
+  if (lane < LPK) s_acc[warp][lane] = st.acc;
+  if (lane == 0) {
+    s_ml[warp][0] = st.m;
+    s_ml[warp][1] = st.l;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    RowAcc<D> tot;
+    tot.m = neg_inf();
+    tot.l = 0.f;
+    tot.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int sub = lane % LPK;
+#pragma unroll 4
+    for (int wv = 0; wv < NW; ++wv) {  // in slot order, like the single-warp walk
+      const float mo = s_ml[wv][0], lo = s_ml[wv][1];
+      const float4 ao = s_acc[wv][sub];
+      const float mn = fmaxf(tot.m, mo);
+      const float ms = (mn == neg_inf()) ? 0.f : mn;
+      const float c1 = fast_exp2((tot.m - ms) * kLog2e);
+      const float c2 = fast_exp2((mo - ms) * kLog2e);
+      tot.l = tot.l * c1 + lo * c2;
+      tot.acc.x = tot.acc.x * c1 + ao.x * c2;
+      tot.acc.y = tot.acc.y * c1 + ao.y * c2;
+      tot.acc.z = tot.acc.z * c1 + ao.z * c2;
+      tot.acc.w = tot.acc.w * c1 + ao.w * c2;
+      tot.m = mn;
+    }
+    if (tot.l > 0.f) store_row<D>(tot, m, l, O, r, lane);
+  }
+  __syncthreads();
+}
+
+struct RowCtaShared {
+  int heavy[kRowWarps];
+  int n_heavy;
+  float ml[kRowWarps][2];
+};
+
+// Rows [block*kRowWarps, (block+1)*kRowWarps) of the shard, by one CTA of kRowWarps warps.
+template <int D, class Cols>
+__device__ __forceinline__ void gather_rows_cta(int64_t block, const float* __restrict__ Q, const float* __restrict__ K,
+                                                const float* __restrict__ V, float* __restrict__ m,
+                                                float* __restrict__ l, float* __restrict__ O, const Cols& cols,
+                                                int64_t row_begin, int64_t n_rows, int use_nan, float scale,
+                                                RowCtaShared& sh, float4 (*s_acc)[D / 4]) {
+  constexpr int LPK = D / 4;
+  int* s_heavy = sh.heavy;
+  int& s_n_heavy = sh.n_heavy;
+  float (*s_ml)[2] = sh.ml;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) s_n_heavy = 0;
   __syncthreads();
-  const int64_t r = (int64_t)blockIdx.x * kRowWarps + warp;
+  const int64_t r = block * kRowWarps + warp;
   if (r < n_rows) {
     const typename Cols::Row row = cols.open(r, row_begin + r);
     if (row.n <= 0) {
@@ -252,52 +315,47 @@ gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
   __syncthreads();
   const int n_heavy = s_n_heavy;  // uniform over the CTA
   for (int h = 0; h < n_heavy; ++h) {
-    const int64_t rh = (int64_t)blockIdx.x * kRowWarps + s_heavy[h];
+    const int64_t rh = block * kRowWarps + s_heavy[h];
     const typename Cols::Row row = cols.open(rh, row_begin + rh);
-    int64_t per = (row.n + kRowWarps - 1) / kRowWarps;
-    per = (per + 31) / 32 * 32;  // whole 32-slot batches per warp
-    const int64_t t0 = (int64_t)warp * per;
-    int64_t t1 = t0 + per;
-    if (t1 > row.n) t1 = row.n;
-    RowAcc<D> st;
-    st.m = neg_inf();
-    st.l = 0.f;
-    st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (t0 < t1) {
-      const float4 q = ldg4(Q + (size_t)rh * D + (lane % LPK) * 4);
-      accumulate_slots<D, Cols>(cols, row, t0, t1, q, K, V, scale, lane, st);
-      merge_groups<D>(st);
-    }
-    if (lane < LPK) s_acc[warp][lane] = st.acc;
-    if (lane == 0) {
-      s_ml[warp][0] = st.m;
-      s_ml[warp][1] = st.l;
-    }
-    __syncthreads();
-    if (warp == 0) {
-      RowAcc<D> tot;
-      tot.m = neg_inf();
-      tot.l = 0.f;
-      tot.acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int sub = lane % LPK;
-#pragma unroll
-      for (int wv = 0; wv < kRowWarps; ++wv) {  // in slot order, like the single-warp walk
-        const float mo = s_ml[wv][0], lo = s_ml[wv][1];
-        const float4 ao = s_acc[wv][sub];
-        const float mn = fmaxf(tot.m, mo);
-        const float ms = (mn == neg_inf()) ? 0.f : mn;
-        const float c1 = fast_exp2((tot.m - ms) * kLog2e);
-        const float c2 = fast_exp2((mo - ms) * kLog2e);
-        tot.l = tot.l * c1 + lo * c2;
-        tot.acc.x = tot.acc.x * c1 + ao.x * c2;
-        tot.acc.y = tot.acc.y * c1 + ao.y * c2;
-        tot.acc.z = tot.acc.z * c1 + ao.z * c2;
-        tot.acc.w = tot.acc.w * c1 + ao.w * c2;
-        tot.m = mn;
-      }
-      if (tot.l > 0.f) store_row<D>(tot, m, l, O, rh, lane);
-    }
-    __syncthreads();
+    walk_row_with_cta<D, Cols, kRowWarps>(cols, row, rh, Q, K, V, m, l, O, scale, warp, lane, s_ml, s_acc);
+  }
+}
+
+template <int D, class Cols>
+__global__ void __launch_bounds__(kRowWarps * 32, 7)
+gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                   float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
+                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale) {
+  __shared__ RowCtaShared sh;
+  __shared__ float4 s_acc[kRowWarps][D / 4];
+  gather_rows_cta<D, Cols>(blockIdx.x, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, sh, s_acc);
+}
+
+// Same, for a shard whose long rows were listed beforehand (the explicit-mask plan lists the rows whose residual
+// part exceeds kHeavyRowSlots; `cols` reports those rows as empty). The first n_list_blocks CTAs stride over the
+// list, one listed row at a time with all their warps (`listed` opens the same rows at full length); the other
+// CTAs do the ordinary rows. Blocks are dispatched in index order, so the long rows start with the launch
+// instead of wherever their row number falls. The list length lives in device memory (it is produced there).
+template <int D, class Cols>
+__global__ void __launch_bounds__(kRowWarps * 32, 7)
+gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Cols cols,
+                                const Cols listed, const int* __restrict__ row_list,
+                                const unsigned int* __restrict__ n_listed, int n_list_blocks, int64_t row_begin,
+                                int64_t n_rows, int use_nan, float scale) {
+  __shared__ RowCtaShared sh;
+  __shared__ float4 s_acc[kRowWarps][D / 4];
+  if ((int)blockIdx.x >= n_list_blocks) {
+    gather_rows_cta<D, Cols>((int64_t)blockIdx.x - n_list_blocks, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan,
+                             scale, sh, s_acc);
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned int n = *n_listed;
+  for (unsigned int e = blockIdx.x; e < n; e += (unsigned int)n_list_blocks) {
+    const int64_t r = row_list[e];
+    const typename Cols::Row row = listed.open(r, row_begin + r);
+    walk_row_with_cta<D, Cols, kRowWarps>(listed, row, r, Q, K, V, m, l, O, scale, warp, lane, sh.ml, s_acc);
   }
 }
 

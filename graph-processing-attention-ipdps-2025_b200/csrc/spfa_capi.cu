@@ -176,7 +176,7 @@ struct HybridLayout {
   int64_t n_blocks;
   long long cap_words;
   size_t smem;
-  size_t off_pool, off_nt, off_kt, off_moff, off_cnt, off_res, off_masks, total;
+  size_t off_pool, off_nt, off_kt, off_moff, off_cnt, off_heavy, off_res, off_masks, total;
 };
 
 inline bool hybrid_shape_ok(int d, int64_t n_rows, int64_t nnz, int64_t Lk) {
@@ -200,7 +200,8 @@ inline HybridLayout hybrid_layout(int64_t n_rows, int64_t nnz, int64_t Lk, int d
   h.off_kt = h.off_nt + align_up((size_t)h.n_blocks * 4);
   h.off_moff = h.off_kt + align_up((size_t)h.n_blocks * tile::kMaxDenseTiles * 4);
   h.off_cnt = h.off_moff + align_up((size_t)h.n_blocks * 8);
-  h.off_res = h.off_cnt + align_up((size_t)n_rows * 4);
+  h.off_heavy = h.off_cnt + align_up((size_t)n_rows * 4);
+  h.off_res = h.off_heavy + align_up((size_t)n_rows * 4);
   h.off_masks = h.off_res + align_up((size_t)nnz * 4);
   h.total = h.off_masks + align_up((size_t)h.cap_words * 4);
   return h;
@@ -232,7 +233,9 @@ int launch_hybrid(const float* Q, const float* K, const float* V, const uint64_t
   plan.res_col = reinterpret_cast<uint32_t*>(ws + h.off_res);
   plan.masks = reinterpret_cast<uint32_t*>(ws + h.off_masks);
   plan.cap_words = h.cap_words;
-  if (cudaMemsetAsync(plan.pool_used, 0, 8, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  plan.heavy_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 8);
+  plan.heavy_rows = reinterpret_cast<int*>(ws + h.off_heavy);
+  if (cudaMemsetAsync(plan.pool_used, 0, 16, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
   auto plan_kern = explicit_plan_kernel<BN>;
   if (cudaFuncSetAttribute(plan_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h.smem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
@@ -259,11 +262,18 @@ int launch_hybrid(const float* Q, const float* K, const float* V, const uint64_t
     return SPFA_ERR_LAUNCH;
   int rc = launch_band_raw<D, BN, NS, 2, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + 255) / 256)), st);
   if (rc) return rc;
-  // everything else
-  ResidualCols cols{row_off, plan.res_cnt, plan.res_col};
-  rc = launch_gather<D, ResidualCols>(Q, K, V, m, l, O, cols, 0, n_rows, 0, st);
+  // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
+  const float scale = 1.0f / sqrtf((float)D);
+  ResidualCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu};
+  ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kHeavyRowSlots};
+  const int64_t row_blocks = (n_rows + kRowWarps - 1) / kRowWarps;
+  const int list_blocks = (int)(row_blocks < 512 ? row_blocks : 512);
+  if (row_blocks + list_blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  gather_rows_listed_first_kernel<D, ResidualCols><<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(
+      Q, K, V, m, l, O, cols, listed, plan.heavy_rows, plan.heavy_count, list_blocks, 0, n_rows, 0, scale);
+  g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_TILED);
-  return rc;
+  return launch_status();
 }
 
 inline int hybrid_forward(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off,

@@ -580,3 +580,37 @@ def test_explicit_auto_takes_dense_tiles_for_large_masks(capi, orc):
     assert capi.last_path() == capi.PATH_TILED
     assert capi.last_csr_dense_tiles() >= 2 * (L // 128)
     assert_state_close(to_np(st), want, TOL_TILED, "auto dense tiles")
+
+
+def test_explicit_dense_tiles_on_a_coo_row_shard(capi, orc):
+    """Rows [300, 700) of a COO mask, given the full entry list: the shard's own row numbering feeds the split."""
+    L, d, r0, r1 = 900, 64, 300, 700
+    Q, K, V = seeded_qkv(L, d, 41, L)
+    mask = _band_plus_random(L, L, 45, 0.003, 3, empty_rows=(310,))
+    row_off, col = _csr_of(mask)
+    rows = np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)
+    want = orc.coo_forward(Q[r0:r1], K, V, rows, col, use_nan=True, row_begin=r0)
+    capi.set_path(capi.PATH_TILED)
+    st = capi.new_state(r1 - r0, d)
+    capi.coo_forward(dev(Q[r0:r1]), dev(K), dev(V), dev(rows), dev(col), *st, use_nan=True, row_begin=r0)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want, TOL_TILED, "coo shard, dense tiles")
+    capi.set_path(capi.PATH_AUTO)
+
+
+def test_explicit_dense_tiles_with_very_long_residual_rows(capi, orc):
+    """Rows whose entries outside the dense tiles number in the thousands take the listed-rows kernel."""
+    L, Lk, d = 520, 9000, 64
+    Q, K, V = seeded_qkv(L, d, 52, Lk)
+    mask = _band_plus_random(L, Lk, 50, 0.001, 6)
+    rng = np.random.default_rng(1)
+    for r, n in ((0, 5000), (77, 1025), (300, 3000), (519, 2048)):
+        mask[r, rng.permutation(Lk)[:n]] = True
+    row_off, col = _csr_of(mask)
+    want = orc.csr_forward(Q, K, V, row_off, col)
+    capi.set_path(capi.PATH_TILED)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st)
+    assert capi.last_csr_dense_tiles() > 0
+    assert_state_close(to_np(st), want, TOL_TILED, "long residual rows")
+    capi.set_path(capi.PATH_AUTO)
