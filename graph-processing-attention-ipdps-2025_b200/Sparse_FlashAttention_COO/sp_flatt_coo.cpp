@@ -39,6 +39,25 @@ torch::Tensor spfa_coo_forward(torch::Tensor Q, torch::Tensor K, torch::Tensor V
   return spfa_coo_cuda_forward(Q, K, V, W_row_ind, W_col_ind, W_val, m, l, O, use_nan);
 }
 
+// Additive: run the mask inspector once and keep its output. plan(W_row_ind, W_col_ind, n_rows, n_keys, d) -> plan
+// tensor for forward_planned(Q, K, V, plan, nnz, m, l, O, use_nan) with nnz = W_col_ind.numel().
+torch::Tensor spfa_coo_plan(torch::Tensor W_row_ind, torch::Tensor W_col_ind, int64_t n_rows, int64_t n_keys, int64_t d) {
+  using namespace spfa_binding;
+  CHECK_INPUT(W_row_ind);
+  CHECK_INPUT(W_col_ind);
+  TORCH_CHECK(W_row_ind.dim() == 1 && W_col_ind.dim() == 1 && W_row_ind.size(0) == W_col_ind.size(0),
+              "W_row_ind and W_col_ind must be 1-D with one entry per mask non-zero");
+  c10::cuda::CUDAGuard guard(W_col_ind.device());
+  const int64_t nnz = W_col_ind.size(0);
+  torch::Tensor plan = new_plan_tensor(n_rows, nnz, n_keys, (int)d, W_col_ind.device());
+  raise_for_status(spfa_coo_plan_build(u64_ptr(W_row_ind, "W_row_ind"), u32_ptr(W_col_ind, "W_col_ind"), nnz,
+                                       /*row_begin=*/0, n_rows, n_keys, (int)d, plan.data_ptr(), (size_t)plan.numel(),
+                                       at::cuda::getCurrentCUDAStream().stream()));
+  return plan;
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("forward", &spfa_coo_forward, "Sparse-FlashAttention forward (CUDA)");
+  mod.def("plan", &spfa_coo_plan, "Dense-tile plan of a COO mask (CUDA)");
+  mod.def("forward_planned", &spfa_binding::planned_forward, "Sparse-FlashAttention forward from a stored plan (CUDA)");
 }

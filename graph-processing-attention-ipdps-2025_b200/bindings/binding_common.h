@@ -82,4 +82,35 @@ struct Workspace {
   }
 };
 
+// ---- stored plans for explicit masks (additive: the reference's modules export `forward` only) ----------
+// A plan is a uint8 CUDA tensor whose first byte is 256-byte aligned (a view into a slightly larger buffer).
+inline torch::Tensor new_plan_tensor(int64_t n_rows, int64_t nnz, int64_t n_keys, int d, const torch::Device& dev) {
+  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, n_keys, d);
+  TORCH_CHECK(need > 0, "spfa_b200: no dense-tile plan for this shape (d must be 32, 64 or 128; the mask non-empty)");
+  torch::Tensor buf = torch::empty({(int64_t)need + 256}, torch::TensorOptions().dtype(torch::kUInt8).device(dev));
+  const uintptr_t p = reinterpret_cast<uintptr_t>(buf.data_ptr());
+  return buf.narrow(0, (int64_t)(((p + 255) & ~uintptr_t(255)) - p), (int64_t)need);
+}
+
+// forward_planned(Q, K, V, plan, nnz, m, l, O, use_nan): the forward of the module whose plan() made `plan`.
+inline torch::Tensor planned_forward(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor plan, int64_t nnz,
+                                     torch::Tensor m, torch::Tensor l, torch::Tensor O, bool use_nan) {
+  CHECK_INPUT(Q);
+  CHECK_INPUT(K);
+  CHECK_INPUT(V);
+  CHECK_INPUT(plan);
+  CHECK_INPUT(m);
+  CHECK_INPUT(l);
+  CHECK_INPUT(O);
+  check_qkv_state(Q, K, V, m, l, O);
+  TORCH_CHECK(plan.scalar_type() == torch::kUInt8 && plan.dim() == 1, "plan must be the tensor returned by plan()");
+  c10::cuda::CUDAGuard guard(Q.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  raise_for_status(spfa_planned_forward_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
+                                            m.data_ptr<float>(), l.data_ptr<float>(), O.data_ptr<float>(), Q.size(0), nnz,
+                                            K.size(0), (int)Q.size(1), use_nan ? 1 : 0, plan.data_ptr(),
+                                            (size_t)plan.numel(), stream.stream()));
+  return O;
+}
+
 }  // namespace spfa_binding

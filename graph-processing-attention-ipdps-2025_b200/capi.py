@@ -27,7 +27,8 @@ MASK_KIND = {"local": 0, "local_1d_dilated": 1, "local_2d_dilated": 2, "global_n
 EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
-    "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
+    "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32",
+    "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -73,6 +74,14 @@ def lib() -> ctypes.CDLL:
     L.spfa_coo_min_workspace_bytes.argtypes = [i64]
     L.spfa_coo_forward_f32.restype = i32
     L.spfa_coo_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_explicit_plan_bytes.restype = sz
+    L.spfa_explicit_plan_bytes.argtypes = [i64, i64, i64, i32]
+    L.spfa_csr_plan_build.restype = i32
+    L.spfa_csr_plan_build.argtypes = [vp, vp, i64, i64, i64, i32, vp, sz, vp]
+    L.spfa_coo_plan_build.restype = i32
+    L.spfa_coo_plan_build.argtypes = [vp, vp, i64, i64, i64, i64, i32, vp, sz, vp]
+    L.spfa_planned_forward_f32.restype = i32
+    L.spfa_planned_forward_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, vp]
     L.spfa_coo_static_max_rows.restype = i64
     L.spfa_coo_forward_f32_static.restype = i32
     L.spfa_coo_forward_f32_static.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp]
@@ -207,6 +216,53 @@ def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):
         check(lib().spfa_coo_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)),
                                          row_ind.shape[0], _ptr(m), _ptr(l), _ptr(O), row_begin, n_rows, K.shape[0],
                                          d, int(use_nan), wp, wb, _stream(dev)))
+    return O
+
+
+class ExplicitPlan:
+    """Inspector output for one CSR/COO mask (device memory), reusable across forward calls on that mask."""
+
+    def __init__(self, buf, ptr, nbytes, n_rows, nnz, n_keys, d):
+        self.buf, self.ptr, self.nbytes = buf, ptr, nbytes
+        self.n_rows, self.nnz, self.n_keys, self.d = n_rows, nnz, n_keys, d
+
+
+def _new_plan(n_rows, nnz, n_keys, d, dev):
+    need = lib().spfa_explicit_plan_bytes(n_rows, nnz, n_keys, d)
+    if need == 0:
+        raise SpfaError(-1, "no dense-tile plan for this shape (d must be 32, 64 or 128 and the mask non-empty)")
+    buf, wp, wb = workspace(need, dev)
+    return ExplicitPlan(buf, wp, wb, n_rows, nnz, n_keys, d)
+
+
+def csr_plan(row_off, col_ind, n_keys, d):
+    """Run the inspector once for a CSR mask of row_off.numel()-1 rows over n_keys keys."""
+    dev = col_ind.device
+    with torch.cuda.device(dev):
+        plan = _new_plan(row_off.shape[0] - 1, col_ind.shape[0], n_keys, d, dev)
+        check(lib().spfa_csr_plan_build(_ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)), plan.nnz, plan.n_rows, n_keys, d,
+                                        plan.ptr, plan.nbytes, _stream(dev)))
+    return plan
+
+
+def coo_plan(row_ind, col_ind, n_rows, n_keys, d, row_begin=0):
+    """Run the inspector once for the rows [row_begin, row_begin + n_rows) of a row-sorted COO mask."""
+    dev = col_ind.device
+    with torch.cuda.device(dev):
+        plan = _new_plan(n_rows, col_ind.shape[0], n_keys, d, dev)
+        check(lib().spfa_coo_plan_build(_ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), plan.nnz, row_begin, n_rows,
+                                        n_keys, d, plan.ptr, plan.nbytes, _stream(dev)))
+    return plan
+
+
+def planned_forward(Q, K, V, m, l, O, plan: ExplicitPlan, use_nan=False):
+    """Forward from a stored plan: dense tiles on the tiled kernel, the other entries on the gather kernel."""
+    dev = _f32(Q, K, V, m, l, O)
+    if Q.shape[0] != plan.n_rows or K.shape[0] != plan.n_keys or Q.shape[1] != plan.d:
+        raise SpfaError(-1, "the plan was built for another shape")
+    with torch.cuda.device(dev):
+        check(lib().spfa_planned_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows, plan.nnz,
+                                             plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes, _stream(dev)))
     return O
 
 

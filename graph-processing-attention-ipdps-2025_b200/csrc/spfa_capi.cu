@@ -219,31 +219,61 @@ inline int hybrid_decision(int d, int64_t n_rows, int64_t nnz, int64_t Lk, const
   return 1;
 }
 
-template <int D, int BN, int NS>
-int launch_hybrid(const float* Q, const float* K, const float* V, const uint64_t* row_off, const uint32_t* col,
-                  float* m, float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, int use_nan, char* ws,
-                  cudaStream_t st) {
-  const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
+inline ExplicitPlan plan_view(const HybridLayout& h, char* ws) {
   ExplicitPlan plan;
   plan.pool_used = reinterpret_cast<unsigned long long*>(ws + h.off_pool);
+  plan.heavy_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 8);
   plan.rb_nt = reinterpret_cast<int*>(ws + h.off_nt);
   plan.rb_kt = reinterpret_cast<int*>(ws + h.off_kt);
   plan.rb_moff = reinterpret_cast<long long*>(ws + h.off_moff);
   plan.res_cnt = reinterpret_cast<uint32_t*>(ws + h.off_cnt);
+  plan.heavy_rows = reinterpret_cast<int*>(ws + h.off_heavy);
   plan.res_col = reinterpret_cast<uint32_t*>(ws + h.off_res);
   plan.masks = reinterpret_cast<uint32_t*>(ws + h.off_masks);
   plan.cap_words = h.cap_words;
-  plan.heavy_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 8);
-  plan.heavy_rows = reinterpret_cast<int*>(ws + h.off_heavy);
+  return plan;
+}
+
+// The inspector: fills the plan region `ws` for the mask (row_off, col). With use_nan it also NaN-fills the O
+// rows of rows without entries (a per-call effect; plans built for later use pass use_nan = 0, O = nullptr).
+template <int BN>
+int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t Lk, int d,
+                const HybridLayout& h, char* ws, int use_nan, float* O, cudaStream_t st) {
+  const ExplicitPlan plan = plan_view(h, ws);
   if (cudaMemsetAsync(plan.pool_used, 0, 16, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
   auto plan_kern = explicit_plan_kernel<BN>;
   if (cudaFuncSetAttribute(plan_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h.smem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
   plan_kern<<<(unsigned)h.n_blocks, kPlanThreads, h.smem, st>>>(row_off, col, n_rows, Lk, h.n_key_tiles, h.min_entries,
-                                                                plan, use_nan, O, D);
+                                                                plan, use_nan, O, d);
   g_launches.fetch_add(1);
-  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
-  // dense tiles
+  return launch_status();
+}
+
+inline int build_plan(int d, const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk,
+                      char* ws, int use_nan, float* O, cudaStream_t st) {
+  const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, d);
+  return (h.bn == 96) ? launch_plan<96>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st)
+                      : launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
+}
+
+// Rows without any mask entry get a NaN output row (what the inspector does in a one-shot call, for calls that
+// run from a stored plan).
+__global__ void nan_fill_empty_rows_kernel(const uint64_t* __restrict__ row_off, float* __restrict__ O, int64_t n_rows,
+                                           int d) {
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= n_rows || row_off[r + 1] > row_off[r]) return;
+  const float nn = __int_as_float(0x7fc00000);
+  for (int i = lane * 4; i < d; i += 128) *reinterpret_cast<float4*>(O + (size_t)r * d + i) = make_float4(nn, nn, nn, nn);
+}
+
+// The two compute launches of the split, from a filled plan region: dense tiles, then everything else.
+template <int D, int BN, int NS>
+int launch_from_plan(const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m, float* l,
+                     float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
+  const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
+  const ExplicitPlan plan = plan_view(h, ws);
   tile::BandParams prm{};
   prm.mode = 3;
   prm.n_keys = Lk;
@@ -276,15 +306,23 @@ int launch_hybrid(const float* Q, const float* K, const float* V, const uint64_t
   return launch_status();
 }
 
+inline int forward_from_plan(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m,
+                             float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
+  switch (d) {
+    case 32: return launch_from_plan<32, 96, 2>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 64: return launch_from_plan<64, 96, 2>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 128: return launch_from_plan<128, 64, 1>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
+}
+
+// One-shot call: inspector, then the two compute launches.
 inline int hybrid_forward(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off,
                           const uint32_t* col, float* m, float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk,
                           int use_nan, char* ws, cudaStream_t st) {
-  switch (d) {
-    case 32: return launch_hybrid<32, 96, 2>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
-    case 64: return launch_hybrid<64, 96, 2>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
-    case 128: return launch_hybrid<128, 64, 1>(Q, K, V, row_off, col, m, l, O, n_rows, nnz, Lk, use_nan, ws, st);
-  }
-  return SPFA_ERR_EMBED_DIM;
+  const int rc = build_plan(d, row_off, col, n_rows, nnz, Lk, ws, use_nan, O, st);
+  if (rc) return rc;
+  return forward_from_plan(d, Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
 }
 
 // ---- scratch for the allocation-free COO entry point ---------------------------------------------------
@@ -412,6 +450,68 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const u
   if (hy == 1) return hybrid_forward(d, Q, K, V, ptr, col_ind, m, l, O, n_rows, nnz, Lk, use_nan, rest, st);
   CsrCols cols{ptr, col_ind, Lk};
   return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+}
+
+// ---- stored plans for explicit masks ---------------------------------------------------------------------
+// Plan region = [row offsets: n_rows + 1 x u64][the inspector's output, laid out as in a one-shot call].
+size_t spfa_explicit_plan_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
+  if (!hybrid_shape_ok(d, n_rows, nnz, Lk)) return 0;
+  return spfa_coo_min_workspace_bytes(n_rows) + hybrid_layout(n_rows, nnz, Lk, d).total;
+}
+
+int spfa_csr_plan_build(const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz, int64_t n_rows, int64_t Lk, int d,
+                        void* plan, size_t plan_bytes, void* stream) {
+  if (!row_off || !col_ind || n_rows <= 0 || nnz <= 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
+  if (need == 0) return supported_d(d) ? (int)SPFA_ERR_BAD_ARG : (int)SPFA_ERR_EMBED_DIM;
+  int rc = check_workspace(plan, plan_bytes, need);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* offs = reinterpret_cast<uint64_t*>(plan);
+  if (cudaMemcpyAsync(offs, row_off, (size_t)(n_rows + 1) * sizeof(uint64_t), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+    return SPFA_ERR_LAUNCH;
+  return build_plan(d, offs, col_ind, n_rows, nnz, Lk, static_cast<char*>(plan) + spfa_coo_min_workspace_bytes(n_rows), 0,
+                    nullptr, st);
+}
+
+int spfa_coo_plan_build(const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz, int64_t row_begin, int64_t n_rows,
+                        int64_t Lk, int d, void* plan, size_t plan_bytes, void* stream) {
+  if (!row_ind || !col_ind || n_rows <= 0 || nnz <= 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31))
+    return SPFA_ERR_BAD_ARG;
+  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
+  if (need == 0) return supported_d(d) ? (int)SPFA_ERR_BAD_ARG : (int)SPFA_ERR_EMBED_DIM;
+  int rc = check_workspace(plan, plan_bytes, need);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* offs = reinterpret_cast<uint64_t*>(plan);
+  int64_t blocks = (nnz + 1 + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, offs);
+  g_launches.fetch_add(1);
+  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  return build_plan(d, offs, col_ind, n_rows, nnz, Lk, static_cast<char*>(plan) + spfa_coo_min_workspace_bytes(n_rows), 0,
+                    nullptr, st);
+}
+
+int spfa_planned_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                             int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan, const void* plan,
+                             size_t plan_bytes, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (n_rows <= 0 || nnz <= 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
+  if (need == 0) return SPFA_ERR_BAD_ARG;
+  rc = check_workspace(plan, plan_bytes, need);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* base = static_cast<char*>(const_cast<void*>(plan));
+  const uint64_t* offs = reinterpret_cast<const uint64_t*>(base);
+  if (use_nan) {
+    nan_fill_empty_rows_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(offs, O, n_rows, d);
+    g_launches.fetch_add(1);
+    if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  }
+  return forward_from_plan(d, Q, K, V, offs, m, l, O, n_rows, nnz, Lk, base + spfa_coo_min_workspace_bytes(n_rows), st);
 }
 
 int64_t spfa_coo_static_max_rows(void) { return kStaticCooMaxRows; }

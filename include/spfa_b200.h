@@ -105,6 +105,31 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V,
                          int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- stored plans for explicit masks ---------------------------------------------------------------
+ * No counterpart in the reference (its callers rebuild nothing between calls because its kernels inspect
+ * nothing). The dense-tile split of a CSR/COO mask depends on the mask only, so a caller that applies one
+ * mask many times (layers, heads, training steps) can run the inspector once:
+ *
+ *   bytes = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);           0: shape not supported by the split
+ *   spfa_csr_plan_build(...) or spfa_coo_plan_build(...)            fills `plan` (device memory, 256-B aligned)
+ *   spfa_planned_forward_f32(Q, K, V, m, l, O, ..., plan, bytes)    any number of times, any Q/K/V
+ *
+ * The plan holds everything the forward call needs of the mask (row offsets, residual column list, tile bit
+ * masks); the mask arrays themselves may be freed after the build. n_rows, nnz, Lk and d must be the values
+ * the plan was built with. The plan is read-only in spfa_planned_forward_f32, so concurrent calls may share it.
+ * Same results as a one-shot call that takes the split (TF32 accuracy class for entries in dense tiles). */
+size_t spfa_explicit_plan_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d);
+int spfa_csr_plan_build(const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                        int64_t n_rows, int64_t Lk, int d,
+                        void* plan, size_t plan_bytes, void* stream);
+int spfa_coo_plan_build(const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                        int64_t row_begin, int64_t n_rows, int64_t Lk, int d,
+                        void* plan, size_t plan_bytes, void* stream);
+int spfa_planned_forward_f32(const float* Q, const float* K, const float* V,
+                             float* m, float* l, float* O,
+                             int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan,
+                             const void* plan, size_t plan_bytes, void* stream);
+
 /* ---- explicit COO mask, allocation-free variant ---------------------------------------------------
  * No counterpart in the reference (its COO kernel needs no scratch because it re-scans the row array
  * for every row, sp_flatt_coo_kernel.cu:47-79).

@@ -614,3 +614,38 @@ def test_explicit_dense_tiles_with_very_long_residual_rows(capi, orc):
     assert capi.last_csr_dense_tiles() > 0
     assert_state_close(to_np(st), want, TOL_TILED, "long residual rows")
     capi.set_path(capi.PATH_AUTO)
+
+
+def test_stored_plan_matches_one_shot_calls(capi, orc, pkg):
+    """A plan built once serves several forward calls (other Q/K/V, chained states, use_nan) with the results of
+    the one-shot call that takes the split; through the C ABI and through the torch modules."""
+    L, Lk, d = 700, 900, 64
+    mask = _band_plus_random(L, Lk, 40, 0.003, 23, empty_rows=(0, 333))
+    row_off, col = _csr_of(mask)
+    rows = np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)
+    p_csr = capi.csr_plan(dev(row_off), dev(col), Lk, d)
+    p_coo = capi.coo_plan(dev(rows), dev(col), L, Lk, d)
+    mods = {n: pkg.binding(n) for n in ("spfa_csr", "spfa_coo")}
+    t_csr = mods["spfa_csr"].plan(dev(row_off), dev(col), Lk, d)
+    t_coo = mods["spfa_coo"].plan(dev(rows), dev(col), L, Lk, d)
+    for seed in (1, 2):
+        Q, K, V = seeded_qkv(L, d, 500 + seed, Lk)
+        want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+        for plan in (p_csr, p_coo):
+            st = capi.new_state(L, d)
+            capi.planned_forward(dev(Q), dev(K), dev(V), *st, plan, use_nan=True)
+            assert capi.last_path() == capi.PATH_TILED
+            assert_state_close(to_np(st), want, TOL_TILED, "planned forward")
+        for name, t in (("spfa_csr", t_csr), ("spfa_coo", t_coo)):
+            st = capi.new_state(L, d)
+            out = mods[name].forward_planned(dev(Q), dev(K), dev(V), t, int(col.size), *st, True)
+            assert out.data_ptr() == st[2].data_ptr()
+            assert_state_close(to_np(st), want, TOL_TILED, name + ".forward_planned")
+    # chained on an existing state, without NaN fill
+    Q, K, V = seeded_qkv(L, d, 509, Lk)
+    _, off_a, col_a = random_csr(L, Lk, 0.01, 2)
+    first = orc.csr_forward(Q, K, V, off_a, col_a)
+    want = orc.csr_forward(Q, K, V, row_off, col, state=tuple(x.copy() for x in first))
+    st = state_to_dev(first)
+    capi.planned_forward(dev(Q), dev(K), dev(V), *st, p_csr)
+    assert_state_close(to_np(st), want, TOL_TILED, "planned forward, chained")
