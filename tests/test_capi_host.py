@@ -83,6 +83,15 @@ def test_argument_validation_without_gpu(pkg):
     assert big >= (1 << 27) * 4 + lib.spfa_coo_min_workspace_bytes(1 << 20)
     assert lib.spfa_csr_workspace_bytes(1 << 20, 1 << 27, 1 << 20, 16) == 0          # d = 16 has no tiled path
     assert lib.spfa_csr_forward_f32(p, p, p, None, p, 10, p, p, p, L, L, d, 0, None, 0, None) == -1
+    # stored plans: sizes and argument checks (no launch without a GPU)
+    need = lib.spfa_explicit_plan_bytes(L, 5000, L, d)
+    assert need > lib.spfa_coo_min_workspace_bytes(L) + 4 * 5000
+    assert lib.spfa_explicit_plan_bytes(L, 5000, L, 16) == 0 and lib.spfa_explicit_plan_bytes(L, 0, L, d) == 0
+    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, d, None, 0, None) == -3         # no plan memory
+    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 16, p, need, None) == -1        # d without a tiled path
+    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 48, p, need, None) == -2        # d not supported at all
+    assert lib.spfa_coo_plan_build(None, p, 5000, 0, L, L, d, p, need, None) == -1
+    assert lib.spfa_planned_forward_f32(p, p, p, p, p, p, L, 5000, L, d, 0, p, need - 1, None) == -3
 
 
 def test_capi_refuses_cpu_tensors(pkg):

@@ -649,3 +649,45 @@ def test_stored_plan_matches_one_shot_calls(capi, orc, pkg):
     st = state_to_dev(first)
     capi.planned_forward(dev(Q), dev(K), dev(V), *st, p_csr)
     assert_state_close(to_np(st), want, TOL_TILED, "planned forward, chained")
+
+
+def test_full_size_coo_graph_split_vs_gather_and_oracle(capi, orc):
+    """The benchmark's COO graph generator at L=262144 (4.2e7 entries; rows of up to 8k keys): the dense-tile
+    split (taken by AUTO at this size) against the exact gather path on every row, against the oracle on sampled
+    row windows, and the constant-V property (every output equals the constant)."""
+    import bench
+
+    L, d = 262144, 64
+    dev_ = torch.device("cuda")
+    rows, cols = bench.make_coo_graph(L, 64, 1005, dev_)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    Q, K, V = (torch.randn(L, d, device="cuda", generator=g) for _ in range(3))
+    capi.set_path(capi.PATH_AUTO)
+    st = capi.new_state(L, d)
+    capi.coo_forward(Q, K, V, rows, cols, *st, use_nan=True)
+    assert capi.last_path() == capi.PATH_TILED
+    capi.set_path(capi.PATH_GATHER)
+    sg = capi.new_state(L, d)
+    capi.coo_forward(Q, K, V, rows, cols, *sg, use_nan=True)
+    capi.set_path(capi.PATH_AUTO)
+    assert torch.equal(torch.isnan(st[2]), torch.isnan(sg[2]))
+    assert (st[2] - sg[2]).abs().nan_to_num().max().item() <= TOL_TILED
+    assert torch.allclose(st[1], sg[1], rtol=4e-3, atol=TOL_TILED)
+    # oracle on row windows (edges, interior, and the window around the longest row)
+    counts = torch.bincount(rows, minlength=L)
+    longest = int(counts.argmax())
+    Qc, Kc, Vc = Q.cpu().numpy(), K.cpu().numpy(), V.cpu().numpy()
+    for rb in (0, L // 2, L - 300, max(0, min(L - 300, longest - 150))):
+        re = rb + 300
+        e = torch.searchsorted(rows, torch.tensor([rb, re], device="cuda"))
+        lo, hi = int(e[0]), int(e[1])
+        want = orc.coo_forward(Qc[rb:re], Kc, Vc, rows[lo:hi].cpu().numpy(), cols[lo:hi].cpu().numpy(), use_nan=True,
+                               row_begin=rb)
+        got = tuple(t[rb:re].detach().cpu().double().numpy() for t in st)
+        assert_state_close(got, want, TOL_TILED, f"rows {rb}:{re}")
+    # constant V
+    Vk = torch.full_like(V, -1.25)
+    sk = capi.new_state(L, d)
+    capi.coo_forward(Q, K, Vk, rows, cols, *sk, use_nan=False)
+    live = counts > 0
+    assert (sk[2][live] + 1.25).abs().max().item() <= TOL_TILED
