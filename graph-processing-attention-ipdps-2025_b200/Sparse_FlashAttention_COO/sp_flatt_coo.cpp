@@ -8,6 +8,14 @@ torch::Tensor spfa_coo_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
                                     torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
                                     torch::Tensor O, bool use_nan) {
   using namespace spfa_binding;
+  if (needs_float32_copy(Q)) {
+    TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
+    torch::Tensor w32 = W_val.to(torch::kFloat32);
+    return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
+                                             torch::Tensor ll, torch::Tensor oo) {
+      spfa_coo_cuda_forward(q, k, v, W_row_ind, W_col_ind, w32, mm, ll, oo, use_nan);
+    });
+  }
   check_qkv_state(Q, K, V, m, l, O);
   TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
   TORCH_CHECK(W_row_ind.dim() == 1 && W_col_ind.dim() == 1 && W_row_ind.size(0) == W_col_ind.size(0),

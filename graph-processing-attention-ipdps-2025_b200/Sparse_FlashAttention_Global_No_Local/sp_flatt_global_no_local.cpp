@@ -10,6 +10,12 @@ torch::Tensor spfa_global_no_local_cuda_forward(torch::Tensor Q, torch::Tensor K
                                                 torch::Tensor l, torch::Tensor O, torch::Tensor global_inds,
                                                 int local_size_each_dir) {
   using namespace spfa_binding;
+  if (needs_float32_copy(Q)) {
+    return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
+                                             torch::Tensor ll, torch::Tensor oo) {
+      spfa_global_no_local_cuda_forward(q, k, v, mm, ll, oo, global_inds, local_size_each_dir);
+    });
+  }
   check_qkv_state(Q, K, V, m, l, O);
   TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");
   TORCH_CHECK(global_inds.dim() == 1, "global_inds must be 1-D");

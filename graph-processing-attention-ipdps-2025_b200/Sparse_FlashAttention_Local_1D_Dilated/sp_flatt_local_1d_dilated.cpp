@@ -10,6 +10,12 @@ torch::Tensor spfa_local_1d_dilated_cuda_forward(torch::Tensor Q, torch::Tensor 
                                                  torch::Tensor l, torch::Tensor O, int local_size_each_dir,
                                                  int dil_factor) {
   using namespace spfa_binding;
+  if (needs_float32_copy(Q)) {
+    return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
+                                             torch::Tensor ll, torch::Tensor oo) {
+      spfa_local_1d_dilated_cuda_forward(q, k, v, mm, ll, oo, local_size_each_dir, dil_factor);
+    });
+  }
   check_qkv_state(Q, K, V, m, l, O);
   TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");
   c10::cuda::CUDAGuard guard(Q.device());

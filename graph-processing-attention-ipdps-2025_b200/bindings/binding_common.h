@@ -45,8 +45,8 @@ inline void check_qkv_state(const torch::Tensor& Q, const torch::Tensor& K, cons
                             const torch::Tensor& m, const torch::Tensor& l, const torch::Tensor& O) {
   TORCH_CHECK(Q.dim() == 2 && K.dim() == 2 && V.dim() == 2 && O.dim() == 2, "Q, K, V, O must be 2-D [L, d]");
   TORCH_CHECK(m.dim() == 1 && l.dim() == 1, "m and l must be 1-D [L]");
-  TORCH_CHECK(Q.scalar_type() == torch::kFloat32,
-              "spfa_b200 computes in float32; got ", Q.scalar_type(), " (float16/float64 I/O is not built)");
+  TORCH_CHECK(Q.scalar_type() == torch::kFloat32, "spfa_b200: internal error, float32 tensors expected here, got ",
+              Q.scalar_type());
   for (const torch::Tensor* t : {&K, &V, &m, &l, &O}) {
     TORCH_CHECK(t->scalar_type() == Q.scalar_type(), "expected all floating tensors to share Q's dtype");
     TORCH_CHECK(t->device() == Q.device(), "expected all tensors on Q's device");
@@ -55,6 +55,33 @@ inline void check_qkv_state(const torch::Tensor& Q, const torch::Tensor& K, cons
   TORCH_CHECK(K.size(1) == d && V.size(1) == d && O.size(1) == d, "K, V, O must have Q's embedded dimension");
   TORCH_CHECK(K.size(0) == V.size(0), "K and V must have the same number of rows");
   TORCH_CHECK(O.size(0) == L && m.size(0) == L && l.size(0) == L, "O, m, l must have Q's number of rows");
+}
+
+// The reference dispatches over double, float and half (AT_DISPATCH_FLOATING_TYPES_AND_HALF,
+// Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:270). The kernels here compute in float32 (TF32 on the tiled
+// path), so tensors of another floating dtype are converted on the way in and (m, l, O) are written back in their
+// own dtype: float16 / bfloat16 results are at least as accurate as arithmetic in that dtype would be, float64
+// results carry float32 accuracy (a stated difference from the reference, which computes in double there).
+inline bool needs_float32_copy(const torch::Tensor& Q) {
+  const auto t = Q.scalar_type();
+  if (t == torch::kFloat32) return false;
+  TORCH_CHECK(t == torch::kFloat16 || t == torch::kBFloat16 || t == torch::kFloat64,
+              "spfa_b200: Q, K, V, m, l, O must be float32, float16, bfloat16 or float64; got ", t);
+  return true;
+}
+
+// f(Q32, K32, V32, m32, l32, O32) runs the float32 path on converted copies; the state is copied back in place.
+template <class F>
+torch::Tensor via_float32(const torch::Tensor& Q, const torch::Tensor& K, const torch::Tensor& V, torch::Tensor m,
+                          torch::Tensor l, torch::Tensor O, F&& f) {
+  for (const torch::Tensor* t : std::initializer_list<const torch::Tensor*>{&K, &V, &m, &l, &O})
+    TORCH_CHECK(t->scalar_type() == Q.scalar_type(), "expected all floating tensors to share Q's dtype");
+  torch::Tensor m32 = m.to(torch::kFloat32), l32 = l.to(torch::kFloat32), O32 = O.to(torch::kFloat32);
+  f(Q.to(torch::kFloat32), K.to(torch::kFloat32), V.to(torch::kFloat32), m32, l32, O32);
+  m.copy_(m32);
+  l.copy_(l32);
+  O.copy_(O32);
+  return O;
 }
 
 inline const uint64_t* u64_ptr(const torch::Tensor& t, const char* name) {

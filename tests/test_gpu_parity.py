@@ -691,3 +691,31 @@ def test_full_size_coo_graph_split_vs_gather_and_oracle(capi, orc):
     capi.coo_forward(Q, K, Vk, rows, cols, *sk, use_nan=False)
     live = counts > 0
     assert (sk[2][live] + 1.25).abs().max().item() <= TOL_TILED
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 4e-3), (torch.bfloat16, 3e-2), (torch.float64, TOL_TILED)])
+def test_torch_modules_accept_the_reference_dtypes(pkg, orc, dtype, tol):
+    """The reference dispatches over double, float and half; here such tensors are converted around the float32
+    kernels and (m, l, O) come back in their own dtype, in place."""
+    L, d = 300, 32
+    Q, K, V = seeded_qkv(L, d, 88)
+    q, k, v = (dev(x).to(dtype) for x in (Q, K, V))
+    Qr, Kr, Vr = (x.float().cpu().numpy() for x in (q, k, v))  # the values the kernels actually see
+    m = torch.full((L,), float("-inf"), device="cuda", dtype=dtype)
+    l = torch.zeros(L, device="cuda", dtype=dtype)
+    O = torch.zeros(L, d, device="cuda", dtype=dtype)
+    out = pkg.binding("spfa_local").forward(q, k, v, m, l, O, 40)
+    assert out.data_ptr() == O.data_ptr() and O.dtype == dtype and m.dtype == dtype
+    wm, wl, wO = orc.implicit_forward("local", Qr, Kr, Vr, 40)
+    assert (O.double().cpu().numpy() - wO).__abs__().max() <= tol
+    assert np.allclose(l.double().cpu().numpy(), wl, rtol=max(tol, 1e-2))
+    # explicit mask with use_nan: NaN rows survive the conversion back
+    _, row_off, col = random_csr(L, L, 0.05, 7, empty_rows=(4,))
+    m.fill_(float("-inf")); l.zero_(); O.zero_()
+    pkg.binding("spfa_csr").forward(q, k, v, dev(row_off.astype(np.int64)).view(torch.uint64),
+                                    dev(col.astype(np.int32)).view(torch.uint32), torch.ones(1, device="cuda", dtype=dtype),
+                                    m, l, O, True)
+    _, _, wO = orc.csr_forward(Qr, Kr, Vr, row_off, col, use_nan=True)
+    got = O.double().cpu().numpy()
+    assert np.isnan(got[4]).all() and np.array_equal(np.isnan(got), np.isnan(wO))
+    assert np.nanmax(np.abs(got - wO)) <= tol
