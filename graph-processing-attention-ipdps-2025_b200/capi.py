@@ -203,7 +203,7 @@ def last_csr_dense_tiles() -> int:
     buf, p, d = _last_csr_workspace
     off = p - buf.data_ptr()
     words = int(buf[off:off + 8].view(torch.int64).item())  # the plan's mask pool counter sits first
-    return words // ((2 if d == 128 else 3) * 128)
+    return words // (2 * 128)  # 64-key tiles: two 32-bit mask words per row
 
 
 def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):

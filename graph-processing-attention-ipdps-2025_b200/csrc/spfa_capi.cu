@@ -181,13 +181,13 @@ struct HybridLayout {
 
 inline bool hybrid_shape_ok(int d, int64_t n_rows, int64_t nnz, int64_t Lk) {
   if (!(d == 32 || d == 64 || d == 128) || n_rows <= 0 || nnz <= 0 || Lk <= 0) return false;
-  const int bn = (d == 128) ? 64 : 96;
+  const int bn = tile_bn(d);
   return explicit_plan_smem_bytes((Lk + bn - 1) / bn, bn) <= (size_t)kPlanMaxSmem;
 }
 
 inline HybridLayout hybrid_layout(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
   HybridLayout h;
-  h.bn = (d == 128) ? 64 : 96;
+  h.bn = tile_bn(d);
   h.n_key_tiles = (int)((Lk + h.bn - 1) / h.bn);
   h.min_entries = 128 * h.bn / kDenseDivisor;
   h.n_blocks = (n_rows + 127) / 128;
@@ -253,8 +253,7 @@ int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, in
 inline int build_plan(int d, const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk,
                       char* ws, int use_nan, float* O, cudaStream_t st) {
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, d);
-  return (h.bn == 96) ? launch_plan<96>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st)
-                      : launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
+  return launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
 }
 
 // Rows without any mask entry get a NaN output row (what the inspector does in a one-shot call, for calls that
@@ -269,9 +268,11 @@ __global__ void nan_fill_empty_rows_kernel(const uint64_t* __restrict__ row_off,
 }
 
 // The two compute launches of the split, from a filled plan region: dense tiles, then everything else.
-template <int D, int BN, int NS>
+template <int D>
 int launch_from_plan(const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m, float* l,
                      float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
+  constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
+  static_assert(BN == 64, "the inspector builds masks for 64-key tiles");
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
   const ExplicitPlan plan = plan_view(h, ws);
   tile::BandParams prm{};
@@ -290,7 +291,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, Lk, pitch, BN) ||
       !make_row_map(&tmV, V, D, Lk, pitch, BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
-  int rc = launch_band_raw<D, BN, NS, 2, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + 255) / 256)), st);
+  int rc = launch_band_raw<D, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
   if (rc) return rc;
   // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
   const float scale = 1.0f / sqrtf((float)D);
@@ -309,9 +310,9 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
 inline int forward_from_plan(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m,
                              float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
   switch (d) {
-    case 32: return launch_from_plan<32, 96, 2>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
-    case 64: return launch_from_plan<64, 96, 2>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
-    case 128: return launch_from_plan<128, 64, 1>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 32: return launch_from_plan<32>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 64: return launch_from_plan<64>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 128: return launch_from_plan<128>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
   }
   return SPFA_ERR_EMBED_DIM;
 }

@@ -22,6 +22,19 @@ constexpr int64_t kTileMaxStride = 16;
 
 extern std::atomic<int64_t> g_launches;
 
+// Kernel shape per head dimension. d <= 64: one 128-row sub-tile per CTA, 64-key tiles, two K and two V stages
+// (96 KB of shared memory, 256 TMEM columns, 128 registers x 256 threads), so that TWO CTAs share an SM and one
+// CTA's prologue, epilogue and softmax phases overlap the other's MMAs. d = 128: the Q tile alone is 64 KB per
+// sub-tile, two such CTAs do not fit; one CTA of two sub-tiles per SM, one K and one V stage.
+template <int D>
+struct TileCfg {
+  static constexpr int BN = 64, NS = (D == 128) ? 1 : 2, NSV = NS, NSUB = (D == 128) ? 2 : 1;
+  static constexpr int kRows = 128 * NSUB, kCtasPerSm = (D == 128) ? 1 : 2;
+};
+inline int tile_bn(int /*d*/) { return 64; }
+inline int tile_rows_per_cta(int d) { return d == 128 ? 256 : 128; }
+inline int tile_ctas_per_sm(int d) { return d == 128 ? 1 : 2; }
+
 // Error word of the tiled kernels (bounded waits record a code here). One per device context.
 __device__ int g_tile_error;
 
@@ -60,12 +73,14 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
 }
 
 // Common launch steps of band_forward_kernel: shared-memory opt-in, register-budget guard, error word.
-template <int D, int BN, int NS, int NSUB, bool EXPL = false>
+template <int D, bool EXPL = false>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
                     const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
-  using P = tile::Plan<D, BN, NS, NSUB>;
+  using C = TileCfg<D>;
+  constexpr int NSUB = C::NSUB;
+  using P = tile::Plan<D, C::BN, C::NS, NSUB, C::NSV>;
   using G = tile::Geo<NSUB>;
-  auto kern = tile::band_forward_kernel<D, BN, NS, NSUB, EXPL>;
+  auto kern = tile::band_forward_kernel<D, C::BN, C::NS, NSUB, EXPL, C::NSV>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
   cudaFuncAttributes attr;
@@ -78,10 +93,11 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
 }
 
-template <int D, int BN, int NS, int NSUB>
+template <int D>
 int launch_band(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t w,
                 int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
-  using G = tile::Geo<NSUB>;
+  using C = TileCfg<D>;
+  constexpr int BN = C::BN;
   for (int64_t r = 0; r < s && r < L; ++r) {
     tile::BandParams prm{};
     prm.n_keys = (L - r + s - 1) / s;
@@ -101,9 +117,9 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
     if (!make_row_map(&tmQ, Q + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128) ||
         !make_row_map(&tmK, K + r * D, D, prm.n_keys, pitch, BN) || !make_row_map(&tmV, V + r * D, D, prm.n_keys, pitch, BN, /*mn_major=*/true))
       return SPFA_ERR_LAUNCH;
-    const int64_t grid = (prm.n_q + G::kQRows - 1) / G::kQRows;
+    const int64_t grid = (prm.n_q + C::kRows - 1) / C::kRows;
     if (grid > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
-    const int rc = launch_band_raw<D, BN, NS, NSUB>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid), st);
+    const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid), st);
     if (rc) return rc;
   }
   return SPFA_OK;
@@ -117,9 +133,9 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
   if (!shape_ok) return forced ? (int)SPFA_ERR_BAD_ARG : SPFA_TILE_NOT_TAKEN;
   if (!forced && w < kTileMinHalfWidth) return SPFA_TILE_NOT_TAKEN;
   switch (d) {
-    case 32: return launch_band<32, 96, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 64: return launch_band<64, 96, 2, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 128: return launch_band<128, 64, 1, 2>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 32: return launch_band<32>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 64: return launch_band<64>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 128: return launch_band<128>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
   }
   return SPFA_TILE_NOT_TAKEN;
 }
@@ -189,10 +205,10 @@ struct GnlTiledPlan {
 inline GnlTiledPlan gnl_tiled_plan(int64_t L, int d, int64_t nG) {
   auto up = [](size_t x) { return (x + 255) / 256 * 256; };
   GnlTiledPlan p;
-  p.bn = (d == 128) ? 64 : 96;
+  p.bn = tile_bn(d);
   const int64_t tiles = (L + p.bn - 1) / p.bn;
-  const int64_t q_tiles = (nG + 255) / 256;
-  int64_t ctas = 148 / q_tiles;
+  const int64_t q_tiles = (nG + tile_rows_per_cta(d) - 1) / tile_rows_per_cta(d);
+  int64_t ctas = 148 * tile_ctas_per_sm(d) / q_tiles;
   if (ctas < 1) ctas = 1;
   int64_t chunk_tiles = (tiles + ctas - 1) / ctas;
   if (chunk_tiles < 2) chunk_tiles = 2;
@@ -213,7 +229,7 @@ inline bool gnl_tiled_shape_ok(int d, int64_t nG) {
   return (d == 32 || d == 64 || d == 128) && nG >= 1 && nG <= kGnlTiledMaxGlobals;
 }
 
-template <int D, int BN, int NS>
+template <int D>
 int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, float* l, float* O, const int32_t* G,
                      int64_t nG, int64_t L, int64_t w, int64_t row_begin, int64_t row_end, char* ws,
                      const GnlTiledPlan& plan, bool ordinary_rows_too, cudaStream_t st) {
@@ -230,6 +246,7 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
                                                                       KG, VG, live);
   g_launches.fetch_add(1);
   if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+  constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
   const int64_t pitch = D * (int64_t)sizeof(float);
   const int64_t n_rows = row_end - row_begin;
   tile::BandParams prm{};
@@ -250,7 +267,8 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
       !make_row_map(&tmV, VG, D, nG, pitch, BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
   int rc = SPFA_OK;
-  if (ordinary_rows_too) rc = launch_band_raw<D, BN, NS, 2>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + 255) / 256)), st);
+  if (ordinary_rows_too)
+    rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
   if (rc) return rc;
   // mode 2: the gathered global rows against every key, key range split over grid.y
   prm.mode = 2;
@@ -264,8 +282,8 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   if (!make_row_map(&tmQ, QG, D, nG, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, BN) ||
       !make_row_map(&tmV, V, D, L, pitch, BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
-  rc = launch_band_raw<D, BN, NS, 2>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((nG + 255) / 256), (unsigned)plan.n_split),
-                                     st);
+  rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm,
+                          dim3((unsigned)((nG + kRows - 1) / kRows), (unsigned)plan.n_split), st);
   if (rc) return rc;
   combine_partials_kernel<D><<<(unsigned)nG, kGatherWarps * 32, 0, st>>>(
       partials, sorted, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
@@ -278,9 +296,9 @@ inline int tiled_gnl_forward(const float* Q, const float* K, const float* V, flo
                              int64_t row_end, char* ws, bool ordinary_rows_too, cudaStream_t st) {
   const GnlTiledPlan plan = gnl_tiled_plan(L, d, nG);
   switch (d) {
-    case 32: return launch_gnl_tiled<32, 96, 2>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
-    case 64: return launch_gnl_tiled<64, 96, 2>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
-    case 128: return launch_gnl_tiled<128, 64, 1>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+    case 32: return launch_gnl_tiled<32>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+    case 64: return launch_gnl_tiled<64>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+    case 128: return launch_gnl_tiled<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
   }
   return SPFA_ERR_EMBED_DIM;
 }

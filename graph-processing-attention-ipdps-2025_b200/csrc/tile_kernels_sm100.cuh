@@ -267,7 +267,7 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int b_mn_major) 
 }
 
 // ---- shared-memory plan --------------------------------------------------------------------------------
-template <int D, int BN, int NS, int NSUB>
+template <int D, int BN, int NS, int NSUB, int NSV = NS>  // NS: K stages, NSV: V stages
 struct Plan {
   static constexpr int kChunks = D / 32;                    // 32-float (128 B) column chunks per row
   static constexpr int kQChunkBytes = 128 * 128;            // 128 rows x 128 B
@@ -277,9 +277,9 @@ struct Plan {
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + kQBytes;
   static constexpr int kOffV = kOffK + NS * kKVStageBytes;
-  static constexpr int kOffBar = kOffV + NS * kKVStageBytes;
-  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NS], v_empty[NS], s_ready[2 NSUB], p_ready[2 NSUB], o_ready[2 NSUB] (one per S buffer / tile parity)
-  static constexpr int kNumBars = 1 + 4 * NS + 6 * NSUB;
+  static constexpr int kOffBar = kOffV + NSV * kKVStageBytes;
+  // barriers: q_full, k_full[NS], k_empty[NS], v_full[NSV], v_empty[NSV], s_ready[2 NSUB], p_ready[2 NSUB], o_ready[2 NSUB] (one per S buffer / tile parity)
+  static constexpr int kNumBars = 1 + 2 * NS + 2 * NSV + 6 * NSUB;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
   static constexpr int kOffCoef = (kOffMisc + 16 + 15) / 16 * 16;  // epilogue: 256 floats per sub-tile
   // explicit masks: merged key-tile list of the CTA: kt[64] (int), act[NSUB] (u64, bit j = sub-tile uses tile j;
@@ -294,12 +294,12 @@ struct Plan {
   static_assert(kColO + NSUB * D <= kTmemCols, "S buffers and O accumulators exceed the TMEM allocation");
 };
 
-template <int D, int BN, int NS, int NSUB, bool EXPL = false>
+template <int D, int BN, int NS, int NSUB, bool EXPL = false, int NSV = NS>
 __global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, float* __restrict__ m_out, float* __restrict__ l_out,
                     float* __restrict__ O_out, const BandParams prm, int* __restrict__ err) {
-  using P = Plan<D, BN, NS, NSUB>;
+  using P = Plan<D, BN, NS, NSUB, NSV>;
   using G = Geo<NSUB>;
   constexpr int kQRows = G::kQRows;
   constexpr int W_TMA = G::kSoftmaxWarps, W_MMA = G::kSoftmaxWarps + 1;
@@ -308,8 +308,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + P::kOffBar;
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  const int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 1 + NS, B_VFULL = 1 + 2 * NS, B_VEMPTY = 1 + 3 * NS,
-            B_SREADY = 1 + 4 * NS, B_PREADY = B_SREADY + 2 * NSUB, B_OREADY = B_SREADY + 4 * NSUB;
+  const int B_QFULL = 0, B_KFULL = 1, B_KEMPTY = 1 + NS, B_VFULL = 1 + 2 * NS, B_VEMPTY = 1 + 2 * NS + NSV,
+            B_SREADY = 1 + 2 * NS + 2 * NSV, B_PREADY = B_SREADY + 2 * NSUB, B_OREADY = B_SREADY + 4 * NSUB;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + P::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
 #ifdef SPFA_TILE_TRACE
@@ -385,6 +385,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int s = 0; s < NS; ++s) {
       mbar_init(bar(B_KFULL + s), 1);
       mbar_init(bar(B_KEMPTY + s), 1);
+    }
+    for (int s = 0; s < NSV; ++s) {
       mbar_init(bar(B_VFULL + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
     }
@@ -476,25 +478,33 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c = 0; c < P::kChunks; ++c)
           tma_load_2d(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes, &tmQ, c * 32, yq + 128 * x,
                       bar(B_QFULL));
+      // K runs NS tiles ahead of V (the S MMAs are issued ahead of the softmax, the PV MMAs behind it), so the
+      // order is K(0..NS-1), then V(j), K(j+NS) for every tile j: a wait for a V stage never holds back a K tile
+      // that the MMA thread needs first.
       bool ok = true;
-      for (int j = 0; j < nT && ok; ++j) {
+      auto load_k = [&](int j) -> bool {
         const int st = j % NS;
-        const uint32_t ph = (uint32_t)((j / NS) & 1);
-        const int32_t yk = tile_key0(j);
-        ok = mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, err, 101);
-        if (!ok) break;
+        if (!mbar_wait(bar(B_KEMPTY + st), (uint32_t)((j / NS) & 1) ^ 1u, abort_flag, err, 101)) return false;
         mbar_expect_tx(bar(B_KFULL + st), P::kKVStageBytes);
+        const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
           tma_load_2d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmK, c * 32, yk,
                       bar(B_KFULL + st));
-        ok = mbar_wait(bar(B_VEMPTY + st), ph ^ 1u, abort_flag, err, 102);
+        return true;
+      };
+      for (int j = 0; j < NS && j < nT && ok; ++j) ok = load_k(j);
+      for (int j = 0; j < nT && ok; ++j) {
+        const int st = j % NSV;
+        ok = mbar_wait(bar(B_VEMPTY + st), (uint32_t)((j / NSV) & 1) ^ 1u, abort_flag, err, 102);
         if (!ok) break;
         mbar_expect_tx(bar(B_VFULL + st), P::kKVStageBytes);
+        const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
           tma_load_2d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmV, c * 32, yk,
                       bar(B_VFULL + st));
+        if (j + NS < nT) ok = load_k(j + NS);
       }
     }
   } else if (warp == W_MMA) {
@@ -522,7 +532,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_commit(bar(B_SREADY + sb));
       };
       auto issue_PV = [&](int x, int j) {
-        const int st = j % NS;
+        const int st = j % NSV;
         const int it = it_of(x, j);
         const int sb = x * 2 + (it & 1);
         // 8 keys per MMA = two 4-row swizzle groups (stride 512 B); 32-dim blocks are kKVChunkBytes apart
@@ -556,8 +566,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = ok && issue_S_tile(0);
       ok = ok && issue_S_tile(1);
       for (int j = 0; j < nT && ok; ++j) {
-        const int st = j % NS;
-        const uint32_t ph = (uint32_t)((j / NS) & 1);
+        const int st = j % NSV;
+        const uint32_t ph = (uint32_t)((j / NSV) & 1);
         bool have_v = false;
         for (int x = 0; x < NSUB && ok; ++x) {
           if (!active(x, j)) continue;
