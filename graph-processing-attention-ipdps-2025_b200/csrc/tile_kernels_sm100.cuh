@@ -1,16 +1,15 @@
 // Tiled tensor-core path for banded masks on sm_100a: TMA-staged K/V tiles, tcgen05 TF32 MMAs with
 // TMEM accumulators, online softmax in registers.
 //
-// One CTA owns 256 consecutive query rows of a (strided) row sequence, as two 128-row sub-tiles A and
-// B, and walks the key tiles (BN keys each) that intersect the band |u_q - u_k| <= w. A kernel that
-// allocates TMEM runs one CTA per SM on this toolchain (the occupancy API reports 1 for any kernel
-// containing tcgen05.alloc), so all overlap is arranged inside the CTA. Roles (384 threads):
-//   warps 0-3  softmax group A   thread t <-> query row t of sub-tile A  <-> TMEM lane t
-//   warps 4-7  softmax group B
-//   warp  8    TMA producer (one elected lane) + TMEM allocation
-//   warp  9    MMA issuer (one elected lane)
-//   warps 10-11 idle (they complete the third warpgroup so registers can be re-balanced:
-//              setmaxnreg gives the softmax groups 216 registers/thread and leaves 72 to this group)
+// One CTA owns 128 * NSUB consecutive query rows of a (strided) row sequence, as NSUB 128-row sub-tiles, and
+// walks the key tiles (BN keys each) that intersect the band |u_q - u_k| <= w. Two shapes are launched:
+// NSUB = 1 for d <= 64, sized so that two CTAs share an SM and fill each other's gaps (the occupancy API
+// reports 1 CTA/SM for any kernel containing tcgen05.alloc; the hardware does co-schedule them), and NSUB = 2
+// for d = 128, where one CTA interleaves its two sub-tiles on the tensor pipe. Roles (128 * NSUB + 128 threads):
+//   warps 0 .. 4 NSUB-1  softmax groups, one per sub-tile: thread t <-> query row t <-> TMEM lane t
+//   next warp            TMA producer (one elected lane) + TMEM allocation
+//   next warp            MMA issuer (one elected lane)
+//   last two warps       idle (they complete the last warpgroup so registers can be re-balanced with setmaxnreg)
 // Per key tile j and sub-tile X (S has two TMEM buffers per sub-tile, used alternately):
 //   S_X = Q_X K_j^T      tcgen05.mma kind::tf32, A = Q_X (smem, K-major), B = K_j (smem, K-major), D in TMEM;
 //                         issued TWO tiles ahead of the softmax group, so that group never waits for it
@@ -19,8 +18,8 @@
 //                         reference that moves only when the row maximum outgrows it by 2^8)
 //   O_X += P_X V_j       tcgen05.mma kind::tf32, A = P_X (TMEM), B = V_j (smem, MN-major), D stays in TMEM
 //                         for the whole CTA; a row whose reference moves rescales its own O row in TMEM
-// MMA issue order per key tile j: PV_A(j), PV_B(j), S_A(j+2), S_B(j+2). TMEM: 4 S buffers of BN columns +
-// 2 O accumulators of d columns <= 512 columns (BN = 96 for d <= 64, BN = 64 for d = 128).
+// MMA issue order per key tile j: PV_X(j) for every sub-tile, then S_X(j+2). TMEM per CTA: 2 NSUB S buffers of
+// BN columns + NSUB O accumulators of d columns <= 256 NSUB columns.
 // Epilogue: O rows leave TMEM through shared memory (the dead Q tile) so that the read-modify-write of
 // the caller's O is coalesced.
 //
@@ -63,8 +62,8 @@ constexpr int kTraceSlots = 3, kTraceCap = 400;  // slot 0: MMA thread, 1: softm
 #endif
 
 // Geometry of a CTA with NSUB 128-row sub-tiles: NSUB softmax warpgroups + one warpgroup holding the
-// TMA warp, the MMA warp and two idle warps. NSUB = 2 is what the dispatcher launches (the sub-tiles
-// interleave on the tensor pipe inside the CTA); NSUB = 1 is kept as a smaller variant of the same code.
+// TMA warp, the MMA warp and two idle warps. NSUB = 1 (two CTAs per SM) serves d <= 64, NSUB = 2 (one CTA per
+// SM, the sub-tiles interleave on the tensor pipe inside the CTA) serves d = 128.
 //
 // Register re-balancing. A CTA is launched with Geo::kRegsLaunch registers per thread (what the compiler
 // assigns under __launch_bounds__(kThreads, kCtasPerSm)). setmaxnreg.inc BLOCKS until the CTA's pool can

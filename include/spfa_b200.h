@@ -76,7 +76,7 @@ int spfa_last_path(void);
  * The reference's W_val argument is never read by the reference kernel and is not part of the ABI.
  *
  * Dense-tile split (north of ~1e6 entries under SPFA_PATH_AUTO, always under SPFA_PATH_TILED, d in
- * {32, 64, 128}): the rows are cut into 128-row blocks and the keys into tiles of 96 (d = 128: 64) rows; a
+ * {32, 64, 128}): the rows are cut into 128-row blocks and the keys into tiles of 64 rows; a
  * (block, tile) pair holding at least 1/24 of its possible entries runs on the tcgen05 tiled kernel under a
  * bit mask (TF32 accuracy class), all other entries on the FP32 gather kernel. It is taken only if the
  * workspace is at least spfa_csr_workspace_bytes(); with a smaller (or no) workspace every entry takes the
