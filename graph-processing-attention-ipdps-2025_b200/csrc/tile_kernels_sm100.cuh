@@ -379,6 +379,11 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 
   // ---- setup ----
+  if (threadIdx.x == 64) {  // descriptor fetches off the first loads' critical path
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+  }
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 1);
     for (int s = 0; s < NS; ++s) {
