@@ -253,7 +253,8 @@ int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, in
 inline int build_plan(int d, const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk,
                       char* ws, int use_nan, float* O, cudaStream_t st) {
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, d);
-  return launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
+  return (h.bn == 64) ? launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st)
+                      : launch_plan<32>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
 }
 
 // Rows without any mask entry get a NaN output row (what the inspector does in a one-shot call, for calls that
@@ -272,7 +273,6 @@ template <int D>
 int launch_from_plan(const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m, float* l,
                      float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
   constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
-  static_assert(BN == 64, "the inspector builds masks for 64-key tiles");
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
   const ExplicitPlan plan = plan_view(h, ws);
   tile::BandParams prm{};
