@@ -6,7 +6,7 @@
 // into the caller's (m, l, O) state, so their order does not matter and the result is the union.
 //
 // explicit_plan_kernel does the split, one CTA per 128-row block:
-//   1. histogram of the block's entries over ALL key tiles (shared memory, one counter per tile)
+//   1. histogram of the block's entries over ALL key tiles (shared memory, one 16-bit counter per tile)
 //   2. the tiles with at least `min_entries` entries, ascending, at most kMaxDenseTiles, become "dense"
 //   3. bit masks of the dense tiles are built in shared memory; a tile in which some (row, key) pair occurs
 //      twice is demoted (a bit cannot say "twice", and the reference counts such a key twice)
@@ -70,7 +70,7 @@ struct ResidualCols {
 };
 
 inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
-  const size_t hist = (size_t)n_key_tiles * 4;
+  const size_t hist = (size_t)(n_key_tiles + 1) / 2 * 4;  // 16-bit counters, two per word
   const size_t masks = (size_t)tile::kMaxDenseTiles * (bn / 32) * 128 * 4;
   const size_t words = (size_t)(n_key_tiles + 31) / 32;
   return (hist > masks ? hist : masks) + words * 4 + (words + 3) / 4 * 4;
@@ -96,8 +96,13 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   constexpr uint32_t kNoKey = 0xffffffffu;
   extern __shared__ uint32_t plan_smem[];
   const int n_words = (n_key_tiles + 31) / 32;
-  const int region = (n_key_tiles > MAXT * NC * 128) ? n_key_tiles : MAXT * NC * 128;
-  uint32_t* hist = plan_smem;                 // [n_key_tiles] entry counts            (steps 1-2)
+  const int n_hist_words = (n_key_tiles + 1) / 2;
+  const int region = (n_hist_words > MAXT * NC * 128) ? n_hist_words : MAXT * NC * 128;
+  // Entry counts as 16-bit halves of 32-bit words. A count beyond 65535 (only possible with heavily duplicated
+  // entries) carries into its neighbour: that can only change which tiles are CALLED dense, never the result,
+  // because masks and residual lists are built from the entries themselves.
+  uint32_t* hist = plan_smem;                 // [(n_key_tiles + 1) / 2]               (steps 1-2)
+  auto count_of = [&](int k) -> uint32_t { return (hist[k >> 1] >> ((k & 1) * 16)) & 0xffffu; };
   uint32_t* masks = plan_smem;                // [MAXT][NC][128], same storage         (steps 3-4)
   uint32_t* dense_bits = plan_smem + region;  // [n_words] bit k: key tile k is dense
   uint8_t* dense_before = reinterpret_cast<uint8_t*>(dense_bits + n_words);  // [n_words] dense tiles in earlier words
@@ -113,7 +118,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const int64_t r0 = b * 128;
   const int nr = (int)((n_rows - r0 < 128) ? (n_rows - r0) : 128);
   if (tid <= nr) s_off[tid] = row_off[r0 + tid];
-  for (int k = tid; k < n_key_tiles; k += kPlanThreads) hist[k] = 0;
+  for (int k = tid; k < n_hist_words; k += kPlanThreads) hist[k] = 0;
   for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
   __syncthreads();
@@ -132,7 +137,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
       const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
       bool lead;
       const int end = run_end_of(kt, lane, &lead);
-      if (lead && kt != kNoKey) atomicAdd(&hist[kt], (uint32_t)(end - lane));
+      if (lead && kt != kNoKey) atomicAdd(&hist[kt >> 1], (uint32_t)(end - lane) << ((kt & 1) * 16));
     }
   }
   __syncthreads();
@@ -141,7 +146,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const int per = (n_key_tiles + kPlanThreads - 1) / kPlanThreads;
   const int k_lo = tid * per, k_hi = (k_lo + per < n_key_tiles) ? (k_lo + per) : n_key_tiles;
   int mine = 0;
-  for (int k = k_lo; k < k_hi; ++k) mine += (hist[k] >= (uint32_t)min_entries);
+  for (int k = k_lo; k < k_hi; ++k) mine += (count_of(k) >= (uint32_t)min_entries);
   int incl = mine;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -155,7 +160,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   if (tid == kPlanThreads - 1) s_nt = (before + mine < MAXT) ? (before + mine) : MAXT;
   if (mine > 0)
     for (int k = k_lo; k < k_hi && before < MAXT; ++k)
-      if (hist[k] >= (uint32_t)min_entries) {
+      if (count_of(k) >= (uint32_t)min_entries) {
         s_sel[before++] = k;
         atomicOr(&dense_bits[k >> 5], 1u << (k & 31));
       }
