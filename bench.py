@@ -526,13 +526,26 @@ def cpu_baseline(job, budget):
     spec = importlib.util.spec_from_file_location("spfa_dense_sdpa", os.path.join(ROOT, "oracle", "dense_sdpa.py"))
     ds = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ds)
-    if job.kind in ("csr", "coo"):
-        return {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-                "sample": "not timed for explicit masks in this run"}
     q, k, v = job.Q.cpu(), job.K.cpu(), job.V.cpu()
     G = job.G_cpu if job.kind == "global_no_local" else None
-    chunk = 1024 if job.L <= 65536 else 512
-    r = ds.time_dense_cpu(job.kind, q, k, v, job.p0, job.p1, G, chunk_rows=chunk, budget_s=budget, max_chunks=64)
+    chunk = 1024 if job.L <= 65536 else (512 if job.L <= 262144 else 128)
+    mask_fn = None
+    if job.kind in ("csr", "coo"):  # explicit masks: scatter the chunk's entries into a dense boolean chunk
+        if job.kind == "csr":
+            row_off, cols = job.mask[0].cpu(), job.mask[1].cpu().long()
+        else:
+            rows, cols = job.mask[0].cpu(), job.mask[1].cpu().long()
+            row_off = torch.searchsorted(rows, torch.arange(job.L + 1))
+            del rows
+
+        def mask_fn(r0, r1):
+            lo, hi = int(row_off[r0]), int(row_off[r1])
+            m = torch.zeros(r1 - r0, job.L, dtype=torch.bool)
+            rr = torch.repeat_interleave(torch.arange(r1 - r0), (row_off[r0 + 1:r1 + 1] - row_off[r0:r1]))
+            m[rr, cols[lo:hi]] = True
+            return m
+    r = ds.time_dense_cpu(job.kind, q, k, v, job.p0, job.p1, G, chunk_rows=chunk, budget_s=budget, max_chunks=64,
+                          mask_fn=mask_fn)
     val = 4.0 * r["nnz"] * job.d / r["seconds"] / 1e12
     return {"value": val, "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
             "sample": f"{r['chunks']} evenly spaced chunks of {chunk} rows x all {job.L} keys ({r['rows']} of {job.L} rows), "

@@ -45,23 +45,25 @@ def sdpa_rows(q_rows: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torc
 
 def time_dense_cpu(kind: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, p0: int, p1: int = 0, G=None,
                    chunk_rows: int = 1024, budget_s: float = 15.0, max_chunks: int | None = None,
-                   nnz_of_rows=None):
+                   nnz_of_rows=None, mask_fn=None):
     """Time the dense masked SDPA-MATH path on evenly spaced row chunks until ~budget_s is spent.
 
     Returns dict(seconds, rows, chunks, nnz, threads, cores). `nnz_of_rows(r0, r1)` gives the mask
     non-zeros of a row range (for the effective nnz-FLOP/s figure); mask construction is outside the
-    timed region, as it is in the reference script."""
+    timed region, as it is in the reference script. `mask_fn(r0, r1)` replaces the closed-form mask chunk
+    (explicit masks: the caller scatters its CSR/COO entries into a dense boolean chunk)."""
+    chunk_of = mask_fn if mask_fn is not None else (lambda a, b: mask_chunk(kind, q.shape[0], a, b, p0, p1, G))
     L = q.shape[0]
     n_chunks_total = (L + chunk_rows - 1) // chunk_rows
-    plan = max_chunks or n_chunks_total
+    plan = min(max_chunks or n_chunks_total, n_chunks_total)
     starts = [int(c * n_chunks_total / plan) * chunk_rows for c in range(plan)]
     # warm-up on one chunk (thread pool, allocator)
-    m0 = mask_chunk(kind, L, 0, min(chunk_rows, L), p0, p1, G)
+    m0 = chunk_of(0, min(chunk_rows, L))
     sdpa_rows(q[: m0.shape[0]], k, v, m0)
     spent, rows, nnz, done = 0.0, 0, 0, 0
     for r0 in starts:
         r1 = min(L, r0 + chunk_rows)
-        mask = mask_chunk(kind, L, r0, r1, p0, p1, G)
+        mask = chunk_of(r0, r1)
         t0 = time.perf_counter()
         sdpa_rows(q[r0:r1], k, v, mask)
         spent += time.perf_counter() - t0
