@@ -240,6 +240,9 @@ def parse_args():
     ap.add_argument("--planned", action="store_true",
                     help="csr/coo/blocks: build the dense-tile plan once outside the timed region and time forward calls "
                          "from the stored plan (a caller that applies one mask many times); default: one-shot calls")
+    ap.add_argument("--e2e-whole", action="store_true",
+                    help="end-to-end leg: copy whole tensors, one forward call through the torch module, copy O back "
+                         "(default for banded masks of 48 MB or more per tensor on one GPU: the chunked host pipeline of hostio.py)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
     return ap.parse_args()
@@ -444,7 +447,17 @@ def run_ours(args, rank, world, dev):
         plan_t = (binding.plan(job.mask[0], job.mask[1], job.L, job.d) if job.kind == "csr"
                   else binding.plan(job.mask[0], job.mask[1], job.L_local, job.L, job.d))
 
+    pipe = None
+    # chunking pays once a chunk's copies are large (measured: 8 chunks of 3 x 2 MB gain nothing on cfg2, whose
+    # host->device stream slows down by as much as the overlapped device->host copies save; 3 x 8 MB chunks gain 12 %)
+    if (world == 1 and job.kind in ("local", "local_1d_dilated", "local_2d_dilated") and not args.e2e_whole
+            and job.L * job.d * 4 >= (48 << 20)):
+        pipe = pkg.hostio.BandedHostPipeline(job.kind, job.L, job.d, job.p0, job.p1, n_chunks=8, device=dev)
+
     def e2e_step():
+        if pipe is not None:  # chunked: copies in, row-range calls and copies out overlap
+            pipe.forward(hQ, hK, hV, hO, use_nan=True)
+            return
         dQ.copy_(hQ, non_blocking=True)
         dKs.copy_(hK, non_blocking=True)
         dVs.copy_(hV, non_blocking=True)
@@ -509,7 +522,10 @@ def run_ours(args, rank, world, dev):
         "fwd_ms": total_ms / args.steps,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h,
-                "api": "spfa_%s.forward (torch extension)" % job.kind if world == 1 else "capi.*_forward(row range) + sharding.replicate_kv (NCCL all-gather)"},
+                "api": ("hostio.BandedHostPipeline.forward: 8 row chunks, host->device copies, row-range C-ABI calls and "
+                        "device->host copies overlapped on three streams" if pipe is not None else
+                        "spfa_%s.forward (torch extension), whole-tensor copies" % job.kind) if world == 1
+                else "capi.*_forward(row range) + sharding.replicate_kv (NCCL all-gather)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roof,

@@ -7,7 +7,9 @@ Drop-in for the six operators of KLab-AI3/Graph-Processing-Attention-IPDPS-2025.
   ``forward`` signatures (``import spfa_csr`` etc. once :func:`add_bindings_to_path` ran, or via
   :func:`binding`);
 * :mod:`capi` -- a ctypes view of the C ABI that takes torch CUDA tensors (row-range sharding lives
-  here, it has no counterpart in the reference's single-GPU API).
+  here, it has no counterpart in the reference's single-GPU API);
+* :mod:`hostio` -- forward calls on pinned HOST buffers for the banded masks, with the copies and the row-range
+  kernels overlapped.
 
 The directory name is not a valid Python identifier; load the package with ``importlib`` (see
 ``load()`` in the repository's ``__graft_entry__.py``) under the name ``spfa_b200``.
@@ -49,6 +51,6 @@ def binding(name: str):
 
 
 def __getattr__(attr):
-    if attr in ("capi", "sharding", "build"):
+    if attr in ("capi", "sharding", "build", "hostio"):
         return importlib.import_module(f"{__name__}.{attr}")
     raise AttributeError(attr)

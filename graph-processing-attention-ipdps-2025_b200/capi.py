@@ -184,8 +184,9 @@ def csr_forward(Q, K, V, row_off, col_ind, m, l, O, use_nan=False):
         n_rows, d = Q.shape
         nnz = col_ind.shape[0]
         buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, nnz, K.shape[0], d), dev)
-        global _last_csr_workspace
-        _last_csr_workspace = (buf, wp.value if wp else 0, d)
+        if KEEP_LAST_CSR_WORKSPACE:  # diagnostics only: keeps the scratch buffer alive until the next call
+            global _last_csr_workspace
+            _last_csr_workspace = (buf, wp.value if wp else 0, d)
         check(lib().spfa_csr_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)),
                                          nnz, _ptr(m), _ptr(l), _ptr(O), n_rows, K.shape[0], d, int(use_nan), wp,
                                          wb, _stream(dev)))
@@ -193,6 +194,7 @@ def csr_forward(Q, K, V, row_off, col_ind, m, l, O, use_nan=False):
 
 
 _last_csr_workspace = None
+KEEP_LAST_CSR_WORKSPACE = False  # set True to make last_csr_dense_tiles() meaningful (tests do)
 
 
 def last_csr_dense_tiles() -> int:

@@ -20,7 +20,9 @@ def capi(pkg):
     assert torch.cuda.is_available()
     c = pkg.capi
     c.lib()
+    c.KEEP_LAST_CSR_WORKSPACE = True  # last_csr_dense_tiles() reads the plan's counters
     yield c
+    c.KEEP_LAST_CSR_WORKSPACE = False
     c.set_path(c.PATH_AUTO)
 
 
@@ -719,3 +721,22 @@ def test_torch_modules_accept_the_reference_dtypes(pkg, orc, dtype, tol):
     got = O.double().cpu().numpy()
     assert np.isnan(got[4]).all() and np.array_equal(np.isnan(got), np.isnan(wO))
     assert np.nanmax(np.abs(got - wO)) <= tol
+
+
+@pytest.mark.parametrize("kind,L,d,p0,p1", [("local", 3000, 64, 100, 0), ("local", 700, 32, 650, 0),
+                                            ("local_1d_dilated", 2500, 64, 60, 2), ("local_2d_dilated", 2048, 64, 128, 3)])
+def test_host_pipeline_matches_oracle(pkg, orc, kind, L, d, p0, p1):
+    """Pinned host buffers in, pinned host buffer out, rows cut into chunks with overlapping copies and calls."""
+    Q, K, V = seeded_qkv(L, d, 600 + L)
+    hQ, hK, hV = (torch.from_numpy(x).pin_memory() for x in (Q, K, V))
+    hO = torch.full((L, d), 7.0).pin_memory()
+    pipe = pkg.hostio.BandedHostPipeline(kind, L, d, p0, p1, n_chunks=5)
+    assert len(pipe.edges) >= 3 or L <= 700
+    for _ in range(2):  # buffers and streams are reused across calls
+        pipe.forward(hQ, hK, hV, hO, use_nan=True)
+        torch.cuda.current_stream().synchronize()
+        _, _, want = orc.implicit_forward(kind, Q, K, V, p0, p1, use_nan=True)
+        got = hO.double().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.nanmax(np.abs(got - want)) <= TOL_TILED
+        hO.fill_(7.0)
