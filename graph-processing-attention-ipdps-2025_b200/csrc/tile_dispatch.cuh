@@ -91,7 +91,21 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
   if (attr.numRegs * G::kThreads < G::kRegsSoftmax * 128 * NSUB + G::kRegsAux * 128) return SPFA_ERR_LAUNCH;
   int* err = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
-  kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
+  if (prm.overlap & 2) {  // may start while the previous launch of the stream is still running (see BandParams)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(G::kThreads);
+    cfg.dynamicSmemBytes = P::kDynSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, m, l, O, prm, err) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  } else {
+    kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
+  }
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
 }
@@ -101,6 +115,7 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
                 int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
   using C = TileCfg<D>;
   constexpr int BN = C::BN;
+  bool launched = false;  // residue classes write disjoint rows: consecutive launches may overlap
   for (int64_t r = 0; r < s && r < L; ++r) {
     tile::BandParams prm{};
     prm.n_keys = (L - r + s - 1) / s;
@@ -122,8 +137,10 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
       return SPFA_ERR_LAUNCH;
     const int64_t grid = (prm.n_q + C::kRows - 1) / C::kRows;
     if (grid > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+    prm.overlap = ((r + 1 < s && r + 1 < L) ? 1 : 0) | (launched ? 2 : 0);
     const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid), st);
     if (rc) return rc;
+    launched = true;
   }
   return SPFA_OK;
 }
@@ -270,11 +287,14 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
       !make_row_map(&tmV, VG, D, nG, pitch, BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
   int rc = SPFA_OK;
+  // the two launches write disjoint things (ordinary rows / partial states of the listed rows): they may overlap
+  prm.overlap = 1;
   if (ordinary_rows_too)
     rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
   if (rc) return rc;
   // mode 2: the gathered global rows against every key, key range split over grid.y
   prm.mode = 2;
+  prm.overlap = ordinary_rows_too ? 2 : 0;
   prm.n_keys = L;
   prm.u_q_first = 0;
   prm.n_q = nG;

@@ -111,6 +111,11 @@ struct BandParams {
   // The query rows are cut into 128-row blocks (= sub-tiles); block b has x_nt[b] <= kMaxDenseTiles dense key
   // tiles, numbered x_kt[b*kMaxDenseTiles + t] (ascending; tile k covers keys [k*BN, (k+1)*BN)), and for its
   // t-th tile a bit mask of valid (row, key) pairs at x_masks[x_moff[b] + (t*(BN/32) + chunk)*128 + row].
+  // ---- overlap with a neighbouring launch of this kernel that touches other rows (dilated masks: one launch
+  // per residue class). Bit 0: let the next launch of the stream start as soon as every CTA of this one has
+  // started (griddepcontrol.launch_dependents); bit 1: this launch was started that way, so it must not
+  // complete before its predecessor has (griddepcontrol.wait before the CTA exits). ----
+  int overlap;
   const int* x_nt;
   const int* x_kt;
   const long long* x_moff;
@@ -379,6 +384,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 
   // ---- setup ----
+  if ((prm.overlap & 1) && threadIdx.x == 96) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (threadIdx.x == 64) {  // descriptor fetches off the first loads' critical path
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
@@ -933,6 +939,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // ---- common exit: everyone is done with TMEM before it is released ----
   tc_fence_before();
   __syncthreads();
+  // started early beside its predecessor: completion order (and with it everything later in the stream) must
+  // still see the predecessor finished
+  if ((prm.overlap & 2) && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
 #ifdef SPFA_TILE_TRACE
   if (threadIdx.x == 0 && blockIdx.x < 8192) g_cta_times[blockIdx.x][1] = globaltimer();
   if (blockIdx.x == 1 && threadIdx.x == 0 && gridDim.x < 64) {
