@@ -210,6 +210,16 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
         if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
         kept += __popc(bal);
         if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
+        const uint32_t word0 = __shfl_sync(kFullMask, word, 0);
+        if (word0 != kNoKey && __all_sync(kFullMask, word == word0)) {
+          // the usual case of a sorted row inside a band: all 32 entries fall into one mask word
+          const uint32_t all = __reduce_or_sync(kFullMask, bit);
+          if (lane == 0) {
+            const uint32_t old = atomicOr(&masks[word0], all);
+            if ((old & all) != 0u || all != 0xffffffffu) s_dirty[word0 / (NC * 128)] = 1;
+          }
+          continue;
+        }
         // OR of the bits of each run of equal words, at the run's first lane (suffix scan by doubling)
         bool lead;
         const int end = run_end_of(word, lane, &lead);
