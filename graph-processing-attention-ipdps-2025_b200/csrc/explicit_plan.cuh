@@ -30,7 +30,8 @@
 namespace spfa {
 
 constexpr int kPlanThreads = 512;
-constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread (the passes are latency bound)
+constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread in the row walks
+constexpr int kPlanHistUnroll = 8;  // ... and in the flat histogram pass
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kPlanMaxSmem = 200 * 1024;
 
@@ -125,15 +126,15 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const int64_t e0 = (int64_t)s_off[0], e1 = (int64_t)s_off[nr];
 
   // ---- 1. histogram over key tiles ----
-  for (int64_t base = e0; base < e1; base += kPlanThreads * kPlanUnroll) {  // every warp runs whole iterations
-    uint32_t cu[kPlanUnroll];
+  for (int64_t base = e0; base < e1; base += kPlanThreads * kPlanHistUnroll) {  // every warp runs whole iterations
+    uint32_t cu[kPlanHistUnroll];
 #pragma unroll
-    for (int u = 0; u < kPlanUnroll; ++u) {
+    for (int u = 0; u < kPlanHistUnroll; ++u) {
       const int64_t e = base + u * kPlanThreads + tid;
       cu[u] = (e < e1) ? __ldg(col + e) : kNoKey;
     }
 #pragma unroll
-    for (int u = 0; u < kPlanUnroll; ++u) {
+    for (int u = 0; u < kPlanHistUnroll; ++u) {
       const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
       bool lead;
       const int end = run_end_of(kt, lane, &lead);
@@ -142,28 +143,35 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   }
   __syncthreads();
 
-  // ---- 2. dense tiles, ascending: each thread scans a contiguous range of tiles ----
-  const int per = (n_key_tiles + kPlanThreads - 1) / kPlanThreads;
-  const int k_lo = tid * per, k_hi = (k_lo + per < n_key_tiles) ? (k_lo + per) : n_key_tiles;
-  int mine = 0;
-  for (int k = k_lo; k < k_hi; ++k) mine += (count_of(k) >= (uint32_t)min_entries);
-  int incl = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int v = __shfl_up_sync(kFullMask, incl, o);
-    if (lane >= o) incl += v;
+  // ---- 2. dense tiles, ascending: each warp scans a contiguous range of tiles, 32 at a time (lane <-> tile,
+  //         so the ballot of a step is the step's word of dense_bits and the shared-memory reads do not conflict) ----
+  const int per_w = ((n_key_tiles + kPlanWarps - 1) / kPlanWarps + 31) / 32 * 32;
+  const int w_lo = warp * per_w, w_hi = (w_lo + per_w < n_key_tiles) ? (w_lo + per_w) : n_key_tiles;
+  int mine = 0;  // dense tiles in this warp's range (warp-uniform)
+  for (int k0 = w_lo; k0 < w_hi; k0 += 32) {
+    const int k = k0 + lane;
+    mine += __popc(__ballot_sync(kFullMask, k < w_hi && count_of(k) >= (uint32_t)min_entries));
   }
-  if (lane == 31) s_warp_cnt[warp] = incl;
+  if (lane == 0) s_warp_cnt[warp] = mine;
   __syncthreads();
-  int before = incl - mine;
-  for (int wv = 0; wv < warp; ++wv) before += s_warp_cnt[wv];
-  if (tid == kPlanThreads - 1) s_nt = (before + mine < MAXT) ? (before + mine) : MAXT;
-  if (mine > 0)
-    for (int k = k_lo; k < k_hi && before < MAXT; ++k)
-      if (count_of(k) >= (uint32_t)min_entries) {
-        s_sel[before++] = k;
-        atomicOr(&dense_bits[k >> 5], 1u << (k & 31));
-      }
+  int before = 0, total = 0;
+  for (int wv = 0; wv < kPlanWarps; ++wv) {
+    before += (wv < warp) ? s_warp_cnt[wv] : 0;
+    total += s_warp_cnt[wv];
+  }
+  if (tid == 0) s_nt = (total < MAXT) ? total : MAXT;
+  if (mine > 0 && before < MAXT)
+    for (int k0 = w_lo; k0 < w_hi; k0 += 32) {
+      const int k = k0 + lane;
+      const bool dense = k < w_hi && count_of(k) >= (uint32_t)min_entries;
+      const uint32_t bal = __ballot_sync(kFullMask, dense);
+      const int idx = before + __popc(bal & ((1u << lane) - 1u));
+      const bool keep = dense && idx < MAXT;
+      const uint32_t kept = __ballot_sync(kFullMask, keep);
+      if (keep) s_sel[idx] = k;
+      if (lane == 0 && kept) dense_bits[k0 >> 5] = kept;  // w_lo is a multiple of 32: one word per step
+      before += __popc(bal);
+    }
   __syncthreads();  // the histogram is dead from here on: its storage becomes the masks
   const int nt = s_nt;
   for (int w = tid; w < n_words; w += kPlanThreads) {
