@@ -35,8 +35,10 @@ __host__ __device__ constexpr size_t block2d_smem_bytes(int64_t n) {
   return (size_t)((n * (D + 1) + 3) / 4 * 4 + n * D + kBlockWarps * (D + ((n + 31) / 32) * 32)) * sizeof(float);
 }
 
+// Few keys per lane leave room for seven CTAs per SM (36 registers per thread, ~30 KB of shared memory each):
+// 1036 slots, so that the 1024 blocks of the 262144-row configuration are one wave instead of one and a bit.
 template <int D, int NK>  // NK = keys per lane (n <= 32 NK)
-__global__ void __launch_bounds__(kBlockWarps * 32)
+__global__ void __launch_bounds__(kBlockWarps * 32, (NK <= 2) ? 7 : 1)
 local2d_block_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                      float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Block2dParams prm) {
   extern __shared__ float smem_f[];
@@ -136,14 +138,18 @@ local2d_block_kernel(const float* __restrict__ Q, const float* __restrict__ K, c
     }
   }
 
-  // ---- dead rows: NaN fill ----
+  // ---- dead rows: NaN fill (32-bit index arithmetic: B < 2^31; one modulo per row, RPI rows per warp store) ----
   if (prm.use_nan && prm.s > 1) {
     const float nn = __int_as_float(0x7fc00000);
     const float4 nan4 = make_float4(nn, nn, nn, nn);
-    for (int64_t idx = threadIdx.x; idx < prm.B * C4; idx += blockDim.x) {
-      const int64_t rr = idx / C4, i = start + rr;
-      if (rr % prm.s == 0 || i < prm.row_begin || i >= prm.row_end) continue;
-      reinterpret_cast<float4*>(O + (size_t)(i - prm.row_begin) * D)[idx % C4] = nan4;
+    constexpr int RPI = (C4 >= 32) ? 1 : 32 / C4;  // rows covered by one warp-wide float4 store
+    const int B = (int)prm.B, s32 = (int)prm.s;
+    for (int r_base = warp * RPI; r_base < B; r_base += kBlockWarps * RPI) {
+      const int rr = r_base + lane / C4;
+      const int64_t i = start + rr;
+      if (rr >= B || rr % s32 == 0 || i < prm.row_begin || i >= prm.row_end) continue;
+      float4* row = reinterpret_cast<float4*>(O + (size_t)(i - prm.row_begin) * D);
+      for (int c = lane % C4; c < C4; c += 32) row[c] = nan4;
     }
   }
 }
