@@ -401,19 +401,21 @@ gather_split_rows_kernel(const float* __restrict__ Q, const float* __restrict__ 
   }
 }
 
-// One CTA (four warps) per list entry: folds that entry's n_split partial states into (m, l, O).
+// One CTA (kCombineWarps warps) per list entry: folds that entry's n_split partial states into (m, l, O).
 // The partial maxima are reduced first, so the accumulation over splits has no serial dependency: every
-// warp takes a quarter of the splits with several loads in flight, and the four warp results are merged
-// through shared memory.
+// warp takes its share of the splits with several loads in flight, and the warp results are summed through
+// shared memory in a fixed order.
+constexpr int kCombineWarps = 16;
+
 template <int D>
-__global__ void __launch_bounds__(kGatherWarps * 32)
+__global__ void __launch_bounds__(kCombineWarps * 32)
 combine_partials_kernel(const float* __restrict__ partials, const int32_t* __restrict__ row_list,
                         const uint8_t* __restrict__ entry_live, int n_entries, int64_t row_begin,
                         int64_t row_end, int n_split, float* __restrict__ m, float* __restrict__ l,
                         float* __restrict__ O) {
   constexpr int LPK = D / 4;
-  __shared__ float s_l[kGatherWarps];
-  __shared__ float4 s_acc[kGatherWarps][LPK];
+  __shared__ float s_l[kCombineWarps];
+  __shared__ float4 s_acc[kCombineWarps][LPK];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int e = blockIdx.x;
   if (e >= n_entries) return;
@@ -430,7 +432,7 @@ combine_partials_kernel(const float* __restrict__ partials, const int32_t* __res
   float lsum = 0.f;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-  for (int sp = warp; sp < n_split; sp += kGatherWarps) {
+  for (int sp = warp; sp < n_split; sp += kCombineWarps) {
     const float* part = base + (size_t)sp * (D + 4);
     const float w = fast_exp2((__ldg(part + D) - ms) * kLog2e);
     const float4 a = ldg4(part + sub * 4);
@@ -446,10 +448,17 @@ combine_partials_kernel(const float* __restrict__ partials, const int32_t* __res
   if (warp == 0) {
     RowAcc<D> st;
     st.m = mx;
-    st.l = (s_l[0] + s_l[1]) + (s_l[2] + s_l[3]);
-    const float4 a0 = s_acc[0][sub], a1 = s_acc[1][sub], a2 = s_acc[2][sub], a3 = s_acc[3][sub];
-    st.acc = make_float4((a0.x + a1.x) + (a2.x + a3.x), (a0.y + a1.y) + (a2.y + a3.y), (a0.z + a1.z) + (a2.z + a3.z),
-                         (a0.w + a1.w) + (a2.w + a3.w));
+    st.l = 0.f;
+    st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int wv = 0; wv < kCombineWarps; ++wv) {
+      const float4 a = s_acc[wv][sub];
+      st.l += s_l[wv];
+      st.acc.x += a.x;
+      st.acc.y += a.y;
+      st.acc.z += a.z;
+      st.acc.w += a.w;
+    }
     if (st.l > 0.f) store_row<D>(st, m, l, O, i - row_begin, lane);
   }
 }

@@ -107,7 +107,7 @@ int launch_gnl_global_rows(const float* Q, const float* K, const float* V, float
       Q, K, V, cols, G, live, (int)nG, row_begin, row_end, plan.n_split, plan.slots_per_split, partials, scale);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
-  combine_partials_kernel<D><<<(unsigned)nG, kGatherWarps * 32, 0, st>>>(
+  combine_partials_kernel<D><<<(unsigned)nG, kCombineWarps * 32, 0, st>>>(
       partials, G, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
   g_launches.fetch_add(1);
   return launch_status();

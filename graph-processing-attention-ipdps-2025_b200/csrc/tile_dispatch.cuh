@@ -308,7 +308,7 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm,
                           dim3((unsigned)((nG + kRows - 1) / kRows), (unsigned)plan.n_split), st);
   if (rc) return rc;
-  combine_partials_kernel<D><<<(unsigned)nG, kGatherWarps * 32, 0, st>>>(
+  combine_partials_kernel<D><<<(unsigned)nG, kCombineWarps * 32, 0, st>>>(
       partials, sorted, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
