@@ -740,3 +740,19 @@ def test_host_pipeline_matches_oracle(pkg, orc, kind, L, d, p0, p1):
         assert np.array_equal(np.isnan(got), np.isnan(want))
         assert np.nanmax(np.abs(got - want)) <= TOL_TILED
         hO.fill_(7.0)
+
+
+@pytest.mark.parametrize("L,Lk,d", [(5, 7, 32), (129, 64, 64), (128, 129, 128), (1, 1, 64)])
+def test_explicit_split_on_tiny_and_ragged_shapes(capi, orc, L, Lk, d):
+    """Shapes around the 128-row / 64-key granules of the split, fully dense masks (which may or may not reach
+    the dense-tile threshold): forced onto the split, results as the oracle's either way."""
+    Q, K, V = seeded_qkv(L, d, 900 + L, Lk)
+    mask = np.ones((L, Lk), dtype=bool)
+    row_off, col = _csr_of(mask)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    capi.set_path(capi.PATH_TILED)
+    st = capi.new_state(L, d)
+    capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st, use_nan=True)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want, TOL_TILED, "tiny split")
+    capi.set_path(capi.PATH_AUTO)
