@@ -454,9 +454,29 @@ def run_ours(args, rank, world, dev):
             and job.L * job.d * 4 >= (48 << 20)):
         pipe = pkg.hostio.BandedHostPipeline(job.kind, job.L, job.d, job.p0, job.p1, n_chunks=8, device=dev)
 
+    full_pipe, chunk_call = None, None
+    if (world == 1 and job.kind in ("csr", "coo", "global_no_local") and not args.e2e_whole and not args.planned
+            and job.L * job.d * 4 >= (48 << 20)):
+        full_pipe = pkg.hostio.FullKeyHostPipeline(job.L, job.L, job.d, n_chunks=8, device=dev)
+        if job.kind == "global_no_local":
+            def chunk_call(a, b, q, k, v, m_, l_, o_):
+                capi.global_no_local_forward(q, k, v, m_, l_, o_, job.G, job.p0, a, b)
+        elif job.kind == "coo":
+            cut = torch.searchsorted(job.mask[0], torch.tensor(full_pipe.edges, device=dev)).cpu().tolist()
+
+            def chunk_call(a, b, q, k, v, m_, l_, o_):
+                lo, hi = cut[full_pipe.edges.index(a)], cut[full_pipe.edges.index(b)]
+                capi.coo_forward(q, k, v, job.mask[0][lo:hi], job.mask[1][lo:hi], m_, l_, o_, use_nan=False, row_begin=a)
+        else:
+            def chunk_call(a, b, q, k, v, m_, l_, o_):  # offsets index the full column array
+                capi.csr_forward(q, k, v, job.mask[0][a:b + 1], job.mask[1], m_, l_, o_, use_nan=False)
+
     def e2e_step():
         if pipe is not None:  # chunked: copies in, row-range calls and copies out overlap
             pipe.forward(hQ, hK, hV, hO, use_nan=True)
+            return
+        if full_pipe is not None:  # K, V first, then Q chunks in / row-range calls / O chunks out overlap
+            full_pipe.forward(chunk_call, hQ, hK, hV, hO)
             return
         dQ.copy_(hQ, non_blocking=True)
         dKs.copy_(hK, non_blocking=True)
@@ -524,6 +544,8 @@ def run_ours(args, rank, world, dev):
                 "d2h_bytes_per_step": d2h,
                 "api": ("hostio.BandedHostPipeline.forward: 8 row chunks, host->device copies, row-range C-ABI calls and "
                         "device->host copies overlapped on three streams" if pipe is not None else
+                        "hostio.FullKeyHostPipeline.forward: K and V first, then 8 row chunks of Q in, row-range C-ABI "
+                        "calls and O chunks out overlapped on three streams" if full_pipe is not None else
                         "spfa_%s.forward (torch extension), whole-tensor copies" % job.kind) if world == 1
                 else "capi.*_forward(row range) + sharding.replicate_kv (NCCL all-gather)"},
         "gpu_launches": int(launches),

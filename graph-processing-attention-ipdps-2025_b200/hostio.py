@@ -1,4 +1,4 @@
-"""Forward calls on HOST buffers for the masks whose rows need only nearby keys.
+"""Forward calls on HOST buffers, with the PCIe copies and the kernels overlapped.
 
 For Local, Local-1D-dilated and Local-2D-dilated masks a query row attends to keys within a fixed distance
 (w, w*(dil+1), or its own block), so a row range can be computed as soon as the K/V rows up to its far edge are
@@ -7,7 +7,8 @@ host->device copies of Q/K/V chunks, row-range forward calls through the C ABI (
 device->host copies of finished O chunks. PCIe is full duplex, so the O traffic hides behind the Q/K/V traffic
 and the kernels hide behind both; what remains is the time of the host->device copies.
 
-Masks that need all keys for every row (CSR, COO, Global-no-local) gain nothing from this and are not covered.
+Masks whose rows may attend to any key (CSR, COO, Global-no-local) cannot start before all of K and V have
+arrived; `FullKeyHostPipeline` still overlaps the Q chunks coming in, the row-range calls and the O chunks going out.
 """
 from __future__ import annotations
 
@@ -82,6 +83,63 @@ class BandedHostPipeline:
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(copied[last])
                 self._forward_rows(a, b, use_nan)
+                done[c].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done[c])
+                hO[a:b].copy_(self.O[a:b], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_in)
+        return hO
+
+
+class FullKeyHostPipeline:
+    """Host buffers for the masks whose rows may attend to ANY key (CSR, COO, Global-no-local).
+
+    Nothing can be computed before all of K and V are on the device, but the query side still pipelines: K and
+    V go first, then Q arrives in row chunks while the previous chunk is computed (row-range call through the C
+    ABI) and the chunk before that travels back. The device->host traffic and the kernels hide behind the
+    host->device traffic; what remains is the time of the host->device copies plus the last chunk.
+
+    `call(a, b, Q_ab, K, V, m_ab, l_ab, O_ab)` must enqueue the forward of rows [a, b) on the current stream, e.g.
+    `capi.coo_forward(Q_ab, K, V, rows[lo:hi], cols[lo:hi], m_ab, l_ab, O_ab, row_begin=a)`.
+    """
+
+    def __init__(self, n_rows: int, n_keys: int, d: int, n_chunks: int = 8, device=None):
+        self.n_rows, self.n_keys, self.d = n_rows, n_keys, d
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        rows = -(-max(256, -(-n_rows // n_chunks)) // 256) * 256
+        self.edges = list(range(0, n_rows, rows)) + [n_rows]
+        with torch.cuda.device(self.dev):
+            f = dict(device=self.dev, dtype=torch.float32)
+            self.Q, self.O = torch.empty(n_rows, d, **f), torch.empty(n_rows, d, **f)
+            self.K, self.V = torch.empty(n_keys, d, **f), torch.empty(n_keys, d, **f)
+            self.m, self.l = torch.empty(n_rows, **f), torch.empty(n_rows, **f)
+            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(device=self.dev) for _ in range(3))
+
+    def forward(self, call, hQ, hK, hV, hO):
+        """Fresh state, host in, host out (hO). Asynchronous like BandedHostPipeline.forward."""
+        cur = torch.cuda.current_stream(self.dev)
+        n = len(self.edges) - 1
+        copied = [torch.cuda.Event() for _ in range(n)]
+        done = [torch.cuda.Event() for _ in range(n)]
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(cur)
+        with torch.cuda.stream(self.s_run):
+            self.m.fill_(float("-inf"))
+            self.l.zero_()
+            self.O.zero_()
+        with torch.cuda.stream(self.s_in):
+            self.K.copy_(hK, non_blocking=True)
+            self.V.copy_(hV, non_blocking=True)
+            for c in range(n):
+                a, b = self.edges[c], self.edges[c + 1]
+                self.Q[a:b].copy_(hQ[a:b], non_blocking=True)
+                copied[c].record(self.s_in)
+        for c in range(n):
+            a, b = self.edges[c], self.edges[c + 1]
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(copied[c])
+                call(a, b, self.Q[a:b], self.K, self.V, self.m[a:b], self.l[a:b], self.O[a:b])
                 done[c].record(self.s_run)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done[c])

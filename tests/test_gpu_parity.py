@@ -756,3 +756,35 @@ def test_explicit_split_on_tiny_and_ragged_shapes(capi, orc, L, Lk, d):
     assert capi.last_path() == capi.PATH_TILED
     assert_state_close(to_np(st), want, TOL_TILED, "tiny split")
     capi.set_path(capi.PATH_AUTO)
+
+
+def test_full_key_host_pipeline_matches_oracle(pkg, capi, orc):
+    """COO and Global-no-local through the row-chunked host pipeline (K/V first, Q chunks in, O chunks out)."""
+    L, d = 1500, 64
+    Q, K, V = seeded_qkv(L, d, 321)
+    hQ, hK, hV = (torch.from_numpy(x).pin_memory() for x in (Q, K, V))
+    hO = torch.zeros(L, d).pin_memory()
+    pipe = pkg.hostio.FullKeyHostPipeline(L, L, d, n_chunks=4)
+    mask = _band_plus_random(L, L, 30, 0.01, 2)
+    row_off, col = _csr_of(mask)
+    rows_d, cols_d = dev(np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)), dev(col)
+    cut = torch.searchsorted(rows_d, torch.tensor(pipe.edges, device="cuda")).cpu().tolist()
+
+    def coo_call(a, b, q, k, v, m_, l_, o_):
+        lo, hi = cut[pipe.edges.index(a)], cut[pipe.edges.index(b)]
+        capi.coo_forward(q, k, v, rows_d[lo:hi], cols_d[lo:hi], m_, l_, o_, row_begin=a)
+
+    pipe.forward(coo_call, hQ, hK, hV, hO)
+    torch.cuda.current_stream().synchronize()
+    _, _, want = orc.csr_forward(Q, K, V, row_off, col)
+    assert np.abs(hO.double().numpy() - want).max() <= TOL_GATHER
+    G = np.array([5, 700, 1499, 33], dtype=np.int32)
+    Gd = dev(G)
+
+    def gnl_call(a, b, q, k, v, m_, l_, o_):
+        capi.global_no_local_forward(q, k, v, m_, l_, o_, Gd, 20, a, b)
+
+    pipe.forward(gnl_call, hQ, hK, hV, hO)
+    torch.cuda.current_stream().synchronize()
+    _, _, want = orc.implicit_forward("global_no_local", Q, K, V, 20, G=G)
+    assert np.abs(hO.double().numpy() - want).max() <= TOL_TILED
