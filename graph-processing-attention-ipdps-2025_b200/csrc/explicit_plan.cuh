@@ -29,6 +29,10 @@
 
 namespace spfa {
 
+// Residual rows longer than this are listed and walked by all warps of a CTA at the start of the gather launch:
+// one warp needs about a microsecond per eight scattered keys, so longer rows left to single warps would form
+// the launch's tail.
+constexpr int kListedRowSlots = 128;
 constexpr int kPlanThreads = 512;
 constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread in the row walks
 constexpr int kPlanHistUnroll = 8;  // ... and in the flat histogram pass
@@ -47,7 +51,7 @@ struct ExplicitPlan {
   // residual entries for the gather path
   uint32_t* res_cnt;                // [n_rows]
   uint32_t* res_col;                // [nnz], row r at res_col + row_off[r]
-  // rows whose residual part is longer than kHeavyRowSlots get CTAs of their own (gather_rows_listed_first_kernel)
+  // rows whose residual part is longer than kListedRowSlots get CTAs of their own (gather_rows_listed_first_kernel)
   unsigned int* heavy_count;        // zeroed before the kernel
   int* heavy_rows;                  // [n_rows]
 };
@@ -245,7 +249,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
     }
     if (lane == 0) {
       plan.res_cnt[r0 + rl] = kept;
-      if (kept > (uint32_t)kHeavyRowSlots) plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
+      if (kept > (uint32_t)kListedRowSlots) plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
     }
     if (z <= a && use_nan) {  // a row without any entry
       const float nn = __int_as_float(0x7fc00000);
@@ -319,7 +323,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
     if (lane == 0) {
       const uint32_t before_cnt = plan.res_cnt[r0 + rl];  // listed already if it was long before the demotion
       plan.res_cnt[r0 + rl] = kept;
-      if (kept > (uint32_t)kHeavyRowSlots && before_cnt <= (uint32_t)kHeavyRowSlots)
+      if (kept > (uint32_t)kListedRowSlots && before_cnt <= (uint32_t)kListedRowSlots)
         plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
     }
   }

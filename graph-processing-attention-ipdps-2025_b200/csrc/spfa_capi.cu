@@ -296,7 +296,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
   const float scale = 1.0f / sqrtf((float)D);
   ResidualCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu};
-  ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kHeavyRowSlots};
+  ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots};
   const int64_t row_blocks = (n_rows + kRowWarps - 1) / kRowWarps;
   const int list_blocks = (int)(row_blocks < 512 ? row_blocks : 512);
   if (row_blocks + list_blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
