@@ -210,7 +210,7 @@ inline HybridLayout hybrid_layout(int64_t n_rows, int64_t nnz, int64_t Lk, int d
 // Does this call take the dense-tile split? 1 = yes, 0 = gather path, negative = status to return.
 inline int hybrid_decision(int d, int64_t n_rows, int64_t nnz, int64_t Lk, const void* ws, size_t ws_bytes) {
   const int path = g_path.load();
-  if (path == SPFA_PATH_GATHER) return 0;
+  if (path == SPFA_PATH_GATHER || nnz <= 0) return 0;  // an empty mask has nothing to tile (NaN rows: gather kernel)
   const bool shape = hybrid_shape_ok(d, n_rows, nnz, Lk);
   if (path == SPFA_PATH_TILED && !shape) return SPFA_ERR_BAD_ARG;
   if (!shape || (path == SPFA_PATH_AUTO && nnz < kHybridMinNnz)) return 0;

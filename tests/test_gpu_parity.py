@@ -788,3 +788,39 @@ def test_full_key_host_pipeline_matches_oracle(pkg, capi, orc):
     torch.cuda.current_stream().synchronize()
     _, _, want = orc.implicit_forward("global_no_local", Q, K, V, 20, G=G)
     assert np.abs(hO.double().numpy() - want).max() <= TOL_TILED
+
+
+def test_explicit_split_randomised_against_the_gather_path(capi):
+    """Seeded random masks (bands, dense patches, stray entries; sorted or shuffled rows; sprinkled duplicates):
+    the split must reproduce the exact gather path up to TF32 rounding on every one of them."""
+    rng = np.random.default_rng(2024)
+    for case in range(24):
+        L = int(rng.integers(1, 1800))
+        Lk = int(rng.integers(1, 2600))
+        d = int(rng.choice([32, 64, 128]))
+        mask = rng.random((L, Lk)) < rng.choice([0.0, 0.002, 0.02])
+        if rng.random() < 0.7:  # a band
+            half = int(rng.integers(0, 120))
+            i, j = np.arange(L)[:, None], np.arange(Lk)[None, :]
+            mask |= np.abs(i * Lk // max(L, 1) - j) <= half
+        for _ in range(int(rng.integers(0, 4))):  # dense patches anywhere
+            r0, c0 = int(rng.integers(0, L)), int(rng.integers(0, Lk))
+            mask[r0:r0 + int(rng.integers(1, 300)), c0:c0 + int(rng.integers(1, 300))] |= rng.random() < 0.9
+        row_off, col = _csr_of(mask, shuffle_seed=case if rng.random() < 0.5 else None)
+        if col.size and rng.random() < 0.4:  # duplicate a few entries in place (row lengths unchanged)
+            for _ in range(5):
+                r = int(rng.integers(0, L))
+                a, b = int(row_off[r]), int(row_off[r + 1])
+                if b - a >= 2:
+                    col[a + 1] = col[a]
+        Q, K, V = seeded_qkv(L, d, 3000 + case, Lk)
+        outs = {}
+        for path in (capi.PATH_GATHER, capi.PATH_TILED):
+            capi.set_path(path)
+            st = capi.new_state(L, d)
+            capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), dev(col), *st, use_nan=True)
+            outs[path] = to_np(st)
+        capi.set_path(capi.PATH_AUTO)
+        if col.size:
+            assert capi.last_path() == capi.PATH_TILED
+        assert_state_close(outs[capi.PATH_TILED], outs[capi.PATH_GATHER], TOL_TILED, f"case {case}: L={L} Lk={Lk} d={d}")
