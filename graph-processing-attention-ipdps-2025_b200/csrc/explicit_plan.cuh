@@ -6,8 +6,10 @@
 // into the caller's (m, l, O) state, so their order does not matter and the result is the union.
 //
 // explicit_plan_kernel does the split, one CTA per 128-row block:
-//   1. histogram of the block's entries over ALL key tiles (shared memory, one 16-bit counter per tile)
-//   2. the tiles with at least `min_entries` entries, ascending, at most kMaxDenseTiles, become "dense"
+//   1. histogram of the entries of every 4th row of the block over ALL key tiles (shared memory, one 16-bit
+//      counter per tile)
+//   2. the tiles with at least a quarter of `min_entries` sampled entries, ascending, at most kMaxDenseTiles,
+//      become "dense"
 //   3. bit masks of the dense tiles are built in shared memory; a tile in which some (row, key) pair occurs
 //      twice is demoted (a bit cannot say "twice", and the reference counts such a key twice)
 //   4. space for the masks is taken from a pool in the workspace (one atomicAdd per block); a block that does
@@ -35,7 +37,8 @@ namespace spfa {
 constexpr int kListedRowSlots = 128;
 constexpr int kPlanThreads = 512;
 constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread in the row walks
-constexpr int kPlanHistUnroll = 8;  // ... and in the flat histogram pass
+constexpr int kPlanHistUnroll = 8;  // ... and in the histogram pass
+constexpr int kPlanSampleStride = 4;  // the histogram looks at every 4th row of a block
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kPlanMaxSmem = 200 * 1024;
 
@@ -127,25 +130,31 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
   __syncthreads();
-  const int64_t e0 = (int64_t)s_off[0], e1 = (int64_t)s_off[nr];
 
-  // ---- 1. histogram over key tiles ----
-  for (int64_t base = e0; base < e1; base += kPlanThreads * kPlanHistUnroll) {  // every warp runs whole iterations
-    uint32_t cu[kPlanHistUnroll];
+  // ---- 1. histogram over key tiles, from every kPlanSampleStride-th row of the block ----
+  // The counts only decide which tiles are CALLED dense (masks and residual lists are built from all entries
+  // below), so a sample is enough: a tile is dense if the sampled rows hold their share of min_entries.
+  for (int rl = warp * kPlanSampleStride; rl < nr; rl += kPlanWarps * kPlanSampleStride) {
+    const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
+    for (int64_t base = a; base < z; base += 32 * kPlanHistUnroll) {
+      uint32_t cu[kPlanHistUnroll];
 #pragma unroll
-    for (int u = 0; u < kPlanHistUnroll; ++u) {
-      const int64_t e = base + u * kPlanThreads + tid;
-      cu[u] = (e < e1) ? __ldg(col + e) : kNoKey;
-    }
+      for (int u = 0; u < kPlanHistUnroll; ++u) {
+        const int64_t e = base + u * 32 + lane;
+        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+      }
 #pragma unroll
-    for (int u = 0; u < kPlanHistUnroll; ++u) {
-      const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
-      bool lead;
-      const int end = run_end_of(kt, lane, &lead);
-      if (lead && kt != kNoKey) atomicAdd(&hist[kt >> 1], (uint32_t)(end - lane) << ((kt & 1) * 16));
+      for (int u = 0; u < kPlanHistUnroll; ++u) {
+        if (base + u * 32 >= z) break;  // warp-uniform
+        const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
+        bool lead;
+        const int end = run_end_of(kt, lane, &lead);
+        if (lead && kt != kNoKey) atomicAdd(&hist[kt >> 1], (uint32_t)(end - lane) << ((kt & 1) * 16));
+      }
     }
   }
   __syncthreads();
+  min_entries = (min_entries + kPlanSampleStride - 1) / kPlanSampleStride;
 
   // ---- 2. dense tiles, ascending: each warp scans a contiguous range of tiles, 32 at a time (lane <-> tile,
   //         so the ballot of a step is the step's word of dense_bits and the shared-memory reads do not conflict) ----
