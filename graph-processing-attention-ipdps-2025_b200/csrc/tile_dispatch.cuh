@@ -26,12 +26,13 @@ extern std::atomic<int64_t> g_launches;
 // (96 KB of shared memory, 256 TMEM columns, 128 registers x 256 threads), so that TWO CTAs share an SM and one
 // CTA's prologue, epilogue and softmax phases overlap the other's MMAs. d = 128: the Q tile alone is 64 KB per
 // sub-tile, so two CTAs per SM only fit with 32-key tiles and single K/V stages, which measured 5-10 % slower
-// than one CTA of two sub-tiles per SM with 64-key tiles, one K and one V stage: that is what d = 128 uses.
+// than one CTA of two sub-tiles per SM with 64-key tiles, one K and two V stages (224 KB of shared memory): that is
+// what d = 128 uses.
 // Three CTAs per SM for d <= 64 (32-key tiles, 128 TMEM columns, 80 registers x 256 threads) measured 10-20 %
 // slower than two: S MMAs with N = 32 cost as much per instruction as with N = 64.
 template <int D>
 struct TileCfg {
-  static constexpr int BN = 64, NS = (D == 128) ? 1 : 2, NSV = NS, NSUB = (D == 128) ? 2 : 1;
+  static constexpr int BN = 64, NS = (D == 128) ? 1 : 2, NSV = 2, NSUB = (D == 128) ? 2 : 1;
   static constexpr int kRows = 128 * NSUB, kCtasPerSm = (D == 128) ? 1 : 2;
 };
 inline int tile_bn(int d) { return d == 128 ? TileCfg<128>::BN : TileCfg<64>::BN; }

@@ -285,13 +285,13 @@ struct Plan {
   // barriers: q_full, k_full[NS], k_empty[NS], v_full[NSV], v_empty[NSV], s_ready[2 NSUB], p_ready[2 NSUB], o_ready[2 NSUB] (one per S buffer / tile parity)
   static constexpr int kNumBars = 1 + 2 * NS + 2 * NSV + 6 * NSUB;
   static constexpr int kOffMisc = kOffBar + kNumBars * 8;   // tmem base (4 B), abort flag (4 B)
-  static constexpr int kOffCoef = (kOffMisc + 16 + 15) / 16 * 16;  // epilogue: 256 floats per sub-tile
   // explicit masks: merged key-tile list of the CTA: kt[64] (int), act[NSUB] (u64, bit j = sub-tile uses tile j;
   // tile j is then the popcount(act & (2^j - 1))-th tile of the sub-tile's own list), nT (int)
-  static constexpr int kOffX = kOffCoef + NSUB * 256 * 4;
+  static constexpr int kOffX = (kOffMisc + 16 + 15) / 16 * 16;
   static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB;
   static constexpr int kBytes = kOffX + (kXNt + 4 + 15) / 16 * 16;
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
+  static_assert(kDynSmem <= 227 * 1024, "beyond the shared memory one CTA can opt into");
   // TMEM columns: two S buffers per sub-tile (BN each, at BN (2x + b)), then O_x (D each, at 2 BN NSUB + D x)
   static constexpr int kTmemCols = 256 * NSUB;
   static constexpr int kColS = 0, kColO = 2 * BN * NSUB;
@@ -870,9 +870,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // writes here and the row-per-lane-group reads below spread over the banks.
         constexpr int LPR = D / 4;  // float4 chunks (= lanes) per row
         uint8_t* stage = smem + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
-        float* coef = reinterpret_cast<float*>(smem + P::kOffCoef) + x * 256;  // [0,128): ca, [128,256): store flag
-        coef[row] = ca;
-        coef[128 + row] = store ? 1.f : 0.f;
+        const uint32_t store_mask = __ballot_sync(kFullMask, store);  // bit = row of this warp (lane <-> row)
         {
           uint32_t ob[32];
 #pragma unroll
@@ -888,7 +886,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
           }
         }
-        asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");  // this softmax group only
+        __syncwarp();  // every warp reads back only the 32 rows it staged itself
         if (row == 0) SPFA_TRACE_AT(1 + x, 12, x, 0);
         // Coalesced read-modify-write of the caller's O rows: LPR lanes cover one row (D*4 contiguous bytes).
         constexpr int RPI = 32 / LPR;    // rows per warp instruction
@@ -897,8 +895,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (partial_out) {
 #pragma unroll
           for (int i = 0; i < NIT; ++i) {
-            const int r = wrow0 + i * RPI + lane / LPR;
-            if (coef[128 + r] != 0.f) {
+            const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
+            if ((store_mask >> rw) & 1u) {
               float* part = prm.partials + ((size_t)(uq0 + 128 * x + r) * prm.n_split + blockIdx.y) * (D + 4);
               *reinterpret_cast<float4*>(part + sub * 4) =
                   *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
@@ -908,19 +906,19 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           float4 oin[NIT];
 #pragma unroll
           for (int i = 0; i < NIT; ++i) {
-            const int r = wrow0 + i * RPI + lane / LPR;
+            const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
             oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (coef[128 + r] != 0.f) {
+            if ((store_mask >> rw) & 1u) {
               const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
               oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
             }
           }
 #pragma unroll
           for (int i = 0; i < NIT; ++i) {
-            const int r = wrow0 + i * RPI + lane / LPR;
-            if (coef[128 + r] != 0.f) {
+            const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
+            const float car = __shfl_sync(kFullMask, ca, rw);  // the row's coefficient lives in the lane that owns the row
+            if ((store_mask >> rw) & 1u) {
               const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
-              const float car = coef[r];
               const float4 t = *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
               float4 o;
               o.x = fmaf(car, oin[i].x, t.x);
