@@ -28,7 +28,7 @@ EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
     "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32",
-    "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
+    "spfa_selftest_wait_limit", "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -131,6 +131,15 @@ def last_path() -> int:
 def last_device_error() -> int:
     """Synchronise and return (then clear) the tiled kernels' error word; 0 means no bounded wait gave up."""
     return int(lib().spfa_last_device_error())
+
+
+def selftest_wait_limit(device=None) -> None:
+    """Launch the wait-limit self-test (see include/spfa_b200.h); last_device_error() returns 9001 afterwards."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        lib().spfa_selftest_wait_limit.restype = ctypes.c_int
+        lib().spfa_selftest_wait_limit.argtypes = [ctypes.c_void_p]
+        check(lib().spfa_selftest_wait_limit(_stream(dev)))
 
 
 def launch_count() -> int:

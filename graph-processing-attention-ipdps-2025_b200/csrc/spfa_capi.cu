@@ -385,6 +385,8 @@ int64_t spfa_launch_count(void) { return g_launches.load(); }
 
 int spfa_last_device_error(void) { return read_and_clear_tile_error(); }
 
+int spfa_selftest_wait_limit(void* stream) { return launch_wait_limit_selftest(9001, (cudaStream_t)stream); }
+
 #ifdef SPFA_TILE_TRACE
 int spfa_debug_cta_times(unsigned long long* host, int n) {
   cudaDeviceSynchronize();

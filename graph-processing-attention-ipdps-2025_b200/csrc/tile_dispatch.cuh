@@ -327,6 +327,28 @@ inline int tiled_gnl_forward(const float* Q, const float* K, const float* V, flo
   return SPFA_ERR_EMBED_DIM;
 }
 
+// Self-test of the bounded waits: one thread waits on an mbarrier that nothing ever arrives at. After the wait
+// limit (tile::kWaitNs) it must give up, record `code` in the error word and return, leaving the context usable.
+__global__ void wait_limit_selftest_kernel(int* err, int code) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tile::mbar_init(tile::smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tile::mbar_wait(tile::smem_u32(&bar), 0, &abort_flag, err, code);
+}
+
+inline int launch_wait_limit_selftest(int code, cudaStream_t st) {
+  int* err = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  wait_limit_selftest_kernel<<<1, 32, 0, st>>>(err, code);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
+}
+
 // Reads and clears the tiled kernels' error word (synchronises the device). 0 = no error.
 inline int read_and_clear_tile_error() {
   int v = 0, zero = 0;

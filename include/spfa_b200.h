@@ -227,6 +227,12 @@ int spfa_mask_fill(int kind, int64_t L, int64_t p0, int64_t p1,
  * launches are never checked (sp_flatt_csr_kernel.cu:271). */
 int spfa_last_device_error(void);
 
+/* Diagnostics: exercises the time limit of the device-side waits without touching any data. Launches a
+ * one-thread kernel that waits on a barrier nothing ever arrives at; after the limit (0.2 s) the wait gives up
+ * and records code 9001, which the next spfa_last_device_error() returns (and clears). The context stays
+ * usable. No counterpart in the reference. */
+int spfa_selftest_wait_limit(void* stream);
+
 /* Number of kernels this library has launched in the calling process since load (monotonic).
  * Benchmarks subtract two readings to report how many launches a timed region contained. */
 int64_t spfa_launch_count(void);

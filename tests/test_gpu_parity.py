@@ -857,3 +857,22 @@ def test_banded_masks_randomised_tiled_against_gather(capi):
         # per-score rounding is about 2.5e-3 there, so this sweep uses 3e-3; the configuration-sized tests keep 2e-3.
         assert_state_close(outs[capi.PATH_TILED], outs[capi.PATH_GATHER], 3e-3,
                            f"case {case}: {kind} L={L} d={d} w={w} dil={dil} rows {rb}:{re}")
+
+
+def test_device_wait_limit_reports_and_leaves_the_context_usable(capi):
+    """A wait that can never be satisfied (a barrier nothing arrives at) gives up after its limit, the host reads
+    the code, and the next call works: no trap, no hang, no lost context."""
+    import time
+
+    t0 = time.perf_counter()
+    capi.selftest_wait_limit()
+    assert capi.last_device_error() == 9001          # synchronises; reading clears the word
+    waited = time.perf_counter() - t0
+    assert 0.15 <= waited <= 5.0, f"the wait limit is 0.2 s, the call took {waited:.2f} s"
+    assert capi.last_device_error() == 0
+    L, d = 300, 64
+    Q, K, V = seeded_qkv(L, d, 5)
+    st = capi.new_state(L, d)
+    capi.local_forward(dev(Q), dev(K), dev(V), *st, 64)
+    torch.cuda.synchronize()
+    assert torch.isfinite(st[2]).all() and capi.last_device_error() == 0
