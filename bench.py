@@ -2,10 +2,14 @@
 """Benchmark of the sparse FlashAttention forward path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference] [--path auto|gather|tiled]
+                    [--strong] [--planned] [--e2e-whole] [--rows L] [--no-cpu-baseline]
 
 One "step" = one forward of one mask family over one batch of seeded synthetic input. The default
 workload is the Local (sliding-window) configuration: L=65536, d=64, fp32 Q/K/V ~ N(0,1), window
-|i-j| <= 256. Other workloads (--workload csr|l1d|gnl|l2d|coo) are the remaining benchmark shapes.
+|i-j| <= 256. Other workloads (--workload csr|l1d|gnl|l2d|coo) are the remaining benchmark shapes; `blocks` is the
+block-level dilation pattern as an explicit CSR mask (not expressible through the reference's own 2D operator).
+--planned times explicit-mask calls from a dense-tile plan built once outside the timed region. The end-to-end
+leg uses the host pipelines of hostio.py where they pay (see its `api` field); --e2e-whole forces whole-tensor copies.
 
 Multi-GPU (launched by torch.distributed.run, one rank per GPU): weak scaling over query-row ranges.
 The sequence has N*L rows; rank r owns rows [r*L, (r+1)*L) and K/V of the whole sequence are
