@@ -19,6 +19,19 @@ from . import capi
 _KINDS = ("local", "local_1d_dilated", "local_2d_dilated")
 
 
+def chunk_edges(n_rows: int, n_chunks: int, unit: int = 256) -> list[int]:
+    """Row boundaries of at most n_chunks chunks whose sizes are multiples of `unit` (the last one may be ragged)."""
+    rows = max(unit, -(-n_rows // max(1, n_chunks)))
+    rows = -(-rows // unit) * unit
+    return list(range(0, n_rows, rows)) + [n_rows]
+
+
+def chunk_needed_last(edges: list[int], c: int, halo: int, n_keys: int) -> int:
+    """Index of the last chunk whose K/V rows chunk c reads when a row looks `halo` rows past its own."""
+    need = min(n_keys, edges[c + 1] + halo) - 1
+    return next(i for i in range(len(edges) - 1) if edges[i + 1] > need)
+
+
 class BandedHostPipeline:
     """Device buffers, streams and the chunk plan for repeated calls on one shape.
 
@@ -37,9 +50,7 @@ class BandedHostPipeline:
             self.halo = 0
         else:
             self.halo = p0 * (p1 + 1)
-        rows = max(unit, -(-L // n_chunks))
-        rows = -(-rows // unit) * unit
-        self.edges = list(range(0, L, rows)) + [L]
+        self.edges = chunk_edges(L, n_chunks, unit)
         with torch.cuda.device(self.dev):
             f = dict(device=self.dev, dtype=torch.float32)
             self.Q, self.K, self.V, self.O = (torch.empty(L, d, **f) for _ in range(4))
@@ -78,8 +89,7 @@ class BandedHostPipeline:
                 copied[c].record(self.s_in)
         for c in range(n):
             a, b = self.edges[c], self.edges[c + 1]
-            need = min(self.L, b + self.halo) - 1          # last key row this chunk reads
-            last = next(i for i in range(n) if self.edges[i + 1] > need)
+            last = chunk_needed_last(self.edges, c, self.halo, self.L)  # chunk holding the last key row it reads
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(copied[last])
                 self._forward_rows(a, b, use_nan)
@@ -107,8 +117,7 @@ class FullKeyHostPipeline:
     def __init__(self, n_rows: int, n_keys: int, d: int, n_chunks: int = 8, device=None):
         self.n_rows, self.n_keys, self.d = n_rows, n_keys, d
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        rows = -(-max(256, -(-n_rows // n_chunks)) // 256) * 256
-        self.edges = list(range(0, n_rows, rows)) + [n_rows]
+        self.edges = chunk_edges(n_rows, n_chunks, 256)
         with torch.cuda.device(self.dev):
             f = dict(device=self.dev, dtype=torch.float32)
             self.Q, self.O = torch.empty(n_rows, d, **f), torch.empty(n_rows, d, **f)

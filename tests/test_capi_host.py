@@ -101,3 +101,18 @@ def test_capi_refuses_cpu_tensors(pkg):
     t = torch.zeros(8, 16)
     with pytest.raises(c.SpfaError):
         c.local_forward(t, t, t, torch.zeros(8), torch.zeros(8), t.clone(), 1)
+
+
+def test_host_pipeline_chunk_planning(pkg):
+    """Pure host logic of hostio: chunk edges cover the rows exactly once on unit multiples, and every chunk waits
+    for the chunk that holds the last key row it can read."""
+    h = pkg.hostio
+    for n_rows, n_chunks, unit in ((65536, 8, 256), (3000, 5, 256), (700, 5, 256), (2048, 8, 128), (1, 3, 256), (257, 2, 256)):
+        e = h.chunk_edges(n_rows, n_chunks, unit)
+        assert e[0] == 0 and e[-1] == n_rows and all(b > a for a, b in zip(e, e[1:]))
+        assert all(x % unit == 0 for x in e[:-1]) and len(e) - 1 <= max(1, n_chunks)
+        for halo in (0, 1, 255, 256, 1000, 10 ** 6):
+            for c in range(len(e) - 1):
+                last = h.chunk_needed_last(e, c, halo, n_rows)
+                need = min(n_rows, e[c + 1] + halo) - 1
+                assert e[last] <= need < e[last + 1] and last >= c
