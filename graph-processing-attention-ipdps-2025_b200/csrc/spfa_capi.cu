@@ -13,8 +13,15 @@
 namespace spfa {
 
 std::atomic<int64_t> g_launches{0};
-std::atomic<int> g_path{SPFA_PATH_AUTO};
-std::atomic<int> g_last_path{SPFA_PATH_GATHER};
+// Path selector and "path taken" record are per host thread: two threads that force different paths (tests,
+// benchmarks) do not see each other's choice, so the forward entry points stay re-entrant.
+struct PathCell {
+  int v;
+  int load() const { return v; }
+  void store(int x) { v = x; }
+};
+thread_local PathCell g_path{SPFA_PATH_AUTO};
+thread_local PathCell g_last_path{SPFA_PATH_GATHER};
 
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -216,6 +223,9 @@ inline int hybrid_decision(int d, int64_t n_rows, int64_t nnz, int64_t Lk, const
   if (!shape || (path == SPFA_PATH_AUTO && nnz < kHybridMinNnz)) return 0;
   if (check_workspace(ws, ws_bytes, hybrid_layout(n_rows, nnz, Lk, d).total) != SPFA_OK)
     return path == SPFA_PATH_TILED ? (int)SPFA_ERR_WORKSPACE : 0;
+  const bool usable = d == 32 ? band_kernel_usable<32, true>()
+                              : (d == 64 ? band_kernel_usable<64, true>() : band_kernel_usable<128, true>());
+  if (!usable) return path == SPFA_PATH_TILED ? (int)SPFA_ERR_REGISTER_BUDGET : 0;
   return 1;
 }
 
@@ -369,6 +379,8 @@ const char* spfa_status_string(int s) {
     case SPFA_ERR_DILATION_BLOCK: return "The dilation factor must be less than the block/window size.";
     case SPFA_ERR_GLOBAL_COUNT: return "There are either no global tokens provided or there are more than the sequence length given.";
     case SPFA_ERR_TOO_LARGE: return "size beyond a fixed maximum";
+    case SPFA_ERR_REGISTER_BUDGET: return "the tiled kernel of this build cannot run (register allocation below its setmaxnreg budgets)";
+    case SPFA_ERR_PLAN_MISMATCH: return "the stored plan was built for another (n_rows, nnz, Lk, d)";
   }
   return "unknown status";
 }
@@ -386,13 +398,6 @@ int64_t spfa_launch_count(void) { return g_launches.load(); }
 int spfa_last_device_error(void) { return read_and_clear_tile_error(); }
 
 int spfa_selftest_wait_limit(void* stream) { return launch_wait_limit_selftest(9001, (cudaStream_t)stream); }
-
-#ifdef SPFA_TILE_TRACE
-int spfa_debug_cta_times(unsigned long long* host, int n) {
-  cudaDeviceSynchronize();
-  return (int)cudaMemcpyFromSymbol(host, tile::g_cta_times, sizeof(unsigned long long) * 3 * n);
-}
-#endif
 
 // ---- CSR -----------------------------------------------------------------------------------------
 size_t spfa_csr_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {

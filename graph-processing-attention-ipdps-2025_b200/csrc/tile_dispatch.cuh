@@ -76,7 +76,31 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Common launch steps of band_forward_kernel: shared-memory opt-in, register-budget guard, error word.
+// setmaxnreg.inc blocks without a timeout when the CTA's register pool cannot satisfy it, so the kernel is only
+// launched if the pool the compiler's allocation gives a CTA covers the two budgets of Geo. The answer depends on
+// the build alone (a different nvcc may assign fewer registers): it is computed once per instantiation and device.
+// Callers on SPFA_PATH_AUTO fall back to the gather path when it is false; a forced tiled call reports
+// SPFA_ERR_REGISTER_BUDGET.
+template <int D, bool EXPL>
+bool band_kernel_usable() {
+  using C = TileCfg<D>;
+  using G = tile::Geo<C::NSUB>;
+  static std::atomic<int> cached[64];  // per device: 0 unknown, 1 usable, 2 not
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    cudaFuncAttributes attr;
+    auto kern = tile::band_forward_kernel<D, C::BN, C::NS, C::NSUB, EXPL, C::NSV>;
+    const bool ok = cudaFuncGetAttributes(&attr, kern) == cudaSuccess &&
+                    attr.numRegs * G::kThreads >= G::kRegsSoftmax * 128 * C::NSUB + G::kRegsAux * 128;
+    v = ok ? 1 : 2;
+    cached[dev].store(v, std::memory_order_relaxed);
+  }
+  return v == 1;
+}
+
+// Common launch steps of band_forward_kernel: register-budget guard, shared-memory opt-in, error word.
 template <int D, bool EXPL = false>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
                     const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
@@ -85,11 +109,9 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
   using P = tile::Plan<D, C::BN, C::NS, NSUB, C::NSV>;
   using G = tile::Geo<NSUB>;
   auto kern = tile::band_forward_kernel<D, C::BN, C::NS, NSUB, EXPL, C::NSV>;
+  if (!band_kernel_usable<D, EXPL>()) return SPFA_ERR_REGISTER_BUDGET;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
-  cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, kern) != cudaSuccess) return SPFA_ERR_LAUNCH;
-  if (attr.numRegs * G::kThreads < G::kRegsSoftmax * 128 * NSUB + G::kRegsAux * 128) return SPFA_ERR_LAUNCH;
   int* err = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
   if (prm.overlap & 2) {  // may start while the previous launch of the stream is still running (see BandParams)
@@ -153,6 +175,9 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
   const bool shape_ok = (d == 32 || d == 64 || d == 128) && s >= 1 && s <= kTileMaxStride && row_end > row_begin;
   if (!shape_ok) return forced ? (int)SPFA_ERR_BAD_ARG : SPFA_TILE_NOT_TAKEN;
   if (!forced && w < kTileMinHalfWidth) return SPFA_TILE_NOT_TAKEN;
+  const bool usable = d == 32 ? band_kernel_usable<32, false>()
+                              : (d == 64 ? band_kernel_usable<64, false>() : band_kernel_usable<128, false>());
+  if (!usable) return forced ? (int)SPFA_ERR_REGISTER_BUDGET : SPFA_TILE_NOT_TAKEN;
   switch (d) {
     case 32: return launch_band<32>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
     case 64: return launch_band<64>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
@@ -247,7 +272,9 @@ inline GnlTiledPlan gnl_tiled_plan(int64_t L, int d, int64_t nG) {
 }
 
 inline bool gnl_tiled_shape_ok(int d, int64_t nG) {
-  return (d == 32 || d == 64 || d == 128) && nG >= 1 && nG <= kGnlTiledMaxGlobals;
+  if (!((d == 32 || d == 64 || d == 128) && nG >= 1 && nG <= kGnlTiledMaxGlobals)) return false;
+  return d == 32 ? band_kernel_usable<32, false>()
+                 : (d == 64 ? band_kernel_usable<64, false>() : band_kernel_usable<128, false>());
 }
 
 template <int D>

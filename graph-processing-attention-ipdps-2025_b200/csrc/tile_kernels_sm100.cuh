@@ -35,31 +35,10 @@
 #include <stdint.h>
 
 #include "spfa_common.cuh"
-#ifdef SPFA_TILE_TRACE
-#include <cstdio>
-#endif
 
 namespace spfa {
 namespace tile {
 
-#ifdef SPFA_TILE_TRACE
-__device__ unsigned long long g_cta_times[8192][3];  // probe build only: start, end (globaltimer ns), SM id
-#endif
-#ifdef SPFA_TILE_TRACE  // probe build only: per-event cycle stamps of one CTA, kept in shared memory
-// (a global atomic per event would perturb the timeline) and printed at the CTA's exit.
-constexpr int kTraceSlots = 3, kTraceCap = 400;  // slot 0: MMA thread, 1: softmax A row 0, 2: softmax B row 0
-#define SPFA_TRACE_AT(slot, tag, a, b)                                                                       \
-  do {                                                                                                       \
-    if (blockIdx.x == 1) {                                                                                   \
-      int& n_ = trace_n[slot];                                                                               \
-      if (n_ < kTraceCap)                                                                                    \
-        trace_buf[(slot) * kTraceCap + n_++] =                                                               \
-            ((long long)(tag) << 56) | ((long long)(a) << 52) | ((long long)(b) << 44) | (clock64() & 0xfffffffffffLL); \
-    }                                                                                                        \
-  } while (0)
-#else
-#define SPFA_TRACE_AT(slot, tag, a, b) do {} while (0)
-#endif
 
 // Geometry of a CTA with NSUB 128-row sub-tiles: NSUB softmax warpgroups + one warpgroup holding the
 // TMA warp, the MMA warp and two idle warps. NSUB = 1 (two CTAs per SM) serves d <= 64, NSUB = 2 (one CTA per
@@ -316,21 +295,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             B_SREADY = 1 + 2 * NS + 2 * NSV, B_PREADY = B_SREADY + 2 * NSUB, B_OREADY = B_SREADY + 4 * NSUB;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + P::kOffMisc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
-#ifdef SPFA_TILE_TRACE
-  __shared__ long long trace_buf[kTraceSlots * kTraceCap];
-  __shared__ int trace_n[kTraceSlots];
-  if (threadIdx.x < kTraceSlots) trace_n[threadIdx.x] = 0;
-#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef SPFA_TILE_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 8192) {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    g_cta_times[blockIdx.x][0] = globaltimer();
-    g_cta_times[blockIdx.x][2] = smid;
-  }
-#endif
 
   // ---- tile geometry (uniform across the CTA) ----
   const int64_t uq0 = prm.u_q_first + (int64_t)blockIdx.x * kQRows;  // first query u of this CTA
@@ -565,9 +531,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
         for (int x = 0; x < NSUB; ++x)
           if (active(x, jj)) {
-            SPFA_TRACE_AT(0, 3, x, jj);
             issue_S(x, jj);
-            SPFA_TRACE_AT(0, 4, x, jj);
             if (last_active(x, jj)) tc_commit(bar(B_KEMPTY + jj % NS));
           }
         return true;
@@ -590,9 +554,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             have_v = true;
           }
           tc_fence_after();
-          SPFA_TRACE_AT(0, 1, x, j);
           issue_PV(x, j);
-          SPFA_TRACE_AT(0, 2, x, j);
           if (last_active(x, j)) tc_commit(bar(B_VEMPTY + st));
         }
         // the S buffers of tile j are free again once its PVs are queued (the pipe runs them in order)
@@ -666,7 +628,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       asm volatile("prefetch.global.L2 [%0];" ::"l"(m_out + rl0));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(l_out + rl0));
     }
-    if (row == 0) SPFA_TRACE_AT(1 + x, 14, x, 0);
     float m_true = neg_inf();   // running maximum of the scaled scores (log2 units)
     float shift = neg_inf();    // reference the exponentials and O are currently expressed against
     float l_run = 0.f;          // row sum relative to `shift`
@@ -724,7 +685,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = __all_sync(kFullMask, mbar_wait(bar(B_SREADY + sb), (uint32_t)((it >> 1) & 1), abort_flag, err, 301));
       if (!ok) break;
       tc_fence_after();
-      if (row == 0) SPFA_TRACE_AT(1 + x, 5, x, j);
       // ---- the whole S row, one TMEM latency ----
 #pragma unroll
       for (int c = 0; c < NC; ++c)
@@ -745,7 +705,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       const float t_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
       m_true = fmaxf(m_true, t_max);
-      if (row == 0) SPFA_TRACE_AT(1 + x, 6, x, j);
       // ---- move the reference if this row outgrew it (always on the row's first valid tile) ----
       const bool move = t_max > shift + kShiftSlack;  // shift = -inf: true as soon as the row has a valid column
       if (__any_sync(kFullMask, move)) {
@@ -804,11 +763,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar(B_PREADY + sb));
-      if (row == 0) SPFA_TRACE_AT(1 + x, 8, x, j);
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
     // ---- epilogue: O row from TMEM, normalised and merged with the caller's (m, l, O) ----
-    if (row == 0) SPFA_TRACE_AT(1 + x, 10, x, 0);
     if (nx > 0) {  // uniform over the softmax group, so the group barriers below are safe
       // both tile parities: the PVs of the last two tiles
       if (ok && nx > 1)
@@ -833,7 +790,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // mode 2 writes a partial state for every real row (also rows with no key in this range);
         // the other modes touch a row only if it attended to something and is theirs to write
         const bool store = partial_out ? row_valid : (row_valid && l_run > 0.f && !listed);
-        if (row == 0) SPFA_TRACE_AT(1 + x, 11, x, 0);
         // Per-row coefficients of  O_out = ca * O_in + cb * O_tmem  (state in natural-log units, as the
         // gather path; l is re-expressed against the true maximum, O in TMEM is relative to `shift`).
         float ca = 0.f, cb = 0.f;
@@ -887,7 +843,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
         __syncwarp();  // every warp reads back only the 32 rows it staged itself
-        if (row == 0) SPFA_TRACE_AT(1 + x, 12, x, 0);
         // Coalesced read-modify-write of the caller's O rows: LPR lanes cover one row (D*4 contiguous bytes).
         constexpr int RPI = 32 / LPR;    // rows per warp instruction
         constexpr int NIT = 32 / RPI;    // instructions for this warp's 32 rows
@@ -929,7 +884,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
           }
         }
-        if (row == 0) SPFA_TRACE_AT(1 + x, 13, x, 0);
       }
     }
   }
@@ -940,16 +894,6 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // started early beside its predecessor: completion order (and with it everything later in the stream) must
   // still see the predecessor finished
   if ((prm.overlap & 2) && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef SPFA_TILE_TRACE
-  if (threadIdx.x == 0 && blockIdx.x < 8192) g_cta_times[blockIdx.x][1] = globaltimer();
-  if (blockIdx.x == 1 && threadIdx.x == 0 && gridDim.x < 64) {
-    for (int sl = 0; sl < kTraceSlots; ++sl)
-      for (int i = 0; i < trace_n[sl]; ++i) {
-        const long long v = trace_buf[sl * kTraceCap + i];
-        printf("T %d %d %d %lld\n", (int)(v >> 56), (int)((v >> 52) & 15), (int)((v >> 44) & 255), v & 0xfffffffffffLL);
-      }
-  }
-#endif
   if (warp == W_TMA) {
     tc_fence_after();
     if (*abort_flag && lane == 0) {

@@ -45,7 +45,10 @@ typedef enum spfa_status {
   SPFA_ERR_BLOCK_DIVISOR = -8,  /* L % block_size != 0 (sp_flatt_local_2d_dilated_kernel.cu:274-276) */
   SPFA_ERR_DILATION_BLOCK = -9, /* block_size / (dil_factor+1) < 1 (sp_flatt_local_2d_dilated_kernel.cu:284-286) */
   SPFA_ERR_GLOBAL_COUNT = -10,  /* n_global == 0 or > L (sp_flatt_global_no_local_kernel.cu:325-327) */
-  SPFA_ERR_TOO_LARGE = -11      /* size beyond a stated fixed maximum */
+  SPFA_ERR_TOO_LARGE = -11,     /* size beyond a stated fixed maximum */
+  SPFA_ERR_REGISTER_BUDGET = -12, /* SPFA_PATH_TILED forced, but this build's tiled kernel got fewer registers than its
+                                     setmaxnreg budgets need (AUTO falls back to the gather path instead) */
+  SPFA_ERR_PLAN_MISMATCH = -13  /* a stored plan was built for other (n_rows, nnz, Lk, d) than the call passes */
 } spfa_status;
 
 /* Human-readable text for a status code (static storage). */
@@ -54,17 +57,20 @@ const char* spfa_status_string(int status);
 /* Library/ABI version: major*1000 + minor. */
 int spfa_abi_version(void);
 
-/* Execution path selector.
+/* Execution path selector -- TEST AND BENCHMARK SUPPORT, not part of the drop-in surface (the reference has no
+ * counterpart: each of its operators has one kernel).
  *   SPFA_PATH_AUTO   library picks (tiled tensor-core path when the window is wide enough or, for explicit
  *                    masks, when the mask is large and the workspace allows the dense-tile split; else gather)
  *   SPFA_PATH_GATHER FP32 warp-per-row gather path (max-abs error ~1e-6 vs fp64)
  *   SPFA_PATH_TILED  tcgen05 TF32 tiled path (max-abs error <= 2e-3 vs fp64); falls back to
  *                    SPFA_ERR_BAD_ARG if the shape is not supported by that path
- * The choice is process-wide state for testing and benchmarking; default AUTO. */
+ * The selector and the record of the path taken are PER HOST THREAD (thread-local, default AUTO): a thread that
+ * never calls spfa_set_path always gets AUTO, and threads forcing different paths do not interfere, so the forward
+ * entry points stay stateless and re-entrant for production callers. */
 enum { SPFA_PATH_AUTO = 0, SPFA_PATH_GATHER = 1, SPFA_PATH_TILED = 2 };
 void spfa_set_path(int path);
 int spfa_get_path(void);
-/* Path the most recent forward call of this process actually took (SPFA_PATH_GATHER or SPFA_PATH_TILED). */
+/* Path the most recent forward call of the calling thread actually took (SPFA_PATH_GATHER or SPFA_PATH_TILED). */
 int spfa_last_path(void);
 
 /* ---- explicit CSR mask ------------------------------------------------------------------------
