@@ -28,7 +28,7 @@ EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
     "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32",
-    "spfa_selftest_wait_limit", "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
+    "spfa_selftest_wait_limit", "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_planned_forward_keys_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -82,6 +82,8 @@ def lib() -> ctypes.CDLL:
     L.spfa_coo_plan_build.argtypes = [vp, vp, i64, i64, i64, i64, i32, vp, sz, vp]
     L.spfa_planned_forward_f32.restype = i32
     L.spfa_planned_forward_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_planned_forward_keys_f32.restype = i32
+    L.spfa_planned_forward_keys_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, i64, i64, vp]
     L.spfa_coo_static_max_rows.restype = i64
     L.spfa_coo_forward_f32_static.restype = i32
     L.spfa_coo_forward_f32_static.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp]
@@ -246,21 +248,31 @@ def _new_plan(n_rows, nnz, n_keys, d, dev):
     return ExplicitPlan(buf, wp, wb, n_rows, nnz, n_keys, d)
 
 
-def csr_plan(row_off, col_ind, n_keys, d):
-    """Run the inspector once for a CSR mask of row_off.numel()-1 rows over n_keys keys."""
+def _reuse_or_new(out, n_rows, nnz, n_keys, d, dev):
+    if out is None:
+        return _new_plan(n_rows, nnz, n_keys, d, dev)
+    if (out.n_rows, out.nnz, out.n_keys, out.d) != (n_rows, nnz, n_keys, d):
+        raise SpfaError(-1, "`out` was allocated for another shape")
+    return out
+
+
+def csr_plan(row_off, col_ind, n_keys, d, out: ExplicitPlan | None = None):
+    """Run the inspector once for a CSR mask of row_off.numel()-1 rows over n_keys keys. `out`: an earlier plan of
+    the same shape whose memory is refilled instead of allocating (callers that re-inspect every step)."""
     dev = col_ind.device
     with torch.cuda.device(dev):
-        plan = _new_plan(row_off.shape[0] - 1, col_ind.shape[0], n_keys, d, dev)
+        plan = _reuse_or_new(out, row_off.shape[0] - 1, col_ind.shape[0], n_keys, d, dev)
         check(lib().spfa_csr_plan_build(_ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)), plan.nnz, plan.n_rows, n_keys, d,
                                         plan.ptr, plan.nbytes, _stream(dev)))
     return plan
 
 
-def coo_plan(row_ind, col_ind, n_rows, n_keys, d, row_begin=0):
-    """Run the inspector once for the rows [row_begin, row_begin + n_rows) of a row-sorted COO mask."""
+def coo_plan(row_ind, col_ind, n_rows, n_keys, d, row_begin=0, out: ExplicitPlan | None = None):
+    """Run the inspector once for the rows [row_begin, row_begin + n_rows) of a row-sorted COO mask (`out` as in
+    csr_plan)."""
     dev = col_ind.device
     with torch.cuda.device(dev):
-        plan = _new_plan(n_rows, col_ind.shape[0], n_keys, d, dev)
+        plan = _reuse_or_new(out, n_rows, col_ind.shape[0], n_keys, d, dev)
         check(lib().spfa_coo_plan_build(_ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), plan.nnz, row_begin, n_rows,
                                         n_keys, d, plan.ptr, plan.nbytes, _stream(dev)))
     return plan
@@ -274,6 +286,19 @@ def planned_forward(Q, K, V, m, l, O, plan: ExplicitPlan, use_nan=False):
     with torch.cuda.device(dev):
         check(lib().spfa_planned_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows, plan.nnz,
                                              plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes, _stream(dev)))
+    return O
+
+
+def planned_forward_keys(Q, K, V, m, l, O, plan: ExplicitPlan, key_begin: int, key_end: int, use_nan=False):
+    """One pass of a forward split along the key axis: the plan's dense tiles and residual entries whose key lies in
+    [key_begin, key_end). Only those K/V rows are read, so a pass can run as soon as its chunk of K/V is on the device."""
+    dev = _f32(Q, K, V, m, l, O)
+    if Q.shape[0] != plan.n_rows or K.shape[0] != plan.n_keys or Q.shape[1] != plan.d:
+        raise SpfaError(-1, "the plan was built for another shape")
+    with torch.cuda.device(dev):
+        check(lib().spfa_planned_forward_keys_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows,
+                                                  plan.nnz, plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes,
+                                                  int(key_begin), int(key_end), _stream(dev)))
     return O
 
 

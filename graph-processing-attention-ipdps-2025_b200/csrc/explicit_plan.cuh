@@ -57,6 +57,10 @@ struct ExplicitPlan {
   // rows whose residual part is longer than kListedRowSlots get CTAs of their own (gather_rows_listed_first_kernel)
   unsigned int* heavy_count;        // zeroed before the kernel
   int* heavy_rows;                  // [n_rows]
+  // set to 1 by any block that meets a row whose kept columns are not ascending (zeroed before the kernel):
+  // key-range passes may binary-search the residual rows only while it stays 0
+  unsigned int* unsorted;
+  PlanHeader* header;
 };
 
 // Residual rows of the hybrid (see above): same offsets as the caller's CSR, fewer entries, all < Lk.
@@ -75,6 +79,46 @@ struct ResidualCols {
     return r;
   }
   __device__ __forceinline__ int32_t slot(const Row& r, int64_t t) const { return (int32_t)__ldg(col + r.lo + t); }
+};
+
+// The same rows restricted to the keys [key_lo, key_hi): one pass of a forward that is split along the key axis
+// (multi-GPU callers run one pass per K/V chunk as the chunks arrive; the passes chain through (m, l, O)).
+// Rows whose columns ascend -- the inspector records whether all do -- are cut by two binary searches;
+// otherwise every slot is looked at and the ones outside the range are skipped.
+struct ResidualRangeCols {
+  const uint64_t* row_off;
+  const uint32_t* cnt;
+  const uint32_t* col;
+  uint32_t skip_above;
+  uint32_t key_lo, key_hi;
+  const unsigned int* unsorted;  // the plan's flag
+  static constexpr bool kNanFillEmpty = false;
+  struct Row { int64_t lo; int64_t n; bool filter; };
+  __device__ __forceinline__ int64_t lower_bound(int64_t lo, int64_t n, uint32_t v) const {
+    int64_t a = 0, b = n;
+    while (a < b) {
+      const int64_t mid = (a + b) >> 1;
+      if (__ldg(col + lo + mid) < v) a = mid + 1; else b = mid;
+    }
+    return a;
+  }
+  __device__ __forceinline__ Row open(int64_t r_local, int64_t) const {
+    Row r;
+    r.lo = (int64_t)row_off[r_local];
+    const uint32_t n = cnt[r_local];
+    r.n = (n > skip_above) ? 0 : (int64_t)n;
+    r.filter = (*unsorted != 0u);
+    if (!r.filter && r.n > 0) {
+      const int64_t a = lower_bound(r.lo, r.n, key_lo), b = lower_bound(r.lo, r.n, key_hi);
+      r.lo += a;
+      r.n = b - a;
+    }
+    return r;
+  }
+  __device__ __forceinline__ int32_t slot(const Row& r, int64_t t) const {
+    const uint32_t c = __ldg(col + r.lo + t);
+    return (!r.filter || (c >= key_lo && c < key_hi)) ? (int32_t)c : -1;
+  }
 };
 
 inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
@@ -97,8 +141,9 @@ __device__ __forceinline__ int run_end_of(uint32_t key, int lane, bool* lead) {
 
 template <int BN>
 __global__ void __launch_bounds__(kPlanThreads, 4)
-explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __restrict__ col, int64_t n_rows, int64_t Lk,
-                     int n_key_tiles, int min_entries, ExplicitPlan plan, int use_nan, float* __restrict__ O, int d) {
+explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __restrict__ col, int64_t n_rows, int64_t nnz,
+                     int64_t Lk, int n_key_tiles, int min_entries, ExplicitPlan plan, int use_nan, float* __restrict__ O,
+                     int d) {
   constexpr int NC = BN / 32;
   constexpr int MAXT = tile::kMaxDenseTiles;
   constexpr uint32_t kNoKey = 0xffffffffu;
@@ -125,7 +170,20 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const int64_t b = blockIdx.x;
   const int64_t r0 = b * 128;
   const int nr = (int)((n_rows - r0 < 128) ? (n_rows - r0) : 128);
-  if (tid <= nr) s_off[tid] = row_off[r0 + tid];
+  if (tid <= nr) {  // offsets beyond the column array (a malformed mask) are clamped: nothing is read or written past nnz
+    unsigned long long o = row_off[r0 + tid];
+    s_off[tid] = (o > (unsigned long long)nnz) ? (unsigned long long)nnz : o;
+  }
+  if (b == 0 && tid == 0) {
+    PlanHeader h;
+    h.magic = kPlanMagic;
+    h.n_rows = n_rows;
+    h.nnz = nnz;
+    h.n_keys = Lk;
+    h.d = d;
+    h.bn = BN;
+    *plan.header = h;
+  }
   for (int k = tid; k < n_hist_words; k += kPlanThreads) hist[k] = 0;
   for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
@@ -204,6 +262,8 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   for (int rl = warp; rl < nr; rl += kPlanWarps) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
+    uint32_t last_col = kNoKey;  // column of the previous batch's last entry
+    bool row_unsorted = false;
     for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
       uint32_t cu[kPlanUnroll];
 #pragma unroll
@@ -230,6 +290,12 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
         const uint32_t bal = __ballot_sync(kFullMask, keep);
         if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
         kept += __popc(bal);
+        {  // ascending order of the row's columns (all entries, so the kept ones as well)
+          const uint32_t before = __shfl_up_sync(kFullMask, c, 1);
+          const uint32_t prev = (lane == 0) ? last_col : before;
+          if (c != kNoKey && prev != kNoKey && c < prev) row_unsorted = true;
+          last_col = __shfl_sync(kFullMask, c, 31);  // kNoKey only in a row's last, ragged batch
+        }
         if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
         const uint32_t word0 = __shfl_sync(kFullMask, word, 0);
         if (word0 != kNoKey && __all_sync(kFullMask, word == word0)) {
@@ -256,6 +322,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
         }
       }
     }
+    if (__any_sync(kFullMask, row_unsorted) && lane == 0) *plan.unsorted = 1u;  // benign race: every writer stores 1
     if (lane == 0) {
       plan.res_cnt[r0 + rl] = kept;
       if (kept > (uint32_t)kListedRowSlots) plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);

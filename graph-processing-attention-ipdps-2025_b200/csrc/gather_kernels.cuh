@@ -336,15 +336,21 @@ gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
 // list, one listed row at a time with all their warps (`listed` opens the same rows at full length); the other
 // CTAs do the ordinary rows. Blocks are dispatched in index order, so the long rows start with the launch
 // instead of wherever their row number falls. The list length lives in device memory (it is produced there).
+// The lists come from a stored plan: its identity block is compared with the shape the caller passed first.
 template <int D, class Cols>
 __global__ void __launch_bounds__(kRowWarps * 32, 7)
 gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                                 float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Cols cols,
                                 const Cols listed, const int* __restrict__ row_list,
                                 const unsigned int* __restrict__ n_listed, int n_list_blocks, int64_t row_begin,
-                                int64_t n_rows, int use_nan, float scale) {
+                                int64_t n_rows, int use_nan, float scale, const PlanHeader* __restrict__ hdr,
+                                const PlanHeader want, int* __restrict__ err) {
   __shared__ RowCtaShared sh;
   __shared__ float4 s_acc[kRowWarps][D / 4];
+  if (!plan_header_matches(hdr, want)) {  // uniform over the grid: the lists belong to a plan of another shape
+    if (threadIdx.x == 0) atomicCAS(err, 0, kPlanMismatchCode);
+    return;
+  }
   if ((int)blockIdx.x >= n_list_blocks) {
     gather_rows_cta<D, Cols>((int64_t)blockIdx.x - n_list_blocks, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan,
                              scale, sh, s_acc);

@@ -233,6 +233,8 @@ inline ExplicitPlan plan_view(const HybridLayout& h, char* ws) {
   ExplicitPlan plan;
   plan.pool_used = reinterpret_cast<unsigned long long*>(ws + h.off_pool);
   plan.heavy_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 8);
+  plan.unsorted = reinterpret_cast<unsigned int*>(ws + h.off_pool + 12);
+  plan.header = reinterpret_cast<PlanHeader*>(ws + h.off_pool + kPlanHeaderOffset);
   plan.rb_nt = reinterpret_cast<int*>(ws + h.off_nt);
   plan.rb_kt = reinterpret_cast<int*>(ws + h.off_kt);
   plan.rb_moff = reinterpret_cast<long long*>(ws + h.off_moff);
@@ -247,15 +249,15 @@ inline ExplicitPlan plan_view(const HybridLayout& h, char* ws) {
 // The inspector: fills the plan region `ws` for the mask (row_off, col). With use_nan it also NaN-fills the O
 // rows of rows without entries (a per-call effect; plans built for later use pass use_nan = 0, O = nullptr).
 template <int BN>
-int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t Lk, int d,
+int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk, int d,
                 const HybridLayout& h, char* ws, int use_nan, float* O, cudaStream_t st) {
   const ExplicitPlan plan = plan_view(h, ws);
   if (cudaMemsetAsync(plan.pool_used, 0, 16, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
   auto plan_kern = explicit_plan_kernel<BN>;
   if (cudaFuncSetAttribute(plan_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h.smem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
-  plan_kern<<<(unsigned)h.n_blocks, kPlanThreads, h.smem, st>>>(row_off, col, n_rows, Lk, h.n_key_tiles, h.min_entries,
-                                                                plan, use_nan, O, d);
+  plan_kern<<<(unsigned)h.n_blocks, kPlanThreads, h.smem, st>>>(row_off, col, n_rows, nnz, Lk, h.n_key_tiles,
+                                                                h.min_entries, plan, use_nan, O, d);
   g_launches.fetch_add(1);
   return launch_status();
 }
@@ -263,8 +265,8 @@ int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, in
 inline int build_plan(int d, const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk,
                       char* ws, int use_nan, float* O, cudaStream_t st) {
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, d);
-  return (h.bn == 64) ? launch_plan<64>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st)
-                      : launch_plan<32>(row_off, col, n_rows, Lk, d, h, ws, use_nan, O, st);
+  return (h.bn == 64) ? launch_plan<64>(row_off, col, n_rows, nnz, Lk, d, h, ws, use_nan, O, st)
+                      : launch_plan<32>(row_off, col, n_rows, nnz, Lk, d, h, ws, use_nan, O, st);
 }
 
 // Rows without any mask entry get a NaN output row (what the inspector does in a one-shot call, for calls that
@@ -279,12 +281,23 @@ __global__ void nan_fill_empty_rows_kernel(const uint64_t* __restrict__ row_off,
 }
 
 // The two compute launches of the split, from a filled plan region: dense tiles, then everything else.
+// [key_begin, key_end) restricts both to a range of keys (whole mask: 0, Lk): a forward split along the key axis
+// runs once per range and the passes chain through (m, l, O). key_begin must be a multiple of the key-tile size.
 template <int D>
 int launch_from_plan(const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m, float* l,
-                     float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
+                     float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, int64_t key_begin, int64_t key_end,
+                     cudaStream_t st) {
   constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
   const ExplicitPlan plan = plan_view(h, ws);
+  const bool whole = (key_begin <= 0 && key_end >= Lk);
+  PlanHeader want;
+  want.magic = kPlanMagic;
+  want.n_rows = n_rows;
+  want.nnz = nnz;
+  want.n_keys = Lk;
+  want.d = D;
+  want.bn = BN;
   tile::BandParams prm{};
   prm.mode = 3;
   prm.n_keys = Lk;
@@ -296,6 +309,10 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   prm.x_kt = plan.rb_kt;
   prm.x_moff = plan.rb_moff;
   prm.x_masks = plan.masks;
+  prm.x_hdr = plan.header;
+  prm.x_want = want;
+  prm.x_kt_lo = whole ? 0 : (int)(key_begin / BN);
+  prm.x_kt_hi = whole ? 0x7fffffff : (int)((key_end + BN - 1) / BN);
   CUtensorMap tmQ, tmK, tmV;
   const int64_t pitch = D * (int64_t)sizeof(float);
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, Lk, pitch, BN) ||
@@ -305,24 +322,38 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   if (rc) return rc;
   // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
   const float scale = 1.0f / sqrtf((float)D);
-  ResidualCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu};
-  ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots};
   const int64_t row_blocks = (n_rows + kRowWarps - 1) / kRowWarps;
   const int list_blocks = (int)(row_blocks < 512 ? row_blocks : 512);
   if (row_blocks + list_blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
-  gather_rows_listed_first_kernel<D, ResidualCols><<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(
-      Q, K, V, m, l, O, cols, listed, plan.heavy_rows, plan.heavy_count, list_blocks, 0, n_rows, 0, scale);
+  int* err = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_tile_error) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  if (whole) {
+    ResidualCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu};
+    ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots};
+    gather_rows_listed_first_kernel<D, ResidualCols><<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(
+        Q, K, V, m, l, O, cols, listed, plan.heavy_rows, plan.heavy_count, list_blocks, 0, n_rows, 0, scale, plan.header,
+        want, err);
+  } else {
+    const uint32_t klo = (uint32_t)key_begin, khi = (uint32_t)(key_end < Lk ? key_end : Lk);
+    ResidualRangeCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu, klo, khi, plan.unsorted};
+    ResidualRangeCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots, klo, khi, plan.unsorted};
+    gather_rows_listed_first_kernel<D, ResidualRangeCols>
+        <<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, listed, plan.heavy_rows,
+                                                                        plan.heavy_count, list_blocks, 0, n_rows, 0, scale,
+                                                                        plan.header, want, err);
+  }
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_TILED);
   return launch_status();
 }
 
 inline int forward_from_plan(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m,
-                             float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st) {
+                             float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st,
+                             int64_t key_begin = 0, int64_t key_end = INT64_MAX) {
   switch (d) {
-    case 32: return launch_from_plan<32>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
-    case 64: return launch_from_plan<64>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
-    case 128: return launch_from_plan<128>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, st);
+    case 32: return launch_from_plan<32>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
+    case 64: return launch_from_plan<64>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
+    case 128: return launch_from_plan<128>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
   }
   return SPFA_ERR_EMBED_DIM;
 }
@@ -380,7 +411,6 @@ const char* spfa_status_string(int s) {
     case SPFA_ERR_GLOBAL_COUNT: return "There are either no global tokens provided or there are more than the sequence length given.";
     case SPFA_ERR_TOO_LARGE: return "size beyond a fixed maximum";
     case SPFA_ERR_REGISTER_BUDGET: return "the tiled kernel of this build cannot run (register allocation below its setmaxnreg budgets)";
-    case SPFA_ERR_PLAN_MISMATCH: return "the stored plan was built for another (n_rows, nnz, Lk, d)";
   }
   return "unknown status";
 }
@@ -504,9 +534,17 @@ int spfa_coo_plan_build(const uint64_t* row_ind, const uint32_t* col_ind, int64_
 int spfa_planned_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
                              int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan, const void* plan,
                              size_t plan_bytes, void* stream) {
+  return spfa_planned_forward_keys_f32(Q, K, V, m, l, O, n_rows, nnz, Lk, d, use_nan, plan, plan_bytes, 0, Lk, stream);
+}
+
+int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                  int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan, const void* plan,
+                                  size_t plan_bytes, int64_t key_begin, int64_t key_end, void* stream) {
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
   if (n_rows <= 0 || nnz <= 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (key_begin < 0 || key_end < key_begin || (key_begin % 64) != 0) return SPFA_ERR_BAD_ARG;
+  if (key_end > Lk) key_end = Lk;
   const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
   if (need == 0) return SPFA_ERR_BAD_ARG;
   rc = check_workspace(plan, plan_bytes, need);
@@ -519,7 +557,9 @@ int spfa_planned_forward_f32(const float* Q, const float* K, const float* V, flo
     g_launches.fetch_add(1);
     if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
   }
-  return forward_from_plan(d, Q, K, V, offs, m, l, O, n_rows, nnz, Lk, base + spfa_coo_min_workspace_bytes(n_rows), st);
+  if (key_end == key_begin) return SPFA_OK;
+  return forward_from_plan(d, Q, K, V, offs, m, l, O, n_rows, nnz, Lk, base + spfa_coo_min_workspace_bytes(n_rows), st,
+                           key_begin, key_end);
 }
 
 int64_t spfa_coo_static_max_rows(void) { return kStaticCooMaxRows; }

@@ -23,6 +23,24 @@ __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); 
 
 __device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
 
+// Identity of a filled plan region, written by the inspector into the region's first 256-byte block (behind the
+// two counters) and compared by every kernel that consumes the region with the shape its caller passed: a plan
+// built for another mask shape would otherwise shift every table behind it and send the tiled kernel to wild
+// addresses. On a mismatch the consuming kernels record code kPlanMismatchCode in the error word and do nothing.
+struct PlanHeader {
+  unsigned long long magic;
+  long long n_rows, nnz, n_keys;
+  int d, bn;
+};
+constexpr unsigned long long kPlanMagic = 0x53504641504c414eull;  // "SPFAPLAN"
+constexpr int kPlanMismatchCode = 401;
+constexpr int kPlanHeaderOffset = 32;  // bytes into the region: [pool_used u64][heavy_count u32][unsorted u32][pad] then this
+
+__device__ __forceinline__ bool plan_header_matches(const PlanHeader* __restrict__ h, const PlanHeader& want) {
+  return h->magic == want.magic && h->n_rows == want.n_rows && h->nnz == want.nnz && h->n_keys == want.n_keys &&
+         h->d == want.d && h->bn == want.bn;
+}
+
 // ---- explicit CSR rows (also used for COO after the row-pointer pass) ---------------------------
 // Row r of the shard owns col[row_off[r] .. row_off[r+1])   (reference: sp_flatt_csr_kernel.cu:29-33,117)
 struct CsrCols {

@@ -99,6 +99,12 @@ struct BandParams {
   const int* x_kt;
   const long long* x_moff;
   const uint32_t* x_masks;
+  // explicit masks: the plan's identity block and what the caller expects to find there (every CTA compares them
+  // before touching the tables above), and the range of key tiles [x_kt_lo, x_kt_hi) this launch works on (a
+  // forward split along the key axis runs one launch per range; the whole mask is [0, INT_MAX))
+  const PlanHeader* x_hdr;
+  PlanHeader x_want;
+  int x_kt_lo, x_kt_hi;
 };
 constexpr int kMaxDenseTiles = 32;  // per 128-row block; a CTA (two blocks) walks at most 64 key tiles
 
@@ -267,8 +273,8 @@ struct Plan {
   // explicit masks: merged key-tile list of the CTA: kt[64] (int), act[NSUB] (u64, bit j = sub-tile uses tile j;
   // tile j is then the popcount(act & (2^j - 1))-th tile of the sub-tile's own list), nT (int)
   static constexpr int kOffX = (kOffMisc + 16 + 15) / 16 * 16;
-  static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB;
-  static constexpr int kBytes = kOffX + (kXNt + 4 + 15) / 16 * 16;
+  static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB, kXFirst = kXNt + 4;  // first[NSUB] (int)
+  static constexpr int kBytes = kOffX + (kXFirst + 4 * NSUB + 15) / 16 * 16;
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
   static_assert(kDynSmem <= 227 * 1024, "beyond the shared memory one CTA can opt into");
   // TMEM columns: two S buffers per sub-tile (BN each, at BN (2x + b)), then O_x (D each, at 2 BN NSUB + D x)
@@ -297,6 +303,13 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (EXPL) {  // uniform over the CTA: a plan of another shape is not walked at all
+    if (!plan_header_matches(prm.x_hdr, prm.x_want)) {
+      if (threadIdx.x == 0) atomicCAS(err, 0, kPlanMismatchCode);
+      if ((prm.overlap & 2) && threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+      return;
+    }
+  }
 
   // ---- tile geometry (uniform across the CTA) ----
   const int64_t uq0 = prm.u_q_first + (int64_t)blockIdx.x * kQRows;  // first query u of this CTA
@@ -382,6 +395,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     int n[NSUB], pos[NSUB];
     const int* list[NSUB];
     uint64_t a[NSUB];
+    int* s_first = reinterpret_cast<int*>(smem + P::kOffX + P::kXFirst);
 #pragma unroll
     for (int x = 0; x < NSUB; ++x) {
       const int64_t b = (int64_t)blockIdx.x * NSUB + x;
@@ -390,6 +404,10 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       list[x] = prm.x_kt + b * kMaxDenseTiles;
       pos[x] = 0;
       a[x] = 0;
+      // the lists ascend, so the tiles inside [x_kt_lo, x_kt_hi) are a contiguous piece of each
+      while (pos[x] < n[x] && list[x][pos[x]] < prm.x_kt_lo) ++pos[x];
+      while (n[x] > pos[x] && list[x][n[x] - 1] >= prm.x_kt_hi) --n[x];
+      s_first[x] = pos[x];
     }
     int nt = 0;
     while (nt < 64) {
@@ -637,7 +655,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float sc = prm.scale_log2e;
     uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
     const uint32_t* xm = nullptr;
-    if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
+    if (EXPL && nx > 0)  // masks are stored per tile of the block's whole list; this launch starts at its first kept tile
+      xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row +
+           (size_t)reinterpret_cast<const int*>(smem + P::kOffX + P::kXFirst)[x] * (NC * 128);
     for (int it = 0; it < nx && ok; ++it) {
       int j;
       if (EXPL) {

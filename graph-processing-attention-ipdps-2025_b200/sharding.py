@@ -10,6 +10,9 @@ Host-side pieces (pure index arithmetic + torch.distributed, usable with the glo
   equal_row_ranges / nnz_balanced_row_ranges / coo_nnz_balanced_row_ranges   who owns which rows
   csr_shard / coo_shard                                                      a rank's slice of an explicit mask
   replicate_kv                                                               K/V row shards -> full K/V on every rank
+  KeyChunkExchange                                                           the same replication as world-1 rounds of
+                                                                             point-to-point sends, with the compute on
+                                                                             the chunks that have arrived overlapped
 The compute itself is `capi.*_forward(..., row_begin, row_end)` on each rank's rows.
 """
 from __future__ import annotations
@@ -101,3 +104,104 @@ def replicate_kv(K_shard: torch.Tensor, V_shard: torch.Tensor, ranges: list[tupl
                 dist.broadcast(K[b:e], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
                 dist.broadcast(V[b:e], src=dist.get_global_rank(group, r) if group is not None else r, group=group)
     return K, V
+
+
+def exchange_offsets(world: int) -> list[int]:
+    """Order in which a rank receives the other ranks' K/V chunks: in round t it receives from rank - o_t and sends
+    to rank + o_t (mod world). Neighbours first (1, world-1, 2, world-2, ...): the keys nearest to a rank's own rows,
+    where banded structure lives, arrive before the far ones."""
+    out = []
+    for k in range(1, world // 2 + 1):
+        out.append(k)
+        if world - k != k:
+            out.append(world - k)
+    return out
+
+
+class KeyChunkExchange:
+    """K/V replication overlapped with the forward, for operators that can work on one range of keys at a time.
+
+    K and V start row-sharded in equal chunks `kv_ranges` (rank r owns chunk r, already stored at its place inside
+    the full-size buffers `self.K`, `self.V`). `run()` sends the own chunk to every other rank and receives theirs in
+    world-1 rounds of point-to-point transfers (NCCL send/recv over NVLink on a communication stream; gloo on CPU),
+    and calls back on the compute stream:
+
+        before()                       work that needs no K/V at all (mask inspection), overlaps the first rounds
+        on_chunk(key_begin, key_end, i)  once for the own chunk (i = 0), then once per received chunk as soon as it has
+                                       landed (i = 1 .. world-1); the callee may read only K/V rows in that range
+
+    No reduction and no softmax-state exchange are involved: every pass chains into the rank's own (m, l, O).
+    """
+
+    def __init__(self, L: int, d: int, kv_ranges, rank: int, world: int, device, dtype=torch.float32, group=None):
+        self.L, self.d, self.rank, self.world, self.group = L, d, rank, world, group
+        self.kv_ranges = list(kv_ranges)
+        self.dev = torch.device(device)
+        self.K = torch.empty(L, d, dtype=dtype, device=self.dev)
+        self.V = torch.empty(L, d, dtype=dtype, device=self.dev)
+        self.cuda = self.dev.type == "cuda"
+        self.s_comm = torch.cuda.Stream(device=self.dev) if self.cuda else None
+        self.offsets = exchange_offsets(world)
+
+    def own(self):
+        b, e = self.kv_ranges[self.rank]
+        return self.K[b:e], self.V[b:e]
+
+    def _peer(self, r):
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    def _round(self, o):
+        """One round: own chunk to rank + o, chunk of rank - o into its place."""
+        dst, src = (self.rank + o) % self.world, (self.rank - o) % self.world
+        sb, se = self.kv_ranges[src]
+        Ko, Vo = self.own()
+        ops = [dist.P2POp(dist.isend, Ko, self._peer(dst), self.group), dist.P2POp(dist.isend, Vo, self._peer(dst), self.group),
+               dist.P2POp(dist.irecv, self.K[sb:se], self._peer(src), self.group),
+               dist.P2POp(dist.irecv, self.V[sb:se], self._peer(src), self.group)]
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()  # NCCL: makes the communication stream wait; gloo: blocks the host until the round is done
+        return sb, se
+
+    def exchange_only(self):
+        """The replication alone (for timing it): all rounds, then the current stream waits for the last."""
+        if self.world == 1:
+            return
+        if not self.cuda:
+            for o in self.offsets:
+                self._round(o)
+            return
+        cur = torch.cuda.current_stream(self.dev)
+        self.s_comm.wait_stream(cur)
+        with torch.cuda.stream(self.s_comm):
+            for o in self.offsets:
+                self._round(o)
+        cur.wait_stream(self.s_comm)
+
+    def run(self, on_chunk, before=None):
+        b, e = self.kv_ranges[self.rank]
+        if not self.cuda:  # host ranks (tests): rounds and passes alternate
+            if before is not None:
+                before()
+            on_chunk(b, e, 0)
+            for i, o in enumerate(self.offsets):
+                sb, se = self._round(o)
+                on_chunk(sb, se, i + 1)
+            return
+        cur = torch.cuda.current_stream(self.dev)
+        arrived = []
+        if self.world > 1:
+            self.s_comm.wait_stream(cur)  # the own chunk is final once the caller's earlier work is done
+            with torch.cuda.stream(self.s_comm):
+                for o in self.offsets:
+                    sb, se = self._round(o)
+                    ev = torch.cuda.Event()
+                    ev.record(self.s_comm)
+                    arrived.append((sb, se, ev))
+        if before is not None:
+            before()
+        on_chunk(b, e, 0)
+        for i, (sb, se, ev) in enumerate(arrived):
+            cur.wait_event(ev)
+            on_chunk(sb, se, i + 1)
+        if self.world > 1:
+            cur.wait_stream(self.s_comm)  # the sends read the own chunk: nothing later may overwrite it before they end

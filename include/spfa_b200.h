@@ -46,9 +46,8 @@ typedef enum spfa_status {
   SPFA_ERR_DILATION_BLOCK = -9, /* block_size / (dil_factor+1) < 1 (sp_flatt_local_2d_dilated_kernel.cu:284-286) */
   SPFA_ERR_GLOBAL_COUNT = -10,  /* n_global == 0 or > L (sp_flatt_global_no_local_kernel.cu:325-327) */
   SPFA_ERR_TOO_LARGE = -11,     /* size beyond a stated fixed maximum */
-  SPFA_ERR_REGISTER_BUDGET = -12, /* SPFA_PATH_TILED forced, but this build's tiled kernel got fewer registers than its
-                                     setmaxnreg budgets need (AUTO falls back to the gather path instead) */
-  SPFA_ERR_PLAN_MISMATCH = -13  /* a stored plan was built for other (n_rows, nnz, Lk, d) than the call passes */
+  SPFA_ERR_REGISTER_BUDGET = -12 /* SPFA_PATH_TILED forced, but this build's tiled kernel got fewer registers than its
+                                    setmaxnreg budgets need (AUTO falls back to the gather path instead) */
 } spfa_status;
 
 /* Human-readable text for a status code (static storage). */
@@ -135,6 +134,25 @@ int spfa_planned_forward_f32(const float* Q, const float* K, const float* V,
                              float* m, float* l, float* O,
                              int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan,
                              const void* plan, size_t plan_bytes, void* stream);
+/* A plan carries the (n_rows, nnz, Lk, d) it was built for. The kernels of spfa_planned_forward_f32 compare them
+ * with the arguments of the call before they read any table of the plan; on a mismatch they compute nothing and
+ * record code 401, which spfa_last_device_error() returns (the call itself has returned SPFA_OK by then: it is
+ * asynchronous). A plan region smaller than spfa_explicit_plan_bytes() is refused at once (SPFA_ERR_WORKSPACE).
+ *
+ * The same forward restricted to the keys [key_begin, key_end): dense tiles and residual entries whose key lies in
+ * the range are applied to (m, l, O), everything else is left for other calls. Calls over disjoint ranges that
+ * cover [0, Lk), in any order on one stream, give the result of spfa_planned_forward_f32 (the passes chain through
+ * the softmax state like any two calls on disjoint masks). It exists for multi-GPU callers that receive K and V
+ * in chunks and want to compute on the chunks that have arrived: only K/V rows inside the range are read.
+ * key_begin must be a multiple of 64 (the key-tile size); key_end is clipped to Lk. use_nan NaN-fills the rows
+ * without any mask entry and belongs on exactly one call of the series, before the others (the first one issued).
+ * Residual rows are cut by binary search when every row of the mask stores its columns in ascending order
+ * (recorded by the inspector); otherwise each pass walks all residual entries and skips the foreign ones. */
+int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V,
+                                  float* m, float* l, float* O,
+                                  int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan,
+                                  const void* plan, size_t plan_bytes,
+                                  int64_t key_begin, int64_t key_end, void* stream);
 
 /* ---- explicit COO mask, allocation-free variant ---------------------------------------------------
  * No counterpart in the reference (its COO kernel needs no scratch because it re-scans the row array

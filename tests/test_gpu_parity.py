@@ -653,6 +653,49 @@ def test_stored_plan_matches_one_shot_calls(capi, orc, pkg):
     assert_state_close(to_np(st), want, TOL_TILED, "planned forward, chained")
 
 
+def test_stored_plan_of_another_shape_is_refused_on_the_device(capi):
+    """A plan names the (n_rows, nnz, Lk, d) it was built for; a forward call that passes other values finds the
+    mismatch on the device, computes nothing and reports code 401 (no table of the foreign plan is read)."""
+    L, Lk, d = 700, 900, 64
+    mask = _band_plus_random(L, Lk, 40, 0.003, 23)
+    row_off, col = _csr_of(mask)
+    plan = capi.csr_plan(dev(row_off), dev(col), Lk, d)
+    Q, K, V = (dev(x) for x in seeded_qkv(L, d, 1, Lk))
+    st = capi.new_state(L, d)
+    plan.nnz -= 7  # same buffer, wrong description: still large enough, so only the device-side check can tell
+    capi.planned_forward(Q, K, V, *st, plan)
+    assert capi.last_device_error() == 401
+    assert torch.isinf(st[0]).all() and (st[1] == 0).all() and (st[2] == 0).all()
+    plan.nnz += 7
+    capi.planned_forward(Q, K, V, *st, plan)
+    assert capi.last_device_error() == 0 and (st[1] > 0).any()
+
+
+@pytest.mark.parametrize("shuffle", [False, True])
+@pytest.mark.parametrize("L,Lk,d,chunks", [(700, 900, 64, 3), (1000, 2048, 128, 8), (300, 640, 32, 2)])
+def test_planned_forward_split_along_the_key_axis(capi, orc, L, Lk, d, chunks, shuffle):
+    """Passes over disjoint key ranges, chained through (m, l, O) in any order, equal the whole forward: rows with
+    ascending columns are cut by binary search, shuffled rows are filtered slot by slot; a row with more than 128
+    residual entries (walked by a whole CTA) is present."""
+    mask = _band_plus_random(L, Lk, 40, 0.004, 5 + L, empty_rows=(3,))
+    mask[10, ::3] = True  # a long row
+    row_off, col = _csr_of(mask, shuffle_seed=9 if shuffle else None)
+    Q, K, V = seeded_qkv(L, d, 77, Lk)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    plan = capi.csr_plan(dev(row_off), dev(col), Lk, d)
+    edges = sorted({0, Lk} | {int(x) // 64 * 64 for x in np.linspace(0, Lk, chunks + 1)[1:-1]})
+    ranges = list(zip(edges[:-1], edges[1:]))
+    order = ranges[1:] + ranges[:1]  # not in key order
+    Kd, Vd = dev(K), dev(V)
+    st = capi.new_state(L, d)
+    for n, (a, b) in enumerate(order):
+        # only the rows of this range are present on the device copy the pass sees: foreign K/V rows are poison
+        Kp, Vp = torch.full_like(Kd, float("nan")), torch.full_like(Vd, float("nan"))
+        Kp[a:b], Vp[a:b] = Kd[a:b], Vd[a:b]
+        capi.planned_forward_keys(dev(Q), Kp, Vp, *st, plan, a, b, use_nan=(n == 0))
+    assert_state_close(to_np(st), want, TOL_TILED, f"key-split forward, {len(ranges)} ranges")
+
+
 @pytest.mark.parametrize("L", [262144, 1048576])
 def test_full_size_coo_graph_split_vs_gather_and_oracle(capi, orc, L):
     """The benchmark's COO graph generator at a quarter of and at the benchmarked size (L=1048576: 1.6e8 entries, rows

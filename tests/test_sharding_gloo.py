@@ -88,3 +88,78 @@ def test_two_rank_row_sharding_matches_unsharded(pkg, orc, tmp_path):
         parts = [np.load(os.path.join(tmp_path, f"rank{r}.npz")) for r in range(world)]
         got = np.concatenate([p[key] for p in parts])
         np.testing.assert_array_equal(got, want)
+
+
+def _exchange_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+
+    pkg, orc = entry.load(), entry.load_oracle()
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        L, d = 192, 16
+        Q, K, V = seeded_qkv(L, d, 31)
+        _, row_off, col = random_csr(L, L, 0.15, 8, empty_rows=(7,))
+        off_t, col_t = torch.from_numpy(row_off.astype(np.int64)), torch.from_numpy(col.astype(np.int32))
+        q_ranges = pkg.sharding.nnz_balanced_row_ranges(off_t, world)   # query rows: balanced by mask entries
+        kv_ranges = pkg.sharding.equal_row_ranges(L, world, multiple=64)  # K/V: equal chunks on key-tile multiples
+        rb, re = q_ranges[rank]
+        my_off, my_col = pkg.sharding.csr_shard(off_t, col_t, rb, re)
+        my_off, my_col = my_off.numpy(), my_col.numpy()
+        ex = pkg.sharding.KeyChunkExchange(L, d, kv_ranges, rank, world, "cpu")
+        ex.K.fill_(float("nan"))
+        ex.V.fill_(float("nan"))
+        kb, ke = kv_ranges[rank]
+        Ko, Vo = ex.own()
+        Ko.copy_(torch.from_numpy(K[kb:ke]))
+        Vo.copy_(torch.from_numpy(V[kb:ke]))
+        state = orc.new_state(re - rb, d)
+        seen, log = [], []
+
+        def before():
+            log.append("before")
+
+        def on_chunk(a, b, i):
+            log.append(i)
+            # the chunk has landed; chunks not yet received are still poison
+            assert not torch.isnan(ex.K[a:b]).any() and not torch.isnan(ex.V[a:b]).any()
+            seen.append((a, b))
+            have = np.zeros(L, dtype=bool)
+            for x, y in seen:
+                have[x:y] = True
+            assert np.array_equal(~np.isnan(ex.K.numpy()).any(axis=1), have)
+            # this pass: the mask entries of my rows whose key lies in [a, b)
+            keep = (my_col >= a) & (my_col < b)
+            rows = np.repeat(np.arange(re - rb), np.diff(my_off))
+            cnt = np.bincount(rows[keep], minlength=re - rb)
+            off2 = np.concatenate([[0], np.cumsum(cnt)]).astype(np.uint64)
+            Kc, Vc = np.nan_to_num(ex.K.numpy()), np.nan_to_num(ex.V.numpy())
+            orc.csr_forward(Q[rb:re], Kc, Vc, off2, my_col[keep], state=state)
+
+        ex.run(on_chunk, before)
+        assert log[0] == "before" and log[1:] == list(range(world))
+        assert sorted(seen) == sorted(kv_ranges) and seen[0] == kv_ranges[rank]
+        assert torch.equal(ex.K, torch.from_numpy(K)) and torch.equal(ex.V, torch.from_numpy(V))
+        np.savez(os.path.join(tmp, f"ex{rank}.npz"), rb=rb, re=re, O=state[2], l=state[1])
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_key_chunk_exchange_orders_passes_behind_arrivals(pkg, orc, tmp_path, world):
+    """The overlapped K/V replication: every pass runs only after its chunk has landed (the rest of the buffers is
+    still poison), the own chunk comes first, all chunks are seen exactly once, and the passes chained through the
+    softmax state give the unsplit result."""
+    assert pkg.sharding.exchange_offsets(8) == [1, 7, 2, 6, 3, 5, 4] and pkg.sharding.exchange_offsets(2) == [1]
+    assert pkg.sharding.exchange_offsets(1) == [] and sorted(pkg.sharding.exchange_offsets(5)) == [1, 2, 3, 4]
+    port = 31500 + (os.getpid() % 2000) + world
+    mp.spawn(_exchange_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    L, d = 192, 16
+    Q, K, V = seeded_qkv(L, d, 31)
+    _, row_off, col = random_csr(L, L, 0.15, 8, empty_rows=(7,))
+    want = orc.csr_forward(Q, K, V, row_off, col)
+    parts = sorted((np.load(os.path.join(tmp_path, f"ex{r}.npz")) for r in range(world)), key=lambda p: int(p["rb"]))
+    np.testing.assert_allclose(np.concatenate([p["O"] for p in parts]), want[2], rtol=0, atol=1e-12)
+    np.testing.assert_allclose(np.concatenate([p["l"] for p in parts]), want[1], rtol=1e-12)
