@@ -2,24 +2,31 @@
 """Benchmark of the sparse FlashAttention forward path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference] [--path auto|gather|tiled]
-                    [--strong] [--planned] [--e2e-whole] [--rows L] [--no-cpu-baseline]
+                    [--weak] [--planned] [--no-overlap] [--rows L] [--no-cpu-baseline] [--no-per-workload]
 
-One "step" = one forward of one mask family over one batch of seeded synthetic input. The default
-workload is the Local (sliding-window) configuration: L=65536, d=64, fp32 Q/K/V ~ N(0,1), window
-|i-j| <= 256. Other workloads (--workload csr|l1d|gnl|l2d|coo) are the remaining benchmark shapes; `blocks` is the
-block-level dilation pattern as an explicit CSR mask (not expressible through the reference's own 2D operator).
---planned times explicit-mask calls from a dense-tile plan built once outside the timed region. The end-to-end
-leg uses the host pipelines of hostio.py where they pay (see its `api` field); --e2e-whole forces whole-tensor copies.
+One "step" = one forward of one mask family over one batch of seeded synthetic input. The default workload
+is the COO graph configuration: L=1048576, d=64, fp32 Q/K/V ~ N(0,1), power-law row degrees plus a band
+(1.6e8 mask entries), the largest configuration and the one that is split over GPUs. The other workloads
+(--workload local|l1d|gnl|l2d|csr) are the remaining benchmark shapes; `blocks` is the block-level dilation
+pattern as an explicit CSR mask (not expressible through the reference's own 2D operator). With the default
+workload on one GPU the line also carries `per_workload`: a short measurement of every mask family.
+--planned times explicit-mask calls from a dense-tile plan built once outside the timed region.
 
-Multi-GPU (launched by torch.distributed.run, one rank per GPU): weak scaling over query-row ranges.
-The sequence has N*L rows; rank r owns rows [r*L, (r+1)*L) and K/V of the whole sequence are
-replicated on every rank (no reduction, no softmax-state exchange). `value` is measured with K/V
-already replicated; `e2e` includes the host->device copy of the rank's Q/K/V rows, the NCCL all-gather
-that replicates K/V, the state initialisation, the forward and the device->host copy of O.
+Multi-GPU (launched by torch.distributed.run, one rank per GPU): STRONG scaling. The workload's rows are split
+into one contiguous query-row range per rank (balanced by mask entries for CSR/COO), K and V start row-sharded
+in equal chunks, and every timed step contains the replication of K/V to all ranks: for explicit masks as world-1
+rounds of point-to-point transfers with the forward of each arrived key chunk overlapped (sharding.KeyChunkExchange;
+--no-overlap: all-gather first, then one forward), for implicit masks as an all-gather followed by the forward.
+`compute_only_ms` (K/V already replicated) and `replicate_ms` (the exchange alone) are printed beside `value`.
+--weak restores weak scaling (L rows per GPU) for the implicit masks.
 
-Prints ONE JSON line (rank 0). Timing: CUDA events on the launching stream around each step, L2
-flushed (256 MiB memset) and the (m, l, O) state re-initialised before each step outside the timed
-span; per-rank total = sum of step times; reported time = max over ranks.
+`e2e` is the same step from pinned HOST buffers: host->device copies of Q/K/V (per rank: its shards), the forward,
+the device->host copy of O, overlapped where the data dependencies allow (hostio.py); `e2e_plugin` is the plain
+drop-in call `spfa_<mask>.forward` between whole-tensor copies (one GPU).
+
+Prints ONE JSON line (rank 0). Timing: CUDA events on the launching stream around each step, L2 flushed
+(256 MiB memset) and the (m, l, O) state re-initialised before each step outside the timed span; per-rank
+total = sum of step times; reported time = max over ranks.
 """
 from __future__ import annotations
 
@@ -59,7 +66,9 @@ WORKLOADS = {
     "coo": dict(kind="coo", L=1048576, d=64, p0=64, p1=0,
                 desc="COO explicit graph mask, L=1048576, d=64, fp32, Zipf(2.1) mean-32 max-8192 random cols + band 64"),
 }
-
+DEFAULT_WORKLOAD = "coo"
+FULL_SIZE_L = {k: v["L"] for k, v in WORKLOADS.items()}  # --rows shrinks WORKLOADS; recorded ncu traffic is full-size
+PER_WORKLOAD = ("local", "l1d", "gnl", "l2d", "csr", "coo")
 
 # ---------------------------------------------------------------------------------------------------------
 # mask sizes (closed forms) and algorithmic bytes
@@ -236,33 +245,40 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="local", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default="auto", choices=["auto", "gather", "tiled"])
     ap.add_argument("--rows", type=int, default=0, help="override the workload's L (smaller cases for profiling)")
-    ap.add_argument("--strong", action="store_true", help="N>1: split the workload's L rows over the GPUs (default: L rows per GPU)")
+    ap.add_argument("--weak", action="store_true",
+                    help="N>1, implicit masks: L rows per GPU (sequence of N*L rows) instead of splitting L rows")
     ap.add_argument("--planned", action="store_true",
                     help="csr/coo/blocks: build the dense-tile plan once outside the timed region and time forward calls "
                          "from the stored plan (a caller that applies one mask many times); default: one-shot calls")
-    ap.add_argument("--e2e-whole", action="store_true",
-                    help="end-to-end leg: copy whole tensors, one forward call through the torch module, copy O back "
-                         "(default for banded masks of 48 MB or more per tensor on one GPU: the chunked host pipeline of hostio.py)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="N>1, explicit masks: all-gather K/V first, then one forward (default: forward of each key chunk "
+                         "overlapped with the arrival of the next)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-per-workload", action="store_true", help="skip the short measurement of every mask family")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer legs (profiling runs)")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
     return ap.parse_args()
 
 
 class Job:
-    """One rank's share of the workload, resident on its GPU."""
+    """One rank's share of a workload, resident on its GPU: its query rows, the mask slice of those rows, all of K/V."""
 
-    def __init__(self, workload, rank, world, dev, whole_on_one_gpu=False, strong=False):
+    def __init__(self, workload, rank, world, dev, whole_on_one_gpu=False, weak=False):
         w = WORKLOADS[workload]
-        self.w, self.kind, self.d = w, w["kind"], w["d"]
-        # weak scaling: N*L rows in the sequence, L per GPU; strong scaling: L rows split over the GPUs
-        self.L = w["L"] if strong else w["L"] * world
+        self.name, self.w, self.kind, self.d = workload, w, w["kind"], w["d"]
+        weak = weak and self.kind not in ("csr", "coo")
+        self.weak = weak
+        # strong scaling: L rows split over the GPUs; weak scaling: N*L rows in the sequence, L per GPU
+        self.L = w["L"] * world if weak else w["L"]
         self.rank, self.world, self.dev = rank, world, dev
         self.p0, self.p1 = w["p0"], w["p1"]
         seed = 1000 + sorted(WORKLOADS).index(workload)
+        self.seed = seed
+        sh = entry.load().sharding
         full_mask = None
         if self.kind == "csr":
             full_mask = (make_block_dilated_csr(self.L, self.p0, self.p1, dev) if w.get("gen") == "block_dilated"
@@ -272,16 +288,16 @@ class Job:
         if whole_on_one_gpu:  # a single-GPU implementation given the whole job
             self.ranges = [(0, self.L)]
             rank = 0
-        elif not strong:
+        elif weak:
             self.ranges = [(r * w["L"], (r + 1) * w["L"]) for r in range(world)]
+        elif self.kind == "csr":
+            self.ranges = sh.nnz_balanced_row_ranges(full_mask[0], world)
+        elif self.kind == "coo":
+            self.ranges = sh.coo_nnz_balanced_row_ranges(full_mask[0], self.L, world)
         else:
-            sh = entry.load().sharding
-            if self.kind == "csr":
-                self.ranges = sh.nnz_balanced_row_ranges(full_mask[0], world)
-            elif self.kind == "coo":
-                self.ranges = sh.coo_nnz_balanced_row_ranges(full_mask[0], self.L, world)
-            else:
-                self.ranges = sh.equal_row_ranges(self.L, world, multiple=256)
+            self.ranges = sh.equal_row_ranges(self.L, world, multiple=256)
+        # K/V start row-sharded in equal chunks on key-tile multiples, whatever the query split is
+        self.kv_ranges = sh.equal_row_ranges(self.L, 1 if whole_on_one_gpu else world, multiple=64)
         self.rb, self.re = self.ranges[rank]
         self.L_local = self.re - self.rb
         Q, self.K, self.V = make_qkv(self.L, self.d, seed, dev)
@@ -289,6 +305,7 @@ class Job:
         del Q
         self.G = None
         self.mask = None
+        self.plan = None
         n_live = self.L_local
         if self.kind == "global_no_local":
             g = torch.Generator().manual_seed(seed)
@@ -309,10 +326,8 @@ class Job:
         else:
             self.nnz = implicit_nnz(self.kind, self.L, self.p0, self.p1, None, self.rb, self.re)
             if self.kind == "local_2d_dilated":
-                n_live = self.L_local // (self.p1 + 1) if self.p0 % (self.p1 + 1) == 0 else None
-                if n_live is None:
-                    i = torch.arange(self.rb, self.re)
-                    n_live = int(((i % self.p0) % (self.p1 + 1) == 0).sum())
+                i = torch.arange(self.rb, self.re)
+                n_live = int(((i % self.p0) % (self.p1 + 1) == 0).sum())
         del full_mask
         self.n_live = n_live
         self.flops = 4.0 * self.nnz * self.d
@@ -330,20 +345,19 @@ class Job:
     def flush_l2(self):
         self.flush_buf.zero_()
 
-    def build_plan(self, capi):
+    def build_plan(self, capi, out=None):
         if self.kind == "csr":
-            self.plan = capi.csr_plan(self.mask[0], self.mask[1], self.L, self.d)
-        elif self.kind == "coo":
-            self.plan = capi.coo_plan(self.mask[0], self.mask[1], self.L_local, self.L, self.d, row_begin=self.rb)
-        else:
-            raise SystemExit("--planned applies to the explicit masks only")
+            return capi.csr_plan(self.mask[0], self.mask[1], self.L, self.d, out=out)
+        if self.kind == "coo":
+            return capi.coo_plan(self.mask[0], self.mask[1], self.L_local, self.L, self.d, row_begin=self.rb, out=out)
+        raise SystemExit("--planned applies to the explicit masks only")
 
     def forward(self, capi, Q=None, K=None, V=None):
         Q = self.Q if Q is None else Q
         K = self.K if K is None else K
         V = self.V if V is None else V
         k, st = self.kind, (self.m, self.l, self.O)
-        if getattr(self, "plan", None) is not None:
+        if self.plan is not None:
             capi.planned_forward(Q, K, V, *st, self.plan, use_nan=False)
             return
         if k == "local":
@@ -358,6 +372,20 @@ class Job:
             capi.csr_forward(Q, K, V, self.mask[0], self.mask[1], *st, use_nan=False)
         else:
             capi.coo_forward(Q, K, V, self.mask[0], self.mask[1], *st, use_nan=False, row_begin=self.rb)
+
+    def plugin_forward(self, binding, Q, K, V, w_val):
+        """The drop-in call of the reference's API (one GPU, whole tensors)."""
+        st, k = (self.m, self.l, self.O), self.kind
+        if k == "local":
+            binding.forward(Q, K, V, *st, self.p0)
+        elif k == "local_1d_dilated":
+            binding.forward(Q, K, V, *st, self.p0, self.p1)
+        elif k == "local_2d_dilated":
+            binding.forward(Q, K, V, *st, self.p0, self.p1, True)
+        elif k == "global_no_local":
+            binding.forward(Q, K, V, *st, self.G, self.p0)
+        else:
+            binding.forward(Q, K, V, self.mask[0], self.mask[1], w_val, *st, False)
 
 
 def dist_max(x: float, world: int, dev) -> float:
@@ -389,18 +417,24 @@ def barrier(world):
         torch.cuda.synchronize()
 
 
-def timed_steps(job, fn, steps, warmup, world, counter=None):
+def timed_steps(job, fn, steps, warmup, world, counter=None, before_each=None):
     """warmup untimed calls, then `steps` calls each bracketed by CUDA events (flush + reset outside).
     Returns (per-step ms, kernels launched by the library inside the timed loop)."""
     for _ in range(warmup):
         job.reset_state()
+        if before_each:
+            before_each()
         fn()
     barrier(world)
     n0 = counter() if counter else 0
     evs = []
     for _ in range(steps):
         job.reset_state()
+        if before_each:
+            before_each()
         job.flush_l2()
+        if world > 1:  # every rank enters the step together: a step contains an exchange between the ranks
+            barrier(world)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -411,166 +445,321 @@ def timed_steps(job, fn, steps, warmup, world, counter=None):
     return [a.elapsed_time(b) for a, b in evs], n1 - n0
 
 
+def roofline_of(job, workload, kernel_ms, tiled, peaks, peak_src, full_size):
+    """Roofline object of one workload from its mean step time on one GPU.
+    Banded masks on the tiled path (and the all-dense block pattern): tensor pipe, useful flops 4*nnz*d.
+    Implicit HBM-bound masks: compulsory bytes. Explicit masks: the DRAM traffic recorded by ncu for the same
+    call decides the fraction (their gather-counted bytes assume no cache reuse and exceed what DRAM moves; that
+    figure is kept as `effective_gbs`)."""
+    tensor_bound = tiled and (job.kind in ("local", "local_1d_dilated") or job.w.get("gen") == "block_dilated")
+    if tensor_bound:
+        peak = peaks["bf16_tflops"] / 2.0
+        achieved = job.flops / (kernel_ms * 1e-3) / 1e12
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": recorded_traffic(f"tiled_{workload}") if full_size else None,
+                "note": f"useful flops 4*nnz*d per step / mean step time; peak = {peak_src} bf16 matmul / 2 taken as TF32"}
+    peak = peaks["hbm_gbs"]
+    algorithmic = job.bytes / (kernel_ms * 1e-3) / 1e9
+    traffic = recorded_traffic(f"gather_{workload}") if full_size else None
+    if job.kind in ("csr", "coo"):
+        real = (traffic / (kernel_ms * 1e-3) / 1e9) if traffic else None
+        return {"bound": "hbm", "achieved": real, "peak": peak, "unit": "GB/s", "frac": (real / peak) if real else None,
+                "traffic": traffic, "effective_gbs": algorithmic,
+                "note": "achieved = DRAM bytes of one step as recorded by ncu (profiles/) / mean step time here; "
+                        "effective_gbs = gather-counted bytes nnz*(2*d*4+4)+... / time (no credit for cache reuse taken "
+                        f"out, so it may exceed the peak); peak = {peak_src} copy bandwidth"}
+    return {"bound": "hbm", "achieved": algorithmic, "peak": peak, "unit": "GB/s", "frac": algorithmic / peak,
+            "traffic": traffic,
+            "note": f"compulsory bytes per step / mean step time; peak = {peak_src} copy bandwidth"}
+
+
+def measure_one_gpu(workload, capi, dev, steps, warmup, peaks, peak_src, path, planned=False, job=None):
+    """Short device-timed measurement of one workload on one GPU (inputs resident): the per_workload entries."""
+    own = job is None
+    if own:
+        job = Job(workload, 0, 1, dev)
+    job.plan = job.build_plan(capi) if planned else None
+    times, launches = timed_steps(job, lambda: job.forward(capi), steps, warmup, 1, capi.launch_count)
+    tiled = capi.last_path() == capi.PATH_TILED
+    ms = statistics.mean(times)
+    full = WORKLOADS[workload]["L"] == FULL_SIZE_L.get(workload)
+    out = {"workload": job.w["desc"], "fwd_ms": ms, "fwd_ms_median": statistics.median(times), "steps": steps,
+           "tflops": job.flops / (ms * 1e-3) / 1e12, "nnz": int(job.nnz), "dtype": "tf32" if tiled else "f32",
+           "path": "tiled" if tiled else "gather", "launches_per_step": launches / max(1, steps),
+           "roofline": roofline_of(job, workload, ms, tiled, peaks, peak_src, full)}
+    if planned:
+        out["plan"] = "dense-tile plan built once outside the timed region"
+    job.plan = None
+    if own:
+        del job
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args, rank, world, dev):
     pkg = entry.load()
     capi = pkg.capi
     capi.lib()
     capi.set_path({"auto": capi.PATH_AUTO, "gather": capi.PATH_GATHER, "tiled": capi.PATH_TILED}[args.path])
-    job = Job(args.workload, rank, world, dev, strong=args.strong)
-    if args.planned:
-        job.build_plan(capi)
+    job = Job(args.workload, rank, world, dev, weak=args.weak)
+    explicit = job.kind in ("csr", "coo")
     peaks, peak_src = load_peaks()
+    nan = float("nan")
+    if args.planned:
+        job.plan = job.build_plan(capi)
 
-    # ---- kernel-only: inputs resident in HBM ----
+    # ---- compute only: inputs (all of K/V included) resident in HBM ----
     sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
     if sampler:
         sampler.start()
-    times, launches = timed_steps(job, lambda: job.forward(capi), args.steps, args.warmup, world, capi.launch_count)
+    times_c, launches = timed_steps(job, lambda: job.forward(capi), args.steps, args.warmup, world, capi.launch_count)
     tiled = capi.last_path() == capi.PATH_TILED
-    # Global-no-local stays HBM-bound on the tiles; explicit masks are tensor-bound only when (nearly) every
-    # entry lies in a dense tile, which of the benchmark shapes is the block pattern
-    tensor_bound = tiled and (job.kind in ("local", "local_1d_dilated") or job.w.get("gen") == "block_dilated")
+    O_compute = job.O.clone() if world > 1 else None
+
+    # ---- N > 1: the step that is reported contains the replication of K/V ----
+    times, times_x, ex, step, poison, exchange_note = times_c, None, None, None, None, None
+    if world > 1:
+        sh = pkg.sharding
+        ex = sh.KeyChunkExchange(job.L, job.d, job.kv_ranges, rank, world, dev)
+        kb, ke = job.kv_ranges[rank]
+        Ko, Vo = ex.own()
+        Ko.copy_(job.K[kb:ke])
+        Vo.copy_(job.V[kb:ke])
+        job.K = job.V = None  # from here on K/V exist only as this rank's chunk plus what the exchange delivers
+        torch.cuda.empty_cache()
+
+        def poison():  # outside the timed span: a step must not live on the chunks the previous step received
+            for t in (ex.K, ex.V):
+                t[:kb].fill_(nan)
+                t[ke:].fill_(nan)
+
+        overlap = (explicit and not args.no_overlap and args.path != "gather" and job.nnz >= (1 << 20)
+                   and capi.lib().spfa_explicit_plan_bytes(job.L_local, job.nnz, job.L, job.d) > 0)
+        if overlap:
+            plan_buf = job.plan if job.plan is not None else job.build_plan(capi)
+            before = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
+
+            def step():
+                ex.run(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b),
+                       before)
+            exchange_note = ("%d rounds of NCCL send/recv (own K/V chunk out, one chunk in); mask inspection and the "
+                             "forward of every arrived key chunk overlap the later rounds" % (world - 1))
+        elif explicit:
+            def step():
+                ex.exchange_only()
+                job.forward(capi, job.Q, ex.K, ex.V)
+            exchange_note = "%d rounds of NCCL send/recv, then one forward over all keys" % (world - 1)
+        else:
+            def step():
+                Kf, Vf = sh.replicate_kv(Ko, Vo, job.kv_ranges)
+                job.forward(capi, job.Q, Kf, Vf)
+            exchange_note = "NCCL all-gather of K and of V, then the forward"
+        times, launches = timed_steps(job, step, args.steps, args.warmup, world, capi.launch_count, before_each=poison)
+        torch.cuda.synchronize()
+        check = float((job.O - O_compute).abs().nan_to_num(nan=1e30).max().item())  # both paths, same rows
+        check = dist_max(check, world, dev)
+        xfn = ex.exchange_only if explicit else (lambda: sh.replicate_kv(Ko, Vo, job.kv_ranges))
+        times_x, _ = timed_steps(job, xfn, args.steps, args.warmup, world, before_each=poison)
     clocks = sampler.stop() if sampler else None
     total_ms = dist_max(sum(times), world, dev)
     total_flops = dist_sum(job.flops, world, dev)
     total_nnz = dist_sum(float(job.nnz), world, dev)
     nnz_imbalance = dist_max(float(job.nnz), world, dev) / max(total_nnz / world, 1.0)
     value = total_flops * args.steps / (total_ms * 1e-3) / 1e12
+    compute_ms = dist_max(sum(times_c), world, dev) / args.steps
+    replicate_ms = dist_max(sum(times_x), world, dev) / args.steps if times_x else 0.0
+    median_ms = dist_max(statistics.median(times), world, dev)
 
-    # ---- end to end: pinned host buffers -> device -> (all-gather K/V) -> forward -> host ----
-    hQ = job.Q.cpu().pin_memory()
-    hK = job.K[job.rb:job.re].cpu().pin_memory()
-    hV = job.V[job.rb:job.re].cpu().pin_memory()
-    hO = torch.empty_like(job.O, device="cpu").pin_memory()
-    dQ, dKs, dVs = torch.empty_like(job.Q), torch.empty_like(job.Q), torch.empty_like(job.Q)
-    ranges = job.ranges
-    binding = pkg.binding("spfa_" + job.kind) if world == 1 else None
-    w_val = torch.ones(1, device=dev)
-    plan_t = None
-    if args.planned and world == 1:
-        plan_t = (binding.plan(job.mask[0], job.mask[1], job.L, job.d) if job.kind == "csr"
-                  else binding.plan(job.mask[0], job.mask[1], job.L_local, job.L, job.d))
-
-    pipe = None
-    # chunking pays once a chunk's copies are large (measured: 8 chunks of 3 x 2 MB gain nothing on cfg2, whose
-    # host->device stream slows down by as much as the overlapped device->host copies save; 3 x 8 MB chunks gain 12 %)
-    if (world == 1 and job.kind in ("local", "local_1d_dilated", "local_2d_dilated") and not args.e2e_whole
-            and job.L * job.d * 4 >= (48 << 20)):
-        pipe = pkg.hostio.BandedHostPipeline(job.kind, job.L, job.d, job.p0, job.p1, n_chunks=8, device=dev)
-
-    full_pipe, chunk_call = None, None
-    small_banded = (pipe is None and job.kind in ("local", "local_1d_dilated", "local_2d_dilated")
-                    and job.L * job.d * 4 >= (8 << 20))
-    if (world == 1 and not args.e2e_whole and not args.planned
-            and (small_banded or (job.kind in ("csr", "coo", "global_no_local") and job.L * job.d * 4 >= (48 << 20)))):
-        # smaller banded workloads: K and V whole, then three Q chunks (measured 1.21 vs 1.29 ms on cfg2)
-        full_pipe = pkg.hostio.FullKeyHostPipeline(job.L, job.L, job.d, n_chunks=3 if small_banded else 8, device=dev)
-        if small_banded:
-            def chunk_call(a, b, q, k, v, m_, l_, o_):
-                if job.kind == "local":
-                    capi.local_forward(q, k, v, m_, l_, o_, job.p0, a, b)
-                elif job.kind == "local_1d_dilated":
-                    capi.local_1d_dilated_forward(q, k, v, m_, l_, o_, job.p0, job.p1, a, b)
-                else:
-                    capi.local_2d_dilated_forward(q, k, v, m_, l_, o_, job.p0, job.p1, True, a, b)
-        elif job.kind == "global_no_local":
-            def chunk_call(a, b, q, k, v, m_, l_, o_):
-                capi.global_no_local_forward(q, k, v, m_, l_, o_, job.G, job.p0, a, b)
-        elif job.kind == "coo":
-            cut = torch.searchsorted(job.mask[0], torch.tensor(full_pipe.edges, device=dev)).cpu().tolist()
-
-            def chunk_call(a, b, q, k, v, m_, l_, o_):
-                lo, hi = cut[full_pipe.edges.index(a)], cut[full_pipe.edges.index(b)]
-                capi.coo_forward(q, k, v, job.mask[0][lo:hi], job.mask[1][lo:hi], m_, l_, o_, use_nan=False, row_begin=a)
-        else:
-            def chunk_call(a, b, q, k, v, m_, l_, o_):  # offsets index the full column array
-                capi.csr_forward(q, k, v, job.mask[0][a:b + 1], job.mask[1], m_, l_, o_, use_nan=False)
-
-    def e2e_step():
-        if pipe is not None:  # chunked: copies in, row-range calls and copies out overlap
-            pipe.forward(hQ, hK, hV, hO, use_nan=True)
-            return
-        if full_pipe is not None:  # K, V first, then Q chunks in / row-range calls / O chunks out overlap
-            full_pipe.forward(chunk_call, hQ, hK, hV, hO)
-            return
-        dQ.copy_(hQ, non_blocking=True)
-        dKs.copy_(hK, non_blocking=True)
-        dVs.copy_(hV, non_blocking=True)
-        job.reset_state()
-        if world > 1:
-            Kf, Vf = pkg.sharding.replicate_kv(dKs, dVs, ranges)
-            job.forward(capi, dQ, Kf, Vf)
-        else:
-            st = (job.m, job.l, job.O)
-            k = job.kind
-            if k == "local":
-                binding.forward(dQ, dKs, dVs, *st, job.p0)
-            elif k == "local_1d_dilated":
-                binding.forward(dQ, dKs, dVs, *st, job.p0, job.p1)
-            elif k == "local_2d_dilated":
-                binding.forward(dQ, dKs, dVs, *st, job.p0, job.p1, True)
-            elif k == "global_no_local":
-                binding.forward(dQ, dKs, dVs, *st, job.G, job.p0)
-            elif args.planned:
-                binding.forward_planned(dQ, dKs, dVs, plan_t, int(job.mask[1].numel()), *st, False)
-            else:
-                binding.forward(dQ, dKs, dVs, job.mask[0], job.mask[1], w_val, *st, False)
-        hO.copy_(job.O, non_blocking=True)
-
-    e2e_times, _ = timed_steps(job, e2e_step, args.steps, args.warmup, world)
-    e2e_ms = dist_max(sum(e2e_times), world, dev)
-    e2e_value = total_flops * args.steps / (e2e_ms * 1e-3) / 1e12
-    h2d = 3 * job.L * job.d * 4
-    d2h = job.L * job.d * 4
+    e2e = None if args.no_e2e else run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops)
 
     if rank != 0:
         return None
-
-    # ---- roofline of the dominant kernel (this rank's launch) ----
-    kernel_ms = statistics.mean(times)
-    if tensor_bound:
-        peak = peaks["bf16_tflops"] / 2.0
-        achieved = job.flops / (kernel_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": recorded_traffic(f"tiled_{args.workload}"),
-                "note": f"useful flops 4*nnz*d per launch / mean launch time; peak = {peak_src} bf16 matmul / 2 taken as TF32"}
-    else:
-        peak = peaks["hbm_gbs"]
-        achieved = job.bytes / (kernel_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": recorded_traffic(f"gather_{args.workload}"),
-                "note": f"algorithmic bytes per launch / mean launch time; peak = {peak_src} copy bandwidth"}
-
+    kernel_ms = statistics.mean(times_c)
+    full = WORKLOADS[args.workload]["L"] == FULL_SIZE_L[args.workload] and world == 1
+    roof = roofline_of(job, args.workload, kernel_ms, tiled, peaks, peak_src, full)
+    scaling = "weak" if job.weak else "strong"
+    desc = job.w["desc"]
+    if world > 1:
+        desc += ("; sequence of %dx%d rows, one row range per GPU" % (world, job.L_local) if job.weak else
+                 "; %d rows split into %d %s query-row ranges" % (job.L, world, "nnz-balanced" if explicit else "equal"))
     line = {
         "metric": "effective_nnz_tflops_fwd", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "strong" if args.strong else "weak",
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "ms_per_step_median": median_ms,
+        "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "tf32" if tiled else "f32", "data": "synthetic",
-        "config": {"workload": job.w["desc"] + (("; %d rows split into %d %s row ranges" % (job.L, world, "nnz-balanced" if job.kind in ("csr", "coo") else "equal"))
-                                           if (world > 1 and args.strong) else
-                                           (f"; sequence of {world}x{job.L_local} rows, one row range per GPU" if world > 1 else "")),
-                   "mask": job.kind, "L": job.L, "rows_per_gpu": job.L_local, "d": job.d, "nnz": int(total_nnz),
-                   "nnz_imbalance_max_over_mean": round(nnz_imbalance, 4),
+        "config": {"workload": desc, "mask": job.kind, "L": job.L, "rows_per_gpu": job.L_local, "d": job.d,
+                   "nnz": int(total_nnz), "nnz_imbalance_max_over_mean": round(nnz_imbalance, 4),
                    "flops_per_step": total_flops, "path": args.path,
-                   "plan": "dense-tile plan built once outside the timed region" if args.planned else "none stored: every call is one-shot", "l2": "flushed (256 MiB memset) before every timed step",
+                   "plan": "dense-tile plan built once outside the timed region" if args.planned
+                   else "none stored: every call is one-shot (mask inspection inside the timed step)",
+                   "l2": "flushed (256 MiB memset) before every timed step",
                    "state": "m=-inf,l=0,O=0 re-initialised before every step outside the timed span"},
         "fwd_ms": total_ms / args.steps,
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
-                "api": ("hostio.BandedHostPipeline.forward: 8 row chunks, host->device copies, row-range C-ABI calls and "
-                        "device->host copies overlapped on three streams" if pipe is not None else
-                        "hostio.FullKeyHostPipeline.forward: K and V first, then %d row chunks of Q in, row-range C-ABI "
-                        "calls and O chunks out overlapped on three streams" % (len(full_pipe.edges) - 1)
-                        if full_pipe is not None else
-                        "spfa_%s.forward (torch extension), whole-tensor copies" % job.kind) if world == 1
-                else "capi.*_forward(row range) + sharding.replicate_kv (NCCL all-gather)"},
+        "compute_only_ms": compute_ms,
+        "replicate_ms": replicate_ms,
+        "nnz_imbalance_max_over_mean": round(nnz_imbalance, 4),
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roof,
     }
+    if world > 1:
+        line["config"]["kv"] = ("K and V start row-sharded in %d equal chunks; every timed step replicates them: %s; chunks "
+                                "received by the previous step are overwritten with NaN before each step" % (world, exchange_note))
+        line["config"]["exchange_vs_resident_max_abs_diff"] = check
+    if e2e:
+        line.update(e2e)
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(job, args.cpu_budget)
+    if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_per_workload and args.rows == 0:
+        per = {}
+        for name in PER_WORKLOAD:
+            per[name] = measure_one_gpu(name, capi, dev, 6, 3, peaks, peak_src, args.path,
+                                        job=job if name == args.workload else None)
+        per["coo_planned"] = measure_one_gpu("coo", capi, dev, 6, 3, peaks, peak_src, args.path, planned=True, job=job)
+        line["per_workload"] = per
     return line
+
+
+def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
+    """The step from pinned host buffers: host->device copies of this rank's Q/K/V rows, the forward (with the K/V
+    exchange at N > 1), the device->host copy of its O rows -- all inside the timed span."""
+    explicit = job.kind in ("csr", "coo")
+    banded = job.kind in ("local", "local_1d_dilated", "local_2d_dilated")
+    nan = float("nan")
+    hQ = job.Q.cpu().pin_memory()
+    hO = torch.empty_like(job.O, device="cpu").pin_memory()
+    out = {}
+    if world == 1:
+        hK, hV = job.K.cpu().pin_memory(), job.V.cpu().pin_memory()
+        big = job.L * job.d * 4 >= (48 << 20)
+        pipe = full_pipe = chunk_call = None
+        # chunking pays once a chunk's copies are large (8 chunks of 3 x 2 MB gain nothing on the 65536-row Local
+        # workload: the host->device stream slows down by as much as the overlapped device->host copies save)
+        if banded and big and not args.planned:
+            pipe = pkg.hostio.BandedHostPipeline(job.kind, job.L, job.d, job.p0, job.p1, n_chunks=8, device=dev)
+        elif not args.planned and ((banded and job.L * job.d * 4 >= (8 << 20)) or (not banded and big)):
+            full_pipe = pkg.hostio.FullKeyHostPipeline(job.L, job.L, job.d, n_chunks=3 if banded else 8, device=dev)
+            if banded:
+                def chunk_call(a, b, q, k, v, m_, l_, o_):
+                    if job.kind == "local":
+                        capi.local_forward(q, k, v, m_, l_, o_, job.p0, a, b)
+                    elif job.kind == "local_1d_dilated":
+                        capi.local_1d_dilated_forward(q, k, v, m_, l_, o_, job.p0, job.p1, a, b)
+                    else:
+                        capi.local_2d_dilated_forward(q, k, v, m_, l_, o_, job.p0, job.p1, True, a, b)
+            elif job.kind == "global_no_local":
+                def chunk_call(a, b, q, k, v, m_, l_, o_):
+                    capi.global_no_local_forward(q, k, v, m_, l_, o_, job.G, job.p0, a, b)
+            elif job.kind == "coo":
+                cut = torch.searchsorted(job.mask[0], torch.tensor(full_pipe.edges, device=dev)).cpu().tolist()
+
+                def chunk_call(a, b, q, k, v, m_, l_, o_):
+                    lo, hi = cut[full_pipe.edges.index(a)], cut[full_pipe.edges.index(b)]
+                    capi.coo_forward(q, k, v, job.mask[0][lo:hi], job.mask[1][lo:hi], m_, l_, o_, use_nan=False, row_begin=a)
+            else:
+                def chunk_call(a, b, q, k, v, m_, l_, o_):  # offsets index the full column array
+                    capi.csr_forward(q, k, v, job.mask[0][a:b + 1], job.mask[1], m_, l_, o_, use_nan=False)
+
+        binding = pkg.binding("spfa_" + job.kind)
+        w_val = torch.ones(1, device=dev)
+        dQ, dK, dV = torch.empty_like(job.Q), torch.empty_like(job.K), torch.empty_like(job.V)
+        plan_t = None
+        if args.planned:
+            plan_t = (binding.plan(job.mask[0], job.mask[1], job.L, job.d) if job.kind == "csr"
+                      else binding.plan(job.mask[0], job.mask[1], job.L_local, job.L, job.d))
+
+        def plugin_step():
+            dQ.copy_(hQ, non_blocking=True)
+            dK.copy_(hK, non_blocking=True)
+            dV.copy_(hV, non_blocking=True)
+            job.reset_state()
+            if args.planned:
+                binding.forward_planned(dQ, dK, dV, plan_t, int(job.mask[1].numel()), job.m, job.l, job.O, False)
+            else:
+                job.plugin_forward(binding, dQ, dK, dV, w_val)
+            hO.copy_(job.O, non_blocking=True)
+
+        def pipe_step():
+            if pipe is not None:
+                pipe.forward(hQ, hK, hV, hO, use_nan=True)
+            else:
+                full_pipe.forward(chunk_call, hQ, hK, hV, hO)
+
+        t_plugin, _ = timed_steps(job, plugin_step, args.steps, args.warmup, 1)
+        plugin_ms = statistics.mean(t_plugin)
+        h2d, d2h = 3 * job.L * job.d * 4, job.L * job.d * 4
+        plugin = {"value": total_flops / (plugin_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": plugin_ms,
+                  "ms_per_step_median": statistics.median(t_plugin), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                  "api": "spfa_%s.%s (torch extension, the reference's module name), whole-tensor copies around one call"
+                         % (job.kind, "forward_planned" if args.planned else "forward")}
+        out["e2e_plugin"] = plugin
+        if pipe is None and full_pipe is None:
+            out["e2e"] = plugin
+            return out
+        t_pipe, _ = timed_steps(job, pipe_step, args.steps, args.warmup, 1)
+        pipe_ms = statistics.mean(t_pipe)
+        out["e2e"] = {"value": total_flops / (pipe_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": pipe_ms,
+                      "ms_per_step_median": statistics.median(t_pipe), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                      "api": ("hostio.BandedHostPipeline.forward: 8 row chunks, host->device copies, row-range C-ABI calls "
+                              "and device->host copies overlapped on three streams" if pipe is not None else
+                              "hostio.FullKeyHostPipeline.forward: K and V first, then %d row chunks of Q in, row-range "
+                              "C-ABI calls and O chunks out overlapped on three streams" % (len(full_pipe.edges) - 1))}
+        return out
+
+    # ---- N > 1: this rank's Q rows and its K/V chunk come from the host; the other chunks over NVLink ----
+    sh = pkg.sharding
+    kb, ke = job.kv_ranges[rank]
+    Ko, Vo = ex.own()
+    hK, hV = Ko.cpu().pin_memory(), Vo.cpu().pin_memory()
+    dQ = torch.empty_like(job.Q)
+    s_in = torch.cuda.Stream(device=dev)
+    overlap = (explicit and not args.no_overlap and args.path != "gather" and job.nnz >= (1 << 20)
+               and capi.lib().spfa_explicit_plan_bytes(job.L_local, job.nnz, job.L, job.d) > 0)
+    plan_buf = (job.plan if job.plan is not None else job.build_plan(capi)) if overlap else None
+
+    def poison():
+        for t in (ex.K, ex.V):
+            t.fill_(nan)
+        dQ.fill_(nan)
+
+    def step():
+        cur = torch.cuda.current_stream(dev)
+        kv_up, q_up = torch.cuda.Event(), torch.cuda.Event()
+        s_in.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            Ko.copy_(hK, non_blocking=True)
+            Vo.copy_(hV, non_blocking=True)
+            kv_up.record(s_in)
+            dQ.copy_(hQ, non_blocking=True)
+            q_up.record(s_in)
+        job.reset_state()
+        if overlap:
+            def on_chunk(a, b, i):
+                if i == 0:
+                    cur.wait_event(q_up)
+                capi.planned_forward_keys(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b)
+            ex.run(on_chunk, None if args.planned else (lambda: job.build_plan(capi, out=plan_buf)), own_ready=kv_up)
+        else:
+            cur.wait_event(q_up)
+            if explicit:
+                ex.exchange_only()
+                job.forward(capi, dQ, ex.K, ex.V)
+            else:
+                Kf, Vf = sh.replicate_kv(Ko, Vo, job.kv_ranges)
+                job.forward(capi, dQ, Kf, Vf)
+        hO.copy_(job.O, non_blocking=True)
+
+    t_e2e, _ = timed_steps(job, step, args.steps, args.warmup, world, before_each=poison)
+    e2e_ms = dist_max(sum(t_e2e), world, dev) / args.steps
+    h2d = dist_sum(float(job.L_local + 2 * (ke - kb)) * job.d * 4, world, dev)
+    d2h = dist_sum(float(job.L_local) * job.d * 4, world, dev)
+    out["e2e"] = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                  "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                  "api": "per rank: K/V chunk and Q rows host->device on a copy stream, " +
+                         ("sharding.KeyChunkExchange.run (exchange rounds start when the chunk is up; inspection, "
+                          "capi.planned_forward_keys per arrived chunk)" if overlap else
+                          "K/V replication, capi.*_forward(row range)") + ", O rows device->host; bytes are the sum over ranks"}
+    return out
 
 
 def cpu_baseline(job, budget):
@@ -588,9 +777,8 @@ def cpu_baseline(job, budget):
         if job.kind == "csr":
             row_off, cols = job.mask[0].cpu(), job.mask[1].cpu().long()
         else:
-            rows, cols = job.mask[0].cpu(), job.mask[1].cpu().long()
-            row_off = torch.searchsorted(rows, torch.arange(job.L + 1))
-            del rows
+            row_off = torch.searchsorted(job.mask[0], torch.arange(job.L + 1, device=job.mask[0].device)).cpu()
+            cols = job.mask[1].cpu().long()
 
         def mask_fn(r0, r1):
             lo, hi = int(row_off[r0]), int(row_off[r1])
@@ -607,6 +795,37 @@ def cpu_baseline(job, budget):
                       f"{r['threads']} torch threads on {r['cores']} logical cores; useful flops 4*nnz*d of the sampled rows"}
 
 
+def reference_step_fn(job, mods, dev):
+    """(step function, note) running the reference's own kernel for this job's mask on the whole job.
+    COO above 65536 rows: the reference COO kernel scans the row-index array once per row (O(L*nnz)) and does not
+    complete; its CSR kernel on the identical mask (row offsets derived from the sorted row indices) stands in."""
+    w_val = torch.ones(1, device=dev)
+    st = (job.m, job.l, job.O)
+    k, note = job.kind, None
+    if k == "coo" and job.L > 65536:
+        row_off = torch.searchsorted(job.mask[0], torch.arange(job.L + 1, device=dev)).contiguous()
+        mod = mods("csr")
+        if mod is None:
+            return None, None
+        note = ("reference CSR kernel on the identical mask: the reference COO kernel re-scans the row-index array for "
+                "every row (O(L*nnz)) and does not complete at this size")
+        return (lambda: mod.forward(job.Q, job.K, job.V, row_off.view(torch.uint64), job.mask[1].view(torch.uint32), w_val,
+                                    *st, False)), note
+    mod = mods(k)
+    if mod is None:
+        return None, None
+    if k == "local":
+        return (lambda: mod.forward(job.Q, job.K, job.V, *st, job.p0)), note
+    if k == "local_1d_dilated":
+        return (lambda: mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1)), note
+    if k == "local_2d_dilated":
+        return (lambda: mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1, True)), note
+    if k == "global_no_local":
+        return (lambda: mod.forward(job.Q, job.K, job.V, *st, job.G, job.p0)), note
+    return (lambda: mod.forward(job.Q, job.K, job.V, job.mask[0].view(torch.uint64), job.mask[1].view(torch.uint32), w_val,
+                                *st, False)), note
+
+
 def run_reference(args, rank, world, dev):
     """The reference's own CUDA kernels (compiled unmodified into oracle/_ref/) on the same workload, one GPU."""
     if rank != 0:
@@ -616,38 +835,20 @@ def run_reference(args, rank, world, dev):
     spec = importlib.util.spec_from_file_location("spfa_build_ref", os.path.join(ROOT, "oracle", "build_ref.py"))
     br = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(br)
-    job = Job(args.workload, 0, world, dev, whole_on_one_gpu=True, strong=args.strong)  # the reference is single-GPU
-    mod = br.load(job.kind)
+    job = Job(args.workload, 0, world, dev, whole_on_one_gpu=True, weak=args.weak)  # the reference is single-GPU
     base = {"impl": "reference", "metric": "effective_nnz_tflops_fwd", "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "scaling": "weak" if job.weak else "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": job.w["desc"], "mask": job.kind, "L": job.L, "d": job.d, "nnz": int(job.nnz)}}
-    if job.kind == "coo" and job.L > 65536:
-        base.update({"unavailable": "reference COO kernel scans the whole row-index array per row (O(L*nnz)); does not complete at this size"})
-        return base
-    if mod is None:
+    step, note = reference_step_fn(job, br.load, dev)
+    if step is None:
         # no rebuilt reference kernels on this box: time the reference's dense CPU path instead
         cb = cpu_baseline(job, max(args.cpu_budget, 10.0))
         base.update({"value": cb["value"], "ms_per_step": None, "cpu_baseline": cb,
                      "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                      "gpu_launches": 0, "config": {**base["config"], "arm": "dense SDPA-MATH on CPU (oracle/_ref not built)"}})
         return base
-    w_val = torch.ones(1, device=dev)
-    st = (job.m, job.l, job.O)
-
-    def step():
-        k = job.kind
-        if k == "local":
-            mod.forward(job.Q, job.K, job.V, *st, job.p0)
-        elif k == "local_1d_dilated":
-            mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1)
-        elif k == "local_2d_dilated":
-            mod.forward(job.Q, job.K, job.V, *st, job.p0, job.p1, True)
-        elif k == "global_no_local":
-            mod.forward(job.Q, job.K, job.V, *st, job.G, job.p0)
-        else:
-            mod.forward(job.Q, job.K, job.V, job.mask[0].view(torch.uint64), job.mask[1].view(torch.uint32), w_val, *st, False)
-
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     # the reference launches on the legacy default stream; events are recorded there too
@@ -659,12 +860,31 @@ def run_reference(args, rank, world, dev):
     cb = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "reference",
           "sample": "this arm runs the reference's CUDA kernels on the GPU (the reference has no CPU implementation); "
                     "the dense CPU path is timed in the other arm's cpu_baseline"}
-    base.update({"value": value, "ms_per_step": total_ms / args.steps, "fwd_ms": total_ms / args.steps, "clocks": clocks,
+    arm = ("reference CUDA kernels compiled unmodified for sm_100a (oracle/_ref), device-resident inputs, legacy default "
+           "stream, the whole workload on one GPU (the reference is single-GPU)")
+    base.update({"value": value, "ms_per_step": total_ms / args.steps, "ms_per_step_median": statistics.median(times),
+                 "fwd_ms": total_ms / args.steps, "clocks": clocks,
                  "cpu_baseline": cb, "gpu_launches": args.steps,
                  "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                 "config": {**base["config"], "arm": "reference CUDA kernels compiled unmodified for sm_100a (oracle/_ref), "
-                                                      "device-resident inputs, legacy default stream",
+                 "config": {**base["config"], "arm": arm + ("; " + note if note else ""),
                             "l2": "flushed (256 MiB memset) before every timed step"}})
+    if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_per_workload and args.rows == 0:
+        per = {}
+        for name in PER_WORKLOAD:
+            j = job if name == args.workload else Job(name, 0, 1, dev, whole_on_one_gpu=True)
+            fn, nt = reference_step_fn(j, br.load, dev)
+            if fn is None:
+                continue
+            with torch.cuda.stream(torch.cuda.default_stream(dev)):
+                t, _ = timed_steps(j, fn, 3, 1, 1)
+            ms = statistics.mean(t)
+            per[name] = {"workload": j.w["desc"], "fwd_ms": ms, "tflops": j.flops / (ms * 1e-3) / 1e12, "steps": 3}
+            if nt:
+                per[name]["note"] = nt
+            if j is not job:
+                del j
+                torch.cuda.empty_cache()
+        base["per_workload"] = per
     return base
 
 

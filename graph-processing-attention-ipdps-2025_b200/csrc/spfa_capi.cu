@@ -7,6 +7,7 @@
 
 #include "block_kernels.cuh"
 #include "explicit_plan.cuh"
+#include "gather_generic.cuh"
 #include "gather_kernels.cuh"
 #include "tile_dispatch.cuh"
 
@@ -25,7 +26,10 @@ thread_local PathCell g_last_path{SPFA_PATH_GATHER};
 
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-inline bool supported_d(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+// Head dimensions with specialised kernels; every other d in [1, kGenericMaxD] takes the generic gather kernel.
+inline bool specialised_d(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+inline bool supported_d(int d) { return d >= 1 && d <= kGenericMaxD; }
+inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
 inline int launch_status() {
   return cudaGetLastError() == cudaSuccess ? SPFA_OK : SPFA_ERR_LAUNCH;
@@ -45,6 +49,32 @@ int launch_gather(const float* Q, const float* K, const float* V, float* m, floa
   return launch_status();
 }
 
+template <int VW, int NC, class Cols>
+int launch_gather_generic(const float* Q, const float* K, const float* V, float* m, float* l, float* O, const Cols& cols,
+                          int64_t row_begin, int64_t n_rows, int use_nan, int d, cudaStream_t st) {
+  if (n_rows <= 0) return SPFA_OK;
+  const int64_t blocks = (n_rows + kRowWarps - 1) / kRowWarps;
+  if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  const float scale = 1.0f / sqrtf((float)d);
+  gather_rows_generic_kernel<VW, NC, Cols><<<(unsigned)blocks, kRowWarps * 32, (size_t)kRowWarps * d * sizeof(float), st>>>(
+      Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, d);
+  g_launches.fetch_add(1);
+  g_last_path.store(SPFA_PATH_GATHER);
+  return launch_status();
+}
+
+// Any d in [1, kGenericMaxD]: 128-bit pieces when the rows allow it, scalar pieces otherwise.
+template <class Cols>
+int dispatch_gather_generic(int d, const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                            const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
+  if (d < 1 || d > kGenericMaxD) return SPFA_ERR_EMBED_DIM;
+  if (d % 4 == 0)
+    return d <= 256 ? launch_gather_generic<4, 2, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, d, st)
+                    : launch_gather_generic<4, 8, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, d, st);
+  return d <= 256 ? launch_gather_generic<1, 8, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, d, st)
+                  : launch_gather_generic<1, 32, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, d, st);
+}
+
 template <class Cols>
 int dispatch_gather(int d, const float* Q, const float* K, const float* V, float* m, float* l, float* O,
                     const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
@@ -54,14 +84,18 @@ int dispatch_gather(int d, const float* Q, const float* K, const float* V, float
     case 64: return launch_gather<64, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
     case 128: return launch_gather<128, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
   }
-  return SPFA_ERR_EMBED_DIM;
+  return dispatch_gather_generic(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
 }
 
 inline int check_common(const void* Q, const void* K, const void* V, const void* m, const void* l, const void* O,
                         int d) {
   if (!supported_d(d)) return SPFA_ERR_EMBED_DIM;
   if (!Q || !K || !V || !m || !l || !O) return SPFA_ERR_BAD_ARG;
-  if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return SPFA_ERR_BAD_ARG;
+  if (d % 4 == 0) {  // rows are read and written in 128-bit pieces
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return SPFA_ERR_BAD_ARG;
+  } else if (!aligned4(Q) || !aligned4(K) || !aligned4(V) || !aligned4(O)) {
+    return SPFA_ERR_BAD_ARG;
+  }
   return SPFA_OK;
 }
 
@@ -400,7 +434,7 @@ const char* spfa_status_string(int s) {
   switch (s) {
     case SPFA_OK: return "ok";
     case SPFA_ERR_BAD_ARG: return "bad argument (null or misaligned pointer, negative size, or row range outside [0, L])";
-    case SPFA_ERR_EMBED_DIM: return "The embedded dimension is not supported (must be 16, 32, 64 or 128).";
+    case SPFA_ERR_EMBED_DIM: return "The embedded dimension is too large for the amount of shared memory on your GPU.";
     case SPFA_ERR_WORKSPACE: return "workspace missing, not 256-byte aligned, or too small";
     case SPFA_ERR_LAUNCH: return "CUDA reported an error while enqueueing a kernel";
     case SPFA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
@@ -725,6 +759,12 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
   gnl_mark_globals_kernel<<<(unsigned)((nG + 255) / 256), 256, 0, st>>>(G, nG, L, bits, live);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  if (!specialised_d(d)) {  // one launch: a listed row is a long row walked by its whole CTA
+    GnlAnyRowCols any;
+    any.list = GnlCols{G, nG, L, w, bits};
+    any.strip = GnlGlobalRowCols{L, w};
+    return dispatch_gather_generic(d, Q, K, V, m, l, O, any, row_begin, row_end - row_begin, 0, st);
+  }
   // rows outside the list: listed keys outside the window
   GnlCols cols{G, nG, L, w, bits};
   rc = dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);

@@ -177,7 +177,9 @@ class KeyChunkExchange:
                 self._round(o)
         cur.wait_stream(self.s_comm)
 
-    def run(self, on_chunk, before=None):
+    def run(self, on_chunk, before=None, own_ready=None):
+        """`own_ready`: a CUDA event after which the own chunk is final (e.g. its host->device copy on another
+        stream); the rounds and the own-chunk pass wait for it, `before()` does not."""
         b, e = self.kv_ranges[self.rank]
         if not self.cuda:  # host ranks (tests): rounds and passes alternate
             if before is not None:
@@ -191,6 +193,8 @@ class KeyChunkExchange:
         arrived = []
         if self.world > 1:
             self.s_comm.wait_stream(cur)  # the own chunk is final once the caller's earlier work is done
+            if own_ready is not None:
+                self.s_comm.wait_event(own_ready)
             with torch.cuda.stream(self.s_comm):
                 for o in self.offsets:
                     sb, se = self._round(o)
@@ -199,6 +203,8 @@ class KeyChunkExchange:
                     arrived.append((sb, se, ev))
         if before is not None:
             before()
+        if own_ready is not None:
+            cur.wait_event(own_ready)
         on_chunk(b, e, 0)
         for i, (sb, se, ev) in enumerate(arrived):
             cur.wait_event(ev)
