@@ -23,6 +23,14 @@ torch::Tensor spfa_coo_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
   c10::cuda::CUDAGuard guard(Q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   Workspace ws(spfa_coo_workspace_bytes(Q.size(0), W_row_ind.size(0), K.size(0), (int)Q.size(1)), Q.device());
+  if (is_idx32(W_row_ind)) {
+    raise_for_status(spfa_coo_forward_f32_idx32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
+                                                i32_ptr(W_row_ind), u32_ptr(W_col_ind, "W_col_ind"), W_row_ind.size(0),
+                                                m.data_ptr<float>(), l.data_ptr<float>(), O.data_ptr<float>(),
+                                                /*row_begin=*/0, Q.size(0), K.size(0), (int)Q.size(1), use_nan ? 1 : 0,
+                                                ws.ptr, ws.bytes, stream.stream()));
+    return O;
+  }
   raise_for_status(spfa_coo_forward_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
                                         u64_ptr(W_row_ind, "W_row_ind"), u32_ptr(W_col_ind, "W_col_ind"),
                                         W_row_ind.size(0), m.data_ptr<float>(), l.data_ptr<float>(),
@@ -58,6 +66,12 @@ torch::Tensor spfa_coo_plan(torch::Tensor W_row_ind, torch::Tensor W_col_ind, in
   c10::cuda::CUDAGuard guard(W_col_ind.device());
   const int64_t nnz = W_col_ind.size(0);
   torch::Tensor plan = new_plan_tensor(n_rows, nnz, n_keys, (int)d, W_col_ind.device());
+  if (is_idx32(W_row_ind)) {
+    raise_for_status(spfa_coo_plan_build_idx32(i32_ptr(W_row_ind), u32_ptr(W_col_ind, "W_col_ind"), nnz, /*row_begin=*/0,
+                                               n_rows, n_keys, (int)d, plan.data_ptr(), (size_t)plan.numel(),
+                                               at::cuda::getCurrentCUDAStream().stream()));
+    return plan;
+  }
   raise_for_status(spfa_coo_plan_build(u64_ptr(W_row_ind, "W_row_ind"), u32_ptr(W_col_ind, "W_col_ind"), nnz,
                                        /*row_begin=*/0, n_rows, n_keys, (int)d, plan.data_ptr(), (size_t)plan.numel(),
                                        at::cuda::getCurrentCUDAStream().stream()));

@@ -23,6 +23,15 @@ torch::Tensor spfa_csr_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
   TORCH_CHECK(W_col_ind.dim() == 1, "W_col_ind must be 1-D");
   c10::cuda::CUDAGuard guard(Q.device());
   auto stream = at::cuda::getCurrentCUDAStream();
+  if (is_idx32(W_row_off)) {
+    Workspace ws32(spfa_csr_workspace_bytes_idx32(Q.size(0), W_col_ind.size(0), K.size(0), (int)Q.size(1)), Q.device());
+    raise_for_status(spfa_csr_forward_f32_idx32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
+                                                i32_ptr(W_row_off), u32_ptr(W_col_ind, "W_col_ind"), W_col_ind.size(0),
+                                                m.data_ptr<float>(), l.data_ptr<float>(), O.data_ptr<float>(), Q.size(0),
+                                                K.size(0), (int)Q.size(1), use_nan ? 1 : 0, ws32.ptr, ws32.bytes,
+                                                stream.stream()));
+    return O;
+  }
   Workspace ws(spfa_csr_workspace_bytes(Q.size(0), W_col_ind.size(0), K.size(0), (int)Q.size(1)), Q.device());
   raise_for_status(spfa_csr_forward_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
                                         u64_ptr(W_row_off, "W_row_off"), u32_ptr(W_col_ind, "W_col_ind"),

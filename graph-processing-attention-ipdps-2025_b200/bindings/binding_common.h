@@ -90,6 +90,10 @@ inline const uint64_t* u64_ptr(const torch::Tensor& t, const char* name) {
   return reinterpret_cast<const uint64_t*>(t.data_ptr());
 }
 
+// Row offsets / row indices may also be stored as torch.int32 (additive; the reference's are 64-bit).
+inline bool is_idx32(const torch::Tensor& t) { return t.scalar_type() == torch::kInt32; }
+inline const int32_t* i32_ptr(const torch::Tensor& t) { return reinterpret_cast<const int32_t*>(t.data_ptr()); }
+
 inline const uint32_t* u32_ptr(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.scalar_type() == torch::kUInt32 || t.scalar_type() == torch::kInt32, name,
               " must be torch.uint32 (torch.int32 is also accepted)");

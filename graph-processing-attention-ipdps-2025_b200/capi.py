@@ -34,6 +34,7 @@ EXPORTS = (
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
     "spfa_global_no_local_workspace_bytes", "spfa_global_no_local_forward_f32",
     "spfa_mask_count", "spfa_mask_fill",
+    "spfa_csr_workspace_bytes_idx32", "spfa_csr_forward_f32_idx32", "spfa_coo_forward_f32_idx32", "spfa_coo_plan_build_idx32",
 )
 
 _lib = None
@@ -74,6 +75,14 @@ def lib() -> ctypes.CDLL:
     L.spfa_coo_min_workspace_bytes.argtypes = [i64]
     L.spfa_coo_forward_f32.restype = i32
     L.spfa_coo_forward_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_csr_workspace_bytes_idx32.restype = sz
+    L.spfa_csr_workspace_bytes_idx32.argtypes = [i64, i64, i64, i32]
+    L.spfa_csr_forward_f32_idx32.restype = i32
+    L.spfa_csr_forward_f32_idx32.argtypes = L.spfa_csr_forward_f32.argtypes
+    L.spfa_coo_forward_f32_idx32.restype = i32
+    L.spfa_coo_forward_f32_idx32.argtypes = L.spfa_coo_forward_f32.argtypes
+    L.spfa_coo_plan_build_idx32.restype = i32
+    L.spfa_coo_plan_build_idx32.argtypes = [vp, vp, i64, i64, i64, i64, i32, vp, sz, vp]
     L.spfa_explicit_plan_bytes.restype = sz
     L.spfa_explicit_plan_bytes.argtypes = [i64, i64, i64, i32]
     L.spfa_csr_plan_build.restype = i32
@@ -176,9 +185,14 @@ def workspace(nbytes: int, dev) -> tuple[torch.Tensor | None, ctypes.c_void_p | 
 
 
 def _as_u64(t):
-    if t.dtype not in (torch.uint64, torch.int64) or not t.is_contiguous():
-        raise SpfaError(-1, "row offsets/indices must be contiguous torch.uint64 (or int64)")
+    if t.dtype not in (torch.uint64, torch.int64, torch.int32) or not t.is_contiguous():
+        raise SpfaError(-1, "row offsets/indices must be contiguous torch.uint64 (or int64, or int32)")
     return t
+
+
+def _idx32(t) -> bool:
+    """Row offsets / row indices stored as 32-bit integers take the *_idx32 entry points."""
+    return t.dtype == torch.int32
 
 
 def _as_u32(t):
@@ -194,6 +208,12 @@ def csr_forward(Q, K, V, row_off, col_ind, m, l, O, use_nan=False):
     with torch.cuda.device(dev):
         n_rows, d = Q.shape
         nnz = col_ind.shape[0]
+        if _idx32(row_off):
+            buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes_idx32(n_rows, nnz, K.shape[0], d), dev)
+            check(lib().spfa_csr_forward_f32_idx32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)),
+                                                   nnz, _ptr(m), _ptr(l), _ptr(O), n_rows, K.shape[0], d, int(use_nan),
+                                                   wp, wb, _stream(dev)))
+            return O
         buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, nnz, K.shape[0], d), dev)
         if KEEP_LAST_CSR_WORKSPACE:  # diagnostics only: keeps the scratch buffer alive until the next call
             global _last_csr_workspace
@@ -226,7 +246,8 @@ def coo_forward(Q, K, V, row_ind, col_ind, m, l, O, use_nan=False, row_begin=0):
     with torch.cuda.device(dev):
         n_rows, d = Q.shape
         buf, wp, wb = workspace(lib().spfa_coo_workspace_bytes(n_rows, row_ind.shape[0], K.shape[0], d), dev)
-        check(lib().spfa_coo_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)),
+        fn = lib().spfa_coo_forward_f32_idx32 if _idx32(row_ind) else lib().spfa_coo_forward_f32
+        check(fn(_ptr(Q), _ptr(K), _ptr(V), _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)),
                                          row_ind.shape[0], _ptr(m), _ptr(l), _ptr(O), row_begin, n_rows, K.shape[0],
                                          d, int(use_nan), wp, wb, _stream(dev)))
     return O
@@ -273,8 +294,9 @@ def coo_plan(row_ind, col_ind, n_rows, n_keys, d, row_begin=0, out: ExplicitPlan
     dev = col_ind.device
     with torch.cuda.device(dev):
         plan = _reuse_or_new(out, n_rows, col_ind.shape[0], n_keys, d, dev)
-        check(lib().spfa_coo_plan_build(_ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), plan.nnz, row_begin, n_rows,
-                                        n_keys, d, plan.ptr, plan.nbytes, _stream(dev)))
+        fn = lib().spfa_coo_plan_build_idx32 if _idx32(row_ind) else lib().spfa_coo_plan_build
+        check(fn(_ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), plan.nnz, row_begin, n_rows, n_keys, d, plan.ptr,
+                 plan.nbytes, _stream(dev)))
     return plan
 
 

@@ -472,7 +472,8 @@ combine_partials_kernel(const float* __restrict__ partials, const int32_t* __res
 // ---- COO row pointers --------------------------------------------------------------------------
 // ptr[r] = first k with row_ind[k] >= row_begin + r, for r in [0, n_rows]. One pass over the sorted
 // row array: position k writes the pointers of all rows in (row_ind[k-1], row_ind[k]].
-__global__ void coo_row_pointers_kernel(const uint64_t* __restrict__ row_ind, int64_t nnz,
+template <class IdxT>  // uint64_t (the reference's layout) or int32_t (halves the bytes this pass reads)
+__global__ void coo_row_pointers_kernel(const IdxT* __restrict__ row_ind, int64_t nnz,
                                         int64_t row_begin, int64_t n_rows, uint64_t* __restrict__ ptr) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k <= nnz; k += stride) {
@@ -485,6 +486,12 @@ __global__ void coo_row_pointers_kernel(const uint64_t* __restrict__ row_ind, in
     if (b > n_rows) b = n_rows;
     for (int64_t r = a; r <= b; ++r) ptr[r] = (uint64_t)k;
   }
+}
+
+// 32-bit row offsets widened to the 64-bit offsets the kernels read (n entries; negative values clamp to 0).
+__global__ void widen_offsets_kernel(const int32_t* __restrict__ in, int64_t n, uint64_t* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = (uint64_t)(in[i] > 0 ? in[i] : 0);
 }
 
 // ---- Global-no-local: mark the listed rows -------------------------------------------------------

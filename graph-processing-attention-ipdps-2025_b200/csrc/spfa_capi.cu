@@ -424,9 +424,62 @@ inline int static_coo_scratch(unsigned long long** out) {
   return SPFA_OK;
 }
 
+template <class IdxT>
+int launch_row_pointers(const IdxT* row_ind, int64_t nnz, int64_t row_begin, int64_t n_rows, uint64_t* ptr,
+                        cudaStream_t st) {
+  int64_t blocks = (nnz + 1 + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  coo_row_pointers_kernel<IdxT><<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  g_launches.fetch_add(1);
+  return launch_status();
+}
+
 }  // namespace spfa
 
 using namespace spfa;
+
+namespace spfa {
+
+template <class IdxT>
+int coo_forward_impl(const float* Q, const float* K, const float* V, const IdxT* row_ind, const uint32_t* col_ind,
+                     int64_t nnz, float* m, float* l, float* O, int64_t row_begin, int64_t n_rows, int64_t Lk, int d,
+                     int use_nan, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (nnz < 0 || n_rows < 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0) return SPFA_OK;
+  const size_t ptr_bytes = spfa_coo_min_workspace_bytes(n_rows);
+  rc = check_workspace(workspace, workspace_bytes, ptr_bytes);
+  if (rc) return rc;
+  char* rest = static_cast<char*>(workspace) + ptr_bytes;
+  const int hy = hybrid_decision(d, n_rows, nnz, Lk, rest, workspace_bytes - ptr_bytes);
+  if (hy < 0) return hy;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
+  if (launch_row_pointers<IdxT>(row_ind, nnz, row_begin, n_rows, ptr, st) != SPFA_OK) return SPFA_ERR_LAUNCH;
+  if (hy == 1) return hybrid_forward(d, Q, K, V, ptr, col_ind, m, l, O, n_rows, nnz, Lk, use_nan, rest, st);
+  CsrCols cols{ptr, col_ind, Lk};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+}
+
+template <class IdxT>
+int coo_plan_build_impl(const IdxT* row_ind, const uint32_t* col_ind, int64_t nnz, int64_t row_begin, int64_t n_rows,
+                        int64_t Lk, int d, void* plan, size_t plan_bytes, void* stream) {
+  if (!row_ind || !col_ind || n_rows <= 0 || nnz <= 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31))
+    return SPFA_ERR_BAD_ARG;
+  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
+  if (need == 0) return supported_d(d) ? (int)SPFA_ERR_BAD_ARG : (int)SPFA_ERR_EMBED_DIM;
+  int rc = check_workspace(plan, plan_bytes, need);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* offs = reinterpret_cast<uint64_t*>(plan);
+  if (launch_row_pointers<IdxT>(row_ind, nnz, row_begin, n_rows, offs, st) != SPFA_OK) return SPFA_ERR_LAUNCH;
+  return build_plan(d, offs, col_ind, n_rows, nnz, Lk, static_cast<char*>(plan) + spfa_coo_min_workspace_bytes(n_rows), 0,
+                    nullptr, st);
+}
+
+}  // namespace spfa
 
 extern "C" {
 
@@ -501,27 +554,37 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V, const u
                          const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t row_begin,
                          int64_t n_rows, int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes,
                          void* stream) {
-  int rc = check_common(Q, K, V, m, l, O, d);
-  if (rc) return rc;
-  if (nnz < 0 || n_rows < 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
-  if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
+  return coo_forward_impl<uint64_t>(Q, K, V, row_ind, col_ind, nnz, m, l, O, row_begin, n_rows, Lk, d, use_nan, workspace,
+                                    workspace_bytes, stream);
+}
+
+// ---- 32-bit row offsets / row indices (additive; the reference's tensors are 64-bit) ------------------------
+int spfa_coo_forward_f32_idx32(const float* Q, const float* K, const float* V, const int32_t* row_ind,
+                               const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t row_begin,
+                               int64_t n_rows, int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  return coo_forward_impl<int32_t>(Q, K, V, row_ind, col_ind, nnz, m, l, O, row_begin, n_rows, Lk, d, use_nan, workspace,
+                                   workspace_bytes, stream);
+}
+
+size_t spfa_csr_workspace_bytes_idx32(int64_t n_rows, int64_t nnz, int64_t Lk, int d) {
+  return spfa_coo_min_workspace_bytes(n_rows) + spfa_csr_workspace_bytes(n_rows, nnz, Lk, d);
+}
+
+int spfa_csr_forward_f32_idx32(const float* Q, const float* K, const float* V, const int32_t* row_off,
+                               const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t n_rows,
+                               int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!row_off || n_rows < 0) return SPFA_ERR_BAD_ARG;
   if (n_rows == 0) return SPFA_OK;
-  const size_t ptr_bytes = spfa_coo_min_workspace_bytes(n_rows);
-  rc = check_workspace(workspace, workspace_bytes, ptr_bytes);
+  const size_t off_bytes = spfa_coo_min_workspace_bytes(n_rows);
+  int rc = check_workspace(workspace, workspace_bytes, off_bytes);
   if (rc) return rc;
-  char* rest = static_cast<char*>(workspace) + ptr_bytes;
-  const int hy = hybrid_decision(d, n_rows, nnz, Lk, rest, workspace_bytes - ptr_bytes);
-  if (hy < 0) return hy;
-  cudaStream_t st = (cudaStream_t)stream;
-  uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
-  int64_t blocks = (nnz + 1 + 255) / 256;
-  if (blocks > 148 * 64) blocks = 148 * 64;
-  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  uint64_t* wide = reinterpret_cast<uint64_t*>(workspace);
+  widen_offsets_kernel<<<(unsigned)((n_rows + 1 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(row_off, n_rows + 1, wide);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
-  if (hy == 1) return hybrid_forward(d, Q, K, V, ptr, col_ind, m, l, O, n_rows, nnz, Lk, use_nan, rest, st);
-  CsrCols cols{ptr, col_ind, Lk};
-  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+  return spfa_csr_forward_f32(Q, K, V, wide, col_ind, nnz, m, l, O, n_rows, Lk, d, use_nan,
+                              static_cast<char*>(workspace) + off_bytes, workspace_bytes - off_bytes, stream);
 }
 
 // ---- stored plans for explicit masks ---------------------------------------------------------------------
@@ -548,21 +611,12 @@ int spfa_csr_plan_build(const uint64_t* row_off, const uint32_t* col_ind, int64_
 
 int spfa_coo_plan_build(const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz, int64_t row_begin, int64_t n_rows,
                         int64_t Lk, int d, void* plan, size_t plan_bytes, void* stream) {
-  if (!row_ind || !col_ind || n_rows <= 0 || nnz <= 0 || row_begin < 0 || Lk <= 0 || Lk >= (1LL << 31))
-    return SPFA_ERR_BAD_ARG;
-  const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
-  if (need == 0) return supported_d(d) ? (int)SPFA_ERR_BAD_ARG : (int)SPFA_ERR_EMBED_DIM;
-  int rc = check_workspace(plan, plan_bytes, need);
-  if (rc) return rc;
-  cudaStream_t st = (cudaStream_t)stream;
-  uint64_t* offs = reinterpret_cast<uint64_t*>(plan);
-  int64_t blocks = (nnz + 1 + 255) / 256;
-  if (blocks > 148 * 64) blocks = 148 * 64;
-  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, offs);
-  g_launches.fetch_add(1);
-  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
-  return build_plan(d, offs, col_ind, n_rows, nnz, Lk, static_cast<char*>(plan) + spfa_coo_min_workspace_bytes(n_rows), 0,
-                    nullptr, st);
+  return coo_plan_build_impl<uint64_t>(row_ind, col_ind, nnz, row_begin, n_rows, Lk, d, plan, plan_bytes, stream);
+}
+
+int spfa_coo_plan_build_idx32(const int32_t* row_ind, const uint32_t* col_ind, int64_t nnz, int64_t row_begin,
+                              int64_t n_rows, int64_t Lk, int d, void* plan, size_t plan_bytes, void* stream) {
+  return coo_plan_build_impl<int32_t>(row_ind, col_ind, nnz, row_begin, n_rows, Lk, d, plan, plan_bytes, stream);
 }
 
 int spfa_planned_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
@@ -614,12 +668,8 @@ int spfa_coo_forward_f32_static(const float* Q, const float* K, const float* V, 
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   uint64_t* ptr = reinterpret_cast<uint64_t*>(scratch);
-  int64_t blocks = (nnz + 1 + 255) / 256;
-  if (blocks > 148 * 64) blocks = 148 * 64;
   // every entry ptr[0 .. n_rows] is written by this pass, so nothing left by an earlier call is read
-  coo_row_pointers_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
-  g_launches.fetch_add(1);
-  if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  if (launch_row_pointers<uint64_t>(row_ind, nnz, row_begin, n_rows, ptr, st) != SPFA_OK) return SPFA_ERR_LAUNCH;
   CsrCols cols{ptr, col_ind, Lk};
   return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
 }

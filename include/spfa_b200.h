@@ -21,7 +21,10 @@
  *     (or O is NaN-filled where the family has a use_nan flag and it is non-zero).
  *   - `stream` is a cudaStream_t passed as void*. Calls are asynchronous; they return after
  *     enqueueing. The return value is SPFA_OK or a negative spfa_status.
- *   - d must be one of 16, 32, 64, 128.
+ *   - d (the embedded dimension) may be anything from 1 to 1024, the range the reference's kernels work for
+ *     (sp_flatt_csr_kernel.cu:183-184). d in {16, 32, 64, 128} has specialised kernels (and, from 32 on, the tensor-core
+ *     path); every other d runs on a generic FP32 gather kernel. Q, K, V, O must be 16-byte aligned when d is a
+ *     multiple of 4, 4-byte aligned otherwise.
  */
 #ifndef SPFA_B200_H_
 #define SPFA_B200_H_
@@ -36,7 +39,7 @@ extern "C" {
 typedef enum spfa_status {
   SPFA_OK = 0,
   SPFA_ERR_BAD_ARG = -1,        /* null pointer, negative size, row range outside [0, L] */
-  SPFA_ERR_EMBED_DIM = -2,      /* d not supported (reference: "embedded dimension is too large", sp_flatt_csr_kernel.cu:264-266) */
+  SPFA_ERR_EMBED_DIM = -2,      /* d < 1 or d > 1024 (reference: "embedded dimension is too large", sp_flatt_csr_kernel.cu:264-266) */
   SPFA_ERR_WORKSPACE = -3,      /* workspace missing, misaligned (256 B) or smaller than *_workspace_bytes() */
   SPFA_ERR_LAUNCH = -4,         /* CUDA reported an error when enqueueing */
   SPFA_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (reported by spfa_last_device_error) */
@@ -109,6 +112,27 @@ int spfa_coo_forward_f32(const float* Q, const float* K, const float* V,
                          float* m, float* l, float* O,
                          int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- explicit masks with 32-bit row offsets / row indices ----------------------------------------------
+ * No counterpart in the reference, whose row tensors are 64-bit (sp_flatt_csr_kernel.cu:19,275;
+ * sp_flatt_coo_kernel.cu:19). Masks that are stored as int32 CSR / int32 COO (every index below 2^31) can be
+ * passed as they are: the COO row-pointer pass then reads half the bytes (4 instead of 8 per mask entry), the CSR
+ * offsets are widened into the workspace first (8 (n_rows + 1) bytes more than spfa_csr_workspace_bytes, also for
+ * small masks). Everything else -- arguments, results, status codes -- is as in the 64-bit entry points. */
+size_t spfa_csr_workspace_bytes_idx32(int64_t n_rows, int64_t nnz, int64_t Lk, int d);
+int spfa_csr_forward_f32_idx32(const float* Q, const float* K, const float* V,
+                               const int32_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                               float* m, float* l, float* O,
+                               int64_t n_rows, int64_t Lk, int d, int use_nan,
+                               void* workspace, size_t workspace_bytes, void* stream);
+int spfa_coo_forward_f32_idx32(const float* Q, const float* K, const float* V,
+                               const int32_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                               float* m, float* l, float* O,
+                               int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
+                               void* workspace, size_t workspace_bytes, void* stream);
+int spfa_coo_plan_build_idx32(const int32_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                              int64_t row_begin, int64_t n_rows, int64_t Lk, int d,
+                              void* plan, size_t plan_bytes, void* stream);
 
 /* ---- stored plans for explicit masks ---------------------------------------------------------------
  * No counterpart in the reference (its callers rebuild nothing between calls because its kernels inspect

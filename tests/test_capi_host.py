@@ -56,7 +56,10 @@ def test_argument_validation_without_gpu(pkg):
     p = ctypes.c_void_p(4096)  # never dereferenced: all these calls fail validation first
     L, d = 1024, 64
     f = lib.spfa_local_forward_f32
-    assert f(p, p, p, p, p, p, L, 48, 5, 0, L, None, 0, None) == -2      # embedded dimension
+    assert f(p, p, p, p, p, p, L, 2048, 5, 0, L, None, 0, None) == -2    # embedded dimension beyond 1024
+    assert f(p, p, p, p, p, p, L, 0, 5, 0, L, None, 0, None) == -2
+    assert f(p, p, p, p, p, p, L, 48, -1, 0, L, None, 0, None) == -6     # d = 48 is accepted (generic gather kernel)
+    assert f(ctypes.c_void_p(4100), p, p, p, p, p, L, 50, -1, 0, L, None, 0, None) == -6  # rows of 50 floats: 4-byte alignment
     assert f(p, p, p, p, p, p, L, d, -1, 0, L, None, 0, None) == -6      # negative window
     assert f(p, p, p, p, p, p, L, d, L, 0, L, None, 0, None) == -6       # window > L-1
     assert f(p, p, p, p, p, p, L, d, 5, 10, 5, None, 0, None) == -1      # bad row range
@@ -89,7 +92,8 @@ def test_argument_validation_without_gpu(pkg):
     assert lib.spfa_explicit_plan_bytes(L, 5000, L, 16) == 0 and lib.spfa_explicit_plan_bytes(L, 0, L, d) == 0
     assert lib.spfa_csr_plan_build(p, p, 5000, L, L, d, None, 0, None) == -3         # no plan memory
     assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 16, p, need, None) == -1        # d without a tiled path
-    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 48, p, need, None) == -2        # d not supported at all
+    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 48, p, need, None) == -1        # d = 48: gather path only
+    assert lib.spfa_csr_plan_build(p, p, 5000, L, L, 4096, p, need, None) == -2      # d not supported at all
     assert lib.spfa_coo_plan_build(None, p, 5000, 0, L, L, d, p, need, None) == -1
     assert lib.spfa_planned_forward_f32(p, p, p, p, p, p, L, 5000, L, d, 0, p, need - 1, None) == -3
 

@@ -167,7 +167,8 @@ def test_explicit_dense_tiles_index_set_exact(capi, L, Lk, d, half, density, shu
 # ------------------------------------------------------------------------------------------------------
 # (b) the CSR benchmark configuration itself: L = 4096, d = 64, eye + Bernoulli(0.01), every row vs the oracle
 # ------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("offsets,columns", [(torch.int64, torch.int32), (torch.uint64, torch.uint32)])
+@pytest.mark.parametrize("offsets,columns", [(torch.int64, torch.int32), (torch.uint64, torch.uint32),
+                                             (torch.int32, torch.int32)])
 def test_csr_benchmark_configuration_vs_oracle(capi, orc, offsets, columns):
     import bench
 
@@ -178,7 +179,7 @@ def test_csr_benchmark_configuration_vs_oracle(capi, orc, offsets, columns):
     nnz = int(row_off[-1])
     assert 150_000 < nnz < 200_000 and int((row_off[1:] - row_off[:-1]).min()) >= 1
     want = orc.csr_forward(Q.cpu().numpy(), K.cpu().numpy(), V.cpu().numpy(), row_off.cpu().numpy(), col.cpu().numpy())
-    ro = row_off.view(torch.uint64) if offsets == torch.uint64 else row_off
+    ro = row_off.view(torch.uint64) if offsets == torch.uint64 else row_off.to(offsets)
     co = col.view(torch.uint32) if columns == torch.uint32 else col
     for path, tol in ((capi.PATH_AUTO, TOL_GATHER), (capi.PATH_GATHER, TOL_GATHER), (capi.PATH_TILED, TOL_TILED)):
         capi.set_path(path)
@@ -196,6 +197,14 @@ def test_csr_benchmark_configuration_vs_oracle(capi, orc, offsets, columns):
     st = capi.new_state(L, d)
     mod.forward(Q, K, V, ro, co, torch.ones(1, device="cuda"), *st, False)
     assert np.abs(st[2].cpu().double().numpy() - want[2]).max() <= TOL_GATHER
+    # ... and as a COO mask with the same index widths
+    rows = torch.repeat_interleave(torch.arange(L, device="cuda"), row_off[1:] - row_off[:-1])
+    ri = rows.view(torch.uint64) if offsets == torch.uint64 else rows.to(offsets)
+    for call in (lambda s_: capi.coo_forward(Q, K, V, ri, co, *s_),
+                 lambda s_: entry.load().binding("spfa_coo").forward(Q, K, V, ri, co, torch.ones(1, device="cuda"), *s_, False)):
+        st = capi.new_state(L, d)
+        call(st)
+        assert np.abs(st[2].cpu().double().numpy() - want[2]).max() <= TOL_GATHER
 
 
 # ------------------------------------------------------------------------------------------------------

@@ -653,6 +653,44 @@ def test_stored_plan_matches_one_shot_calls(capi, orc, pkg):
     assert_state_close(to_np(st), want, TOL_TILED, "planned forward, chained")
 
 
+@pytest.mark.parametrize("d", [48, 80, 96, 256, 20, 7, 1, 600, 1000])
+def test_every_embedded_dimension_up_to_1024(capi, orc, pkg, d):
+    """The reference works for any embedded dimension up to its thread count (sp_flatt_csr_kernel.cu:183-184); sizes
+    without a specialised kernel run on the generic FP32 gather kernel (128-bit pieces when d % 4 == 0, scalar
+    otherwise). All six operators, row shards, a long row (walked by its whole CTA), use_nan."""
+    L = 1500 if d <= 256 else 1300
+    Q, K, V = seeded_qkv(L, d, 40 + d)
+    Qd, Kd, Vd = dev(Q), dev(K), dev(V)
+    capi.set_path(capi.PATH_AUTO)
+    G = np.array([5, 1200, 700, 64], dtype=np.int32)
+    for kind, p0, p1, rb, re in (("local", 40, 0, 0, L), ("local", 9, 0, 101, 1203), ("local_1d_dilated", 25, 2, 0, L),
+                                 ("local_2d_dilated", 100, 3, 0, L), ("global_no_local", 30, 0, 0, L),
+                                 ("global_no_local", 3, 0, 600, 1300)):
+        if kind == "local_2d_dilated" and L % p0:
+            continue
+        want = orc.implicit_forward(kind, Q[rb:re], K, V, p0, p1, G=G if kind == "global_no_local" else None,
+                                    use_nan=True, row_begin=rb, row_end=re)
+        st = capi.new_state(re - rb, d)
+        _run_implicit(capi, kind, dev(Q[rb:re]), Kd, Vd, st, p0, p1, dev(G), True, rb, re)
+        assert capi.last_path() == capi.PATH_GATHER
+        assert_state_close(to_np(st), want, TOL_GATHER, f"{kind} d={d} rows [{rb},{re})")
+    mask, row_off, col = random_csr(L, L, 0.02, d, empty_rows=(3, L - 1))
+    mask[17, ::1] = True  # a row of L keys
+    row_off, col = _csr_of(mask)
+    rows = np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    st = capi.new_state(L, d)
+    capi.csr_forward(Qd, Kd, Vd, dev(row_off), dev(col), *st, use_nan=True)
+    assert_state_close(to_np(st), want, TOL_GATHER, f"csr d={d}")
+    st = capi.new_state(L, d)
+    capi.coo_forward(Qd, Kd, Vd, dev(rows), dev(col), *st, use_nan=True)
+    assert_state_close(to_np(st), want, TOL_GATHER, f"coo d={d}")
+    # the drop-in module accepts it as well
+    st = capi.new_state(L, d)
+    pkg.binding("spfa_local").forward(Qd, Kd, Vd, *st, 40)
+    assert_state_close(to_np(st), orc.implicit_forward("local", Q, K, V, 40), TOL_GATHER, f"spfa_local d={d}")
+
+
 def test_stored_plan_of_another_shape_is_refused_on_the_device(capi):
     """A plan names the (n_rows, nnz, Lk, d) it was built for; a forward call that passes other values finds the
     mismatch on the device, computes nothing and reports code 401 (no table of the foreign plan is read)."""
@@ -713,6 +751,10 @@ def test_full_size_coo_graph_split_vs_gather_and_oracle(capi, orc, L):
     st = capi.new_state(L, d)
     capi.coo_forward(Q, K, V, rows, cols, *st, use_nan=True)
     assert capi.last_path() == capi.PATH_TILED
+    s32 = capi.new_state(L, d)  # the same mask with 32-bit row indices: same split, same arithmetic
+    capi.coo_forward(Q, K, V, rows.to(torch.int32), cols, *s32, use_nan=True)
+    assert (s32[2] - st[2]).abs().nan_to_num().max().item() <= 1e-6 and torch.equal(torch.isnan(s32[2]), torch.isnan(st[2]))
+    del s32
     capi.set_path(capi.PATH_GATHER)
     sg = capi.new_state(L, d)
     capi.coo_forward(Q, K, V, rows, cols, *sg, use_nan=True)
