@@ -257,6 +257,11 @@ def parse_args():
     ap.add_argument("--no-overlap", action="store_true",
                     help="N>1, explicit masks: all-gather K/V first, then one forward (default: forward of each key chunk "
                          "overlapped with the arrival of the next)")
+    ap.add_argument("--transport", default=None, choices=["peer_copy", "nccl"],
+                    help="N>1, explicit masks: how K/V chunks travel (default: peer copies where CUDA IPC works, else NCCL)")
+    ap.add_argument("--phase1-rounds", type=int, default=None,
+                    help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
+                         "(default: about 4/7 of the rounds; N-1 = a single pass after the exchange)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-per-workload", action="store_true", help="skip the short measurement of every mask family")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer legs (profiling runs)")
@@ -520,7 +525,9 @@ def run_ours(args, rank, world, dev):
     times, times_x, ex, step, poison, exchange_note = times_c, None, None, None, None, None
     if world > 1:
         sh = pkg.sharding
-        ex = sh.KeyChunkExchange(job.L, job.d, job.kv_ranges, rank, world, dev)
+        ex = sh.KeyChunkExchange(job.L, job.d, job.kv_ranges, rank, world, dev, transport=args.transport)
+        how = ("device-to-device peer copies over NVLink (copy engines; each rank pulls one chunk per round)"
+               if ex.transport == "peer_copy" else "NCCL send/recv (own K/V chunk out, one chunk in)")
         kb, ke = job.kv_ranges[rank]
         Ko, Vo = ex.own()
         Ko.copy_(job.K[kb:ke])
@@ -540,15 +547,19 @@ def run_ours(args, rank, world, dev):
             before = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
 
             def step():
-                ex.run(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b),
-                       before)
-            exchange_note = ("%d rounds of NCCL send/recv (own K/V chunk out, one chunk in); mask inspection and the "
-                             "forward of every arrived key chunk overlap the later rounds" % (world - 1))
+                ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf,
+                                                                           a, b), before, rounds_in_phase1=args.phase1_rounds)
+            p1, p2 = ex.two_phase_ranges(args.phase1_rounds if args.phase1_rounds is not None
+                                         else ((4 * (world - 1) + 6) // 7 if world > 2 else world - 1))
+            exchange_note = ("%d rounds of %s; the mask inspection overlaps them, and the forward runs as %s" %
+                             (world - 1, how, "one pass after the last round" if p2 is None else
+                              "two passes: one over the keys of the own chunk and its nearest neighbours while the other "
+                              "chunks travel, one over the rest after the last round"))
         elif explicit:
             def step():
                 ex.exchange_only()
                 job.forward(capi, job.Q, ex.K, ex.V)
-            exchange_note = "%d rounds of NCCL send/recv, then one forward over all keys" % (world - 1)
+            exchange_note = "%d rounds of %s, then one forward over all keys" % (world - 1, how)
         else:
             def step():
                 Kf, Vf = sh.replicate_kv(Ko, Vo, job.kv_ranges)
@@ -738,7 +749,8 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
                 if i == 0:
                     cur.wait_event(q_up)
                 capi.planned_forward_keys(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b)
-            ex.run(on_chunk, None if args.planned else (lambda: job.build_plan(capi, out=plan_buf)), own_ready=kv_up)
+            ex.run_two_phase(on_chunk, None if args.planned else (lambda: job.build_plan(capi, out=plan_buf)),
+                             own_ready=kv_up, rounds_in_phase1=args.phase1_rounds)
         else:
             cur.wait_event(q_up)
             if explicit:
@@ -756,8 +768,8 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
     out["e2e"] = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                   "api": "per rank: K/V chunk and Q rows host->device on a copy stream, " +
-                         ("sharding.KeyChunkExchange.run (exchange rounds start when the chunk is up; inspection, "
-                          "capi.planned_forward_keys per arrived chunk)" if overlap else
+                         ("sharding.KeyChunkExchange.run_two_phase (exchange rounds start when the chunk is up; inspection, "
+                          "capi.planned_forward_keys over the arrived keys, then over the rest)" if overlap else
                           "K/V replication, capi.*_forward(row range)") + ", O rows device->host; bytes are the sum over ranks"}
     return out
 

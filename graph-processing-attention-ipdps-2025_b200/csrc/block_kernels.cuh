@@ -154,4 +154,243 @@ local2d_block_kernel(const float* __restrict__ Q, const float* __restrict__ K, c
   }
 }
 
+
+// ---- register-tiled variant for blocks with at most 64 keys per live row --------------------------------------
+// The kernel above reads one shared-memory operand per FMA, which makes the shared-memory pipe its limit. Here a
+// block is a 64 x 64 (padded) dense problem computed as 4 x 4 register tiles: thread (ig, jg) of 16 x 16 owns
+// score rows 4 ig + a and keys jg + 16 b, so one 128-bit shared-memory load feeds 16 FMAs, the q loads of a warp
+// are broadcasts (two row groups per warp) and the k loads fall on distinct bank groups (row pitch D + 4 floats).
+// The live rows and the key rows of a block are the SAME rows (start + t s, t < n), so Q, K and V rows are staged
+// together with 16-byte cp.async copies, all in flight at once; dead rows are NaN-filled while the copies travel.
+// P goes through shared memory (over the dead Q tile) for the P V product, which is tiled the same way
+// (thread = 4 rows x D/16 output dims). Exact FP32 like the kernel above.
+constexpr int kTile2dThreads = 256;
+constexpr int kTile2dMaxKeys = 64;
+constexpr int kTile2dMinKeys = 32;  // blocks with fewer keys keep the kernel above (little padding there)
+
+template <int D>
+__host__ __device__ constexpr size_t tile2d_smem_bytes() {
+  constexpr int PQ = D + 4;
+  constexpr int region_a = (64 * PQ > 64 * 68) ? 64 * PQ : 64 * 68;  // Q tile, later P (pitch 68)
+  return (size_t)(region_a + 64 * PQ + 64 * D) * sizeof(float);
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kTile2dThreads, (D <= 64) ? 3 : 2)
+local2d_tile_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                    float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Block2dParams prm) {
+  constexpr int PQ = D + 4, PP = 68, C4 = D / 4, DV = D / 16;
+  extern __shared__ __align__(16) float smem_t[];
+  constexpr int region_a = (64 * PQ > 64 * PP) ? 64 * PQ : 64 * PP;
+  float* Qs = smem_t;             // [64][PQ]; reused as P [64][PP] after the scores
+  float* Ks = Qs + region_a;      // [64][PQ]
+  float* Vs = Ks + 64 * PQ;       // [64][D]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n = (int)prm.n;
+  const int64_t start = (prm.first_block + blockIdx.x) * prm.B;
+
+  // ---- stage rows start + t s (t < n) of Q, K, V; rows t >= n are zero ----
+  for (int idx = tid; idx < 64 * C4; idx += kTile2dThreads) {
+    const int t = idx / C4, c = idx % C4;
+    float* qd = Qs + t * PQ + c * 4;
+    float* kd = Ks + t * PQ + c * 4;
+    float* vd = Vs + t * D + c * 4;
+    if (t < n) {
+      const int64_t i = start + (int64_t)t * prm.s;
+      const size_t src = (size_t)i * D + c * 4;
+      cp_async16(kd, K + src);
+      cp_async16(vd, V + src);
+      if (i >= prm.row_begin && i < prm.row_end) {
+        cp_async16(qd, Q + (size_t)(i - prm.row_begin) * D + c * 4);
+      } else {
+        *reinterpret_cast<float4*>(qd) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else {
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(qd) = z;
+      *reinterpret_cast<float4*>(kd) = z;
+      *reinterpret_cast<float4*>(vd) = z;
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // the caller's state rows are needed only at the end: ask L2 for them now
+  if (tid < n) {
+    const int64_t i = start + (int64_t)tid * prm.s;
+    if (i >= prm.row_begin && i < prm.row_end) {
+      const int64_t r = i - prm.row_begin;
+      const char* orow = reinterpret_cast<const char*>(O + (size_t)r * D);
+#pragma unroll
+      for (int b = 0; b < D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + b));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(m + r));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(l + r));
+    }
+  }
+
+  // ---- dead rows: NaN fill while the copies are in flight ----
+  if (prm.use_nan && prm.s > 1) {
+    const float nn = __int_as_float(0x7fc00000);
+    const float4 nan4 = make_float4(nn, nn, nn, nn);
+    constexpr int RPI = (C4 >= 32) ? 1 : 32 / C4;  // rows covered by one warp-wide float4 store
+    const int B = (int)prm.B, s32 = (int)prm.s;
+    for (int r_base = warp * RPI; r_base < B; r_base += (kTile2dThreads / 32) * RPI) {
+      const int rr = r_base + lane / C4;
+      const int64_t i = start + rr;
+      if (rr >= B || rr % s32 == 0 || i < prm.row_begin || i >= prm.row_end) continue;
+      float4* row = reinterpret_cast<float4*>(O + (size_t)(i - prm.row_begin) * D);
+      for (int c = lane % C4; c < C4; c += 32) row[c] = nan4;
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+
+  // ---- scores: rows 4 ig + a, keys jg + 16 b ----
+  const int ig = tid >> 4, jg = tid & 15;
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+#pragma unroll 4
+  for (int e4 = 0; e4 < C4; ++e4) {
+    float4 qa[4], kb[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) qa[a] = *reinterpret_cast<const float4*>(Qs + (4 * ig + a) * PQ + 4 * e4);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) kb[b] = *reinterpret_cast<const float4*>(Ks + (jg + 16 * b) * PQ + 4 * e4);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        acc[a][b] = fmaf(qa[a].x, kb[b].x, acc[a][b]);
+        acc[a][b] = fmaf(qa[a].y, kb[b].y, acc[a][b]);
+        acc[a][b] = fmaf(qa[a].z, kb[b].z, acc[a][b]);
+        acc[a][b] = fmaf(qa[a].w, kb[b].w, acc[a][b]);
+      }
+  }
+  // ---- softmax over the row's n keys: 4 local keys, then the 16 lanes that share the row group ----
+  float mx[4], ls[4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    float v = neg_inf();
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      acc[a][b] = (jg + 16 * b < n) ? acc[a][b] * prm.scale : neg_inf();
+      v = fmaxf(v, acc[a][b]);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFullMask, v, o));
+    mx[a] = v;  // finite: every live row has n >= 1 keys
+    float sum = 0.f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      acc[a][b] = (jg + 16 * b < n) ? fast_exp2((acc[a][b] - v) * kLog2e) : 0.f;
+      sum += acc[a][b];
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
+    ls[a] = sum;
+  }
+  __syncthreads();  // every warp is done reading the Q tile: P may overwrite it
+  float* Pm = Qs;
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) Pm[(4 * ig + a) * PP + jg + 16 * b] = acc[a][b];
+  __syncthreads();
+
+  // ---- P V: rows 4 ig + a, output dims dg DV .. dg DV + DV - 1 ----
+  const int dg = jg;
+  float o[4][DV];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int x = 0; x < DV; ++x) o[a][x] = 0.f;
+  const int n4 = (n + 3) / 4;  // keys beyond n carry probability 0 and zero V rows
+#pragma unroll 2
+  for (int j4 = 0; j4 < n4; ++j4) {
+    float4 pa[4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) pa[a] = *reinterpret_cast<const float4*>(Pm + (4 * ig + a) * PP + 4 * j4);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      float vb[DV];
+      const float* vrow = Vs + (4 * j4 + b) * D + dg * DV;
+      if (DV % 4 == 0) {
+#pragma unroll
+        for (int x = 0; x < DV; x += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(vrow + x);
+          vb[x] = t.x;
+          vb[(x + 1) % DV] = t.y;
+          vb[(x + 2) % DV] = t.z;
+          vb[(x + 3) % DV] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < DV; ++x) vb[x] = vrow[x];
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float p = (b == 0) ? pa[a].x : (b == 1) ? pa[a].y : (b == 2) ? pa[a].z : pa[a].w;
+#pragma unroll
+        for (int x = 0; x < DV; ++x) o[a][x] = fmaf(p, vb[x], o[a][x]);
+      }
+    }
+  }
+
+  // ---- merge with the caller's state (same recurrence as store_row of the gather path) and store: the loads of
+  //      all four rows are issued before any of them is used ----
+  bool mine[4];
+  float m_in[4], l_in[4];
+  float4 oin[4][(DV + 3) / 4];
+  float* op[4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int t = 4 * ig + a;
+    const int64_t i = start + (int64_t)t * prm.s;
+    mine[a] = t < n && i >= prm.row_begin && i < prm.row_end;  // uniform over the 16 lanes of the row group
+    const int64_t r = mine[a] ? (i - prm.row_begin) : 0;
+    op[a] = O + (size_t)r * D + dg * DV;
+    m_in[a] = mine[a] ? m[r] : 0.f;
+    l_in[a] = mine[a] ? l[r] : 0.f;
+    if (DV % 4 == 0) {
+#pragma unroll
+      for (int x = 0; x < DV / 4; ++x)
+        oin[a][x] = mine[a] ? *reinterpret_cast<const float4*>(op[a] + 4 * x) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    if (!mine[a]) continue;
+    const int64_t r = start + (int64_t)(4 * ig + a) * prm.s - prm.row_begin;
+    const float m_o = fmaxf(m_in[a], mx[a]);
+    const float ca = l_in[a] * fast_exp2((m_in[a] - m_o) * kLog2e);
+    const float cb = fast_exp2((mx[a] - m_o) * kLog2e);
+    const float l_o = fmaf(ls[a], cb, ca);
+    const float inv = 1.0f / l_o;
+    if (DV % 4 == 0) {
+#pragma unroll
+      for (int x = 0; x < DV / 4; ++x) {
+        float4 t = oin[a][x];
+        t.x = (ca * t.x + cb * o[a][(4 * x) % DV]) * inv;
+        t.y = (ca * t.y + cb * o[a][(4 * x + 1) % DV]) * inv;
+        t.z = (ca * t.z + cb * o[a][(4 * x + 2) % DV]) * inv;
+        t.w = (ca * t.w + cb * o[a][(4 * x + 3) % DV]) * inv;
+        *reinterpret_cast<float4*>(op[a] + 4 * x) = t;
+      }
+    } else {
+#pragma unroll
+      for (int x = 0; x < DV; ++x) op[a][x] = (ca * op[a][x] + cb * o[a][x]) * inv;
+    }
+    if (dg == 0) {
+      m[r] = m_o;
+      l[r] = l_o;
+    }
+  }
+}
+
 }  // namespace spfa

@@ -93,14 +93,51 @@ struct ResidualRangeCols {
   uint32_t key_lo, key_hi;
   const unsigned int* unsorted;  // the plan's flag
   static constexpr bool kNanFillEmpty = false;
-  struct Row { int64_t lo; int64_t n; bool filter; };
-  __device__ __forceinline__ int64_t lower_bound(int64_t lo, int64_t n, uint32_t v) const {
-    int64_t a = 0, b = n;
-    while (a < b) {
-      const int64_t mid = (a + b) >> 1;
-      if (__ldg(col + lo + mid) < v) a = mid + 1; else b = mid;
+  // key_lo > key_hi names the cyclic range [key_lo, inf) + [0, key_hi). A row's share of a range is its ascending
+  // list minus one gap: slots [0, gap_at) and [gap_at + gap_len, ...).
+  struct Row { int64_t lo; int64_t n; int64_t gap_at; int64_t gap_len; bool filter; };
+  __device__ __forceinline__ bool wanted(uint32_t c) const {
+    return (key_lo <= key_hi) ? (c >= key_lo && c < key_hi) : (c >= key_lo || c < key_hi);
+  }
+  // Entries of the ascending list col[lo, lo + n) that are below v1 / below v2, found by the whole warp together
+  // (every lane of the warp must call open() for the same row): short rows are loaded once, coalesced, and counted
+  // with ballots; long rows take a 33-way search, one memory round trip per level instead of one per halving.
+  __device__ __forceinline__ void warp_count_below(int64_t lo, int64_t n, uint32_t v1, uint32_t v2, int64_t* c1,
+                                                   int64_t* c2) const {
+    const int lane = threadIdx.x & 31;
+    if (n <= 128) {
+      uint32_t x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] = (k * 32 + lane < n) ? __ldg(col + lo + k * 32 + lane) : 0xffffffffu;
+      int a = 0, b = 0;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a += __popc(__ballot_sync(kFullMask, x[k] < v1));
+        b += __popc(__ballot_sync(kFullMask, x[k] < v2));
+      }
+      *c1 = a;
+      *c2 = b;
+      return;
     }
-    return a;
+    int64_t res[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint32_t v = q ? v2 : v1;
+      int64_t a = 0, b = n;  // the count lies in [a, b]
+      while (b - a > 32) {
+        const int64_t span = b - a;
+        const int64_t idx = a + span * (lane + 1) / 33;  // a < idx < b, ascending with the lane
+        const int c = __popc(__ballot_sync(kFullMask, __ldg(col + lo + idx) < v));  // lanes 0 .. c-1 saw a smaller entry
+        const int64_t na = (c == 0) ? a : (a + span * c / 33 + 1);
+        const int64_t nb = (c == 32) ? b : (a + span * (c + 1) / 33);
+        a = na;
+        b = nb;
+      }
+      const uint32_t x = (a + lane < b) ? __ldg(col + lo + a + lane) : 0xffffffffu;
+      res[q] = a + __popc(__ballot_sync(kFullMask, x < v));
+    }
+    *c1 = res[0];
+    *c2 = res[1];
   }
   __device__ __forceinline__ Row open(int64_t r_local, int64_t) const {
     Row r;
@@ -108,16 +145,26 @@ struct ResidualRangeCols {
     const uint32_t n = cnt[r_local];
     r.n = (n > skip_above) ? 0 : (int64_t)n;
     r.filter = (*unsorted != 0u);
+    r.gap_at = r.n;
+    r.gap_len = 0;
     if (!r.filter && r.n > 0) {
-      const int64_t a = lower_bound(r.lo, r.n, key_lo), b = lower_bound(r.lo, r.n, key_hi);
-      r.lo += a;
-      r.n = b - a;
+      int64_t a, b;  // entries below key_lo / below key_hi
+      warp_count_below(r.lo, r.n, key_lo, key_hi, &a, &b);
+      if (key_lo <= key_hi) {  // keep [a, b)
+        r.lo += a;
+        r.n = b - a;
+        r.gap_at = r.n;
+      } else {                 // keep [0, b) and [a, n)
+        r.gap_at = b;
+        r.gap_len = a - b;
+        r.n -= r.gap_len;
+      }
     }
     return r;
   }
   __device__ __forceinline__ int32_t slot(const Row& r, int64_t t) const {
-    const uint32_t c = __ldg(col + r.lo + t);
-    return (!r.filter || (c >= key_lo && c < key_hi)) ? (int32_t)c : -1;
+    const uint32_t c = __ldg(col + r.lo + (t < r.gap_at ? t : t + r.gap_len));
+    return (!r.filter || wanted(c)) ? (int32_t)c : -1;
   }
 };
 

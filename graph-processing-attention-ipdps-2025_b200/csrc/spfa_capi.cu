@@ -191,6 +191,32 @@ int launch_local2d_block(const float* Q, const float* K, const float* V, float* 
   return launch_local2d_block_nk<D, 8>(Q, K, V, m, l, O, L, B, s, n, use_nan, row_begin, row_end, st);
 }
 
+// Blocks with 33..64 keys per live row: the register-tiled kernel.
+template <int D>
+int launch_local2d_tile(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t B,
+                        int64_t s, int64_t n, int use_nan, int64_t row_begin, int64_t row_end, cudaStream_t st) {
+  const size_t smem = tile2d_smem_bytes<D>();
+  auto kern = local2d_tile_kernel<D>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return SPFA_ERR_LAUNCH;
+  Block2dParams prm;
+  prm.L = L;
+  prm.B = B;
+  prm.s = s;
+  prm.n = n;
+  prm.row_begin = row_begin;
+  prm.row_end = row_end;
+  prm.first_block = row_begin / B;
+  prm.use_nan = use_nan;
+  prm.scale = 1.0f / sqrtf((float)D);
+  const int64_t blocks = (row_end - 1) / B - prm.first_block + 1;
+  if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  kern<<<(unsigned)blocks, kTile2dThreads, smem, st>>>(Q, K, V, m, l, O, prm);
+  g_launches.fetch_add(1);
+  g_last_path.store(SPFA_PATH_GATHER);  // exact FP32, the accuracy class of the gather kernels
+  return launch_status();
+}
+
 template <class F>
 inline int with_mask_cols(int kind, int64_t L, int64_t p0, int64_t p1, const int32_t* G, int64_t nG, F&& f) {
   switch (kind) {
@@ -325,6 +351,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
   const ExplicitPlan plan = plan_view(h, ws);
   const bool whole = (key_begin <= 0 && key_end >= Lk);
+  const bool cyclic = key_begin > key_end;  // [key_begin, Lk) + [0, key_end)
   PlanHeader want;
   want.magic = kPlanMagic;
   want.n_rows = n_rows;
@@ -369,6 +396,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
         want, err);
   } else {
     const uint32_t klo = (uint32_t)key_begin, khi = (uint32_t)(key_end < Lk ? key_end : Lk);
+    (void)cyclic;  // klo > khi is the cyclic range for the functor and for the tile filter alike
     ResidualRangeCols listed{row_off, plan.res_cnt, plan.res_col, 0xffffffffu, klo, khi, plan.unsorted};
     ResidualRangeCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots, klo, khi, plan.unsorted};
     gather_rows_listed_first_kernel<D, ResidualRangeCols>
@@ -631,8 +659,9 @@ int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
   if (n_rows <= 0 || nnz <= 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
-  if (key_begin < 0 || key_end < key_begin || (key_begin % 64) != 0) return SPFA_ERR_BAD_ARG;
+  if (key_begin < 0 || key_end < 0 || key_begin > Lk || (key_begin % 64) != 0) return SPFA_ERR_BAD_ARG;
   if (key_end > Lk) key_end = Lk;
+  if (key_end < Lk && (key_end % 64) != 0) return SPFA_ERR_BAD_ARG;  // a dense key tile belongs to exactly one pass
   const size_t need = spfa_explicit_plan_bytes(n_rows, nnz, Lk, d);
   if (need == 0) return SPFA_ERR_BAD_ARG;
   rc = check_workspace(plan, plan_bytes, need);
@@ -742,6 +771,15 @@ int spfa_local_2d_dilated_forward_f32(const float* Q, const float* K, const floa
     // path is forced) one warp per row
     const int64_t s1 = dil + 1;
     const int64_t n = ((B - 1) / s1 + 1 < B) ? ((B - 1) / s1 + 1) : B;
+    if (g_path.load() != SPFA_PATH_GATHER && n > kTile2dMinKeys && n <= kTile2dMaxKeys && specialised_d(d)) {
+      cudaStream_t st = (cudaStream_t)stream;
+      switch (d) {
+        case 16: return launch_local2d_tile<16>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st);
+        case 32: return launch_local2d_tile<32>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st);
+        case 64: return launch_local2d_tile<64>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st);
+        case 128: return launch_local2d_tile<128>(Q, K, V, m, l, O, L, B, s1, n, use_nan, row_begin, row_end, st);
+      }
+    }
     if (g_path.load() != SPFA_PATH_GATHER && n <= 32 * kBlockMaxKeysPerLane) {
       cudaStream_t st = (cudaStream_t)stream;
       switch (d) {

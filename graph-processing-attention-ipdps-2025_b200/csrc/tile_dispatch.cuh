@@ -35,6 +35,21 @@ struct TileCfg {
   static constexpr int BN = 64, NS = (D == 128) ? 1 : 2, NSV = 2, NSUB = (D == 128) ? 2 : 1;
   static constexpr int kRows = 128 * NSUB, kCtasPerSm = (D == 128) ? 1 : 2;
 };
+// Global-no-local at d = 128 streams: its two launches get shapes of their own (one 128-row sub-tile per CTA).
+// Ordinary rows x the few gathered listed keys: the work of a CTA is "Q tile in, O tile out", so it is sized for TWO
+// CTAs per SM (32-key tiles, single stages: 97 KB) and one CTA's loads overlap the other's epilogue.
+// Listed rows x all keys: one CTA walks a long key range, so it gets two K stages (K tiles were the exposed latency
+// with one) and fills the SM alone.
+struct GnlRowsCfg128 {
+  static constexpr int BN = 32, NS = 1, NSV = 1, NSUB = 1, kRows = 128, kCtasPerSm = 2;
+};
+struct GnlKeysCfg128 {
+  static constexpr int BN = 64, NS = 2, NSV = 2, NSUB = 1, kRows = 128, kCtasPerSm = 1;
+};
+template <int D> struct GnlRowsCfg { using type = TileCfg<D>; };
+template <> struct GnlRowsCfg<128> { using type = GnlRowsCfg128; };
+template <int D> struct GnlKeysCfg { using type = TileCfg<D>; };
+template <> struct GnlKeysCfg<128> { using type = GnlKeysCfg128; };
 inline int tile_bn(int d) { return d == 128 ? TileCfg<128>::BN : TileCfg<64>::BN; }
 inline int tile_rows_per_cta(int d) { return d == 128 ? TileCfg<128>::kRows : 128; }
 inline int tile_ctas_per_sm(int d) { return d == 128 ? TileCfg<128>::kCtasPerSm : TileCfg<64>::kCtasPerSm; }
@@ -81,9 +96,8 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
 // the build alone (a different nvcc may assign fewer registers): it is computed once per instantiation and device.
 // Callers on SPFA_PATH_AUTO fall back to the gather path when it is false; a forced tiled call reports
 // SPFA_ERR_REGISTER_BUDGET.
-template <int D, bool EXPL>
+template <int D, bool EXPL, class C = TileCfg<D>>
 bool band_kernel_usable() {
-  using C = TileCfg<D>;
   using G = tile::Geo<C::NSUB>;
   static std::atomic<int> cached[64];  // per device: 0 unknown, 1 usable, 2 not
   int dev = 0;
@@ -101,15 +115,14 @@ bool band_kernel_usable() {
 }
 
 // Common launch steps of band_forward_kernel: register-budget guard, shared-memory opt-in, error word.
-template <int D, bool EXPL = false>
+template <int D, bool EXPL = false, class C = TileCfg<D>>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
                     const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
-  using C = TileCfg<D>;
   constexpr int NSUB = C::NSUB;
   using P = tile::Plan<D, C::BN, C::NS, NSUB, C::NSV>;
   using G = tile::Geo<NSUB>;
   auto kern = tile::band_forward_kernel<D, C::BN, C::NS, NSUB, EXPL, C::NSV>;
-  if (!band_kernel_usable<D, EXPL>()) return SPFA_ERR_REGISTER_BUDGET;
+  if (!band_kernel_usable<D, EXPL, C>()) return SPFA_ERR_REGISTER_BUDGET;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P::kDynSmem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
   int* err = nullptr;
@@ -251,10 +264,12 @@ struct GnlTiledPlan {
 inline GnlTiledPlan gnl_tiled_plan(int64_t L, int d, int64_t nG) {
   auto up = [](size_t x) { return (x + 255) / 256 * 256; };
   GnlTiledPlan p;
-  p.bn = tile_bn(d);
+  p.bn = tile_bn(d);  // the listed-rows launch uses 64-key tiles for every d
+  const int rows_per_cta = (d == 128) ? GnlKeysCfg128::kRows : 128;
+  const int ctas_per_sm = (d == 128) ? GnlKeysCfg128::kCtasPerSm : tile_ctas_per_sm(d);
   const int64_t tiles = (L + p.bn - 1) / p.bn;
-  const int64_t q_tiles = (nG + tile_rows_per_cta(d) - 1) / tile_rows_per_cta(d);
-  int64_t ctas = 148 * tile_ctas_per_sm(d) / q_tiles;
+  const int64_t q_tiles = (nG + rows_per_cta - 1) / rows_per_cta;
+  int64_t ctas = 148 * ctas_per_sm / q_tiles;
   if (ctas < 1) ctas = 1;
   int64_t chunk_tiles = (tiles + ctas - 1) / ctas;
   if (chunk_tiles < 2) chunk_tiles = 2;
@@ -274,7 +289,8 @@ inline GnlTiledPlan gnl_tiled_plan(int64_t L, int d, int64_t nG) {
 inline bool gnl_tiled_shape_ok(int d, int64_t nG) {
   if (!((d == 32 || d == 64 || d == 128) && nG >= 1 && nG <= kGnlTiledMaxGlobals)) return false;
   return d == 32 ? band_kernel_usable<32, false>()
-                 : (d == 64 ? band_kernel_usable<64, false>() : band_kernel_usable<128, false>());
+                 : (d == 64 ? band_kernel_usable<64, false>()
+                            : (band_kernel_usable<128, false, GnlRowsCfg128>() && band_kernel_usable<128, false, GnlKeysCfg128>()));
 }
 
 template <int D>
@@ -294,7 +310,8 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
                                                                       KG, VG, live);
   g_launches.fetch_add(1);
   if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
-  constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
+  using CR = typename GnlRowsCfg<D>::type;  // ordinary rows x listed keys
+  using CK = typename GnlKeysCfg<D>::type;  // listed rows x all keys
   const int64_t pitch = D * (int64_t)sizeof(float);
   const int64_t n_rows = row_end - row_begin;
   tile::BandParams prm{};
@@ -311,14 +328,15 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   prm.n_keys = nG;
   prm.u_q_first = row_begin;
   prm.n_q = n_rows;
-  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, KG, D, nG, pitch, BN) ||
-      !make_row_map(&tmV, VG, D, nG, pitch, BN, /*mn_major=*/true))
+  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, KG, D, nG, pitch, CR::BN) ||
+      !make_row_map(&tmV, VG, D, nG, pitch, CR::BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
   int rc = SPFA_OK;
   // the two launches write disjoint things (ordinary rows / partial states of the listed rows): they may overlap
   prm.overlap = 1;
   if (ordinary_rows_too)
-    rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
+    rc = launch_band_raw<D, false, CR>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + CR::kRows - 1) / CR::kRows)),
+                                       st);
   if (rc) return rc;
   // mode 2: the gathered global rows against every key, key range split over grid.y
   prm.mode = 2;
@@ -330,11 +348,11 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   prm.kv_chunk = plan.kv_chunk;
   prm.partials = partials;
   prm.n_split = plan.n_split;
-  if (!make_row_map(&tmQ, QG, D, nG, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, BN) ||
-      !make_row_map(&tmV, V, D, L, pitch, BN, /*mn_major=*/true))
+  if (!make_row_map(&tmQ, QG, D, nG, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, CK::BN) ||
+      !make_row_map(&tmV, V, D, L, pitch, CK::BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
-  rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm,
-                          dim3((unsigned)((nG + kRows - 1) / kRows), (unsigned)plan.n_split), st);
+  rc = launch_band_raw<D, false, CK>(tmQ, tmK, tmV, m, l, O, prm,
+                                     dim3((unsigned)((nG + CK::kRows - 1) / CK::kRows), (unsigned)plan.n_split), st);
   if (rc) return rc;
   combine_partials_kernel<D><<<(unsigned)nG, kCombineWarps * 32, 0, st>>>(
       partials, sorted, live, (int)nG, row_begin, row_end, plan.n_split, m, l, O);

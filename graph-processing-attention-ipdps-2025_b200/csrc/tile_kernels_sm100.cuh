@@ -101,7 +101,8 @@ struct BandParams {
   const uint32_t* x_masks;
   // explicit masks: the plan's identity block and what the caller expects to find there (every CTA compares them
   // before touching the tables above), and the range of key tiles [x_kt_lo, x_kt_hi) this launch works on (a
-  // forward split along the key axis runs one launch per range; the whole mask is [0, INT_MAX))
+  // forward split along the key axis runs one launch per range; the whole mask is [0, INT_MAX); x_kt_lo > x_kt_hi
+  // names the cyclic range [x_kt_lo, INT_MAX) + [0, x_kt_hi))
   const PlanHeader* x_hdr;
   PlanHeader x_want;
   int x_kt_lo, x_kt_hi;
@@ -273,8 +274,16 @@ struct Plan {
   // explicit masks: merged key-tile list of the CTA: kt[64] (int), act[NSUB] (u64, bit j = sub-tile uses tile j;
   // tile j is then the popcount(act & (2^j - 1))-th tile of the sub-tile's own list), nT (int)
   static constexpr int kOffX = (kOffMisc + 16 + 15) / 16 * 16;
-  static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB, kXFirst = kXNt + 4;  // first[NSUB] (int)
-  static constexpr int kBytes = kOffX + (kXFirst + 4 * NSUB + 15) / 16 * 16;
+  // pos[NSUB][64] (u8): position of the CTA's tile j in sub-tile x's own list (where its bit masks are stored)
+  static constexpr int kXKt = 0, kXAct = 256, kXNt = 256 + 8 * NSUB, kXPos = kXNt + 4;
+  static constexpr int kBytesCore = kOffX + (kXPos + 64 * NSUB + 15) / 16 * 16;
+  // mode 1 (rows x listed keys): a copy of the sorted list (<= 1024 entries) for the per-row interval searches, where
+  // the CTA's shared memory has room for it (every shape but the two-sub-tile d = 128 one, which never runs mode 1
+  // from the library's dispatch and would search in global memory)
+  static constexpr int kSortedBytes = 4096;
+  static constexpr bool kStageSorted = kBytesCore + kSortedBytes + 1024 <= 227 * 1024;
+  static constexpr int kOffSorted = kBytesCore;
+  static constexpr int kBytes = kBytesCore + (kStageSorted ? kSortedBytes : 0);
   static constexpr int kDynSmem = kBytes + 1024;            // slack for 1024-B alignment of the base
   static_assert(kDynSmem <= 227 * 1024, "beyond the shared memory one CTA can opt into");
   // TMEM columns: two S buffers per sub-tile (BN each, at BN (2x + b)), then O_x (D each, at 2 BN NSUB + D x)
@@ -395,7 +404,10 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     int n[NSUB], pos[NSUB];
     const int* list[NSUB];
     uint64_t a[NSUB];
-    int* s_first = reinterpret_cast<int*>(smem + P::kOffX + P::kXFirst);
+    uint8_t* s_pos = smem + P::kOffX + P::kXPos;
+    // key tiles this launch works on: [lo, hi), or the cyclic range [lo, inf) + [0, hi) when lo > hi
+    const int lo = prm.x_kt_lo, hi = prm.x_kt_hi;
+    auto wanted = [&](int k) { return (lo <= hi) ? (k >= lo && k < hi) : (k >= lo || k < hi); };
 #pragma unroll
     for (int x = 0; x < NSUB; ++x) {
       const int64_t b = (int64_t)blockIdx.x * NSUB + x;
@@ -404,10 +416,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       list[x] = prm.x_kt + b * kMaxDenseTiles;
       pos[x] = 0;
       a[x] = 0;
-      // the lists ascend, so the tiles inside [x_kt_lo, x_kt_hi) are a contiguous piece of each
-      while (pos[x] < n[x] && list[x][pos[x]] < prm.x_kt_lo) ++pos[x];
-      while (n[x] > pos[x] && list[x][n[x] - 1] >= prm.x_kt_hi) --n[x];
-      s_first[x] = pos[x];
+      while (pos[x] < n[x] && !wanted(list[x][pos[x]])) ++pos[x];
     }
     int nt = 0;
     while (nt < 64) {
@@ -424,13 +433,20 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int x = 0; x < NSUB; ++x)
         if (pos[x] < n[x] && list[x][pos[x]] == best) {
           a[x] |= 1ull << nt;
+          s_pos[x * 64 + nt] = (uint8_t)pos[x];
           ++pos[x];
+          while (pos[x] < n[x] && !wanted(list[x][pos[x]])) ++pos[x];
         }
       ++nt;
     }
 #pragma unroll
     for (int x = 0; x < NSUB; ++x) s_act[x] = a[x];
     *reinterpret_cast<int*>(smem + P::kOffX + P::kXNt) = nt;
+  }
+  if (!EXPL && P::kStageSorted && prm.mode == 1) {
+    int32_t* s_sorted = reinterpret_cast<int32_t*>(smem + P::kOffSorted);
+    const int cap = (prm.n_keys < P::kSortedBytes / 4) ? (int)prm.n_keys : P::kSortedBytes / 4;
+    for (int i = threadIdx.x; i < cap; i += G::kThreads) s_sorted[i] = __ldg(prm.sorted + i);
   }
   if (warp == W_TMA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sbase + P::kOffMisc),
@@ -613,18 +629,21 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     } else if (prm.mode == 1) {
       const int nv = (int)kv_hi;
       const int64_t ic = (uq < uq_end - 1) ? uq : (uq_end - 1);  // clamp keeps the bounds monotone past the end
+      const int32_t* s_sorted = reinterpret_cast<const int32_t*>(smem + P::kOffSorted);
+      const bool staged = P::kStageSorted && prm.n_keys <= P::kSortedBytes / 4;
+      auto entry = [&](int t) -> int64_t { return staged ? (int64_t)s_sorted[t] : (int64_t)__ldg(prm.sorted + t); };
       auto lower_bound = [&](int64_t v) {  // first t with sorted[t] >= v
         int a = 0, b = nv;
         while (a < b) {
           const int mid = (a + b) >> 1;
-          if ((int64_t)__ldg(prm.sorted + mid) < v) a = mid + 1; else b = mid;
+          if (entry(mid) < v) a = mid + 1; else b = mid;
         }
         return a;
       };
       lo_q = lower_bound(ic - prm.w);
       hi_q = lower_bound(ic + prm.w + 1) - 1;
       const int t = lower_bound(ic);
-      listed = (t < nv) && ((int64_t)__ldg(prm.sorted + t) == ic);
+      listed = (t < nv) && (entry(t) == ic);
     } else {
       const int nv = *prm.n_valid;
       const int64_t rc = (uq < nv - 1) ? uq : (int64_t)(nv - 1);
@@ -655,9 +674,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float sc = prm.scale_log2e;
     uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
     const uint32_t* xm = nullptr;
-    if (EXPL && nx > 0)  // masks are stored per tile of the block's whole list; this launch starts at its first kept tile
-      xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row +
-           (size_t)reinterpret_cast<const int*>(smem + P::kOffX + P::kXFirst)[x] * (NC * 128);
+    if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
+    const uint8_t* x_pos = smem + P::kOffX + P::kXPos + x * 64;  // explicit masks: tile j -> position in the block's list
     for (int it = 0; it < nx && ok; ++it) {
       int j;
       if (EXPL) {
@@ -684,8 +702,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t m_lo = (a <= 0) ? 0xffffffffu : (a >= 32 ? 0u : (0xffffffffu << a));
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
         const uint32_t m_in = m_lo & m_hi;
-        if (EXPL) {  // valid = the pair's bit in the plan (the tile's position in this sub-tile's own list is `it`)
-          const uint32_t vm = __ldg(xm + (size_t)(it * NC + c) * 128);
+        if (EXPL) {  // valid = the pair's bit in the plan (masks are stored by the tile's position in the block's own list)
+          const uint32_t vm = __ldg(xm + (size_t)(x_pos[j] * NC + c) * 128);
           vmask[c] = vm;
           cls[c] = __all_sync(kFullMask, vm == 0xffffffffu) ? 2 : (__all_sync(kFullMask, vm == 0u) ? 0 : 1);
         } else if (prm.mode == 0) {  // valid = inside the interval

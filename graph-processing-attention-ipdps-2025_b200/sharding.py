@@ -122,18 +122,25 @@ class KeyChunkExchange:
     """K/V replication overlapped with the forward, for operators that can work on one range of keys at a time.
 
     K and V start row-sharded in equal chunks `kv_ranges` (rank r owns chunk r, already stored at its place inside
-    the full-size buffers `self.K`, `self.V`). `run()` sends the own chunk to every other rank and receives theirs in
-    world-1 rounds of point-to-point transfers (NCCL send/recv over NVLink on a communication stream; gloo on CPU),
-    and calls back on the compute stream:
+    the full-size buffers `self.K`, `self.V`). `run()` fetches the other ranks' chunks in world-1 rounds and calls
+    back on the compute stream:
 
         before()                       work that needs no K/V at all (mask inspection), overlaps the first rounds
         on_chunk(key_begin, key_end, i)  once for the own chunk (i = 0), then once per received chunk as soon as it has
                                        landed (i = 1 .. world-1); the callee may read only K/V rows in that range
 
+    Transport on GPUs (`transport="peer_copy"`, the default where it can be set up): every rank maps the other ranks'
+    buffers into its address space once (CUDA IPC handles exchanged through the process group) and PULLS chunk
+    rank - o in round o with a device-to-device copy over NVLink. Those copies run on the copy engines, so they take
+    no SM away from the forward passes they overlap. Two one-element all-reduces on the communication stream fence
+    the rounds: the first says "every rank's own chunk is final", the second "every rank has finished reading".
+    `transport="nccl"`: the rounds are NCCL send/recv pairs (also what CPU ranks use, over gloo).
+
     No reduction and no softmax-state exchange are involved: every pass chains into the rank's own (m, l, O).
     """
 
-    def __init__(self, L: int, d: int, kv_ranges, rank: int, world: int, device, dtype=torch.float32, group=None):
+    def __init__(self, L: int, d: int, kv_ranges, rank: int, world: int, device, dtype=torch.float32, group=None,
+                 transport: str | None = None):
         self.L, self.d, self.rank, self.world, self.group = L, d, rank, world, group
         self.kv_ranges = list(kv_ranges)
         self.dev = torch.device(device)
@@ -141,7 +148,37 @@ class KeyChunkExchange:
         self.V = torch.empty(L, d, dtype=dtype, device=self.dev)
         self.cuda = self.dev.type == "cuda"
         self.s_comm = torch.cuda.Stream(device=self.dev) if self.cuda else None
+        self.s_comm2 = torch.cuda.Stream(device=self.dev) if self.cuda else None  # V travels beside K (peer copies)
         self.offsets = exchange_offsets(world)
+        self.transport = "nccl"
+        self.peer_K, self.peer_V = {}, {}
+        if self.cuda and world > 1 and transport in (None, "peer_copy"):
+            try:
+                self._map_peers()
+                self.transport = "peer_copy"
+            except Exception:  # no IPC on this allocator / platform: the NCCL rounds do the same job
+                if transport == "peer_copy":
+                    raise
+        self._fence = torch.zeros(1, dtype=torch.float32, device=self.dev) if self.cuda else None
+
+    def _map_peers(self):
+        """Exchange CUDA IPC handles of self.K / self.V and open every other rank's buffers."""
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        mine = (reduce_tensor(self.K), reduce_tensor(self.V))
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        ok = torch.ones(1, dtype=torch.int32, device=self.dev)
+        try:
+            for r, ((fk, ak), (fv, av)) in enumerate(everyone):
+                if r != self.rank:
+                    self.peer_K[r], self.peer_V[r] = fk(*ak), fv(*av)
+        except Exception:
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)  # all ranks take the same transport
+        if int(ok.item()) != 1:
+            self.peer_K, self.peer_V = {}, {}
+            raise RuntimeError("peer mapping failed on some rank")
 
     def own(self):
         b, e = self.kv_ranges[self.rank]
@@ -151,9 +188,16 @@ class KeyChunkExchange:
         return dist.get_global_rank(self.group, r) if self.group is not None else r
 
     def _round(self, o):
-        """One round: own chunk to rank + o, chunk of rank - o into its place."""
+        """One round: chunk of rank - o into its place (and, with send/recv transport, the own chunk to rank + o)."""
         dst, src = (self.rank + o) % self.world, (self.rank - o) % self.world
         sb, se = self.kv_ranges[src]
+        if self.transport == "peer_copy":  # called with s_comm current: K on it, V on the second stream, joined here
+            self.s_comm2.wait_stream(self.s_comm)
+            self.K[sb:se].copy_(self.peer_K[src][sb:se], non_blocking=True)
+            with torch.cuda.stream(self.s_comm2):
+                self.V[sb:se].copy_(self.peer_V[src][sb:se], non_blocking=True)
+            self.s_comm.wait_stream(self.s_comm2)
+            return sb, se
         Ko, Vo = self.own()
         ops = [dist.P2POp(dist.isend, Ko, self._peer(dst), self.group), dist.P2POp(dist.isend, Vo, self._peer(dst), self.group),
                dist.P2POp(dist.irecv, self.K[sb:se], self._peer(src), self.group),
@@ -161,6 +205,11 @@ class KeyChunkExchange:
         for req in dist.batch_isend_irecv(ops):
             req.wait()  # NCCL: makes the communication stream wait; gloo: blocks the host until the round is done
         return sb, se
+
+    def _fence_ranks(self):
+        """On the communication stream: passes once every rank's communication stream has reached this point."""
+        if self.transport == "peer_copy":
+            dist.all_reduce(self._fence, group=self.group)
 
     def exchange_only(self):
         """The replication alone (for timing it): all rounds, then the current stream waits for the last."""
@@ -173,8 +222,10 @@ class KeyChunkExchange:
         cur = torch.cuda.current_stream(self.dev)
         self.s_comm.wait_stream(cur)
         with torch.cuda.stream(self.s_comm):
+            self._fence_ranks()
             for o in self.offsets:
                 self._round(o)
+            self._fence_ranks()
         cur.wait_stream(self.s_comm)
 
     def run(self, on_chunk, before=None, own_ready=None):
@@ -196,11 +247,13 @@ class KeyChunkExchange:
             if own_ready is not None:
                 self.s_comm.wait_event(own_ready)
             with torch.cuda.stream(self.s_comm):
+                self._fence_ranks()
                 for o in self.offsets:
                     sb, se = self._round(o)
                     ev = torch.cuda.Event()
                     ev.record(self.s_comm)
                     arrived.append((sb, se, ev))
+                self._fence_ranks()
         if before is not None:
             before()
         if own_ready is not None:
@@ -210,4 +263,75 @@ class KeyChunkExchange:
             cur.wait_event(ev)
             on_chunk(sb, se, i + 1)
         if self.world > 1:
-            cur.wait_stream(self.s_comm)  # the sends read the own chunk: nothing later may overwrite it before they end
+            cur.wait_stream(self.s_comm)  # other ranks read the own chunk: nothing later may overwrite it before they end
+
+    def two_phase_ranges(self, rounds_in_phase1: int):
+        """Key ranges of a forward in two passes: what has landed after `rounds_in_phase1` rounds (the own chunk and
+        the chunks on both sides of it: one cyclic interval of keys), and everything else (its complement, also one
+        cyclic interval). Ranges are (key_begin, key_end) with key_begin > key_end meaning [key_begin, L) + [0, key_end)."""
+        k = max(0, min(rounds_in_phase1, self.world - 1))
+        before, after = (k + 1) // 2, k // 2  # chunks rank-1, rank+1, rank-2, ... arrive in that order
+        if k >= self.world - 1:
+            return (0, self.L), None
+        first = (self.rank - before) % self.world
+        last = (self.rank + after) % self.world
+        a, b = self.kv_ranges[first][0], self.kv_ranges[last][1]
+        if b == self.L and a == 0:
+            return (0, self.L), None
+        b_wrapped = 0 if b == self.L else b
+        phase1 = (a, b) if a < b else (a, b_wrapped)
+        phase2 = (b_wrapped, a) if b_wrapped != a else None
+        if phase2 is not None and phase2[0] < phase2[1] and phase2[1] == 0:
+            phase2 = (phase2[0], self.L)
+        return phase1, phase2
+
+    def run_two_phase(self, on_keys, before=None, own_ready=None, rounds_in_phase1=None):
+        """Like run(), with the forward cut into at most two passes instead of one per chunk: pass 1 over the keys that
+        have landed after `rounds_in_phase1` rounds, pass 2 over the rest once every round is done. Short per-row key
+        lists make a pass cost far more than its share of the keys (every pass revisits every row), so few large
+        passes beat many small ones; `rounds_in_phase1 = None` picks about 4/7 of the rounds, 0 rounds means "own
+        chunk first", world-1 or more a single pass after the whole exchange. on_keys(key_begin, key_end, i)."""
+        if rounds_in_phase1 is None:
+            rounds_in_phase1 = (4 * (self.world - 1) + 6) // 7 if self.world > 2 else self.world - 1
+        p1, p2 = self.two_phase_ranges(rounds_in_phase1)
+        k = min(rounds_in_phase1, self.world - 1) if p2 is not None else self.world - 1
+        if not self.cuda:
+            if before is not None:
+                before()
+            for i, o in enumerate(self.offsets):
+                if i == k:
+                    on_keys(p1[0], p1[1], 0)
+                self._round(o)
+            if k >= len(self.offsets):
+                on_keys(p1[0], p1[1], 0)
+            if p2 is not None:
+                on_keys(p2[0], p2[1], 1)
+            return
+        cur = torch.cuda.current_stream(self.dev)
+        ev1, ev2 = torch.cuda.Event(), torch.cuda.Event()
+        if self.world > 1:
+            self.s_comm.wait_stream(cur)
+            if own_ready is not None:
+                self.s_comm.wait_event(own_ready)
+            with torch.cuda.stream(self.s_comm):
+                self._fence_ranks()
+                for i, o in enumerate(self.offsets):
+                    if i == k:
+                        ev1.record(self.s_comm)
+                    self._round(o)
+                if k >= len(self.offsets):
+                    ev1.record(self.s_comm)
+                ev2.record(self.s_comm)
+                self._fence_ranks()
+        if before is not None:
+            before()
+        if own_ready is not None:
+            cur.wait_event(own_ready)
+        if self.world > 1:
+            cur.wait_event(ev1)
+        on_keys(p1[0], p1[1], 0)
+        if p2 is not None:
+            cur.wait_event(ev2)
+            on_keys(p2[0], p2[1], 1)
+        if self.world > 1:
+            cur.wait_stream(self.s_comm)

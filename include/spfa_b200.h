@@ -168,7 +168,9 @@ int spfa_planned_forward_f32(const float* Q, const float* K, const float* V,
  * cover [0, Lk), in any order on one stream, give the result of spfa_planned_forward_f32 (the passes chain through
  * the softmax state like any two calls on disjoint masks). It exists for multi-GPU callers that receive K and V
  * in chunks and want to compute on the chunks that have arrived: only K/V rows inside the range are read.
- * key_begin must be a multiple of 64 (the key-tile size); key_end is clipped to Lk. use_nan NaN-fills the rows
+ * key_begin and key_end must be multiples of 64 (the key-tile size) or, for key_end, >= Lk (clipped to Lk).
+ * key_begin > key_end names the cyclic range [key_begin, Lk) + [0, key_end): the complement of [key_end, key_begin),
+ * which is what a rank holds after it has received the chunks on both sides of its own. use_nan NaN-fills the rows
  * without any mask entry and belongs on exactly one call of the series, before the others (the first one issued).
  * Residual rows are cut by binary search when every row of the mask stores its columns in ascending order
  * (recorded by the inspector); otherwise each pass walks all residual entries and skips the foreign ones. */
@@ -194,7 +196,8 @@ int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V
  *   - Neither this function nor anything it calls uses cudaMalloc, cudaFree or another allocating
  *     routine. The first call on a device resolves the array's device address
  *     (cudaGetSymbolAddress with that device current) and caches it; make that first call on each
- *     device during set-up, before any stream capture is begun.
+ *     device during set-up, before any stream capture is begun. The cached address belongs to the device's
+ *     primary context: it does not survive cudaDeviceReset(), after which this entry point must not be used.
  *   - All calls on a device share the one array. Its previous contents never matter (each call
  *     rewrites every entry it reads), but two calls whose kernels may overlap on the GPU -- different
  *     streams, or different host threads on different streams -- race on it: serialise them. */

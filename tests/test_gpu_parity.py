@@ -732,6 +732,25 @@ def test_planned_forward_split_along_the_key_axis(capi, orc, L, Lk, d, chunks, s
         Kp[a:b], Vp[a:b] = Kd[a:b], Vd[a:b]
         capi.planned_forward_keys(dev(Q), Kp, Vp, *st, plan, a, b, use_nan=(n == 0))
     assert_state_close(to_np(st), want, TOL_TILED, f"key-split forward, {len(ranges)} ranges")
+    # a cyclic range [a, Lk) + [0, b) and its complement [b, a)
+    if len(edges) >= 3:
+        b, a = edges[1], edges[-2] if edges[-2] > edges[1] else edges[1]
+        st = capi.new_state(L, d)
+        for n, (x, y) in enumerate(((a, b), (b, a))):
+            if x == y:
+                continue
+            inside = np.zeros(Lk, dtype=bool)
+            if x < y:
+                inside[x:y] = True
+            else:
+                inside[x:] = True
+                inside[:y] = True
+            sel = torch.from_numpy(inside).cuda()
+            Kp, Vp = torch.full_like(Kd, float("nan")), torch.full_like(Vd, float("nan"))
+            Kp[sel], Vp[sel] = Kd[sel], Vd[sel]
+            capi.planned_forward_keys(dev(Q), Kp, Vp, *st, plan, x, y, use_nan=(n == 0))
+        if a != b:
+            assert_state_close(to_np(st), want, TOL_TILED, "cyclic key range and its complement")
 
 
 @pytest.mark.parametrize("L", [262144, 1048576])

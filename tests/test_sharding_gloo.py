@@ -141,6 +141,32 @@ def _exchange_worker(rank, world, port, tmp):
         assert log[0] == "before" and log[1:] == list(range(world))
         assert sorted(seen) == sorted(kv_ranges) and seen[0] == kv_ranges[rank]
         assert torch.equal(ex.K, torch.from_numpy(K)) and torch.equal(ex.V, torch.from_numpy(V))
+        # the same forward in two passes: keys landed after the first round(s), then the rest (cyclic key ranges)
+        state2 = orc.new_state(re - rb, d)
+        for t in (ex.K, ex.V):
+            t[:kb].fill_(float("nan"))
+            t[ke:].fill_(float("nan"))
+        calls = []
+
+        def on_keys(a, b, i):
+            inside = np.zeros(L, dtype=bool)
+            if a < b:
+                inside[a:b] = True
+            else:
+                inside[a:] = True
+                inside[:b] = True
+            assert not np.isnan(ex.K.numpy()[inside]).any()  # everything this pass may read has landed
+            calls.append((a, b, i))
+            keep = inside[my_col]
+            rows = np.repeat(np.arange(re - rb), np.diff(my_off))
+            cnt = np.bincount(rows[keep], minlength=re - rb)
+            off2 = np.concatenate([[0], np.cumsum(cnt)]).astype(np.uint64)
+            orc.csr_forward(Q[rb:re], np.nan_to_num(ex.K.numpy()), np.nan_to_num(ex.V.numpy()), off2, my_col[keep],
+                            state=state2)
+
+        ex.run_two_phase(on_keys, rounds_in_phase1=1 if world > 2 else 0)
+        assert [c[2] for c in calls] == [0, 1]
+        np.testing.assert_allclose(state2[2], state[2], rtol=0, atol=1e-12)
         np.savez(os.path.join(tmp, f"ex{rank}.npz"), rb=rb, re=re, O=state[2], l=state[1])
         dist.barrier()
     finally:

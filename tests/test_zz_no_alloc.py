@@ -50,10 +50,18 @@ def test_static_scratch_matches_workspace_variant_twice_in_a_row(pkg):
         want.append(tuple(t.clone() for t in st))
     # all buffers exist before the calls under test; two calls in a row share the static array
     states = [capi.new_state(Q.shape[0], Q.shape[1]) for Q, *_ in cases]
+    warm = capi.new_state(cases[0][0].shape[0], cases[0][0].shape[1])
+    assert _call_static(lib, *cases[0], warm, 0, True) == 0  # first call on the device: resolves the array's address
     torch.cuda.synchronize()
+    # the property the entry point exists for: the calls below take no device memory, neither from the driver
+    # (free memory of the device unchanged) nor from torch's caching allocator
+    free_before, alloc_before, reserved_before = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(),
+                                                  torch.cuda.memory_reserved())
     for (Q, K, V, rows, cols), st in zip(cases, states):
         assert _call_static(lib, Q, K, V, rows, cols, st, 0, True) == 0
     torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == alloc_before and torch.cuda.memory_reserved() == reserved_before
     for st, ref in zip(states, want):
         for got, exp in zip(st, ref):
             g, e = got.cpu().double().numpy(), exp.cpu().double().numpy()
@@ -70,6 +78,34 @@ def test_static_scratch_matches_workspace_variant_twice_in_a_row(pkg):
         g, e = got.cpu().double().numpy(), exp[200:500].cpu().double().numpy()
         fin = np.isfinite(e)
         assert np.array_equal(np.isnan(g), np.isnan(e)) and np.max(np.abs(g[fin] - e[fin]), initial=0.0) <= TOL
+    assert capi.last_device_error() == 0
+
+
+def test_static_scratch_empty_mask_small_dimension_and_foreign_entries(pkg):
+    """An empty mask with use_nan (every row NaN), d = 16, and row shards whose entry list holds only entries of
+    other rows before or after them."""
+    capi = pkg.capi
+    lib = capi.lib()
+    L, d = 300, 16
+    Q, K, V = (_dev(x) for x in seeded_qkv(L, d, 5))
+    none = torch.zeros(0, dtype=torch.int64, device="cuda")
+    st = capi.new_state(L, d)
+    assert _call_static(lib, Q, K, V, none, none.to(torch.int32), st, 0, True) == 0
+    torch.cuda.synchronize()
+    assert torch.isnan(st[2]).all() and torch.isinf(st[0]).all() and not st[1].any()
+    mask, row_off, col = random_csr(L, L, 0.05, 3)
+    rows = _dev(np.repeat(np.arange(L, dtype=np.int64), np.diff(row_off.astype(np.int64))))
+    cols = _dev(col.astype(np.int32))
+    want = capi.new_state(L, d)
+    capi.coo_forward(Q, K, V, rows, cols, *want, use_nan=True)
+    for rb, re, keep in ((100, 200, rows < 200), (100, 200, rows >= 100), (0, 50, rows >= 100)):
+        st = capi.new_state(re - rb, d)
+        assert _call_static(lib, Q[rb:re].contiguous(), K, V, rows[keep].contiguous(), cols[keep].contiguous(), st, rb, True) == 0
+        torch.cuda.synchronize()
+        if rb == 0:  # rows 0..49 have no entry in the list: NaN rows
+            assert torch.isnan(st[2]).all()
+        else:
+            assert (st[2] - want[2][rb:re]).abs().max().item() <= TOL and torch.equal(st[1], want[1][rb:re])
     assert capi.last_device_error() == 0
 
 
