@@ -8,6 +8,20 @@ torch::Tensor spfa_coo_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
                                     torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
                                     torch::Tensor O, bool use_nan) {
   using namespace spfa_binding;
+  if (is_16bit(Q)) {  // native 16-bit gather: half the K/V bytes of the float32 call
+    check_qkv_state_16(Q, K, V, m, l, O);
+    TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
+    TORCH_CHECK(W_row_ind.dim() == 1 && W_col_ind.dim() == 1 && W_row_ind.size(0) == W_col_ind.size(0),
+                "W_row_ind and W_col_ind must be 1-D with one entry per mask non-zero");
+    c10::cuda::CUDAGuard guard(Q.device());
+    Workspace ws(spfa_coo_min_workspace_bytes(Q.size(0)), Q.device());
+    raise_for_status(spfa_coo_forward_16(dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(),
+                                         u64_ptr(W_row_ind, "W_row_ind"), u32_ptr(W_col_ind, "W_col_ind"), W_row_ind.size(0),
+                                         m.data_ptr(), l.data_ptr(), O.data_ptr(), /*row_begin=*/0, Q.size(0), K.size(0),
+                                         (int)Q.size(1), use_nan ? 1 : 0, ws.ptr, ws.bytes,
+                                         at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (needs_float32_copy(Q)) {
     TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
     torch::Tensor w32 = W_val.to(torch::kFloat32);
@@ -81,5 +95,7 @@ torch::Tensor spfa_coo_plan(torch::Tensor W_row_ind, torch::Tensor W_col_ind, in
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("forward", &spfa_coo_forward, "Sparse-FlashAttention forward (CUDA)");
   mod.def("plan", &spfa_coo_plan, "Dense-tile plan of a COO mask (CUDA)");
+  mod.def("mask_to_coo", [](torch::Tensor mask) { return spfa_binding::dense_mask_to_index_tensors(mask, true); },
+          "Dense boolean mask -> (row indices uint64, columns uint32) on the GPU");
   mod.def("forward_planned", &spfa_binding::planned_forward, "Sparse-FlashAttention forward from a stored plan (CUDA)");
 }

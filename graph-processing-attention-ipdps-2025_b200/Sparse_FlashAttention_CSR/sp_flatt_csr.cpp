@@ -8,6 +8,18 @@ torch::Tensor spfa_csr_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
                                     torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
                                     torch::Tensor O, bool use_nan) {
   using namespace spfa_binding;
+  if (is_16bit(Q)) {  // native 16-bit gather: half the K/V bytes of the float32 call
+    check_qkv_state_16(Q, K, V, m, l, O);
+    TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
+    TORCH_CHECK(W_row_off.dim() == 1 && W_row_off.size(0) == Q.size(0) + 1, "W_row_off must have L+1 entries");
+    TORCH_CHECK(W_col_ind.dim() == 1, "W_col_ind must be 1-D");
+    c10::cuda::CUDAGuard guard(Q.device());
+    raise_for_status(spfa_csr_forward_16(dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(),
+                                         u64_ptr(W_row_off, "W_row_off"), u32_ptr(W_col_ind, "W_col_ind"), W_col_ind.size(0),
+                                         m.data_ptr(), l.data_ptr(), O.data_ptr(), Q.size(0), K.size(0), (int)Q.size(1),
+                                         use_nan ? 1 : 0, at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (needs_float32_copy(Q)) {
     TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");
     torch::Tensor w32 = W_val.to(torch::kFloat32);
@@ -75,5 +87,7 @@ torch::Tensor spfa_csr_plan(torch::Tensor W_row_off, torch::Tensor W_col_ind, in
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("forward", &spfa_csr_forward, "Sparse-FlashAttention forward (CUDA)");
   mod.def("plan", &spfa_csr_plan, "Dense-tile plan of a CSR mask (CUDA)");
+  mod.def("mask_to_csr", [](torch::Tensor mask) { return spfa_binding::dense_mask_to_index_tensors(mask, false); },
+          "Dense boolean mask -> (row offsets uint64, columns uint32) on the GPU");
   mod.def("forward_planned", &spfa_binding::planned_forward, "Sparse-FlashAttention forward from a stored plan (CUDA)");
 }

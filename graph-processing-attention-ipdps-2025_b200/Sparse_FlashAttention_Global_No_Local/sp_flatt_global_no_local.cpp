@@ -10,6 +10,22 @@ torch::Tensor spfa_global_no_local_cuda_forward(torch::Tensor Q, torch::Tensor K
                                                 torch::Tensor l, torch::Tensor O, torch::Tensor global_inds,
                                                 int local_size_each_dir) {
   using namespace spfa_binding;
+  // 16-bit tensors: short lists of global tokens (where the float32 call keeps the ordinary rows on the gather path)
+  if (is_16bit(Q) && (global_inds.size(0) < 32 || !tiled_d(Q.size(1)))) {
+    check_qkv_state_16(Q, K, V, m, l, O);
+    TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");
+    TORCH_CHECK(global_inds.dim() == 1, "global_inds must be 1-D");
+    TORCH_CHECK(global_inds.scalar_type() == torch::kInt32, "global_inds must be torch.int32");
+    c10::cuda::CUDAGuard guard(Q.device());
+    const int64_t L16 = Q.size(0), nG16 = global_inds.size(0);
+    Workspace ws(spfa_global_no_local_workspace_bytes_16(L16, nG16), Q.device());
+    raise_for_status(spfa_global_no_local_forward_16(dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(), m.data_ptr(),
+                                                     l.data_ptr(), O.data_ptr(),
+                                                     nG16 > 0 ? global_inds.data_ptr<int32_t>() : nullptr, nG16, L16,
+                                                     (int)Q.size(1), local_size_each_dir, 0, L16, ws.ptr, ws.bytes,
+                                                     at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (needs_float32_copy(Q)) {
     return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
                                              torch::Tensor ll, torch::Tensor oo) {

@@ -7,6 +7,16 @@
 torch::Tensor spfa_local_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Tensor V, torch::Tensor m,
                                       torch::Tensor l, torch::Tensor O, int local_size_each_dir) {
   using namespace spfa_binding;
+  // 16-bit tensors: narrow windows (where the float32 call takes the gather path too) run natively in 16 bits
+  if (is_16bit(Q) && (local_size_each_dir < 32 || !tiled_d(Q.size(1)))) {
+    check_qkv_state_16(Q, K, V, m, l, O);
+    TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");
+    c10::cuda::CUDAGuard guard(Q.device());
+    raise_for_status(spfa_local_forward_16(dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(), m.data_ptr(),
+                                           l.data_ptr(), O.data_ptr(), Q.size(0), (int)Q.size(1), local_size_each_dir, 0,
+                                           Q.size(0), at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (needs_float32_copy(Q))
     return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
                                              torch::Tensor ll, torch::Tensor oo) {

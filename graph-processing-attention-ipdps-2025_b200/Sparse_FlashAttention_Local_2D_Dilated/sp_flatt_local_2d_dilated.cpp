@@ -10,6 +10,16 @@ torch::Tensor spfa_local_2d_dilated_cuda_forward(torch::Tensor Q, torch::Tensor 
                                                  torch::Tensor l, torch::Tensor O, int block_size, int dil_factor,
                                                  bool use_nan) {
   using namespace spfa_binding;
+  if (is_16bit(Q)) {  // native 16-bit gather (a live row has at most block_size keys)
+    check_qkv_state_16(Q, K, V, m, l, O);
+    TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");
+    c10::cuda::CUDAGuard guard(Q.device());
+    raise_for_status(spfa_local_2d_dilated_forward_16(dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(), m.data_ptr(),
+                                                      l.data_ptr(), O.data_ptr(), Q.size(0), (int)Q.size(1), block_size,
+                                                      dil_factor, use_nan ? 1 : 0, 0, Q.size(0),
+                                                      at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (needs_float32_copy(Q)) {
     return via_float32(Q, K, V, m, l, O, [&](torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor mm,
                                              torch::Tensor ll, torch::Tensor oo) {

@@ -14,6 +14,7 @@
 
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "spfa_b200.h"
 
@@ -69,6 +70,32 @@ inline bool needs_float32_copy(const torch::Tensor& Q) {
               "spfa_b200: Q, K, V, m, l, O must be float32, float16, bfloat16 or float64; got ", t);
   return true;
 }
+
+// float16 / bfloat16 tensors have native entry points (16-bit loads and stores around fp32 arithmetic, gather path).
+// The bindings take them wherever the fp32 call would take the gather path as well; wide bands and long listed-key
+// strips, which the fp32 entry points run on the tensor cores, are converted instead (via_float32 below).
+inline bool is_16bit(const torch::Tensor& Q) {
+  return Q.scalar_type() == torch::kFloat16 || Q.scalar_type() == torch::kBFloat16;
+}
+inline int dtype_code(const torch::Tensor& Q) { return Q.scalar_type() == torch::kFloat16 ? SPFA_DTYPE_F16 : SPFA_DTYPE_BF16; }
+inline void check_same_dtype(const torch::Tensor& Q, std::initializer_list<const torch::Tensor*> ts) {
+  for (const torch::Tensor* t : ts) {
+    TORCH_CHECK(t->scalar_type() == Q.scalar_type(), "expected all floating tensors to share Q's dtype");
+    TORCH_CHECK(t->device() == Q.device(), "expected all tensors on Q's device");
+  }
+}
+// Shape checks of check_qkv_state without its float32 requirement.
+inline void check_qkv_state_16(const torch::Tensor& Q, const torch::Tensor& K, const torch::Tensor& V,
+                               const torch::Tensor& m, const torch::Tensor& l, const torch::Tensor& O) {
+  TORCH_CHECK(Q.dim() == 2 && K.dim() == 2 && V.dim() == 2 && O.dim() == 2, "Q, K, V, O must be 2-D [L, d]");
+  TORCH_CHECK(m.dim() == 1 && l.dim() == 1, "m and l must be 1-D [L]");
+  check_same_dtype(Q, {&K, &V, &m, &l, &O});
+  const int64_t L = Q.size(0), d = Q.size(1);
+  TORCH_CHECK(K.size(1) == d && V.size(1) == d && O.size(1) == d, "K, V, O must have Q's embedded dimension");
+  TORCH_CHECK(K.size(0) == V.size(0), "K and V must have the same number of rows");
+  TORCH_CHECK(O.size(0) == L && m.size(0) == L && l.size(0) == L, "O, m, l must have Q's number of rows");
+}
+inline bool tiled_d(int64_t d) { return d == 32 || d == 64 || d == 128; }
 
 // f(Q32, K32, V32, m32, l32, O32) runs the float32 path on converted copies; the state is copied back in place.
 template <class F>
@@ -142,6 +169,32 @@ inline torch::Tensor planned_forward(torch::Tensor Q, torch::Tensor K, torch::Te
                                             K.size(0), (int)Q.size(1), use_nan ? 1 : 0, plan.data_ptr(),
                                             (size_t)plan.numel(), stream.stream()));
   return O;
+}
+
+// ---- dense mask -> index tensors (additive: replaces to_sparse_csr()/to_sparse_coo() + casts in caller code) ----
+// mask: [n_rows, n_cols] torch.bool or torch.uint8 on the GPU. Returns (row offsets uint64[n_rows+1], columns uint32[nnz])
+// or, for COO, (row indices uint64[nnz], columns uint32[nnz]); columns ascend within a row.
+inline std::vector<torch::Tensor> dense_mask_to_index_tensors(const torch::Tensor& mask, bool coo) {
+  CHECK_INPUT(mask);
+  TORCH_CHECK(mask.dim() == 2, "mask must be 2-D [n_rows, n_cols]");
+  TORCH_CHECK(mask.scalar_type() == torch::kBool || mask.scalar_type() == torch::kUInt8, "mask must be torch.bool or torch.uint8");
+  c10::cuda::CUDAGuard guard(mask.device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int64_t n_rows = mask.size(0), n_cols = mask.size(1);
+  auto opt = torch::TensorOptions().device(mask.device());
+  torch::Tensor row_off = torch::empty({n_rows + 1}, opt.dtype(torch::kUInt64));
+  raise_for_status(spfa_dense_mask_offsets(static_cast<const uint8_t*>(mask.data_ptr()), n_rows, n_cols,
+                                           static_cast<uint64_t*>(row_off.data_ptr()), stream.stream()));
+  const int64_t nnz = row_off.view(torch::kInt64)[n_rows].item<int64_t>();  // synchronises: the sizes of the outputs
+  torch::Tensor col = torch::empty({nnz}, opt.dtype(torch::kUInt32));
+  torch::Tensor rows = coo ? torch::empty({nnz}, opt.dtype(torch::kUInt64)) : torch::Tensor();
+  if (nnz > 0)
+    raise_for_status(spfa_dense_mask_fill(static_cast<const uint8_t*>(mask.data_ptr()), n_rows, n_cols,
+                                          static_cast<const uint64_t*>(row_off.data_ptr()),
+                                          static_cast<uint32_t*>(col.data_ptr()),
+                                          coo ? static_cast<uint64_t*>(rows.data_ptr()) : nullptr, stream.stream()));
+  if (coo) return {rows, col};
+  return {row_off, col};
 }
 
 }  // namespace spfa_binding

@@ -55,19 +55,53 @@ def lib_sources() -> list[str]:
     return src + [os.path.join(INCLUDE, "spfa_b200.h")]
 
 
+def _check_band_kernel_registers(ptxas_log: str) -> None:
+    """The tiled kernel re-balances registers with setmaxnreg; its budgets assume the allocation the compiler makes
+    under the kernel's launch bounds: 128 registers per thread for one-sub-tile shapes, 168 for two. A toolchain that
+    assigns fewer would make the library fall back to the gather path at run time: fail the build instead."""
+    import re
+
+    want = {"1": 128, "2": 168}
+    for m in re.finditer(r"Compiling entry function '(_ZN4spfa4tile19band_forward_kernelILi\d+ELi\d+ELi\d+ELi(\d)E[^']*)'"
+                         r".*?Used (\d+) registers", ptxas_log, flags=re.S):
+        name, nsub, regs = m.group(1), m.group(2), int(m.group(3))
+        if regs != want[nsub]:
+            raise RuntimeError(f"{name}: ptxas assigned {regs} registers, the setmaxnreg budgets need {want[nsub]}")
+
+
 def build_lib(force: bool = False, verbose: bool = False) -> str:
-    """nvcc -> lib/libspfa_b200.so (static cudart; driver API reached through cudaGetDriverEntryPoint)."""
+    """nvcc -> lib/libspfa_b200.so (static cudart; driver API reached through cudaGetDriverEntryPoint). Every .cu of
+    csrc/ is compiled to an object on its own thread, then the objects are linked."""
     os.makedirs(LIBDIR, exist_ok=True)
     if not force and _newer(LIB_SO, lib_sources()):
         return LIB_SO
     cu = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cu")]
-    tmp = LIB_SO + f".tmp{os.getpid()}"
-    cmd = ["nvcc", *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--extended-lambda", "-shared",
-           "-Xcompiler", "-fPIC", "-I", INCLUDE, "-o", tmp, *cu]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    _run(cmd)
-    os.replace(tmp, LIB_SO)
+    objdir = os.path.join(LIBDIR, f"obj{os.getpid()}")
+    os.makedirs(objdir, exist_ok=True)
+    base = ["nvcc", *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--extended-lambda", "-Xptxas=-v", "-Xcompiler", "-fPIC",
+            "-I", INCLUDE]
+
+    def compile_one(src: str) -> tuple[str, str]:
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        r = subprocess.run([*base, "-c", src, "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("command failed: nvcc -c " + src + "\n" + r.stdout)
+        return obj, r.stdout
+
+    try:
+        with ThreadPoolExecutor(max_workers=min(len(cu), os.cpu_count() or 1)) as ex:
+            results = list(ex.map(compile_one, cu))
+        log = "\n".join(out for _, out in results)
+        _check_band_kernel_registers(log)
+        if verbose:
+            print(log)
+        tmp = LIB_SO + f".tmp{os.getpid()}"
+        _run(["nvcc", *NVCC_ARCH, "-shared", "-o", tmp, *[o for o, _ in results]])
+        os.replace(tmp, LIB_SO)
+    finally:
+        for f in os.listdir(objdir):
+            os.remove(os.path.join(objdir, f))
+        os.rmdir(objdir)
     return LIB_SO
 
 

@@ -34,6 +34,9 @@ EXPORTS = (
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
     "spfa_global_no_local_workspace_bytes", "spfa_global_no_local_forward_f32",
     "spfa_mask_count", "spfa_mask_fill",
+    "spfa_dense_mask_offsets", "spfa_dense_mask_fill",
+    "spfa_csr_forward_16", "spfa_coo_forward_16", "spfa_local_forward_16", "spfa_local_1d_dilated_forward_16",
+    "spfa_local_2d_dilated_forward_16", "spfa_global_no_local_workspace_bytes_16", "spfa_global_no_local_forward_16",
     "spfa_csr_workspace_bytes_idx32", "spfa_csr_forward_f32_idx32", "spfa_coo_forward_f32_idx32", "spfa_coo_plan_build_idx32",
 )
 
@@ -83,6 +86,24 @@ def lib() -> ctypes.CDLL:
     L.spfa_coo_forward_f32_idx32.argtypes = L.spfa_coo_forward_f32.argtypes
     L.spfa_coo_plan_build_idx32.restype = i32
     L.spfa_coo_plan_build_idx32.argtypes = [vp, vp, i64, i64, i64, i64, i32, vp, sz, vp]
+    L.spfa_csr_forward_16.restype = i32
+    L.spfa_csr_forward_16.argtypes = [i32] + [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i32, i32, vp]
+    L.spfa_coo_forward_16.restype = i32
+    L.spfa_coo_forward_16.argtypes = [i32] + [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_local_forward_16.restype = i32
+    L.spfa_local_forward_16.argtypes = [i32] + [vp] * 6 + [i64, i32, i64, i64, i64, vp]
+    L.spfa_local_1d_dilated_forward_16.restype = i32
+    L.spfa_local_1d_dilated_forward_16.argtypes = [i32] + [vp] * 6 + [i64, i32, i64, i64, i64, i64, vp]
+    L.spfa_local_2d_dilated_forward_16.restype = i32
+    L.spfa_local_2d_dilated_forward_16.argtypes = [i32] + [vp] * 6 + [i64, i32, i64, i64, i32, i64, i64, vp]
+    L.spfa_global_no_local_workspace_bytes_16.restype = sz
+    L.spfa_global_no_local_workspace_bytes_16.argtypes = [i64, i64]
+    L.spfa_global_no_local_forward_16.restype = i32
+    L.spfa_global_no_local_forward_16.argtypes = [i32] + [vp] * 7 + [i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_dense_mask_offsets.restype = i32
+    L.spfa_dense_mask_offsets.argtypes = [vp, i64, i64, vp, vp]
+    L.spfa_dense_mask_fill.restype = i32
+    L.spfa_dense_mask_fill.argtypes = [vp, i64, i64, vp, vp, vp, vp]
     L.spfa_explicit_plan_bytes.restype = sz
     L.spfa_explicit_plan_bytes.argtypes = [i64, i64, i64, i32]
     L.spfa_csr_plan_build.restype = i32
@@ -322,6 +343,79 @@ def planned_forward_keys(Q, K, V, m, l, O, plan: ExplicitPlan, key_begin: int, k
                                                   plan.nnz, plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes,
                                                   int(key_begin), int(key_end), _stream(dev)))
     return O
+
+
+DTYPE_CODE = {torch.float16: 1, torch.bfloat16: 2}
+
+
+def _t16(*ts):
+    dev, dt = ts[0].device, ts[0].dtype
+    if dt not in DTYPE_CODE:
+        raise SpfaError(-1, "16-bit entry points take torch.float16 or torch.bfloat16 tensors")
+    for t in ts:
+        if not t.is_cuda or t.dtype != dt or not t.is_contiguous() or t.device != dev:
+            raise SpfaError(-1, "floating tensors must be contiguous CUDA tensors of one 16-bit dtype on one device")
+    return dev, DTYPE_CODE[dt]
+
+
+def forward_16(kind, Q, K, V, m, l, O, *, p0=0, p1=0, global_inds=None, row_off=None, row_ind=None, col_ind=None,
+               use_nan=False, row_begin=0, row_end=None):
+    """Native 16-bit forward of one mask family (`kind`: csr, coo, local, local_1d_dilated, local_2d_dilated,
+    global_no_local) on float16 / bfloat16 tensors: 16-bit loads and stores, fp32 arithmetic, gather path."""
+    dev, code = _t16(Q, K, V, m, l, O)
+    n_rows, d = Q.shape
+    Lk = K.shape[0]
+    with torch.cuda.device(dev):
+        st = _stream(dev)
+        q, k, v, mm, ll, oo = (_ptr(t) for t in (Q, K, V, m, l, O))
+        if kind == "csr":
+            rc = lib().spfa_csr_forward_16(code, q, k, v, _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)), col_ind.shape[0],
+                                           mm, ll, oo, n_rows, Lk, d, int(use_nan), st)
+        elif kind == "coo":
+            buf, wp, wb = workspace(lib().spfa_coo_min_workspace_bytes(n_rows), dev)
+            rc = lib().spfa_coo_forward_16(code, q, k, v, _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), col_ind.shape[0],
+                                           mm, ll, oo, row_begin, n_rows, Lk, d, int(use_nan), wp, wb, st)
+        else:
+            L, row_end = _rows(Q, K, row_begin, row_end)
+            if kind == "local":
+                rc = lib().spfa_local_forward_16(code, q, k, v, mm, ll, oo, L, d, int(p0), row_begin, row_end, st)
+            elif kind == "local_1d_dilated":
+                rc = lib().spfa_local_1d_dilated_forward_16(code, q, k, v, mm, ll, oo, L, d, int(p0), int(p1), row_begin,
+                                                            row_end, st)
+            elif kind == "local_2d_dilated":
+                rc = lib().spfa_local_2d_dilated_forward_16(code, q, k, v, mm, ll, oo, L, d, int(p0), int(p1), int(use_nan),
+                                                            row_begin, row_end, st)
+            elif kind == "global_no_local":
+                nG = global_inds.shape[0]
+                buf, wp, wb = workspace(lib().spfa_global_no_local_workspace_bytes_16(L, nG), dev)
+                rc = lib().spfa_global_no_local_forward_16(code, q, k, v, mm, ll, oo, _ptr(global_inds) if nG else None, nG,
+                                                           L, d, int(p0), row_begin, row_end, wp, wb, st)
+            else:
+                raise ValueError(kind)
+        check(rc)
+    return O
+
+
+def dense_mask_to_csr(mask, coo=False):
+    """Dense boolean (or uint8) CUDA mask [n_rows, n_cols] -> (row_off uint64[n_rows+1], col uint32[nnz]) or, with
+    coo=True, (row uint64[nnz], col uint32[nnz]): the arrays csr_forward / coo_forward take, columns ascending within
+    a row. Two streaming passes over the mask on the GPU; one host synchronisation to learn nnz."""
+    if not mask.is_cuda or mask.dim() != 2 or mask.dtype not in (torch.bool, torch.uint8) or not mask.is_contiguous():
+        raise SpfaError(-1, "mask must be a contiguous 2-D torch.bool / torch.uint8 CUDA tensor")
+    dev = mask.device
+    n_rows, n_cols = mask.shape
+    with torch.cuda.device(dev):
+        row_off = torch.empty(n_rows + 1, dtype=torch.int64, device=dev)
+        check(lib().spfa_dense_mask_offsets(_ptr(mask), n_rows, n_cols, _ptr(row_off), _stream(dev)))
+        nnz = int(row_off[-1].item())
+        col = torch.empty(nnz, dtype=torch.int32, device=dev)
+        rows = torch.empty(nnz, dtype=torch.int64, device=dev) if coo else None
+        if nnz:
+            check(lib().spfa_dense_mask_fill(_ptr(mask), n_rows, n_cols, _ptr(row_off), _ptr(col),
+                                             _ptr(rows) if coo else None, _stream(dev)))
+    if coo:
+        return rows.view(torch.uint64), col.view(torch.uint32)
+    return row_off.view(torch.uint64), col.view(torch.uint32)
 
 
 def _rows(Q, K, row_begin, row_end):

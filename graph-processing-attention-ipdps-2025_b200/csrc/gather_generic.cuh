@@ -10,7 +10,10 @@
 // Same visiting order, same online-softmax recurrence and state merge as the specialised path; rows with more
 // than kHeavyRowSlots slots are walked by all warps of the CTA together. Accuracy class: FP32 (1e-5).
 #pragma once
+#include <type_traits>
+
 #include "gather_kernels.cuh"
+#include "gather_kernels_16.cuh"
 #include "spfa_common.cuh"
 
 namespace spfa {
@@ -22,20 +25,40 @@ struct GenRow {
   float v[NC][VW];
 };
 
-template <int VW, int NC>
-__device__ __forceinline__ void gen_load(const float* __restrict__ p, int d, int lane, GenRow<VW, NC>& r) {
+// Element type of the tensors in memory: float, __half or __nv_bfloat16 (arithmetic is fp32 throughout).
+template <class T> struct Elem {
+  static __device__ __forceinline__ float up(T x) { return Cvt16<T>::up1(x); }
+  static __device__ __forceinline__ T down(float x) { return Cvt16<T>::down1(x); }
+};
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float up(float x) { return x; }
+  static __device__ __forceinline__ float down(float x) { return x; }
+};
+
+// VW elements per piece: 4 (fp32) or 8 (16-bit) when the pieces are 128-bit loads, 1 for scalar loads.
+template <class T, int VW, int NC>
+__device__ __forceinline__ void gen_load(const T* __restrict__ p, int d, int lane, GenRow<VW, NC>& r) {
 #pragma unroll
   for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * VW;
     if (e < d) {
       if (VW == 4) {
-        const float4 t = ldg4(p + e);
+        const float4 t = __ldg(reinterpret_cast<const float4*>(p + e));
         r.v[c][0] = t.x;
         r.v[c][1 % VW] = t.y;
         r.v[c][2 % VW] = t.z;
         r.v[c][3 % VW] = t.w;
+      } else if (VW == 8) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(p + e));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = Cvt16<typename std::conditional<std::is_same<T, float>::value, __half, T>::type>::up(w[i]);
+          r.v[c][(2 * i) % VW] = f.x;
+          r.v[c][(2 * i + 1) % VW] = f.y;
+        }
       } else {
-        r.v[c][0] = __ldg(p + e);
+        r.v[c][0] = Elem<T>::up(__ldg(p + e));
       }
     } else {
 #pragma unroll
@@ -66,10 +89,10 @@ struct GenAcc {
 
 // Slots [t0, t1) of one row into the warp's state. U keys are in flight at a time (U = 1 for the widest rows, whose
 // pieces already fill the register file).
-template <int VW, int NC, int U, class Cols>
+template <class T, int VW, int NC, int U, class Cols>
 __device__ __forceinline__ void gen_accumulate(const Cols& cols, const typename Cols::Row& row, int64_t t0, int64_t t1,
-                                               const GenRow<VW, NC>& q, const float* __restrict__ K,
-                                               const float* __restrict__ V, int d, float scale, int lane,
+                                               const GenRow<VW, NC>& q, const T* __restrict__ K,
+                                               const T* __restrict__ V, int d, float scale, int lane,
                                                GenAcc<VW, NC>& st) {
   for (int64_t base = t0; base < t1; base += 32) {
     const int64_t tl = base + lane;
@@ -83,8 +106,8 @@ __device__ __forceinline__ void gen_accumulate(const Cols& cols, const typename 
       for (int u = 0; u < U; ++u) {
         const int32_t c = (j0 + u < 32) ? __shfl_sync(kFullMask, c_lane, (j0 + u) & 31) : -1;
         if (c >= 0) {  // warp-uniform
-          gen_load<VW, NC>(K + (size_t)c * d, d, lane, k[u]);
-          gen_load<VW, NC>(V + (size_t)c * d, d, lane, v[u]);
+          gen_load<T, VW, NC>(K + (size_t)c * d, d, lane, k[u]);
+          gen_load<T, VW, NC>(V + (size_t)c * d, d, lane, v[u]);
           float p = 0.f;
 #pragma unroll
           for (int cc = 0; cc < NC; ++cc)
@@ -129,35 +152,35 @@ __device__ __forceinline__ void gen_accumulate(const Cols& cols, const typename 
 
 // Fold (m_loc, l_loc, un-normalised acc) into the caller's state, as store_row of the specialised path
 // (sp_flatt_csr_kernel.cu:162-194 applied once to the whole row).
-template <int VW, int NC>
-__device__ __forceinline__ void gen_store(const GenAcc<VW, NC>& st, float* __restrict__ m, float* __restrict__ l,
-                                          float* __restrict__ O, int64_t r, int d, int lane) {
-  const float m_in = m[r], l_in = l[r];
+template <class T, int VW, int NC>
+__device__ __forceinline__ void gen_store(const GenAcc<VW, NC>& st, T* __restrict__ m, T* __restrict__ l,
+                                          T* __restrict__ O, int64_t r, int d, int lane) {
+  const float m_in = Elem<T>::up(m[r]), l_in = Elem<T>::up(l[r]);
   const float m_out = fmaxf(m_in, st.m);
   const float a = l_in * fast_exp2((m_in - m_out) * kLog2e);
   const float b = fast_exp2((st.m - m_out) * kLog2e);
   const float l_out = fmaf(st.l, b, a);
   const float inv = 1.0f / l_out;
-  float* op = O + (size_t)r * d;
+  T* op = O + (size_t)r * d;
 #pragma unroll
   for (int c = 0; c < NC; ++c) {
     const int e = (c * 32 + lane) * VW;
     if (e < d) {
 #pragma unroll
-      for (int i = 0; i < VW; ++i) op[e + i] = (a * op[e + i] + b * st.acc.v[c][i]) * inv;
+      for (int i = 0; i < VW; ++i) op[e + i] = Elem<T>::down((a * Elem<T>::up(op[e + i]) + b * st.acc.v[c][i]) * inv);
     }
   }
   __syncwarp();
   if (lane == 0) {
-    m[r] = m_out;
-    l[r] = l_out;
+    m[r] = Elem<T>::down(m_out);
+    l[r] = Elem<T>::down(l_out);
   }
 }
 
-template <int VW, int NC, class Cols>
+template <class T, int VW, int NC, class Cols>
 __global__ void __launch_bounds__(kRowWarps * 32)
-gather_rows_generic_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
-                           float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Cols cols,
+gather_rows_generic_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V,
+                           T* __restrict__ m, T* __restrict__ l, T* __restrict__ O, const Cols cols,
                            int64_t row_begin, int64_t n_rows, int use_nan, float scale, int d) {
   constexpr int U = (VW * NC <= 8) ? 4 : 1;
   extern __shared__ float gen_smem[];  // heavy rows: [kRowWarps][d] partial accumulators
@@ -172,16 +195,16 @@ gather_rows_generic_kernel(const float* __restrict__ Q, const float* __restrict_
     const typename Cols::Row row = cols.open(r, row_begin + r);
     if (row.n <= 0) {
       if (Cols::kNanFillEmpty && use_nan)
-        for (int e = lane; e < d; e += 32) O[(size_t)r * d + e] = __int_as_float(0x7fc00000);
+        for (int e = lane; e < d; e += 32) O[(size_t)r * d + e] = Elem<T>::down(__int_as_float(0x7fc00000));
     } else if (row.n > kHeavyRowSlots) {
       if (lane == 0) s_heavy[atomicAdd(&s_n_heavy, 1)] = warp;
     } else {
       GenRow<VW, NC> q;
-      gen_load<VW, NC>(Q + (size_t)r * d, d, lane, q);
+      gen_load<T, VW, NC>(Q + (size_t)r * d, d, lane, q);
       GenAcc<VW, NC> st;
       st.clear();
-      gen_accumulate<VW, NC, U, Cols>(cols, row, 0, row.n, q, K, V, d, scale, lane, st);
-      if (st.l > 0.f) gen_store<VW, NC>(st, m, l, O, r, d, lane);
+      gen_accumulate<T, VW, NC, U, Cols>(cols, row, 0, row.n, q, K, V, d, scale, lane, st);
+      if (st.l > 0.f) gen_store<T, VW, NC>(st, m, l, O, r, d, lane);
     }
   }
   __syncthreads();
@@ -198,8 +221,8 @@ gather_rows_generic_kernel(const float* __restrict__ Q, const float* __restrict_
     st.clear();
     if (t0 < t1) {
       GenRow<VW, NC> q;
-      gen_load<VW, NC>(Q + (size_t)rh * d, d, lane, q);
-      gen_accumulate<VW, NC, U, Cols>(cols, row, t0, t1, q, K, V, d, scale, lane, st);
+      gen_load<T, VW, NC>(Q + (size_t)rh * d, d, lane, q);
+      gen_accumulate<T, VW, NC, U, Cols>(cols, row, t0, t1, q, K, V, d, scale, lane, st);
     }
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
@@ -233,7 +256,7 @@ gather_rows_generic_kernel(const float* __restrict__ Q, const float* __restrict_
         }
         tot.m = mn;
       }
-      if (tot.l > 0.f) gen_store<VW, NC>(tot, m, l, O, rh, d, lane);
+      if (tot.l > 0.f) gen_store<T, VW, NC>(tot, m, l, O, rh, d, lane);
     }
     __syncthreads();
   }

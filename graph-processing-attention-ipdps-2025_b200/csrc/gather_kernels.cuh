@@ -489,14 +489,14 @@ __global__ void coo_row_pointers_kernel(const IdxT* __restrict__ row_ind, int64_
 }
 
 // 32-bit row offsets widened to the 64-bit offsets the kernels read (n entries; negative values clamp to 0).
-__global__ void widen_offsets_kernel(const int32_t* __restrict__ in, int64_t n, uint64_t* __restrict__ out) {
+static __global__ void widen_offsets_kernel(const int32_t* __restrict__ in, int64_t n, uint64_t* __restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = (uint64_t)(in[i] > 0 ? in[i] : 0);
 }
 
 // ---- Global-no-local: mark the listed rows -------------------------------------------------------
 // bits must be zero on entry. entry_live[t] = 1 for the first list position naming a row.
-__global__ void gnl_mark_globals_kernel(const int32_t* __restrict__ G, int64_t nG, int64_t L,
+static __global__ void gnl_mark_globals_kernel(const int32_t* __restrict__ G, int64_t nG, int64_t L,
                                         uint32_t* __restrict__ bits, uint8_t* __restrict__ entry_live) {
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= nG) return;

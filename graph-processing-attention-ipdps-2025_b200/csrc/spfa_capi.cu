@@ -6,34 +6,22 @@
 #include <cmath>
 
 #include "block_kernels.cuh"
+#include "capi_common.cuh"
 #include "explicit_plan.cuh"
 #include "gather_generic.cuh"
 #include "gather_kernels.cuh"
+#include "mask_builders.cuh"
 #include "tile_dispatch.cuh"
 
 namespace spfa {
 
 std::atomic<int64_t> g_launches{0};
-// Path selector and "path taken" record are per host thread: two threads that force different paths (tests,
-// benchmarks) do not see each other's choice, so the forward entry points stay re-entrant.
-struct PathCell {
-  int v;
-  int load() const { return v; }
-  void store(int x) { v = x; }
-};
 thread_local PathCell g_path{SPFA_PATH_AUTO};
 thread_local PathCell g_last_path{SPFA_PATH_GATHER};
 
-inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 // Head dimensions with specialised kernels; every other d in [1, kGenericMaxD] takes the generic gather kernel.
 inline bool specialised_d(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
 inline bool supported_d(int d) { return d >= 1 && d <= kGenericMaxD; }
-inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
-
-inline int launch_status() {
-  return cudaGetLastError() == cudaSuccess ? SPFA_OK : SPFA_ERR_LAUNCH;
-}
 
 template <int D, class Cols>
 int launch_gather(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
@@ -56,7 +44,7 @@ int launch_gather_generic(const float* Q, const float* K, const float* V, float*
   const int64_t blocks = (n_rows + kRowWarps - 1) / kRowWarps;
   if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
   const float scale = 1.0f / sqrtf((float)d);
-  gather_rows_generic_kernel<VW, NC, Cols><<<(unsigned)blocks, kRowWarps * 32, (size_t)kRowWarps * d * sizeof(float), st>>>(
+  gather_rows_generic_kernel<float, VW, NC, Cols><<<(unsigned)blocks, kRowWarps * 32, (size_t)kRowWarps * d * sizeof(float), st>>>(
       Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, d);
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_GATHER);
@@ -96,18 +84,6 @@ inline int check_common(const void* Q, const void* K, const void* V, const void*
   } else if (!aligned4(Q) || !aligned4(K) || !aligned4(V) || !aligned4(O)) {
     return SPFA_ERR_BAD_ARG;
   }
-  return SPFA_OK;
-}
-
-inline int check_rows(int64_t L, int64_t row_begin, int64_t row_end) {
-  if (L <= 0 || L >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
-  if (row_begin < 0 || row_end < row_begin || row_end > L) return SPFA_ERR_BAD_ARG;
-  return SPFA_OK;
-}
-
-inline int check_workspace(const void* ws, size_t have, size_t need) {
-  if (need == 0) return SPFA_OK;
-  if (!ws || have < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return SPFA_ERR_WORKSPACE;
   return SPFA_OK;
 }
 
@@ -865,6 +841,38 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
     case 128: return launch_gnl_global_rows<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
   }
   return SPFA_ERR_EMBED_DIM;
+}
+
+// ---- dense mask -> CSR / COO arrays ------------------------------------------------------------------------
+int spfa_dense_mask_offsets(const uint8_t* mask, int64_t n_rows, int64_t n_cols, uint64_t* row_off, void* stream) {
+  if (!row_off || n_rows < 0 || n_cols < 0 || (n_rows > 0 && n_cols > 0 && !mask)) return SPFA_ERR_BAD_ARG;
+  if (n_cols >= (1LL << 32)) return SPFA_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned long long* off = reinterpret_cast<unsigned long long*>(row_off);
+  if (n_rows > 0) {
+    const int64_t blocks = (n_rows + 7) / 8;
+    if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+    mask_row_counts_kernel<<<(unsigned)blocks, 256, 0, st>>>(mask, n_rows, n_cols, off);
+    g_launches.fetch_add(1);
+    if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
+  }
+  offsets_scan_kernel<<<1, 1024, 0, st>>>(off, n_rows);
+  g_launches.fetch_add(1);
+  return launch_status();
+}
+
+int spfa_dense_mask_fill(const uint8_t* mask, int64_t n_rows, int64_t n_cols, const uint64_t* row_off, uint32_t* col_ind,
+                         uint64_t* row_ind, void* stream) {
+  if (n_rows < 0 || n_cols < 0 || !row_off) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0 || n_cols == 0) return SPFA_OK;
+  if (!mask || !col_ind) return SPFA_ERR_BAD_ARG;
+  const int64_t blocks = (n_rows + 7) / 8;
+  if (blocks > 0x7fffffffLL || n_cols >= (1LL << 32)) return SPFA_ERR_TOO_LARGE;
+  mask_fill_columns_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      mask, n_rows, n_cols, reinterpret_cast<const unsigned long long*>(row_off), col_ind,
+      reinterpret_cast<unsigned long long*>(row_ind));
+  g_launches.fetch_add(1);
+  return launch_status();
 }
 
 // ---- visited-pair dump -----------------------------------------------------------------------------

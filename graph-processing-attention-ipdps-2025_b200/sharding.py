@@ -172,6 +172,13 @@ class KeyChunkExchange:
         try:
             for r, ((fk, ak), (fv, av)) in enumerate(everyone):
                 if r != self.rank:
+                    # Open the handle in THIS rank's device context (argument 6 of the rebuild call is the device the
+                    # storage is opened under; CUDA enables peer access lazily for it). The mapped tensor then counts
+                    # as local, so a copy from it is issued on this device's stream and copy engine and reads the
+                    # peer over NVLink -- no context of this process runs on the peer GPU, where it would have to
+                    # time-slice with the peer rank's own kernels.
+                    ak, av = list(ak), list(av)
+                    ak[6] = av[6] = self.dev.index
                     self.peer_K[r], self.peer_V[r] = fk(*ak), fv(*av)
         except Exception:
             ok.zero_()

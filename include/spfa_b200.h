@@ -256,6 +256,52 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
                                      int64_t row_begin, int64_t row_end,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- 16-bit tensors: float16 / bfloat16 Q, K, V, m, l, O ------------------------------------------------------
+ * The reference instantiates its kernels for Half too (AT_DISPATCH_FLOATING_TYPES_AND_HALF,
+ * Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:270; all floating tensors of a call share one dtype). These entry
+ * points read and write such tensors directly -- half the bytes of an fp32 call on the gather path, where HBM traffic
+ * is the limit -- and compute in fp32 (the reference accumulates in half), so results are at least as accurate as
+ * its own. bfloat16 is additive. They always take the warp-per-row gather path (any d from 1 to 1024; d in
+ * {32, 64, 128} has specialised kernels); wide banded masks on 16-bit inputs are better served by converting to fp32
+ * and calling the fp32 entry points, which is what the torch modules do. Arguments are those of the fp32 entry
+ * points with `dtype` in front and without a path choice; pointers must be 16-byte aligned when d % 8 == 0, 2-byte
+ * otherwise. Workspace: COO needs spfa_coo_min_workspace_bytes(n_rows), Global-no-local
+ * spfa_global_no_local_workspace_bytes_16(L, n_global), the others none. */
+typedef enum spfa_dtype { SPFA_DTYPE_F32 = 0, SPFA_DTYPE_F16 = 1, SPFA_DTYPE_BF16 = 2 } spfa_dtype;
+int spfa_csr_forward_16(int dtype, const void* Q, const void* K, const void* V,
+                        const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                        void* m, void* l, void* O, int64_t n_rows, int64_t Lk, int d, int use_nan, void* stream);
+int spfa_coo_forward_16(int dtype, const void* Q, const void* K, const void* V,
+                        const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                        void* m, void* l, void* O, int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int spfa_local_forward_16(int dtype, const void* Q, const void* K, const void* V, void* m, void* l, void* O,
+                          int64_t L, int d, int64_t local_size_each_dir, int64_t row_begin, int64_t row_end, void* stream);
+int spfa_local_1d_dilated_forward_16(int dtype, const void* Q, const void* K, const void* V, void* m, void* l, void* O,
+                                     int64_t L, int d, int64_t local_size_each_dir, int64_t dil_factor,
+                                     int64_t row_begin, int64_t row_end, void* stream);
+int spfa_local_2d_dilated_forward_16(int dtype, const void* Q, const void* K, const void* V, void* m, void* l, void* O,
+                                     int64_t L, int d, int64_t block_size, int64_t dil_factor, int use_nan,
+                                     int64_t row_begin, int64_t row_end, void* stream);
+size_t spfa_global_no_local_workspace_bytes_16(int64_t L, int64_t n_global);
+int spfa_global_no_local_forward_16(int dtype, const void* Q, const void* K, const void* V, void* m, void* l, void* O,
+                                    const int32_t* global_inds, int64_t n_global, int64_t L, int d,
+                                    int64_t local_size_each_dir, int64_t row_begin, int64_t row_end,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- dense boolean mask -> CSR / COO arrays on the GPU ----------------------------------------------------
+ * No counterpart in the reference: its callers convert a dense [n_rows, n_cols] boolean mask with torch's
+ * to_sparse_csr() / to_sparse_coo() and cast the index tensors (verification/verify.py:67-71, 94-98). These two
+ * calls produce the operators' arrays directly. `mask` holds one byte per (row, column), row-major, non-zero =
+ * attend (torch.bool or torch.uint8).
+ *   spfa_dense_mask_offsets  writes row_off[n_rows + 1] (exclusive scan of the entries per row); the total number
+ *                            of entries is row_off[n_rows], which the caller reads back to size col_ind
+ *   spfa_dense_mask_fill     writes col_ind[row_off[r] ...] = the columns of row r in ascending order and, if
+ *                            row_ind is not null, row_ind[...] = r for each of them (the COO row array) */
+int spfa_dense_mask_offsets(const uint8_t* mask, int64_t n_rows, int64_t n_cols, uint64_t* row_off, void* stream);
+int spfa_dense_mask_fill(const uint8_t* mask, int64_t n_rows, int64_t n_cols, const uint64_t* row_off,
+                         uint32_t* col_ind, uint64_t* row_ind, void* stream);
+
 /* ---- visited-pair dump (test support) -----------------------------------------------------------
  * Emits the (row, key) set an implicit mask visits, produced by the same device-side column
  * generators the gather kernels use. No counterpart in the reference (its index arithmetic is inlined

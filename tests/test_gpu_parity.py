@@ -176,9 +176,9 @@ def test_torch_extension_errors_match_reference_types(pkg, capi):
     gnl = pkg.binding("spfa_global_no_local")
     with pytest.raises(ValueError, match="no global tokens"):
         gnl.forward(q, q, q, m, l, O, torch.zeros(0, dtype=torch.int32, device="cuda"), 3)
-    q48 = torch.randn(64, 48, device="cuda")
+    q2k = torch.randn(64, 2048, device="cuda")  # beyond the 1024 the reference's kernels work for
     with pytest.raises(ValueError, match="embedded dimension"):
-        loc.forward(q48, q48, q48, m, l, torch.zeros(64, 48, device="cuda"), 1)
+        loc.forward(q2k, q2k, q2k, m, l, torch.zeros(64, 2048, device="cuda"), 1)
     csr = pkg.binding("spfa_csr")
     with pytest.raises(RuntimeError):
         csr.forward(q, q, q, torch.zeros(65, dtype=torch.float32, device="cuda"),
@@ -691,6 +691,31 @@ def test_every_embedded_dimension_up_to_1024(capi, orc, pkg, d):
     assert_state_close(to_np(st), orc.implicit_forward("local", Q, K, V, 40), TOL_GATHER, f"spfa_local d={d}")
 
 
+@pytest.mark.parametrize("n_rows,n_cols,density", [(300, 517, 0.05), (64, 64, 1.0), (1000, 1, 0.5), (7, 4099, 0.3),
+                                                    (513, 2048, 0.0), (2000, 3001, 0.01)])
+def test_dense_mask_builders_match_torch_sparse_conversion(capi, pkg, n_rows, n_cols, density):
+    """GPU builders of the operators' index arrays from a dense boolean mask: same offsets / rows / columns as
+    torch's to_sparse_csr() / to_sparse_coo() (what the reference's callers use, verification/verify.py:67-71, 94-98),
+    for row lengths and base addresses that are not multiples of 4 bytes, empty rows and full rows."""
+    g = torch.Generator(device="cuda").manual_seed(n_rows + n_cols)
+    big = torch.rand(n_rows + 1, n_cols, device="cuda", generator=g) < density
+    big[0] = True
+    if n_rows > 5:
+        big[4] = False
+    for mask in (big[:n_rows].contiguous(), big[1:], big[1:].to(torch.uint8)):  # big[1:] starts at an odd address
+        assert mask.is_contiguous()
+        want = mask.bool().to_sparse_csr()
+        off, col = capi.dense_mask_to_csr(mask)
+        assert torch.equal(off.view(torch.int64), want.crow_indices()) and torch.equal(col.view(torch.int32).long(), want.col_indices())
+        rows, col2 = capi.dense_mask_to_csr(mask, coo=True)
+        idx = mask.nonzero()
+        assert torch.equal(rows.view(torch.int64), idx[:, 0]) and torch.equal(col2.view(torch.int32).long(), idx[:, 1])
+    off_m, col_m = pkg.binding("spfa_csr").mask_to_csr(big[1:])
+    assert off_m.dtype == torch.uint64 and col_m.dtype == torch.uint32 and torch.equal(off_m.view(torch.int64), off.view(torch.int64))
+    rows_m, col_m2 = pkg.binding("spfa_coo").mask_to_coo(big[1:])
+    assert torch.equal(rows_m.view(torch.int64), rows.view(torch.int64)) and torch.equal(col_m2.view(torch.int32), col2.view(torch.int32))
+
+
 def test_stored_plan_of_another_shape_is_refused_on_the_device(capi):
     """A plan names the (n_rows, nnz, Lk, d) it was built for; a forward call that passes other values finds the
     mismatch on the device, computes nothing and reports code 401 (no table of the foreign plan is read)."""
@@ -827,6 +852,71 @@ def test_torch_modules_accept_the_reference_dtypes(pkg, orc, dtype, tol):
     got = O.double().cpu().numpy()
     assert np.isnan(got[4]).all() and np.array_equal(np.isnan(got), np.isnan(wO))
     assert np.nanmax(np.abs(got - wO)) <= tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 2e-3), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("d", [64, 128, 32, 16, 48, 20, 256])
+def test_native_16bit_gather_all_masks_vs_oracle(capi, orc, pkg, dtype, tol, d):
+    """float16 / bfloat16 tensors read and written directly (the reference dispatches Half as well,
+    sp_flatt_csr_kernel.cu:270): every mask family through the 16-bit C ABI against the fp64 oracle evaluated on the
+    SAME 16-bit input values. Arithmetic is fp32, so the only error is the rounding of the stored (m, l, O): the
+    tolerance is a few units in the last place of the 16-bit format for |O| <~ 4."""
+    L = 1400
+    Q, K, V = seeded_qkv(L, d, 70 + d)
+    q, k, v = (dev(x).to(dtype) for x in (Q, K, V))
+    Qr, Kr, Vr = (x.float().cpu().numpy() for x in (q, k, v))
+    G = np.array([9, 1300, 640, 64, 65], dtype=np.int32)
+
+    def fresh(n):
+        return (torch.full((n,), float("-inf"), device="cuda", dtype=dtype), torch.zeros(n, device="cuda", dtype=dtype),
+                torch.zeros(n, d, device="cuda", dtype=dtype))
+
+    def close(st, want, what):
+        m, l, O = (t.double().cpu().numpy() for t in st)
+        assert np.array_equal(np.isnan(O), np.isnan(want[2])), what
+        assert np.nanmax(np.abs(O - want[2])) <= tol, f"{what}: O {np.nanmax(np.abs(O - want[2])):.3e}"
+        fin = np.isfinite(want[0])
+        assert np.array_equal(np.isfinite(m), fin)
+        np.testing.assert_allclose(m[fin], want[0][fin], rtol=4 * tol, atol=4 * tol, err_msg=what)
+        np.testing.assert_allclose(l, want[1], rtol=4 * tol, atol=1e-6, err_msg=what)
+
+    for kind, p0, p1, rb, re in (("local", 40, 0, 0, L), ("local", 7, 0, 100, 1301), ("local_1d_dilated", 20, 3, 0, L),
+                                 ("local_2d_dilated", 100, 3, 0, L), ("global_no_local", 25, 0, 0, L),
+                                 ("global_no_local", 2, 0, 600, 1400)):
+        want = orc.implicit_forward(kind, Qr[rb:re], Kr, Vr, p0, p1, G=G if kind == "global_no_local" else None,
+                                    use_nan=True, row_begin=rb, row_end=re)
+        st = fresh(re - rb)
+        capi.forward_16(kind, q[rb:re].contiguous(), k, v, *st, p0=p0, p1=p1, global_inds=dev(G), use_nan=True,
+                        row_begin=rb, row_end=re)
+        close(st, want, f"{kind} {dtype} d={d} rows [{rb},{re})")
+    mask, row_off, col = random_csr(L, L, 0.02, d, empty_rows=(3, L - 1))
+    mask[17] = True  # a row of L keys: walked by its whole CTA
+    row_off, col = _csr_of(mask)
+    rows = np.repeat(np.arange(L), mask.sum(1)).astype(np.int64)
+    want = orc.csr_forward(Qr, Kr, Vr, row_off, col, use_nan=True)
+    st = fresh(L)
+    capi.forward_16("csr", q, k, v, *st, row_off=dev(row_off), col_ind=dev(col), use_nan=True)
+    close(st, want, f"csr {dtype} d={d}")
+    st = fresh(L)
+    capi.forward_16("coo", q, k, v, *st, row_ind=dev(rows), col_ind=dev(col), use_nan=True)
+    close(st, want, f"coo {dtype} d={d}")
+    # chained on a 16-bit state: second mask on top of the first (state is read back from 16 bits)
+    _, off_b, col_b = random_csr(L, L, 0.01, 1000 + d)
+    first = orc.csr_forward(Qr, Kr, Vr, off_b, col_b)
+    st = fresh(L)
+    capi.forward_16("csr", q, k, v, *st, row_off=dev(off_b.astype(np.int64)), col_ind=dev(col_b.astype(np.int32)))
+    capi.forward_16("local", q, k, v, *st, p0=0)  # adds the diagonal a second time for rows that have it: use the oracle's chain
+    want2 = orc.implicit_forward("local", Qr, Kr, Vr, 0, state=tuple(x.copy() for x in first))
+    close(st, want2, f"chained {dtype} d={d}")
+    # the drop-in modules route 16-bit explicit masks to the native entry points
+    st = fresh(L)
+    out = pkg.binding("spfa_csr").forward(q, k, v, dev(row_off).view(torch.uint64), dev(col).view(torch.uint32),
+                                          torch.ones(1, device="cuda", dtype=dtype), *st, True)
+    assert out.data_ptr() == st[2].data_ptr()
+    close(st, want, f"spfa_csr.forward {dtype} d={d}")
+    st = fresh(L)
+    pkg.binding("spfa_local").forward(q, k, v, *st, 7)
+    close(st, orc.implicit_forward("local", Qr, Kr, Vr, 7), f"spfa_local.forward {dtype} d={d}")
 
 
 @pytest.mark.parametrize("kind,L,d,p0,p1", [("local", 3000, 64, 100, 0), ("local", 700, 32, 650, 0),

@@ -52,6 +52,7 @@ def test_static_scratch_matches_workspace_variant_twice_in_a_row(pkg):
     states = [capi.new_state(Q.shape[0], Q.shape[1]) for Q, *_ in cases]
     warm = capi.new_state(cases[0][0].shape[0], cases[0][0].shape[1])
     assert _call_static(lib, *cases[0], warm, 0, True) == 0  # first call on the device: resolves the array's address
+    del st  # a leftover state of the loop above would be freed (not allocated) when the name is bound again below
     torch.cuda.synchronize()
     # the property the entry point exists for: the calls below take no device memory, neither from the driver
     # (free memory of the device unchanged) nor from torch's caching allocator
