@@ -63,6 +63,9 @@ WORKLOADS = {
     "blocks": dict(kind="csr", L=262144, d=64, p0=256, p1=4, gen="block_dilated",
                    desc="NON-REFERENCE pattern: block-level dilation as an explicit CSR mask, L=262144, d=64, fp32, "
                         "256-row blocks, block b attends to blocks b, b+-4, b+-8 (3.3e8 entries)"),
+    "bigbird": dict(kind="bigbird", L=131072, d=64, p0=256, p1=32,
+                    desc="NON-REFERENCE fusion: Local(256) + Global-no-local(64 tokens) + random CSR part (~32 keys/row) in "
+                         "one call, L=131072, d=64, fp32; the reference composes it from three chained calls"),
     "coo": dict(kind="coo", L=1048576, d=64, p0=64, p1=0,
                 desc="COO explicit graph mask, L=1048576, d=64, fp32, Zipf(2.1) mean-32 max-8192 random cols + band 64"),
 }
@@ -144,6 +147,22 @@ def make_block_dilated_csr(L, B, step, dev, reach=2):
     per_block = [cols_blk[b][ok[b]].reshape(-1).to(torch.int32) for b in range(nb)]  # keys of one row of block b
     col = torch.cat([c.repeat(B) for c in per_block]).contiguous()
     return row_off, col
+
+
+def make_random_part(L, w, G, per_row, seed, dev):
+    """Random CSR part of a BigBird mask: about per_row uniform columns per row, without the band |i-j| <= w, without
+    global rows and global columns (those are covered by the other two parts), duplicates removed, columns ascending."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    rows = torch.arange(L, device=dev).repeat_interleave(per_row)
+    cols = torch.randint(0, L, (L * per_row,), device=dev, generator=g)
+    isg = torch.zeros(L, dtype=torch.bool, device=dev)
+    isg[G.to(dev).long()] = True
+    keep = ((rows - cols).abs() > w) & ~isg[rows] & ~isg[cols]
+    keys = torch.unique(rows[keep] * L + cols[keep])
+    r, c = keys // L, (keys % L).to(torch.int32)
+    row_off = torch.zeros(L + 1, dtype=torch.int64, device=dev)
+    row_off[1:] = torch.cumsum(torch.bincount(r, minlength=L), 0)
+    return row_off, c.contiguous()
 
 
 def make_coo_graph(L, band, seed, dev, mean_deg=32, max_deg=8192, alpha=2.1):
@@ -293,8 +312,9 @@ class Job:
         if whole_on_one_gpu:  # a single-GPU implementation given the whole job
             self.ranges = [(0, self.L)]
             rank = 0
-        elif weak:
-            self.ranges = [(r * w["L"], (r + 1) * w["L"]) for r in range(world)]
+        elif weak or self.kind == "bigbird":
+            self.ranges = ([(r * w["L"], (r + 1) * w["L"]) for r in range(world)] if weak
+                           else sh.equal_row_ranges(self.L, world, multiple=256))
         elif self.kind == "csr":
             self.ranges = sh.nnz_balanced_row_ranges(full_mask[0], world)
         elif self.kind == "coo":
@@ -312,7 +332,17 @@ class Job:
         self.mask = None
         self.plan = None
         n_live = self.L_local
-        if self.kind == "global_no_local":
+        if self.kind == "bigbird":
+            g = torch.Generator().manual_seed(seed)
+            Gc = torch.sort(torch.randperm(self.L, generator=g)[:64]).values.to(torch.int32)
+            self.G_cpu, self.G = Gc, Gc.to(dev)
+            row_off, col = make_random_part(self.L, self.p0, Gc, self.p1, seed, dev)
+            lo, hi = int(row_off[self.rb]), int(row_off[self.re])
+            self.mask = ((row_off[self.rb:self.re + 1] - lo).contiguous(), col[lo:hi].contiguous())
+            self.nnz_csr = hi - lo
+            self.nnz = (implicit_nnz("local", self.L, self.p0, 0, None, self.rb, self.re)
+                        + implicit_nnz("global_no_local", self.L, self.p0, 0, Gc, self.rb, self.re) + self.nnz_csr)
+        elif self.kind == "global_no_local":
             g = torch.Generator().manual_seed(seed)
             Gc = torch.sort(torch.randperm(self.L, generator=g)[:64]).values.to(torch.int32)
             self.G_cpu, self.G = Gc, Gc.to(dev)
@@ -336,7 +366,11 @@ class Job:
         del full_mask
         self.n_live = n_live
         self.flops = 4.0 * self.nnz * self.d
-        self.bytes = algorithmic_bytes(self.kind, self.L, self.L_local, self.d, self.nnz, n_live)
+        if self.kind == "bigbird":  # compulsory bytes of the implicit parts + gather-counted bytes of the CSR part
+            self.bytes = (algorithmic_bytes("local", self.L, self.L_local, self.d, 0, n_live)
+                          + self.nnz_csr * (2 * self.d * 4 + 4) + 8 * (self.L_local + 1))
+        else:
+            self.bytes = algorithmic_bytes(self.kind, self.L, self.L_local, self.d, self.nnz, n_live)
         self.m = torch.empty(self.L_local, device=dev)
         self.l = torch.empty(self.L_local, device=dev)
         self.O = torch.empty(self.L_local, self.d, device=dev)
@@ -373,6 +407,8 @@ class Job:
             capi.local_2d_dilated_forward(Q, K, V, *st, self.p0, self.p1, True, self.rb, self.re)
         elif k == "global_no_local":
             capi.global_no_local_forward(Q, K, V, *st, self.G, self.p0, self.rb, self.re)
+        elif k == "bigbird":
+            capi.bigbird_forward(Q, K, V, *st, self.G, self.p0, self.mask[0], self.mask[1], self.rb, self.re)
         elif k == "csr":
             capi.csr_forward(Q, K, V, self.mask[0], self.mask[1], *st, use_nan=False)
         else:
@@ -389,8 +425,17 @@ class Job:
             binding.forward(Q, K, V, *st, self.p0, self.p1, True)
         elif k == "global_no_local":
             binding.forward(Q, K, V, *st, self.G, self.p0)
+        elif k == "bigbird":
+            binding.forward(Q, K, V, *st, self.G, self.p0, self.mask[0], self.mask[1])
         else:
             binding.forward(Q, K, V, self.mask[0], self.mask[1], w_val, *st, False)
+
+    def chained_forward(self, capi):
+        """BigBird as the reference composes it: three operator calls on one state (verification/verify.py:337-352)."""
+        st = (self.m, self.l, self.O)
+        capi.local_forward(self.Q, self.K, self.V, *st, self.p0, self.rb, self.re)
+        capi.global_no_local_forward(self.Q, self.K, self.V, *st, self.G, self.p0, self.rb, self.re)
+        capi.csr_forward(self.Q, self.K, self.V, self.mask[0], self.mask[1], *st, use_nan=False)
 
 
 def dist_max(x: float, world: int, dev) -> float:
@@ -617,6 +662,9 @@ def run_ours(args, rank, world, dev):
         line["config"]["kv"] = ("K and V start row-sharded in %d equal chunks; every timed step replicates them: %s; chunks "
                                 "received by the previous step are overwritten with NaN before each step" % (world, exchange_note))
         line["config"]["exchange_vs_resident_max_abs_diff"] = check
+    if job.kind == "bigbird" and world == 1:
+        t_ch, _ = timed_steps(job, lambda: job.chained_forward(capi), args.steps, args.warmup, 1)
+        line["chained_three_calls_ms"] = statistics.mean(t_ch)
     if e2e:
         line.update(e2e)
     if not args.no_cpu_baseline and world == 1:
@@ -661,6 +709,12 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
             elif job.kind == "global_no_local":
                 def chunk_call(a, b, q, k, v, m_, l_, o_):
                     capi.global_no_local_forward(q, k, v, m_, l_, o_, job.G, job.p0, a, b)
+            elif job.kind == "bigbird":
+                def chunk_call(a, b, q, k, v, m_, l_, o_):
+                    ro = job.mask[0][a:b + 1]
+                    lo, hi = int(cut_bb[a]), int(cut_bb[b])
+                    capi.bigbird_forward(q, k, v, m_, l_, o_, job.G, job.p0, (ro - lo).contiguous(), job.mask[1][lo:hi], a, b)
+                cut_bb = {e: int(job.mask[0][e]) for e in full_pipe.edges}
             elif job.kind == "coo":
                 cut = torch.searchsorted(job.mask[0], torch.tensor(full_pipe.edges, device=dev)).cpu().tolist()
 
@@ -782,7 +836,7 @@ def cpu_baseline(job, budget):
     ds = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ds)
     q, k, v = job.Q.cpu(), job.K.cpu(), job.V.cpu()
-    G = job.G_cpu if job.kind == "global_no_local" else None
+    G = job.G_cpu if job.kind in ("global_no_local", "bigbird") else None
     chunk = 1024 if job.L <= 65536 else (512 if job.L <= 262144 else 128)
     mask_fn = None
     if job.kind in ("csr", "coo"):  # explicit masks: scatter the chunk's entries into a dense boolean chunk
@@ -795,6 +849,15 @@ def cpu_baseline(job, budget):
         def mask_fn(r0, r1):
             lo, hi = int(row_off[r0]), int(row_off[r1])
             m = torch.zeros(r1 - r0, job.L, dtype=torch.bool)
+            rr = torch.repeat_interleave(torch.arange(r1 - r0), (row_off[r0 + 1:r1 + 1] - row_off[r0:r1]))
+            m[rr, cols[lo:hi]] = True
+            return m
+    if job.kind == "bigbird":  # union of the two closed-form masks and the scattered CSR part
+        row_off, cols = job.mask[0].cpu(), job.mask[1].cpu().long()
+
+        def mask_fn(r0, r1):
+            m = ds.mask_chunk("local", job.L, r0, r1, job.p0) | ds.mask_chunk("global_no_local", job.L, r0, r1, job.p0, 0, job.G_cpu)
+            lo, hi = int(row_off[r0]), int(row_off[r1])
             rr = torch.repeat_interleave(torch.arange(r1 - r0), (row_off[r0 + 1:r1 + 1] - row_off[r0:r1]))
             m[rr, cols[lo:hi]] = True
             return m
@@ -823,6 +886,16 @@ def reference_step_fn(job, mods, dev):
                 "every row (O(L*nnz)) and does not complete at this size")
         return (lambda: mod.forward(job.Q, job.K, job.V, row_off.view(torch.uint64), job.mask[1].view(torch.uint32), w_val,
                                     *st, False)), note
+    if k == "bigbird":  # the reference's own composition: three chained calls (verification/verify.py:337-352)
+        ml, mg, mc = mods("local"), mods("global_no_local"), mods("csr")
+        if ml is None or mg is None or mc is None:
+            return None, None
+
+        def chain():
+            ml.forward(job.Q, job.K, job.V, *st, job.p0)
+            mg.forward(job.Q, job.K, job.V, *st, job.G, job.p0)
+            mc.forward(job.Q, job.K, job.V, job.mask[0].view(torch.uint64), job.mask[1].view(torch.uint32), w_val, *st, False)
+        return chain, "the reference's chained composition: spfa_local, spfa_global_no_local, spfa_csr on one state"
     mod = mods(k)
     if mod is None:
         return None, None

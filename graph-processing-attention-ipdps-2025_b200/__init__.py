@@ -27,7 +27,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBDIR = os.path.join(_HERE, "lib")
 
 MODULES = ("spfa_csr", "spfa_coo", "spfa_local", "spfa_local_1d_dilated", "spfa_local_2d_dilated",
-           "spfa_global_no_local")
+           "spfa_global_no_local", "spfa_bigbird")
 
 
 def add_bindings_to_path() -> str:

@@ -34,6 +34,7 @@ BINDINGS = {
     "spfa_local_1d_dilated": ("Sparse_FlashAttention_Local_1D_Dilated", "sp_flatt_local_1d_dilated.cpp"),
     "spfa_local_2d_dilated": ("Sparse_FlashAttention_Local_2D_Dilated", "sp_flatt_local_2d_dilated.cpp"),
     "spfa_global_no_local": ("Sparse_FlashAttention_Global_No_Local", "sp_flatt_global_no_local.cpp"),
+    "spfa_bigbird": ("Sparse_FlashAttention_BigBird", "sp_flatt_bigbird.cpp"),  # additive: the fused union of masks
 }
 
 
@@ -141,7 +142,7 @@ def build_binding(name: str, force: bool = False) -> str:
 
 def build_all(force: bool = False, verbose: bool = False) -> dict[str, str]:
     out = {"libspfa_b200": build_lib(force, verbose)}
-    with ThreadPoolExecutor(max_workers=min(6, os.cpu_count() or 1)) as ex:
+    with ThreadPoolExecutor(max_workers=min(7, os.cpu_count() or 1)) as ex:
         for name, path in zip(BINDINGS, ex.map(lambda n: build_binding(n, force), BINDINGS)):
             out[name] = path
     return out

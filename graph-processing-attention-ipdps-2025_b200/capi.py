@@ -34,7 +34,7 @@ EXPORTS = (
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
     "spfa_global_no_local_workspace_bytes", "spfa_global_no_local_forward_f32",
     "spfa_mask_count", "spfa_mask_fill",
-    "spfa_dense_mask_offsets", "spfa_dense_mask_fill",
+    "spfa_dense_mask_offsets", "spfa_dense_mask_fill", "spfa_bigbird_workspace_bytes", "spfa_bigbird_forward_f32",
     "spfa_csr_forward_16", "spfa_coo_forward_16", "spfa_local_forward_16", "spfa_local_1d_dilated_forward_16",
     "spfa_local_2d_dilated_forward_16", "spfa_global_no_local_workspace_bytes_16", "spfa_global_no_local_forward_16",
     "spfa_csr_workspace_bytes_idx32", "spfa_csr_forward_f32_idx32", "spfa_coo_forward_f32_idx32", "spfa_coo_plan_build_idx32",
@@ -100,6 +100,10 @@ def lib() -> ctypes.CDLL:
     L.spfa_global_no_local_workspace_bytes_16.argtypes = [i64, i64]
     L.spfa_global_no_local_forward_16.restype = i32
     L.spfa_global_no_local_forward_16.argtypes = [i32] + [vp] * 7 + [i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_bigbird_workspace_bytes.restype = sz
+    L.spfa_bigbird_workspace_bytes.argtypes = [i64, i64, i32, i64, i64]
+    L.spfa_bigbird_forward_f32.restype = i32
+    L.spfa_bigbird_forward_f32.argtypes = [vp] * 7 + [i64, vp, vp, i64, i64, i32, i64, i64, i64, vp, sz, vp]
     L.spfa_dense_mask_offsets.restype = i32
     L.spfa_dense_mask_offsets.argtypes = [vp, i64, i64, vp, vp]
     L.spfa_dense_mask_fill.restype = i32
@@ -342,6 +346,25 @@ def planned_forward_keys(Q, K, V, m, l, O, plan: ExplicitPlan, key_begin: int, k
         check(lib().spfa_planned_forward_keys_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows,
                                                   plan.nnz, plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes,
                                                   int(key_begin), int(key_end), _stream(dev)))
+    return O
+
+
+def bigbird_forward(Q, K, V, m, l, O, global_inds, local_size_each_dir, row_off=None, col_ind=None, row_begin=0,
+                    row_end=None):
+    """Local(w) + Global-no-local(global_inds, w) + an optional disjoint CSR part (row_off/col_ind of the rows
+    [row_begin, row_end)) in one call: what the reference composes from three chained forward calls."""
+    dev = _f32(Q, K, V, m, l, O)
+    L, row_end = _rows(Q, K, row_begin, row_end)
+    if global_inds.dtype != torch.int32 or not global_inds.is_contiguous() or global_inds.device != dev:
+        raise SpfaError(-1, "global_inds must be a contiguous torch.int32 tensor on Q's device")
+    nnz = 0 if col_ind is None else col_ind.shape[0]
+    with torch.cuda.device(dev):
+        d, nG = Q.shape[1], global_inds.shape[0]
+        buf, wp, wb = workspace(lib().spfa_bigbird_workspace_bytes(L, Q.shape[0], d, nG, nnz), dev)
+        check(lib().spfa_bigbird_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O),
+                                             _ptr(global_inds) if nG else None, nG,
+                                             _ptr(_as_u64(row_off)) if nnz else None, _ptr(_as_u32(col_ind)) if nnz else None,
+                                             nnz, L, d, int(local_size_each_dir), row_begin, row_end, wp, wb, _stream(dev)))
     return O
 
 

@@ -843,6 +843,48 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
   return SPFA_ERR_EMBED_DIM;
 }
 
+// ---- fused union of masks: Local + Global-no-local + an explicit CSR part -----------------------------------
+size_t spfa_bigbird_workspace_bytes(int64_t L, int64_t n_rows, int d, int64_t n_global, int64_t nnz) {
+  return align_up(spfa_global_no_local_workspace_bytes(L, n_rows, d, n_global)) + spfa_csr_workspace_bytes(n_rows, nnz, L, d);
+}
+
+int spfa_bigbird_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                             const int32_t* G, int64_t nG, const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                             int64_t L, int d, int64_t w, int64_t row_begin, int64_t row_end, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  rc = check_rows(L, row_begin, row_end);
+  if (rc) return rc;
+  if (nG == 0 || nG > L || nG < 0) return SPFA_ERR_GLOBAL_COUNT;
+  if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
+  if (!G || nnz < 0 || (nnz > 0 && (!row_off || !col_ind))) return SPFA_ERR_BAD_ARG;
+  const int64_t n_rows = row_end - row_begin;
+  const size_t gnl_bytes = align_up(spfa_global_no_local_workspace_bytes(L, n_rows, d, nG));
+  rc = check_workspace(workspace, workspace_bytes, gnl_bytes + spfa_csr_workspace_bytes(n_rows, nnz, L, d));
+  if (rc) return rc;
+  if (n_rows == 0) return SPFA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = static_cast<char*>(workspace);
+  const int path = g_path.load();
+  // one pass over Q and O for the band and the listed keys together, where the tiled kernel serves the shape
+  const bool fused = path != SPFA_PATH_GATHER && gnl_tiled_shape_ok(d, nG) && (path == SPFA_PATH_TILED || w >= kTileMinHalfWidth);
+  if (fused) {
+    rc = tiled_bigbird_forward(Q, K, V, m, l, O, G, nG, L, d, w, row_begin, row_end, ws + gnl_plan(L, d, nG).total, st);
+    if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
+  } else {  // the two operators one after the other on the same state
+    rc = spfa_local_forward_f32(Q, K, V, m, l, O, L, d, w, row_begin, row_end, nullptr, 0, stream);
+    if (rc == SPFA_OK)
+      rc = spfa_global_no_local_forward_f32(Q, K, V, m, l, O, G, nG, L, d, w, row_begin, row_end, ws, gnl_bytes, stream);
+  }
+  if (rc || nnz == 0) return rc;
+  const int taken = g_last_path.load();
+  rc = spfa_csr_forward_f32(Q, K, V, row_off, col_ind, nnz, m, l, O, n_rows, L, d, 0, ws + gnl_bytes,
+                            workspace_bytes - gnl_bytes, stream);
+  if (taken == SPFA_PATH_TILED) g_last_path.store(SPFA_PATH_TILED);
+  return rc;
+}
+
 // ---- dense mask -> CSR / COO arrays ------------------------------------------------------------------------
 int spfa_dense_mask_offsets(const uint8_t* mask, int64_t n_rows, int64_t n_cols, uint64_t* row_off, void* stream) {
   if (!row_off || n_rows < 0 || n_cols < 0 || (n_rows > 0 && n_cols > 0 && !mask)) return SPFA_ERR_BAD_ARG;

@@ -115,9 +115,14 @@ bool band_kernel_usable() {
 }
 
 // Common launch steps of band_forward_kernel: register-budget guard, shared-memory opt-in, error word.
+// tmK2 / tmV2: the second key source of mode 4 (gathered listed keys); every other mode passes null and the first
+// pair is handed to the kernel twice.
 template <int D, bool EXPL = false, class C = TileCfg<D>>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
-                    const tile::BandParams& prm, dim3 grid, cudaStream_t st) {
+                    const tile::BandParams& prm, dim3 grid, cudaStream_t st, const CUtensorMap* tmK2p = nullptr,
+                    const CUtensorMap* tmV2p = nullptr) {
+  const CUtensorMap& tmK2 = tmK2p ? *tmK2p : tmK;
+  const CUtensorMap& tmV2 = tmV2p ? *tmV2p : tmV;
   constexpr int NSUB = C::NSUB;
   using P = tile::Plan<D, C::BN, C::NS, NSUB, C::NSV>;
   using G = tile::Geo<NSUB>;
@@ -138,9 +143,9 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, m, l, O, prm, err) != cudaSuccess) return SPFA_ERR_LAUNCH;
+    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmK2, tmV2, m, l, O, prm, err) != cudaSuccess) return SPFA_ERR_LAUNCH;
   } else {
-    kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, m, l, O, prm, err);
+    kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, tmK2, tmV2, m, l, O, prm, err);
   }
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
@@ -326,6 +331,7 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   // mode 1: ordinary rows of the shard against the gathered global keys
   prm.mode = 1;
   prm.n_keys = nG;
+  prm.n_listed = nG;
   prm.u_q_first = row_begin;
   prm.n_q = n_rows;
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, KG, D, nG, pitch, CR::BN) ||
@@ -368,6 +374,88 @@ inline int tiled_gnl_forward(const float* Q, const float* K, const float* V, flo
     case 32: return launch_gnl_tiled<32>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
     case 64: return launch_gnl_tiled<64>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
     case 128: return launch_gnl_tiled<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, ordinary_rows_too, st);
+  }
+  return SPFA_ERR_EMBED_DIM;
+}
+
+// ---- fused Local + Global-no-local ("BigBird" without its random part) -----------------------------------------
+// Mask = { |i - j| <= w }  union  { i or j listed, |i - j| > w }. One pass of band_forward_kernel in mode 4 gives every
+// row that is not listed its band tiles and its listed-key tiles (one read of Q, one read-modify-write of O); the
+// listed rows attend to every key and run as the split strip of the Global-no-local path with an empty exclusion
+// window, followed by the combine pass. Scratch: the Global-no-local tiled plan's.
+template <int D>
+int launch_bigbird_tiled(const float* Q, const float* K, const float* V, float* m, float* l, float* O, const int32_t* G,
+                         int64_t nG, int64_t L, int64_t w, int64_t row_begin, int64_t row_end, char* ws,
+                         const GnlTiledPlan& plan, cudaStream_t st) {
+  int32_t* sorted = reinterpret_cast<int32_t*>(ws + plan.off_sorted);
+  int32_t* n_valid = reinterpret_cast<int32_t*>(ws + plan.off_nvalid);
+  uint8_t* live = reinterpret_cast<uint8_t*>(ws + plan.off_live);
+  float* QG = reinterpret_cast<float*>(ws + plan.off_qg);
+  float* KG = reinterpret_cast<float*>(ws + plan.off_kg);
+  float* VG = reinterpret_cast<float*>(ws + plan.off_vg);
+  float* partials = reinterpret_cast<float*>(ws + plan.off_part);
+  gnl_sort_globals_kernel<<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid);
+  g_launches.fetch_add(1);
+  gnl_gather_globals_kernel<<<(unsigned)((nG + 3) / 4), 128, 0, st>>>(sorted, (int)nG, Q, K, V, D, row_begin, row_end, QG,
+                                                                      KG, VG, live);
+  g_launches.fetch_add(1);
+  if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+  using CB = TileCfg<D>;                    // band + listed keys, every row of the shard
+  using CK = typename GnlKeysCfg<D>::type;  // listed rows x all keys
+  const int64_t pitch = D * (int64_t)sizeof(float);
+  const int64_t n_rows = row_end - row_begin;
+  tile::BandParams prm{};
+  prm.mode = 4;
+  prm.n_keys = L;
+  prm.n_listed = nG;
+  prm.u_q_first = row_begin;
+  prm.n_q = n_rows;
+  prm.w = w;
+  prm.s = 1;
+  prm.r = 0;
+  prm.row_begin = row_begin;
+  prm.scale_log2e = (1.0f / sqrtf((float)D)) * kLog2e;
+  prm.sorted = sorted;
+  prm.n_valid = n_valid;
+  prm.overlap = 1;  // the strip launch below writes other things (partial states): it may start beside this one
+  CUtensorMap tmQ, tmK, tmV, tmK2, tmV2;
+  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, CB::BN) ||
+      !make_row_map(&tmV, V, D, L, pitch, CB::BN, /*mn_major=*/true) || !make_row_map(&tmK2, KG, D, nG, pitch, CB::BN) ||
+      !make_row_map(&tmV2, VG, D, nG, pitch, CB::BN, /*mn_major=*/true))
+    return SPFA_ERR_LAUNCH;
+  int rc = launch_band_raw<D, false, CB>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + CB::kRows - 1) / CB::kRows)),
+                                         st, &tmK2, &tmV2);
+  if (rc) return rc;
+  prm.mode = 2;
+  prm.overlap = 2;
+  prm.w = -1;  // an empty exclusion window: the listed rows attend to every key
+  prm.n_keys = L;
+  prm.u_q_first = 0;
+  prm.n_q = nG;
+  prm.row_begin = 0;
+  prm.kv_chunk = plan.kv_chunk;
+  prm.partials = partials;
+  prm.n_split = plan.n_split;
+  if (!make_row_map(&tmQ, QG, D, nG, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, CK::BN) ||
+      !make_row_map(&tmV, V, D, L, pitch, CK::BN, /*mn_major=*/true))
+    return SPFA_ERR_LAUNCH;
+  rc = launch_band_raw<D, false, CK>(tmQ, tmK, tmV, m, l, O, prm,
+                                     dim3((unsigned)((nG + CK::kRows - 1) / CK::kRows), (unsigned)plan.n_split), st);
+  if (rc) return rc;
+  combine_partials_kernel<D><<<(unsigned)nG, kCombineWarps * 32, 0, st>>>(partials, sorted, live, (int)nG, row_begin, row_end,
+                                                                         plan.n_split, m, l, O);
+  g_launches.fetch_add(1);
+  return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
+}
+
+inline int tiled_bigbird_forward(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                 const int32_t* G, int64_t nG, int64_t L, int d, int64_t w, int64_t row_begin,
+                                 int64_t row_end, char* ws, cudaStream_t st) {
+  const GnlTiledPlan plan = gnl_tiled_plan(L, d, nG);
+  switch (d) {
+    case 32: return launch_bigbird_tiled<32>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, st);
+    case 64: return launch_bigbird_tiled<64>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, st);
+    case 128: return launch_bigbird_tiled<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, ws, plan, st);
   }
   return SPFA_ERR_EMBED_DIM;
 }

@@ -80,8 +80,13 @@ struct BandParams {
   //         every key of the full sequence outside [sorted[r]-w, sorted[r]+w]. The key range is split
   //         over blockIdx.y (kv_chunk keys per CTA) and each CTA writes a partial softmax state per
   //         row ((d+4) floats: un-normalised O relative to m, then m, l) for a later combine pass.
+  // mode 4: band AND listed keys in one pass (fused Local + Global-no-local for the rows that are not listed): a
+  //         row attends to the keys [u-w, u+w] of the full sequence (tiles fetched through tmK/tmV) and to every
+  //         listed key outside that window (tiles of the gathered listed rows, fetched through tmK2/tmV2);
+  //         listed rows are skipped as in mode 1.
   int mode;
-  const int32_t* sorted;  // modes 1, 2: ascending global row numbers (invalid entries last, as INT_MAX)
+  int64_t n_listed;       // modes 1, 4: rows of the gathered listed-key arrays (mode 1: equals n_keys)
+  const int32_t* sorted;  // modes 1, 2, 4: ascending global row numbers (invalid entries last, as INT_MAX)
   const int32_t* n_valid; // modes 1, 2: number of real entries in `sorted`
   int64_t kv_chunk;       // mode 2: keys per CTA along blockIdx.y
   float* partials;        // mode 2: [n_keys_of_sorted][n_split][d+4]
@@ -295,7 +300,8 @@ struct Plan {
 template <int D, int BN, int NS, int NSUB, bool EXPL = false, int NSV = NS>
 __global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, float* __restrict__ m_out, float* __restrict__ l_out,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmK2,
+                    const __grid_constant__ CUtensorMap tmV2, float* __restrict__ m_out, float* __restrict__ l_out,
                     float* __restrict__ O_out, const BandParams prm, int* __restrict__ err) {
   using P = Plan<D, BN, NS, NSUB, NSV>;
   using G = Geo<NSUB>;
@@ -329,7 +335,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (EXPL) {
     kv_lo = 0;
     kv_hi = prm.n_keys;
-  } else if (prm.mode == 0) {
+  } else if (prm.mode == 0 || prm.mode == 4) {
     kv_lo = (uq0 - prm.w > 0) ? (uq0 - prm.w) : 0;
     kv_hi = uq0 + rows_here - 1 + prm.w + 1;
     if (kv_hi > prm.n_keys) kv_hi = prm.n_keys;
@@ -345,21 +351,30 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   if (kv_hi < kv_lo) kv_hi = kv_lo;
   int nT = (int)((kv_hi - kv_lo + BN - 1) / BN);
+  // mode 4: the band's tiles are followed by the tiles of the listed keys (every sub-tile with rows uses all of them)
+  const int nTb = nT;
+  int nv4 = 0;  // mode 4: real listed keys
+  if (!EXPL && prm.mode == 4) {
+    nv4 = *prm.n_valid;
+    if (nv4 > prm.n_listed) nv4 = (int)prm.n_listed;
+    nT += (nv4 + BN - 1) / BN;
+  }
   // Key tiles of each sub-tile: a contiguous range [j0, j1) of the CTA's tiles (implicit masks), or the set
   // bits of act[x] over the CTA's merged tile list (explicit masks, read from shared memory after set-up).
-  int j0[NSUB], j1[NSUB];
+  int j0[NSUB], j1[NSUB], jl[NSUB];  // jl: first listed-key tile of the sub-tile (mode 4), else "never"
   uint64_t act[NSUB];
   const int* s_kt = reinterpret_cast<const int*>(smem + P::kOffX + P::kXKt);
 #pragma unroll
   for (int x = 0; x < NSUB; ++x) {
     act[x] = 0;
+    jl[x] = 0x7fffffff;
     const int64_t ux0 = uq0 + 128 * x;
     int64_t ux_last = ux0 + 127;
     if (ux_last > uq_end_eff - 1) ux_last = uq_end_eff - 1;
     if (ux0 >= uq_end_eff) {
       j0[x] = 0;
       j1[x] = 0;
-    } else if (prm.mode != 0) {
+    } else if (prm.mode != 0 && prm.mode != 4) {
       j0[x] = 0;
       j1[x] = nT;
     } else {
@@ -368,6 +383,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (hi > prm.n_keys) hi = prm.n_keys;
       j0[x] = (int)((lo - kv_lo) / BN);
       j1[x] = (int)((hi - kv_lo + BN - 1) / BN);
+      if (prm.mode == 4) jl[x] = nTb;
     }
   }
 
@@ -443,9 +459,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int x = 0; x < NSUB; ++x) s_act[x] = a[x];
     *reinterpret_cast<int*>(smem + P::kOffX + P::kXNt) = nt;
   }
-  if (!EXPL && P::kStageSorted && prm.mode == 1) {
+  if (!EXPL && P::kStageSorted && (prm.mode == 1 || prm.mode == 4)) {
     int32_t* s_sorted = reinterpret_cast<int32_t*>(smem + P::kOffSorted);
-    const int cap = (prm.n_keys < P::kSortedBytes / 4) ? (int)prm.n_keys : P::kSortedBytes / 4;
+    const int cap = (prm.n_listed < P::kSortedBytes / 4) ? (int)prm.n_listed : P::kSortedBytes / 4;
     for (int i = threadIdx.x; i < cap; i += G::kThreads) s_sorted[i] = __ldg(prm.sorted + i);
   }
   if (warp == W_TMA) {
@@ -465,13 +481,14 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   // helpers over both representations of "sub-tile x uses key tile j"
   auto active = [&](int x, int j) -> bool {
-    return EXPL ? (((act[x] >> j) & 1ull) != 0) : (j >= j0[x] && j < j1[x]);
+    return EXPL ? (((act[x] >> j) & 1ull) != 0) : ((j >= j0[x] && j < j1[x]) || j >= jl[x]);
   };
   auto it_of = [&](int x, int j) -> int {  // how many of x's tiles come before tile j
-    return EXPL ? __popcll(act[x] & ((1ull << j) - 1ull)) : (j - j0[x]);
+    return EXPL ? __popcll(act[x] & ((1ull << j) - 1ull)) : ((j < nTb) ? (j - j0[x]) : (j1[x] - j0[x] + j - nTb));
   };
-  auto tile_key0 = [&](int j) -> int32_t {  // first key row of the CTA's tile j
-    return EXPL ? (int32_t)(s_kt[j] * BN) : (int32_t)(kv_lo + (int64_t)j * BN);
+  auto tile_key0 = [&](int j) -> int32_t {  // first key row of the CTA's tile j (listed-key tiles: row of the gathered array)
+    return EXPL ? (int32_t)(s_kt[j] * BN)
+                : ((j < nTb) ? (int32_t)(kv_lo + (int64_t)j * BN) : (int32_t)((j - nTb) * BN));
   };
 
   if (warp >= W_TMA) {
@@ -499,7 +516,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
-          tma_load_2d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmK, c * 32, yk,
+          tma_load_2d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmK : &tmK2, c * 32, yk,
                       bar(B_KFULL + st));
         return true;
       };
@@ -512,7 +529,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
-          tma_load_2d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, &tmV, c * 32, yk,
+          tma_load_2d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmV : &tmV2, c * 32, yk,
                       bar(B_VFULL + st));
         if (j + NS < nT) ok = load_k(j + NS);
       }
@@ -618,19 +635,21 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // attends to (mode 0) or the keys it must skip (modes 1, 2). Both ends grow with the row, so the first
     // and last row of a warp (lo_a/hi_a, lo_b/hi_b) bound every row of the warp: that makes the chunk
     // classes below warp-uniform.
-    int lo_q, hi_q;
-    bool listed = false;  // mode 1: this query row is itself a global row (handled by the mode-2 launch)
+    int lo_q = 0, hi_q = -1;
+    int lo2_q = 0, hi2_q = -1;  // mode 4: the listed keys (positions in the sorted list) this row must skip
+    bool listed = false;  // modes 1, 4: this query row is itself a global row (handled by the mode-2 launch)
     if (EXPL) {
       lo_q = hi_q = 0;  // validity comes from the plan's bit masks
-    } else if (prm.mode == 0) {
+    } else if (prm.mode == 0 || prm.mode == 4) {
       const int64_t n1 = prm.n_keys - 1;
       lo_q = (int)(((uq - prm.w > 0) ? (uq - prm.w) : 0) - kv_lo);
       hi_q = (int)(((uq + prm.w < n1) ? (uq + prm.w) : n1) - kv_lo);
-    } else if (prm.mode == 1) {
-      const int nv = (int)kv_hi;
+    }
+    if (!EXPL && (prm.mode == 1 || prm.mode == 4)) {
+      const int nv = (prm.mode == 1) ? (int)kv_hi : nv4;
       const int64_t ic = (uq < uq_end - 1) ? uq : (uq_end - 1);  // clamp keeps the bounds monotone past the end
       const int32_t* s_sorted = reinterpret_cast<const int32_t*>(smem + P::kOffSorted);
-      const bool staged = P::kStageSorted && prm.n_keys <= P::kSortedBytes / 4;
+      const bool staged = P::kStageSorted && prm.n_listed <= P::kSortedBytes / 4;
       auto entry = [&](int t) -> int64_t { return staged ? (int64_t)s_sorted[t] : (int64_t)__ldg(prm.sorted + t); };
       auto lower_bound = [&](int64_t v) {  // first t with sorted[t] >= v
         int a = 0, b = nv;
@@ -640,11 +659,17 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         return a;
       };
-      lo_q = lower_bound(ic - prm.w);
-      hi_q = lower_bound(ic + prm.w + 1) - 1;
+      const int sk_lo = lower_bound(ic - prm.w), sk_hi = lower_bound(ic + prm.w + 1) - 1;
+      if (prm.mode == 1) {
+        lo_q = sk_lo;
+        hi_q = sk_hi;
+      } else {
+        lo2_q = sk_lo;
+        hi2_q = sk_hi;
+      }
       const int t = lower_bound(ic);
       listed = (t < nv) && (entry(t) == ic);
-    } else {
+    } else if (!EXPL && prm.mode == 2) {
       const int nv = *prm.n_valid;
       const int64_t rc = (uq < nv - 1) ? uq : (int64_t)(nv - 1);
       const int64_t g = (nv > 0) ? (int64_t)__ldg(prm.sorted + (rc > 0 ? rc : 0)) : 0;
@@ -654,6 +679,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     const int lo_a = __shfl_sync(kFullMask, lo_q, 0), lo_b = __shfl_sync(kFullMask, lo_q, 31);
     const int hi_a = __shfl_sync(kFullMask, hi_q, 0), hi_b = __shfl_sync(kFullMask, hi_q, 31);
+    const int lo2_a = __shfl_sync(kFullMask, lo2_q, 0), lo2_b = __shfl_sync(kFullMask, lo2_q, 31);
+    const int hi2_a = __shfl_sync(kFullMask, hi2_q, 0), hi2_b = __shfl_sync(kFullMask, hi2_q, 31);
     const int n_cols = (int)(kv_hi - kv_lo);  // real keys of this CTA's range
     // The caller's state row is needed only in the epilogue; asking L2 for it now takes its DRAM latency
     // off the end of the CTA.
@@ -670,7 +697,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float l_run = 0.f;          // row sum relative to `shift`
     bool ok = true;
     uint32_t sr[NC][32];
-    const int nx = EXPL ? __popcll(act[x]) : (j1[x] - j0[x]);
+    const int n_band = j1[x] - j0[x];
+    const int nx = EXPL ? __popcll(act[x]) : (n_band + ((jl[x] != 0x7fffffff) ? (nT - nTb) : 0));
     const float sc = prm.scale_log2e;
     uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
     const uint32_t* xm = nullptr;
@@ -682,15 +710,18 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         j = __ffsll((long long)rem) - 1;
         rem &= rem - 1;
       } else {
-        j = j0[x] + it;
+        j = (it < n_band) ? (j0[x] + it) : (nTb + it - n_band);
       }
-      const int k0 = j * BN;
+      // mode 4 switches per tile between "keys inside the band" (band tiles) and "listed keys outside the window"
+      const bool lst = !EXPL && prm.mode == 4 && j >= nTb;
+      const int tmode = lst ? 1 : ((prm.mode == 4) ? 0 : prm.mode);
+      const int k0 = (lst ? (j - nTb) : j) * BN;
       // Interval of this tile's columns: this row [c_lo, c_hi]; common to every row of the warp [w_lo, w_hi];
       // touched by some row of the warp [v_lo, v_hi]  (lo and hi grow with the row)
-      const int c_lo = lo_q - k0, c_hi = hi_q - k0;
-      const int w_lo = lo_b - k0, w_hi = hi_a - k0;
-      const int v_lo = lo_a - k0, v_hi = hi_b - k0;
-      const int nvc = n_cols - k0;  // columns of this tile that are real keys
+      const int c_lo = (lst ? lo2_q : lo_q) - k0, c_hi = (lst ? hi2_q : hi_q) - k0;
+      const int w_lo = (lst ? lo2_b : lo_b) - k0, w_hi = (lst ? hi2_a : hi_a) - k0;
+      const int v_lo = (lst ? lo2_a : lo_a) - k0, v_hi = (lst ? hi2_b : hi_b) - k0;
+      const int nvc = (lst ? nv4 : n_cols) - k0;  // columns of this tile that are real keys
       // Chunk classes (warp-uniform): 2 = every (row, column) valid, 0 = none valid, 1 = mixed.
       // Mixed chunks use a per-row bit mask of valid columns.
       int cls[NC];
@@ -706,7 +737,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint32_t vm = __ldg(xm + (size_t)(x_pos[j] * NC + c) * 128);
           vmask[c] = vm;
           cls[c] = __all_sync(kFullMask, vm == 0xffffffffu) ? 2 : (__all_sync(kFullMask, vm == 0u) ? 0 : 1);
-        } else if (prm.mode == 0) {  // valid = inside the interval
+        } else if (tmode == 0) {  // valid = inside the interval
           cls[c] = (cb >= w_lo && cb + 31 <= w_hi) ? 2 : ((cb + 31 < v_lo || cb > v_hi) ? 0 : 1);
           vmask[c] = m_in;
         } else {              // valid = a real key outside the interval

@@ -256,6 +256,25 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
                                      int64_t row_begin, int64_t row_end,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- fused union of masks: Local + Global-no-local + an explicit CSR part ("BigBird") ------------------------
+ * No single counterpart in the reference, which composes this mask from three chained launches on one (m, l, O):
+ * spfa_local.forward, spfa_global_no_local.forward, spfa_csr.forward (verification/verify.py:337-352). This entry
+ * gives the same result -- the attention over
+ *     { |i-j| <= w }  +  { i or j in global_inds, |i-j| > w }  +  { (i, col_ind[row_off[i-row_begin] ...]) }
+ * with the caller keeping the CSR part disjoint from the other two, as the chained calls need it
+ * (verify.py:328) -- with one read of Q and one read-modify-write of (m, l, O) for the band and the global keys
+ * together instead of two: where the tiled kernel serves the shape (d in {32, 64, 128}, at most 1024 global tokens,
+ * w >= 32 or SPFA_PATH_TILED), every row that is not global gets its band tiles and the gathered global-key tiles in
+ * ONE kernel pass; the global rows (which attend to every key) run as a split strip; the CSR part follows on the
+ * gather path (or its dense-tile split). Other shapes run the three operators one after the other internally.
+ * row_off holds n_rows + 1 offsets into col_ind for the rows [row_begin, row_end); nnz = 0 leaves the CSR part out. */
+size_t spfa_bigbird_workspace_bytes(int64_t L, int64_t n_rows, int d, int64_t n_global, int64_t nnz);
+int spfa_bigbird_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                             const int32_t* global_inds, int64_t n_global,
+                             const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                             int64_t L, int d, int64_t local_size_each_dir, int64_t row_begin, int64_t row_end,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- 16-bit tensors: float16 / bfloat16 Q, K, V, m, l, O ------------------------------------------------------
  * The reference instantiates its kernels for Half too (AT_DISPATCH_FLOATING_TYPES_AND_HALF,
  * Sparse_FlashAttention_CSR/sp_flatt_csr_kernel.cu:270; all floating tensors of a call share one dtype). These entry

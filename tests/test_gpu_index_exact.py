@@ -136,6 +136,30 @@ def test_global_no_local_index_set_exact_on_the_tiled_path(capi, orc, L, d, w, n
         re - rb, L, d, what=f"gnl L={L} d={d} w={w} nG={nG} rows [{rb},{re})")
 
 
+@pytest.mark.parametrize("L,d,w,nG,rb,re", [(4096, 64, 50, 300, 0, None), (3000, 128, 33, 64, 0, None),
+                                             (8192, 32, 100, 1024, 1000, 7000), (65536, 64, 256, 64, 0, None)])
+def test_fused_band_and_global_keys_index_set_exact(capi, orc, L, d, w, nG, rb, re):
+    """The fused Local + Global-no-local pass (band tiles and gathered global-key tiles in one kernel, global rows as
+    a strip over all keys): the union of the two closed-form index sets, exactly."""
+    capi.set_path(capi.PATH_TILED)
+    re = L if re is None else re
+    G = np.random.default_rng(L + nG).choice(L, nG, replace=False).astype(np.int32)
+    off_a, col_a = orc.implicit_csr("local", L, w, row_begin=rb, row_end=re)
+    off_b, col_b = orc.implicit_csr("global_no_local", L, w, G=G, row_begin=rb, row_end=re)
+    # union of two disjoint index sets, row by row
+    na, nb = np.diff(off_a.astype(np.int64)), np.diff(off_b.astype(np.int64))
+    row_off = np.concatenate([[0], np.cumsum(na + nb)]).astype(np.int64)
+    col = np.empty(int(row_off[-1]), dtype=np.int64)
+    rows_a = np.repeat(np.arange(re - rb), na)
+    rows_b = np.repeat(np.arange(re - rb), nb)
+    col[row_off[rows_a] + (np.arange(col_a.size) - off_a.astype(np.int64)[rows_a])] = col_a
+    col[row_off[rows_b] + na[rows_b] + (np.arange(col_b.size) - off_b.astype(np.int64)[rows_b])] = col_b
+    Gd = dev(G)
+    assert_exact_index_set(
+        capi, lambda Q, K, V, m, l, O: capi.bigbird_forward(Q, K, V, m, l, O, Gd, w, None, None, rb, re), row_off, col,
+        re - rb, L, d, what=f"fused band + globals L={L} d={d} w={w} nG={nG} rows [{rb},{re})")
+
+
 @pytest.mark.parametrize("L,Lk,d,half,density,shuffle", [(1000, 1300, 64, 70, 0.004, True), (700, 700, 32, 40, 0.003, False),
                                                          (515, 2048, 128, 90, 0.002, True)])
 def test_explicit_dense_tiles_index_set_exact(capi, L, Lk, d, half, density, shuffle):

@@ -342,6 +342,53 @@ def test_chained_bigbird_equals_union(capi, orc):
         assert_state_close(to_np(st), want, tol, "chained bigbird")
 
 
+@pytest.mark.parametrize("L,d,w,nG,density,rb,re", [(1024, 64, 40, 5, 0.02, 0, None), (1500, 128, 70, 48, 0.01, 0, None),
+                                                     (900, 32, 33, 200, 0.0, 0, None), (2048, 64, 100, 64, 0.01, 300, 1700),
+                                                     (640, 16, 12, 4, 0.03, 0, None), (700, 64, 5, 9, 0.02, 0, None)])
+def test_fused_bigbird_equals_the_chained_calls_and_the_union_mask(capi, orc, pkg, L, d, w, nG, density, rb, re):
+    """One call for Local + Global-no-local + a disjoint CSR part: equal to the three chained calls of the reference's
+    composition (verification/verify.py:337-352) and to the fp64 oracle on the union mask. Shapes the tiled kernel
+    serves take the fused pass (band and global-key tiles in one kernel); d = 16 and narrow windows fall back to the
+    chained operators internally. Index-set exactness of the fused pass is checked with the exact-count inputs."""
+    re = L if re is None else re
+    Q, K, V = seeded_qkv(L, d, 505 + L)
+    rng = np.random.default_rng(L + nG)
+    G = rng.choice(L, nG, replace=False).astype(np.int32)
+    band = orc.dense_mask("local", L, w)
+    glob = orc.dense_mask("global_no_local", L, w, G=G)
+    rnd = (rng.random((L, L)) < density) & ~band & ~glob
+    union = band | glob | rnd
+    sub = rnd[rb:re]
+    row_off = np.concatenate([[0], np.cumsum(sub.sum(1))]).astype(np.int64)
+    col = np.nonzero(sub)[1].astype(np.int32)
+    want = orc.dense_forward(Q[rb:re], K, V, union[rb:re])
+    q, k, v, g = dev(Q[rb:re]), dev(K), dev(V), dev(G)
+    ro, co = (dev(row_off), dev(col)) if col.size else (None, None)
+    for path, tol in ((capi.PATH_GATHER, TOL_GATHER), (capi.PATH_AUTO, TOL_TILED), (capi.PATH_TILED, TOL_TILED)):
+        if path == capi.PATH_TILED and d == 16:
+            continue
+        capi.set_path(path)
+        st = capi.new_state(re - rb, d)
+        capi.bigbird_forward(q, k, v, *st, g, w, ro, co, rb, re)
+        fused_taken = capi.last_path() == capi.PATH_TILED
+        assert fused_taken == (path != capi.PATH_GATHER and d != 16 and (w >= 32 or path == capi.PATH_TILED))
+        assert_state_close(to_np(st), want, tol, f"bigbird path={path}")
+        ch = capi.new_state(re - rb, d)
+        capi.local_forward(q, k, v, *ch, w, rb, re)
+        capi.global_no_local_forward(q, k, v, *ch, g, w, rb, re)
+        if col.size:
+            capi.csr_forward(q, k, v, ro, co, *ch, use_nan=False)
+        assert (st[2] - ch[2]).abs().max().item() <= 2 * tol
+    capi.set_path(capi.PATH_AUTO)
+    if rb == 0 and re == L:  # the torch module
+        st = capi.new_state(L, d)
+        empty = torch.zeros(0, dtype=torch.int64, device="cuda")
+        out = pkg.binding("spfa_bigbird").forward(q, k, v, *st, g, w, ro.view(torch.uint64) if col.size else empty.view(torch.uint64),
+                                                  co.view(torch.uint32) if col.size else empty.to(torch.int32).view(torch.uint32))
+        assert out.data_ptr() == st[2].data_ptr()
+        assert_state_close(to_np(st), want, TOL_TILED, "spfa_bigbird.forward")
+
+
 def test_nan_rows_propagate_like_the_reference(capi):
     """A row NaN-filled by a use_nan call stays NaN when a later call adds keys to it (0*NaN in the
     reference's update, sp_flatt_csr_kernel.cu:191)."""
