@@ -8,6 +8,19 @@ torch::Tensor spfa_csr_cuda_forward(torch::Tensor Q, torch::Tensor K, torch::Ten
                                     torch::Tensor W_col_ind, torch::Tensor W_val, torch::Tensor m, torch::Tensor l,
                                     torch::Tensor O, bool use_nan) {
   using namespace spfa_binding;
+  if (const int64_t S = batched_slices(Q, K, V, m, l, O)) {  // [..., L, d]: the mask is inspected once for all slices
+    const int64_t n_rows = Q.size(-2), Lk = K.size(-2);
+    TORCH_CHECK(W_row_off.dim() == 1 && W_row_off.size(0) == n_rows + 1, "W_row_off must have L+1 entries");
+    TORCH_CHECK(W_col_ind.dim() == 1, "W_col_ind must be 1-D");
+    c10::cuda::CUDAGuard guard(Q.device());
+    Workspace ws(spfa_csr_workspace_bytes(n_rows, W_col_ind.size(0), Lk, (int)Q.size(-1)), Q.device());
+    raise_for_status(spfa_csr_forward_batched_f32(Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(),
+                                                  u64_ptr(W_row_off, "W_row_off"), u32_ptr(W_col_ind, "W_col_ind"),
+                                                  W_col_ind.size(0), m.data_ptr<float>(), l.data_ptr<float>(),
+                                                  O.data_ptr<float>(), S, n_rows, Lk, (int)Q.size(-1), use_nan ? 1 : 0, ws.ptr,
+                                                  ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (is_16bit(Q)) {  // native 16-bit gather: half the K/V bytes of the float32 call
     check_qkv_state_16(Q, K, V, m, l, O);
     TORCH_CHECK(W_val.scalar_type() == Q.scalar_type(), "expected W_val to share Q's dtype");

@@ -10,6 +10,18 @@ torch::Tensor spfa_global_no_local_cuda_forward(torch::Tensor Q, torch::Tensor K
                                                 torch::Tensor l, torch::Tensor O, torch::Tensor global_inds,
                                                 int local_size_each_dir) {
   using namespace spfa_binding;
+  if (const int64_t S = batched_slices(Q, K, V, m, l, O)) {
+    const int64_t L = Q.size(-2), nG = global_inds.size(0);
+    TORCH_CHECK(K.size(-2) == L, "implicit masks need K/V with as many rows as Q");
+    TORCH_CHECK(global_inds.dim() == 1 && global_inds.scalar_type() == torch::kInt32, "global_inds must be 1-D torch.int32");
+    c10::cuda::CUDAGuard guard(Q.device());
+    Workspace ws(spfa_global_no_local_workspace_bytes(L, L, (int)Q.size(-1), nG), Q.device());
+    raise_for_status(spfa_global_no_local_forward_batched_f32(
+        Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(), m.data_ptr<float>(), l.data_ptr<float>(),
+        O.data_ptr<float>(), S, nG > 0 ? global_inds.data_ptr<int32_t>() : nullptr, nG, L, (int)Q.size(-1),
+        local_size_each_dir, 0, L, ws.ptr, ws.bytes, at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   // 16-bit tensors: short lists of global tokens (where the float32 call keeps the ordinary rows on the gather path)
   if (is_16bit(Q) && (global_inds.size(0) < 32 || !tiled_d(Q.size(1)))) {
     check_qkv_state_16(Q, K, V, m, l, O);

@@ -10,6 +10,16 @@ torch::Tensor spfa_local_1d_dilated_cuda_forward(torch::Tensor Q, torch::Tensor 
                                                  torch::Tensor l, torch::Tensor O, int local_size_each_dir,
                                                  int dil_factor) {
   using namespace spfa_binding;
+  if (const int64_t S = batched_slices(Q, K, V, m, l, O)) {  // [..., L, d]: every slice in one launch per residue class
+    const int64_t L = Q.size(-2);
+    TORCH_CHECK(K.size(-2) == L, "implicit masks need K/V with as many rows as Q");
+    c10::cuda::CUDAGuard guard(Q.device());
+    raise_for_status(spfa_local_1d_dilated_forward_batched_f32(
+        Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(), m.data_ptr<float>(), l.data_ptr<float>(),
+        O.data_ptr<float>(), S, L, (int)Q.size(-1), local_size_each_dir, dil_factor, 0, L, nullptr, 0,
+        at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   // 16-bit tensors: narrow windows (where the float32 call takes the gather path too) run natively in 16 bits
   if (is_16bit(Q) && (local_size_each_dir < 32 || dil_factor >= 16 || !tiled_d(Q.size(1)))) {
     check_qkv_state_16(Q, K, V, m, l, O);

@@ -10,6 +10,16 @@ torch::Tensor spfa_local_2d_dilated_cuda_forward(torch::Tensor Q, torch::Tensor 
                                                  torch::Tensor l, torch::Tensor O, int block_size, int dil_factor,
                                                  bool use_nan) {
   using namespace spfa_binding;
+  if (const int64_t S = batched_slices(Q, K, V, m, l, O)) {
+    const int64_t L = Q.size(-2);
+    TORCH_CHECK(K.size(-2) == L, "implicit masks need K/V with as many rows as Q");
+    c10::cuda::CUDAGuard guard(Q.device());
+    raise_for_status(spfa_local_2d_dilated_forward_batched_f32(
+        Q.data_ptr<float>(), K.data_ptr<float>(), V.data_ptr<float>(), m.data_ptr<float>(), l.data_ptr<float>(),
+        O.data_ptr<float>(), S, L, (int)Q.size(-1), block_size, dil_factor, use_nan ? 1 : 0, 0, L, nullptr, 0,
+        at::cuda::getCurrentCUDAStream().stream()));
+    return O;
+  }
   if (is_16bit(Q)) {  // native 16-bit gather (a live row has at most block_size keys)
     check_qkv_state_16(Q, K, V, m, l, O);
     TORCH_CHECK(K.size(0) == Q.size(0), "implicit masks need K/V with as many rows as Q");

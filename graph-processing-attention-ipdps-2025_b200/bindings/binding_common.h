@@ -171,6 +171,35 @@ inline torch::Tensor planned_forward(torch::Tensor Q, torch::Tensor K, torch::Te
   return O;
 }
 
+// ---- batches (additive): Q, K, V, O with leading batch / head dimensions [..., L, d] and m, l [..., L] ----------------
+// The reference is single-head, single-batch (README.md:10) and takes 2-D tensors only. Tensors with more dimensions are
+// treated as that many independent problems sharing the mask; the leading dimensions must agree on all six tensors.
+// Returns the number of slices (product of the leading dimensions), or 0 for plain 2-D tensors.
+inline int64_t batched_slices(const torch::Tensor& Q, const torch::Tensor& K, const torch::Tensor& V,
+                              const torch::Tensor& m, const torch::Tensor& l, const torch::Tensor& O) {
+  if (Q.dim() <= 2) return 0;
+  TORCH_CHECK(Q.scalar_type() == torch::kFloat32, "batched calls take float32 tensors");
+  for (const torch::Tensor* t : {&K, &V, &m, &l, &O}) {
+    TORCH_CHECK(t->scalar_type() == Q.scalar_type(), "expected all floating tensors to share Q's dtype");
+    TORCH_CHECK(t->device() == Q.device(), "expected all tensors on Q's device");
+  }
+  const int64_t nd = Q.dim();
+  TORCH_CHECK(K.dim() == nd && V.dim() == nd && O.dim() == nd && m.dim() == nd - 1 && l.dim() == nd - 1,
+              "batched Q, K, V, O must be [..., L, d] and m, l [..., L] with the same leading dimensions");
+  int64_t S = 1;
+  for (int64_t i = 0; i < nd - 2; ++i) {
+    TORCH_CHECK(K.size(i) == Q.size(i) && V.size(i) == Q.size(i) && O.size(i) == Q.size(i) && m.size(i) == Q.size(i) &&
+                    l.size(i) == Q.size(i), "leading (batch / head) dimensions differ");
+    S *= Q.size(i);
+  }
+  const int64_t L = Q.size(nd - 2), d = Q.size(nd - 1);
+  TORCH_CHECK(K.size(nd - 1) == d && V.size(nd - 1) == d && O.size(nd - 1) == d, "K, V, O must have Q's embedded dimension");
+  TORCH_CHECK(K.size(nd - 2) == V.size(nd - 2), "K and V must have the same number of rows");
+  TORCH_CHECK(O.size(nd - 2) == L && m.size(nd - 2) == L && l.size(nd - 2) == L, "O, m, l must have Q's number of rows");
+  TORCH_CHECK(S >= 1, "empty batch");
+  return S;
+}
+
 // ---- dense mask -> index tensors (additive: replaces to_sparse_csr()/to_sparse_coo() + casts in caller code) ----
 // mask: [n_rows, n_cols] torch.bool or torch.uint8 on the GPU. Returns (row offsets uint64[n_rows+1], columns uint32[nnz])
 // or, for COO, (row indices uint64[nnz], columns uint32[nnz]); columns ascend within a row.

@@ -35,6 +35,8 @@ EXPORTS = (
     "spfa_global_no_local_workspace_bytes", "spfa_global_no_local_forward_f32",
     "spfa_mask_count", "spfa_mask_fill",
     "spfa_dense_mask_offsets", "spfa_dense_mask_fill", "spfa_bigbird_workspace_bytes", "spfa_bigbird_forward_f32",
+    "spfa_local_forward_batched_f32", "spfa_local_1d_dilated_forward_batched_f32", "spfa_local_2d_dilated_forward_batched_f32",
+    "spfa_global_no_local_forward_batched_f32", "spfa_csr_forward_batched_f32", "spfa_coo_forward_batched_f32",
     "spfa_csr_forward_16", "spfa_coo_forward_16", "spfa_local_forward_16", "spfa_local_1d_dilated_forward_16",
     "spfa_local_2d_dilated_forward_16", "spfa_global_no_local_workspace_bytes_16", "spfa_global_no_local_forward_16",
     "spfa_csr_workspace_bytes_idx32", "spfa_csr_forward_f32_idx32", "spfa_coo_forward_f32_idx32", "spfa_coo_plan_build_idx32",
@@ -100,6 +102,18 @@ def lib() -> ctypes.CDLL:
     L.spfa_global_no_local_workspace_bytes_16.argtypes = [i64, i64]
     L.spfa_global_no_local_forward_16.restype = i32
     L.spfa_global_no_local_forward_16.argtypes = [i32] + [vp] * 7 + [i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_local_forward_batched_f32.restype = i32
+    L.spfa_local_forward_batched_f32.argtypes = [vp] * 6 + [i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_local_1d_dilated_forward_batched_f32.restype = i32
+    L.spfa_local_1d_dilated_forward_batched_f32.argtypes = [vp] * 6 + [i64, i64, i32, i64, i64, i64, i64, vp, sz, vp]
+    L.spfa_local_2d_dilated_forward_batched_f32.restype = i32
+    L.spfa_local_2d_dilated_forward_batched_f32.argtypes = [vp] * 6 + [i64, i64, i32, i64, i64, i32, i64, i64, vp, sz, vp]
+    L.spfa_global_no_local_forward_batched_f32.restype = i32
+    L.spfa_global_no_local_forward_batched_f32.argtypes = [vp] * 6 + [i64, vp, i64, i64, i32, i64, i64, i64, vp, sz, vp]
+    L.spfa_csr_forward_batched_f32.restype = i32
+    L.spfa_csr_forward_batched_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp, sz, vp]
+    L.spfa_coo_forward_batched_f32.restype = i32
+    L.spfa_coo_forward_batched_f32.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i64, i32, i32, vp, sz, vp]
     L.spfa_bigbird_workspace_bytes.restype = sz
     L.spfa_bigbird_workspace_bytes.argtypes = [i64, i64, i32, i64, i64]
     L.spfa_bigbird_forward_f32.restype = i32
@@ -365,6 +379,52 @@ def bigbird_forward(Q, K, V, m, l, O, global_inds, local_size_each_dir, row_off=
                                              _ptr(global_inds) if nG else None, nG,
                                              _ptr(_as_u64(row_off)) if nnz else None, _ptr(_as_u32(col_ind)) if nnz else None,
                                              nnz, L, d, int(local_size_each_dir), row_begin, row_end, wp, wb, _stream(dev)))
+    return O
+
+
+def forward_batched(kind, Q, K, V, m, l, O, *, p0=0, p1=0, global_inds=None, row_off=None, row_ind=None, col_ind=None,
+                    use_nan=False, row_begin=0, row_end=None):
+    """n_slices attention problems sharing one mask (batch x heads): Q, O [S, rows, d], K, V [S, Lk, d], m, l [S, rows]
+    (float32, contiguous). Local and Local-1D-dilated run all slices in one launch; explicit masks are inspected once."""
+    dev = _f32(Q, K, V, m, l, O)
+    if Q.dim() != 3 or K.dim() != 3 or m.dim() != 2:
+        raise SpfaError(-1, "batched tensors are [slices, rows, d] (m, l: [slices, rows])")
+    S, n_rows, d = Q.shape
+    Lk = K.shape[1]
+    with torch.cuda.device(dev):
+        st = _stream(dev)
+        q, k, v, mm, ll, oo = (_ptr(t) for t in (Q, K, V, m, l, O))
+        if kind == "csr":
+            nnz = col_ind.shape[0]
+            buf, wp, wb = workspace(lib().spfa_csr_workspace_bytes(n_rows, nnz, Lk, d), dev)
+            rc = lib().spfa_csr_forward_batched_f32(q, k, v, _ptr(_as_u64(row_off)), _ptr(_as_u32(col_ind)), nnz, mm, ll, oo, S,
+                                                    n_rows, Lk, d, int(use_nan), wp, wb, st)
+        elif kind == "coo":
+            nnz = col_ind.shape[0]
+            buf, wp, wb = workspace(lib().spfa_coo_workspace_bytes(n_rows, nnz, Lk, d), dev)
+            rc = lib().spfa_coo_forward_batched_f32(q, k, v, _ptr(_as_u64(row_ind)), _ptr(_as_u32(col_ind)), nnz, mm, ll, oo, S,
+                                                    row_begin, n_rows, Lk, d, int(use_nan), wp, wb, st)
+        else:
+            L = Lk
+            row_end = L if row_end is None else row_end
+            if n_rows != row_end - row_begin:
+                raise SpfaError(-1, "Q must hold rows [row_begin, row_end) of every slice")
+            if kind == "local":
+                rc = lib().spfa_local_forward_batched_f32(q, k, v, mm, ll, oo, S, L, d, int(p0), row_begin, row_end, None, 0, st)
+            elif kind == "local_1d_dilated":
+                rc = lib().spfa_local_1d_dilated_forward_batched_f32(q, k, v, mm, ll, oo, S, L, d, int(p0), int(p1), row_begin,
+                                                                     row_end, None, 0, st)
+            elif kind == "local_2d_dilated":
+                rc = lib().spfa_local_2d_dilated_forward_batched_f32(q, k, v, mm, ll, oo, S, L, d, int(p0), int(p1),
+                                                                     int(use_nan), row_begin, row_end, None, 0, st)
+            elif kind == "global_no_local":
+                nG = global_inds.shape[0]
+                buf, wp, wb = workspace(lib().spfa_global_no_local_workspace_bytes(L, n_rows, d, nG), dev)
+                rc = lib().spfa_global_no_local_forward_batched_f32(q, k, v, mm, ll, oo, S, _ptr(global_inds), nG, L, d,
+                                                                    int(p0), row_begin, row_end, wp, wb, st)
+            else:
+                raise ValueError(kind)
+        check(rc)
     return O
 
 

@@ -321,14 +321,18 @@ __device__ __forceinline__ void gather_rows_cta(int64_t block, const float* __re
   }
 }
 
+// Slices of a batched call (batch x heads, one mask for all) ride on blockIdx.y: Q, O advance by n_rows * D elements
+// per slice, m, l by n_rows, K, V by kv_slice elements (0 for an unbatched call, whose grid has y = 1).
 template <int D, class Cols>
 __global__ void __launch_bounds__(kRowWarps * 32, 7)
 gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                    float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
-                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale) {
+                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale, int64_t kv_slice) {
   __shared__ RowCtaShared sh;
   __shared__ float4 s_acc[kRowWarps][D / 4];
-  gather_rows_cta<D, Cols>(blockIdx.x, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, sh, s_acc);
+  const size_t z = blockIdx.y;
+  gather_rows_cta<D, Cols>(blockIdx.x, Q + z * n_rows * D, K + z * kv_slice, V + z * kv_slice, m + z * n_rows, l + z * n_rows,
+                           O + z * n_rows * D, cols, row_begin, n_rows, use_nan, scale, sh, s_acc);
 }
 
 // Same, for a shard whose long rows were listed beforehand (the explicit-mask plan lists the rows whose residual

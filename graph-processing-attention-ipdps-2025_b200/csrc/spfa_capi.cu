@@ -25,13 +25,14 @@ inline bool supported_d(int d) { return d >= 1 && d <= kGenericMaxD; }
 
 template <int D, class Cols>
 int launch_gather(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
-                  const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
+                  const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st, int64_t n_slices = 1,
+                  int64_t kv_slice = 0) {
   if (n_rows <= 0) return SPFA_OK;
   const int64_t blocks = (n_rows + kRowWarps - 1) / kRowWarps;
-  if (blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+  if (blocks > 0x7fffffffLL || n_slices > 65535) return SPFA_ERR_TOO_LARGE;
   const float scale = 1.0f / sqrtf((float)D);
-  gather_rows_kernel<D, Cols><<<(unsigned)blocks, kRowWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, row_begin,
-                                                                             n_rows, use_nan, scale);
+  gather_rows_kernel<D, Cols><<<dim3((unsigned)blocks, (unsigned)n_slices), kRowWarps * 32, 0, st>>>(
+      Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, kv_slice);
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_GATHER);
   return launch_status();
@@ -63,16 +64,23 @@ int dispatch_gather_generic(int d, const float* Q, const float* K, const float* 
                   : launch_gather_generic<1, 32, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, d, st);
 }
 
+// n_slices > 1 (batched calls): one launch for all slices where a specialised kernel exists, else one per slice.
 template <class Cols>
 int dispatch_gather(int d, const float* Q, const float* K, const float* V, float* m, float* l, float* O,
-                    const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st) {
+                    const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st, int64_t n_slices = 1,
+                    int64_t kv_slice = 0) {
   switch (d) {
-    case 16: return launch_gather<16, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
-    case 32: return launch_gather<32, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
-    case 64: return launch_gather<64, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
-    case 128: return launch_gather<128, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+    case 16: return launch_gather<16, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st, n_slices, kv_slice);
+    case 32: return launch_gather<32, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st, n_slices, kv_slice);
+    case 64: return launch_gather<64, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st, n_slices, kv_slice);
+    case 128: return launch_gather<128, Cols>(Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st, n_slices, kv_slice);
   }
-  return dispatch_gather_generic(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st);
+  for (int64_t z = 0; z < n_slices; ++z) {
+    const int rc = dispatch_gather_generic(d, Q + z * n_rows * d, K + z * kv_slice, V + z * kv_slice, m + z * n_rows,
+                                           l + z * n_rows, O + z * n_rows * d, cols, row_begin, n_rows, use_nan, st);
+    if (rc) return rc;
+  }
+  return SPFA_OK;
 }
 
 inline int check_common(const void* Q, const void* K, const void* V, const void* m, const void* l, const void* O,
@@ -683,23 +691,30 @@ int spfa_coo_forward_f32_static(const float* Q, const float* K, const float* V, 
 size_t spfa_local_workspace_bytes(int64_t, int64_t, int) { return 0; }
 
 int spfa_local_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L,
-                           int d, int64_t w, int64_t row_begin, int64_t row_end, void*, size_t, void* stream) {
+                           int d, int64_t w, int64_t row_begin, int64_t row_end, void* ws, size_t ws_bytes, void* stream) {
+  return spfa_local_forward_batched_f32(Q, K, V, m, l, O, 1, L, d, w, row_begin, row_end, ws, ws_bytes, stream);
+}
+
+int spfa_local_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                   int64_t n_slices, int64_t L, int d, int64_t w, int64_t row_begin, int64_t row_end, void*,
+                                   size_t, void* stream) {
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
   rc = check_rows(L, row_begin, row_end);
   if (rc) return rc;
+  if (n_slices < 1) return SPFA_ERR_BAD_ARG;
   if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   const int path = g_path.load();
   if (path != SPFA_PATH_GATHER) {
-    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, /*stride=*/1, row_begin, row_end, path == SPFA_PATH_TILED, st);
+    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, /*stride=*/1, row_begin, row_end, path == SPFA_PATH_TILED, st, n_slices);
     if (rc != SPFA_TILE_NOT_TAKEN) {
       if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
       return rc;
     }
   }
   LocalCols cols{L, w};
-  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st, n_slices, L * d);
 }
 
 // ---- Local 1D dilated ------------------------------------------------------------------------------
@@ -707,25 +722,32 @@ size_t spfa_local_1d_dilated_workspace_bytes(int64_t, int64_t, int) { return 0; 
 
 int spfa_local_1d_dilated_forward_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
                                       int64_t L, int d, int64_t w, int64_t dil, int64_t row_begin, int64_t row_end,
-                                      void*, size_t, void* stream) {
+                                      void* ws, size_t ws_bytes, void* stream) {
+  return spfa_local_1d_dilated_forward_batched_f32(Q, K, V, m, l, O, 1, L, d, w, dil, row_begin, row_end, ws, ws_bytes, stream);
+}
+
+int spfa_local_1d_dilated_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                              int64_t n_slices, int64_t L, int d, int64_t w, int64_t dil, int64_t row_begin,
+                                              int64_t row_end, void*, size_t, void* stream) {
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
   rc = check_rows(L, row_begin, row_end);
   if (rc) return rc;
+  if (n_slices < 1) return SPFA_ERR_BAD_ARG;
   if (w < 0 || w > L - 1) return SPFA_ERR_LOCAL_SIZE;
   if (dil < 0) return SPFA_ERR_DILATION_NEG;
   if (dil >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const int path = g_path.load();
   if (path != SPFA_PATH_GATHER) {
-    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, dil + 1, row_begin, row_end, path == SPFA_PATH_TILED, st);
+    rc = tiled_band_forward(Q, K, V, m, l, O, L, d, w, dil + 1, row_begin, row_end, path == SPFA_PATH_TILED, st, n_slices);
     if (rc != SPFA_TILE_NOT_TAKEN) {
       if (rc == SPFA_OK) g_last_path.store(SPFA_PATH_TILED);
       return rc;
     }
   }
   Local1dCols cols{L, w, dil + 1};
-  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st);
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, row_end - row_begin, 0, st, n_slices, L * d);
 }
 
 // ---- Local 2D dilated ------------------------------------------------------------------------------
@@ -841,6 +863,91 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
     case 128: return launch_gnl_global_rows<128>(Q, K, V, m, l, O, G, nG, L, w, row_begin, row_end, plan, live, partials, st);
   }
   return SPFA_ERR_EMBED_DIM;
+}
+
+// ---- batches of slices (batch x heads sharing one mask) for the operators without a slice dimension in their kernels:
+//      one call per slice on the stream; scratch is reused in stream order ------------------------------------------
+int spfa_local_2d_dilated_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                              int64_t n_slices, int64_t L, int d, int64_t B, int64_t dil, int use_nan,
+                                              int64_t row_begin, int64_t row_end, void* ws, size_t ws_bytes, void* stream) {
+  if (n_slices < 1 || row_end < row_begin) return SPFA_ERR_BAD_ARG;
+  const int64_t n = row_end - row_begin;
+  for (int64_t z = 0; z < n_slices; ++z) {
+    const int rc = spfa_local_2d_dilated_forward_f32(Q + z * n * d, K + z * L * d, V + z * L * d, m + z * n, l + z * n,
+                                                     O + z * n * d, L, d, B, dil, use_nan, row_begin, row_end, ws, ws_bytes,
+                                                     stream);
+    if (rc) return rc;
+  }
+  return SPFA_OK;
+}
+
+int spfa_global_no_local_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                             int64_t n_slices, const int32_t* G, int64_t nG, int64_t L, int d, int64_t w,
+                                             int64_t row_begin, int64_t row_end, void* ws, size_t ws_bytes, void* stream) {
+  if (n_slices < 1 || row_end < row_begin) return SPFA_ERR_BAD_ARG;
+  const int64_t n = row_end - row_begin;
+  for (int64_t z = 0; z < n_slices; ++z) {
+    const int rc = spfa_global_no_local_forward_f32(Q + z * n * d, K + z * L * d, V + z * L * d, m + z * n, l + z * n,
+                                                    O + z * n * d, G, nG, L, d, w, row_begin, row_end, ws, ws_bytes, stream);
+    if (rc) return rc;
+  }
+  return SPFA_OK;
+}
+
+// Explicit masks: the mask is inspected ONCE (row pointers, dense-tile plan), every slice runs from the result.
+static int explicit_batched(const float* Q, const float* K, const float* V, const uint64_t* row_off, const uint32_t* col_ind,
+                            int64_t nnz, float* m, float* l, float* O, int64_t n_slices, int64_t row_begin, int64_t n_rows,
+                            int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  const int hy = hybrid_decision(d, n_rows, nnz, Lk, workspace, workspace_bytes);
+  if (hy < 0) return hy;
+  if (hy == 1) {
+    char* ws = static_cast<char*>(workspace);
+    int rc = build_plan(d, row_off, col_ind, n_rows, nnz, Lk, ws, 0, nullptr, st);
+    for (int64_t z = 0; z < n_slices && rc == SPFA_OK; ++z) {
+      float* Oz = O + z * n_rows * d;
+      if (use_nan) {
+        nan_fill_empty_rows_kernel<<<(unsigned)((n_rows + 7) / 8), 256, 0, st>>>(row_off, Oz, n_rows, d);
+        g_launches.fetch_add(1);
+      }
+      rc = forward_from_plan(d, Q + z * n_rows * d, K + z * Lk * d, V + z * Lk * d, row_off, m + z * n_rows, l + z * n_rows, Oz,
+                             n_rows, nnz, Lk, ws, st);
+    }
+    return rc;
+  }
+  CsrCols cols{row_off, col_ind, Lk};
+  return dispatch_gather(d, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, st, n_slices, Lk * d);
+}
+
+int spfa_csr_forward_batched_f32(const float* Q, const float* K, const float* V, const uint64_t* row_off,
+                                 const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t n_slices,
+                                 int64_t n_rows, int64_t Lk, int d, int use_nan, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (!row_off || n_rows < 0 || nnz < 0 || n_slices < 1 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0) return SPFA_OK;
+  if (!col_ind) return SPFA_ERR_BAD_ARG;
+  return explicit_batched(Q, K, V, row_off, col_ind, nnz, m, l, O, n_slices, 0, n_rows, Lk, d, use_nan, workspace,
+                          workspace_bytes, (cudaStream_t)stream);
+}
+
+int spfa_coo_forward_batched_f32(const float* Q, const float* K, const float* V, const uint64_t* row_ind,
+                                 const uint32_t* col_ind, int64_t nnz, float* m, float* l, float* O, int64_t n_slices,
+                                 int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  int rc = check_common(Q, K, V, m, l, O, d);
+  if (rc) return rc;
+  if (nnz < 0 || n_rows < 0 || row_begin < 0 || n_slices < 1 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
+  if (nnz > 0 && (!row_ind || !col_ind)) return SPFA_ERR_BAD_ARG;
+  if (n_rows == 0) return SPFA_OK;
+  const size_t ptr_bytes = spfa_coo_min_workspace_bytes(n_rows);
+  rc = check_workspace(workspace, workspace_bytes, ptr_bytes);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
+  if (launch_row_pointers<uint64_t>(row_ind, nnz, row_begin, n_rows, ptr, st) != SPFA_OK) return SPFA_ERR_LAUNCH;
+  return explicit_batched(Q, K, V, ptr, col_ind, nnz, m, l, O, n_slices, row_begin, n_rows, Lk, d, use_nan,
+                          static_cast<char*>(workspace) + ptr_bytes, workspace_bytes - ptr_bytes, st);
 }
 
 // ---- fused union of masks: Local + Global-no-local + an explicit CSR part -----------------------------------

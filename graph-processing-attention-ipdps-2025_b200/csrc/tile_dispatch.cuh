@@ -77,15 +77,20 @@ inline TensorMapEncodeTiledFn tensor_map_encoder() {
 // [rows, d] fp32 matrix with a row pitch of `pitch_bytes`, fetched as boxes of box_rows x 32 floats with the
 // 128-byte swizzle the MMA descriptors expect (16-byte units for K-major operands, 32-byte units for the
 // MN-major V operand). Rows outside [0, rows) read as zeros.
+// `slices` such matrices lie `slice_bytes` apart (a batch of heads); the third coordinate of a load picks one.
 inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows, int64_t pitch_bytes, int box_rows,
-                         bool mn_major = false) {
+                         bool mn_major = false, int64_t slices = 1, int64_t slice_bytes = 0) {
   TensorMapEncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch_bytes};
-  cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1u, 1u};
-  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+  if (slices <= 1 || slice_bytes <= 0) {
+    slices = 1;
+    slice_bytes = (rows > 0 ? rows : 1) * pitch_bytes;  // never used to address anything: z is 0
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)slices};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch_bytes, (cuuint64_t)slice_bytes};
+  cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -151,9 +156,11 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
 }
 
+// n_slices > 1: Q, O are [n_slices, rows of the shard, d], K, V [n_slices, L, d], m, l [n_slices, rows]: one launch
+// per residue class covers every slice (grid.z).
 template <int D>
 int launch_band(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L, int64_t w,
-                int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st) {
+                int64_t s, int64_t row_begin, int64_t row_end, cudaStream_t st, int64_t n_slices = 1) {
   using C = TileCfg<D>;
   constexpr int BN = C::BN;
   bool launched = false;  // residue classes write disjoint rows: consecutive launches may overlap
@@ -171,15 +178,19 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
     prm.r = r;
     prm.row_begin = row_begin;
     prm.scale_log2e = (1.0f / sqrtf((float)D)) * kLog2e;
+    prm.slice_o = (row_end - row_begin) * D;
+    prm.slice_ml = row_end - row_begin;
     CUtensorMap tmQ, tmK, tmV;
     const int64_t pitch = s * D * (int64_t)sizeof(float);
-    if (!make_row_map(&tmQ, Q + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128) ||
-        !make_row_map(&tmK, K + r * D, D, prm.n_keys, pitch, BN) || !make_row_map(&tmV, V + r * D, D, prm.n_keys, pitch, BN, /*mn_major=*/true))
+    const int64_t q_slice = (row_end - row_begin) * D * (int64_t)sizeof(float), kv_slice = L * D * (int64_t)sizeof(float);
+    if (!make_row_map(&tmQ, Q + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128, false, n_slices, q_slice) ||
+        !make_row_map(&tmK, K + r * D, D, prm.n_keys, pitch, BN, false, n_slices, kv_slice) ||
+        !make_row_map(&tmV, V + r * D, D, prm.n_keys, pitch, BN, /*mn_major=*/true, n_slices, kv_slice))
       return SPFA_ERR_LAUNCH;
     const int64_t grid = (prm.n_q + C::kRows - 1) / C::kRows;
-    if (grid > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
+    if (grid > 0x7fffffffLL || n_slices > 65535) return SPFA_ERR_TOO_LARGE;
     prm.overlap = ((r + 1 < s && r + 1 < L) ? 1 : 0) | (launched ? 2 : 0);
-    const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid), st);
+    const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid, 1, (unsigned)n_slices), st);
     if (rc) return rc;
     launched = true;
   }
@@ -189,7 +200,7 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
 // Band |u_q - u_k| <= w on every residue class of stride s (s = 1: Local; s = dil+1: Local-1D-dilated).
 inline int tiled_band_forward(const float* Q, const float* K, const float* V, float* m, float* l, float* O, int64_t L,
                               int d, int64_t w, int64_t s, int64_t row_begin, int64_t row_end, bool forced,
-                              cudaStream_t st) {
+                              cudaStream_t st, int64_t n_slices = 1) {
   const bool shape_ok = (d == 32 || d == 64 || d == 128) && s >= 1 && s <= kTileMaxStride && row_end > row_begin;
   if (!shape_ok) return forced ? (int)SPFA_ERR_BAD_ARG : SPFA_TILE_NOT_TAKEN;
   if (!forced && w < kTileMinHalfWidth) return SPFA_TILE_NOT_TAKEN;
@@ -197,9 +208,9 @@ inline int tiled_band_forward(const float* Q, const float* K, const float* V, fl
                               : (d == 64 ? band_kernel_usable<64, false>() : band_kernel_usable<128, false>());
   if (!usable) return forced ? (int)SPFA_ERR_REGISTER_BUDGET : SPFA_TILE_NOT_TAKEN;
   switch (d) {
-    case 32: return launch_band<32>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 64: return launch_band<64>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
-    case 128: return launch_band<128>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st);
+    case 32: return launch_band<32>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st, n_slices);
+    case 64: return launch_band<64>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st, n_slices);
+    case 128: return launch_band<128>(Q, K, V, m, l, O, L, w, s, row_begin, row_end, st, n_slices);
   }
   return SPFA_TILE_NOT_TAKEN;
 }

@@ -100,6 +100,9 @@ struct BandParams {
   // started (griddepcontrol.launch_dependents); bit 1: this launch was started that way, so it must not
   // complete before its predecessor has (griddepcontrol.wait before the CTA exits). ----
   int overlap;
+  // ---- batches of slices (batch x heads): blockIdx.z selects the slice; Q, K, V come through the third coordinate of
+  // the tensor maps, (m, l, O) are offset by these strides (in elements) ----
+  int64_t slice_o, slice_ml;
   const int* x_nt;
   const int* x_kt;
   const long long* x_moff;
@@ -161,10 +164,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int32_t x, int32_t y, uint32_t bar) {
+// Tensor maps are rank 3: (element within a row, row, slice). A slice is one [rows, d] matrix of a batch of them
+// (batch x heads); unbatched calls have one slice and z = 0.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int32_t x, int32_t y, int32_t z,
+                                            uint32_t bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 
@@ -301,8 +307,12 @@ template <int D, int BN, int NS, int NSUB, bool EXPL = false, int NSV = NS>
 __global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmK2,
-                    const __grid_constant__ CUtensorMap tmV2, float* __restrict__ m_out, float* __restrict__ l_out,
-                    float* __restrict__ O_out, const BandParams prm, int* __restrict__ err) {
+                    const __grid_constant__ CUtensorMap tmV2, float* __restrict__ m_base, float* __restrict__ l_base,
+                    float* __restrict__ O_base, const BandParams prm, int* __restrict__ err) {
+  const int32_t zs = (int32_t)blockIdx.z;  // slice of a batched call
+  float* __restrict__ m_out = m_base + (size_t)zs * prm.slice_ml;
+  float* __restrict__ l_out = l_base + (size_t)zs * prm.slice_ml;
+  float* __restrict__ O_out = O_base + (size_t)zs * prm.slice_o;
   using P = Plan<D, BN, NS, NSUB, NSV>;
   using G = Geo<NSUB>;
   constexpr int kQRows = G::kQRows;
@@ -503,7 +513,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int x = 0; x < NSUB; ++x)
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
-          tma_load_2d(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes, &tmQ, c * 32, yq + 128 * x,
+          tma_load_3d(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes, &tmQ, c * 32, yq + 128 * x, zs,
                       bar(B_QFULL));
       // K runs NS tiles ahead of V (the S MMAs are issued ahead of the softmax, the PV MMAs behind it), so the
       // order is K(0..NS-1), then V(j), K(j+NS) for every tile j: a wait for a V stage never holds back a K tile
@@ -516,8 +526,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
-          tma_load_2d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmK : &tmK2, c * 32, yk,
-                      bar(B_KFULL + st));
+          tma_load_3d(sbase + P::kOffK + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmK : &tmK2, c * 32, yk,
+                      zs, bar(B_KFULL + st));
         return true;
       };
       for (int j = 0; j < NS && j < nT && ok; ++j) ok = load_k(j);
@@ -529,8 +539,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int32_t yk = tile_key0(j);
 #pragma unroll
         for (int c = 0; c < P::kChunks; ++c)
-          tma_load_2d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmV : &tmV2, c * 32, yk,
-                      bar(B_VFULL + st));
+          tma_load_3d(sbase + P::kOffV + st * P::kKVStageBytes + c * P::kKVChunkBytes, (j < nTb) ? &tmV : &tmV2, c * 32, yk,
+                      zs, bar(B_VFULL + st));
         if (j + NS < nT) ok = load_k(j + NS);
       }
     }

@@ -256,6 +256,41 @@ int spfa_global_no_local_forward_f32(const float* Q, const float* K, const float
                                      int64_t row_begin, int64_t row_end,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- batches of slices: batch x heads sharing one mask ------------------------------------------------------
+ * No counterpart in the reference, which is "limited to ... single-headed, single-batched attention" (README.md:10).
+ * n_slices independent attention problems share the mask and its parameters: Q, O are [n_slices, rows, d], K, V
+ * [n_slices, Lk, d], m, l [n_slices, rows], contiguous (a [batch, heads, L, d] tensor viewed as [batch*heads, L, d]).
+ * Local and Local-1D-dilated run every slice in ONE launch (the slice is a grid dimension of the tiled and of the
+ * gather kernel: many short sequences fill the GPU that one of them would leave idle); CSR / COO inspect the mask
+ * once (row pointers, dense-tile plan) and run every slice from the result, or take all slices in one gather launch;
+ * Local-2D-dilated and Global-no-local run one call per slice on the stream. Other arguments, workspace sizes (of
+ * ONE slice: scratch is reused in stream order) and results are those of the single-slice entry points. */
+int spfa_local_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                   int64_t n_slices, int64_t L, int d, int64_t local_size_each_dir,
+                                   int64_t row_begin, int64_t row_end, void* workspace, size_t workspace_bytes, void* stream);
+int spfa_local_1d_dilated_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                              int64_t n_slices, int64_t L, int d, int64_t local_size_each_dir,
+                                              int64_t dil_factor, int64_t row_begin, int64_t row_end,
+                                              void* workspace, size_t workspace_bytes, void* stream);
+int spfa_local_2d_dilated_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                              int64_t n_slices, int64_t L, int d, int64_t block_size, int64_t dil_factor,
+                                              int use_nan, int64_t row_begin, int64_t row_end,
+                                              void* workspace, size_t workspace_bytes, void* stream);
+int spfa_global_no_local_forward_batched_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                             int64_t n_slices, const int32_t* global_inds, int64_t n_global, int64_t L,
+                                             int d, int64_t local_size_each_dir, int64_t row_begin, int64_t row_end,
+                                             void* workspace, size_t workspace_bytes, void* stream);
+int spfa_csr_forward_batched_f32(const float* Q, const float* K, const float* V,
+                                 const uint64_t* row_off, const uint32_t* col_ind, int64_t nnz,
+                                 float* m, float* l, float* O, int64_t n_slices,
+                                 int64_t n_rows, int64_t Lk, int d, int use_nan,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+int spfa_coo_forward_batched_f32(const float* Q, const float* K, const float* V,
+                                 const uint64_t* row_ind, const uint32_t* col_ind, int64_t nnz,
+                                 float* m, float* l, float* O, int64_t n_slices,
+                                 int64_t row_begin, int64_t n_rows, int64_t Lk, int d, int use_nan,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- fused union of masks: Local + Global-no-local + an explicit CSR part ("BigBird") ------------------------
  * No single counterpart in the reference, which composes this mask from three chained launches on one (m, l, O):
  * spfa_local.forward, spfa_global_no_local.forward, spfa_csr.forward (verification/verify.py:337-352). This entry
