@@ -438,7 +438,10 @@ def test_batched_slices_equal_per_slice_calls(capi, orc, pkg, path):
         else:
             want = orc.implicit_forward(kind, Q[z], K[z], V[z], kw.get("p0", 0), kw.get("p1", 0), G=G if kind == "global_no_local" else None,
                                         use_nan=kw.get("use_nan", False))
-        assert_state_close(to_np((st[0][z], st[1][z], st[2][z])), want, tol, f"batched {kind} ({path})")
+        # forcing the tiles onto rows with a handful of keys leaves single TF32 roundings un-averaged (AUTO keeps such
+        # shapes on the exact gather path): 3e-3 there, as in the randomised sweep
+        assert_state_close(to_np((st[0][z], st[1][z], st[2][z])), want, 3e-3 if path == "tiled" else tol,
+                           f"batched {kind} ({path})")
     capi.set_path(capi.PATH_AUTO)
     if path == "auto":  # the drop-in modules accept [batch, heads, L, d]
         B, H = 2, 3
