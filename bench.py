@@ -281,6 +281,9 @@ def parse_args():
     ap.add_argument("--phase1-rounds", type=int, default=None,
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
                          "(default: about 4/7 of the rounds; N-1 = a single pass after the exchange)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one process, one GPU: time only the first rank's share of an N-way strong-scaling split with K/V "
+                         "resident (profiling the per-rank kernels without N GPUs); implies --no-e2e --no-cpu-baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-per-workload", action="store_true", help="skip the short measurement of every mask family")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer legs (profiling runs)")
@@ -551,7 +554,12 @@ def run_ours(args, rank, world, dev):
     capi = pkg.capi
     capi.lib()
     capi.set_path({"auto": capi.PATH_AUTO, "gather": capi.PATH_GATHER, "tiled": capi.PATH_TILED}[args.path])
-    job = Job(args.workload, rank, world, dev, weak=args.weak)
+    if args.shard_of > 1 and world == 1:  # the first rank's rows of an N-way split, on this one GPU
+        job = Job(args.workload, 0, args.shard_of, dev, weak=args.weak)
+        job.w = dict(job.w, desc=job.w["desc"] + f" [rows {job.rb}..{job.re}: rank 0 of a {args.shard_of}-way split]")
+        args.no_e2e = args.no_cpu_baseline = args.no_per_workload = True
+    else:
+        job = Job(args.workload, rank, world, dev, weak=args.weak)
     explicit = job.kind in ("csr", "coo")
     peaks, peak_src = load_peaks()
     nan = float("nan")

@@ -35,6 +35,10 @@ namespace spfa {
 // one warp needs about a microsecond per eight scattered keys, so longer rows left to single warps would form
 // the launch's tail.
 constexpr int kListedRowSlots = 128;
+// Residual rows longer than this are cut into slices that different CTAs walk at the same time (partial softmax states
+// in scratch, folded by whichever CTA finishes a row's last slice): a row of 8000 scattered keys walked by one CTA takes
+// about half a millisecond, which is a fixed tail once the rest of a launch is short (a rank's share of a multi-GPU split).
+constexpr int kSplitRowSlots = 1024;
 constexpr int kPlanThreads = 512;
 constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread in the row walks
 constexpr int kPlanHistUnroll = 8;  // ... and in the histogram pass
@@ -61,7 +65,29 @@ struct ExplicitPlan {
   // key-range passes may binary-search the residual rows only while it stays 0
   unsigned int* unsorted;
   PlanHeader* header;
+  // rows cut into slices: one item per (row, slice), items of a row adjacent
+  unsigned int* split_count;        // zeroed before the kernel
+  int4* split_items;                // {row, slice, slices of the row, index of the row's first item}
+  unsigned int* split_done;         // per item index of a row's first item: slices finished (zero outside a forward call)
+  float* split_part;                // [items][d + 4]: un-normalised accumulator, then m, l
+  long long cap_items;
 };
+
+// Adds a row of `kept` residual entries to the split list (kept > kSplitRowSlots). Rows that do not fit the list any
+// more stay whole on the list of long rows.
+__device__ __forceinline__ void list_long_row(const ExplicitPlan& plan, int row, uint32_t kept) {
+  if (kept > (uint32_t)kSplitRowSlots) {
+    const unsigned int ns = (kept + kSplitRowSlots - 1) / kSplitRowSlots;
+    const unsigned int first = atomicAdd(plan.split_count, ns);
+    if ((long long)first + ns <= plan.cap_items) {
+      for (unsigned int sl = 0; sl < ns; ++sl) plan.split_items[first + sl] = make_int4(row, (int)sl, (int)ns, (int)first);
+      return;
+    }
+    for (unsigned int sl = 0; sl < ns && (long long)first + sl < plan.cap_items; ++sl)  // overflowed: neutral items
+      plan.split_items[first + sl] = make_int4(-1, 0, 0, 0);
+  }
+  plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = row;
+}
 
 // Residual rows of the hybrid (see above): same offsets as the caller's CSR, fewer entries, all < Lk.
 struct ResidualCols {
@@ -372,7 +398,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
     if (__any_sync(kFullMask, row_unsorted) && lane == 0) *plan.unsorted = 1u;  // benign race: every writer stores 1
     if (lane == 0) {
       plan.res_cnt[r0 + rl] = kept;
-      if (kept > (uint32_t)kListedRowSlots) plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
+      if (kept > (uint32_t)kListedRowSlots) list_long_row(plan, (int)(r0 + rl), kept);
     }
     if (z <= a && use_nan) {  // a row without any entry
       const float nn = __int_as_float(0x7fc00000);
@@ -446,8 +472,8 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
     if (lane == 0) {
       const uint32_t before_cnt = plan.res_cnt[r0 + rl];  // listed already if it was long before the demotion
       plan.res_cnt[r0 + rl] = kept;
-      if (kept > (uint32_t)kListedRowSlots && before_cnt <= (uint32_t)kListedRowSlots)
-        plan.heavy_rows[atomicAdd(plan.heavy_count, 1u)] = (int)(r0 + rl);
+      // (a row listed before keeps its place: slices are cut from the row's length at forward time, not from this count)
+      if (kept > (uint32_t)kListedRowSlots && before_cnt <= (uint32_t)kListedRowSlots) list_long_row(plan, (int)(r0 + rl), kept);
     }
   }
 }

@@ -274,6 +274,59 @@ __device__ __forceinline__ void walk_row_with_cta(const Cols& cols, const typena
   __syncthreads();
 }
 
+// Slots [t_begin, t_end) of one row by all NW warps of a CTA; afterwards warp 0 holds the folded state of the slice in
+// `tot` (every lane: m, l; lane sub: its accumulator slice). Every thread of the CTA must call this.
+template <int D, class Cols, int NW>
+__device__ __forceinline__ void walk_slice_with_cta(const Cols& cols, const typename Cols::Row& row, int64_t r,
+                                                    int64_t t_begin, int64_t t_end, const float* __restrict__ Q,
+                                                    const float* __restrict__ K, const float* __restrict__ V, float scale,
+                                                    int warp, int lane, float (*s_ml)[2], float4 (*s_acc)[D / 4],
+                                                    RowAcc<D>& tot) {
+  constexpr int LPK = D / 4;
+  int64_t per = (t_end - t_begin + NW - 1) / NW;
+  per = (per + 31) / 32 * 32;  // whole 32-slot batches per warp
+  const int64_t t0 = t_begin + (int64_t)warp * per;
+  int64_t t1 = t0 + per;
+  if (t1 > t_end) t1 = t_end;
+  RowAcc<D> st;
+  st.m = neg_inf();
+  st.l = 0.f;
+  st.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (t0 < t1) {
+    const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
+    accumulate_slots<D, Cols>(cols, row, t0, t1, q, K, V, scale, lane, st);
+    merge_groups<D>(st);
+  }
+  if (lane < LPK) s_acc[warp][lane] = st.acc;
+  if (lane == 0) {
+    s_ml[warp][0] = st.m;
+    s_ml[warp][1] = st.l;
+  }
+  __syncthreads();
+  tot.m = neg_inf();
+  tot.l = 0.f;
+  tot.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (warp == 0) {
+    const int sub = lane % LPK;
+#pragma unroll 4
+    for (int wv = 0; wv < NW; ++wv) {  // in slot order
+      const float mo = s_ml[wv][0], lo = s_ml[wv][1];
+      const float4 ao = s_acc[wv][sub];
+      const float mn = fmaxf(tot.m, mo);
+      const float ms = (mn == neg_inf()) ? 0.f : mn;
+      const float c1 = fast_exp2((tot.m - ms) * kLog2e);
+      const float c2 = fast_exp2((mo - ms) * kLog2e);
+      tot.l = tot.l * c1 + lo * c2;
+      tot.acc.x = tot.acc.x * c1 + ao.x * c2;
+      tot.acc.y = tot.acc.y * c1 + ao.y * c2;
+      tot.acc.z = tot.acc.z * c1 + ao.z * c2;
+      tot.acc.w = tot.acc.w * c1 + ao.w * c2;
+      tot.m = mn;
+    }
+  }
+  __syncthreads();
+}
+
 struct RowCtaShared {
   int heavy[kRowWarps];
   int n_heavy;
@@ -348,9 +401,12 @@ gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __rest
                                 const Cols listed, const int* __restrict__ row_list,
                                 const unsigned int* __restrict__ n_listed, int n_list_blocks, int64_t row_begin,
                                 int64_t n_rows, int use_nan, float scale, const PlanHeader* __restrict__ hdr,
-                                const PlanHeader want, int* __restrict__ err) {
+                                const PlanHeader want, int* __restrict__ err, const int4* __restrict__ split_items,
+                                const unsigned int* __restrict__ n_split_items, long long cap_items,
+                                unsigned int* __restrict__ split_done, float* __restrict__ split_part) {
   __shared__ RowCtaShared sh;
   __shared__ float4 s_acc[kRowWarps][D / 4];
+  __shared__ unsigned int s_last;
   if (!plan_header_matches(hdr, want)) {  // uniform over the grid: the lists belong to a plan of another shape
     if (threadIdx.x == 0) atomicCAS(err, 0, kPlanMismatchCode);
     return;
@@ -361,6 +417,63 @@ gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __rest
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // ---- rows cut into slices: one item at a time per CTA; the CTA that finishes a row's last slice folds them ----
+  {
+    constexpr int LPK = D / 4;
+    unsigned int n_items = *n_split_items;
+    if ((long long)n_items > cap_items) n_items = (unsigned int)cap_items;
+    for (unsigned int it = blockIdx.x; it < n_items; it += (unsigned int)n_list_blocks) {
+      const int4 item = split_items[it];
+      if (item.x < 0) continue;  // uniform over the CTA
+      const int64_t r = item.x;
+      const typename Cols::Row row = listed.open(r, row_begin + r);
+      int64_t per = (row.n + item.z - 1) / item.z;  // slices are cut from the row's length now (a key-range pass is shorter)
+      per = (per + 31) / 32 * 32;
+      const int64_t t_begin = (int64_t)item.y * per;
+      int64_t t_end = t_begin + per;
+      if (t_end > row.n) t_end = row.n;
+      RowAcc<D> tot;
+      walk_slice_with_cta<D, Cols, kRowWarps>(listed, row, r, t_begin < t_end ? t_begin : t_end, t_end, Q, K, V, scale, warp, lane,
+                                              sh.ml, s_acc, tot);
+      float* part = split_part + (size_t)it * (D + 4);
+      if (warp == 0) {
+        if (lane < LPK) reinterpret_cast<float4*>(part)[lane] = tot.acc;
+        if (lane == 0) {
+          part[D] = tot.m;
+          part[D + 1] = tot.l;
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) s_last = (atomicAdd(split_done + item.w, 1u) == (unsigned int)(item.z - 1)) ? 1u : 0u;
+      }
+      __syncthreads();
+      if (s_last && warp == 0) {  // every slice of the row is in scratch: fold them in slice order, store the row
+        __threadfence();
+        RowAcc<D> all;
+        all.m = neg_inf();
+        all.l = 0.f;
+        all.acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int sub = lane % LPK;
+        for (int sl = 0; sl < item.z; ++sl) {
+          const float* p = split_part + (size_t)(item.w + sl) * (D + 4);
+          const float mo = __ldcg(p + D), lo = __ldcg(p + D + 1);
+          const float4 ao = __ldcg(reinterpret_cast<const float4*>(p) + sub);
+          const float mn = fmaxf(all.m, mo);
+          const float ms = (mn == neg_inf()) ? 0.f : mn;
+          const float c1 = fast_exp2((all.m - ms) * kLog2e), c2 = fast_exp2((mo - ms) * kLog2e);
+          all.l = all.l * c1 + lo * c2;
+          all.acc.x = all.acc.x * c1 + ao.x * c2;
+          all.acc.y = all.acc.y * c1 + ao.y * c2;
+          all.acc.z = all.acc.z * c1 + ao.z * c2;
+          all.acc.w = all.acc.w * c1 + ao.w * c2;
+          all.m = mn;
+        }
+        if (all.l > 0.f) store_row<D>(all, m, l, O, r, lane);
+        if (lane == 0) split_done[item.w] = 0u;  // ready for the next forward call from this plan
+      }
+      __syncthreads();
+    }
+  }
   const unsigned int n = *n_listed;
   for (unsigned int e = blockIdx.x; e < n; e += (unsigned int)n_list_blocks) {
     const int64_t r = row_list[e];

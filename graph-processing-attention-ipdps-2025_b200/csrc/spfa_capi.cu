@@ -227,7 +227,8 @@ struct HybridLayout {
   int64_t n_blocks;
   long long cap_words;
   size_t smem;
-  size_t off_pool, off_nt, off_kt, off_moff, off_cnt, off_heavy, off_res, off_masks, total;
+  long long cap_items;
+  size_t off_pool, off_nt, off_kt, off_moff, off_cnt, off_heavy, off_items, off_done, off_part, off_res, off_masks, total;
 };
 
 inline bool hybrid_shape_ok(int d, int64_t n_rows, int64_t nnz, int64_t Lk) {
@@ -252,7 +253,11 @@ inline HybridLayout hybrid_layout(int64_t n_rows, int64_t nnz, int64_t Lk, int d
   h.off_moff = h.off_kt + align_up((size_t)h.n_blocks * tile::kMaxDenseTiles * 4);
   h.off_cnt = h.off_moff + align_up((size_t)h.n_blocks * 8);
   h.off_heavy = h.off_cnt + align_up((size_t)n_rows * 4);
-  h.off_res = h.off_heavy + align_up((size_t)n_rows * 4);
+  h.cap_items = 2 * (nnz / kSplitRowSlots) + 1;  // a split row has more than kSplitRowSlots entries and ceil(n / that) slices
+  h.off_items = h.off_heavy + align_up((size_t)n_rows * 4);
+  h.off_done = h.off_items + align_up((size_t)h.cap_items * sizeof(int4));
+  h.off_part = h.off_done + align_up((size_t)h.cap_items * 4);
+  h.off_res = h.off_part + align_up((size_t)h.cap_items * (d + 4) * 4);
   h.off_masks = h.off_res + align_up((size_t)nnz * 4);
   h.total = h.off_masks + align_up((size_t)h.cap_words * 4);
   return h;
@@ -279,6 +284,11 @@ inline ExplicitPlan plan_view(const HybridLayout& h, char* ws) {
   plan.heavy_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 8);
   plan.unsorted = reinterpret_cast<unsigned int*>(ws + h.off_pool + 12);
   plan.header = reinterpret_cast<PlanHeader*>(ws + h.off_pool + kPlanHeaderOffset);
+  plan.split_count = reinterpret_cast<unsigned int*>(ws + h.off_pool + 16);
+  plan.split_items = reinterpret_cast<int4*>(ws + h.off_items);
+  plan.split_done = reinterpret_cast<unsigned int*>(ws + h.off_done);
+  plan.split_part = reinterpret_cast<float*>(ws + h.off_part);
+  plan.cap_items = h.cap_items;
   plan.rb_nt = reinterpret_cast<int*>(ws + h.off_nt);
   plan.rb_kt = reinterpret_cast<int*>(ws + h.off_kt);
   plan.rb_moff = reinterpret_cast<long long*>(ws + h.off_moff);
@@ -296,7 +306,8 @@ template <int BN>
 int launch_plan(const uint64_t* row_off, const uint32_t* col, int64_t n_rows, int64_t nnz, int64_t Lk, int d,
                 const HybridLayout& h, char* ws, int use_nan, float* O, cudaStream_t st) {
   const ExplicitPlan plan = plan_view(h, ws);
-  if (cudaMemsetAsync(plan.pool_used, 0, 16, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
+  if (cudaMemsetAsync(plan.pool_used, 0, 32, st) != cudaSuccess) return SPFA_ERR_LAUNCH;  // the four counters
+  if (cudaMemsetAsync(plan.split_done, 0, (size_t)h.cap_items * 4, st) != cudaSuccess) return SPFA_ERR_LAUNCH;
   auto plan_kern = explicit_plan_kernel<BN>;
   if (cudaFuncSetAttribute(plan_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)h.smem) != cudaSuccess)
     return SPFA_ERR_LAUNCH;
@@ -377,7 +388,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
     ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots};
     gather_rows_listed_first_kernel<D, ResidualCols><<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(
         Q, K, V, m, l, O, cols, listed, plan.heavy_rows, plan.heavy_count, list_blocks, 0, n_rows, 0, scale, plan.header,
-        want, err);
+        want, err, plan.split_items, plan.split_count, plan.cap_items, plan.split_done, plan.split_part);
   } else {
     const uint32_t klo = (uint32_t)key_begin, khi = (uint32_t)(key_end < Lk ? key_end : Lk);
     (void)cyclic;  // klo > khi is the cyclic range for the functor and for the tile filter alike
@@ -386,7 +397,9 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
     gather_rows_listed_first_kernel<D, ResidualRangeCols>
         <<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(Q, K, V, m, l, O, cols, listed, plan.heavy_rows,
                                                                         plan.heavy_count, list_blocks, 0, n_rows, 0, scale,
-                                                                        plan.header, want, err);
+                                                                        plan.header, want, err, plan.split_items,
+                                                                        plan.split_count, plan.cap_items, plan.split_done,
+                                                                        plan.split_part);
   }
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_TILED);

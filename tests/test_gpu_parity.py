@@ -735,6 +735,23 @@ def test_explicit_dense_tiles_with_very_long_residual_rows(capi, orc):
     assert capi.last_csr_dense_tiles() > 0
     assert_state_close(to_np(st), want, TOL_TILED, "long residual rows")
     capi.set_path(capi.PATH_AUTO)
+    # rows beyond 1024 residual entries are cut into slices walked by several CTAs; the per-row slice counters must be
+    # back at zero after every call, so a stored plan serves repeated calls and passes over key ranges alike
+    for shuffle_seed in (None, 4):
+        ro, co = _csr_of(mask, shuffle_seed=shuffle_seed)
+        plan = capi.csr_plan(dev(ro), dev(co), Lk, d)
+        for rep in range(3):
+            st = capi.new_state(L, d)
+            capi.planned_forward(dev(Q), dev(K), dev(V), *st, plan)
+            assert_state_close(to_np(st), want, TOL_TILED, f"long residual rows, stored plan, call {rep}")
+        st = capi.new_state(L, d)
+        for a, b in ((4480, 9000), (0, 1024), (1024, 4480)):
+            capi.planned_forward_keys(dev(Q), dev(K), dev(V), *st, plan, a, b)
+        assert_state_close(to_np(st), want, TOL_TILED, "long residual rows, three key ranges")
+        st = capi.new_state(L, d)
+        for a, b in ((6400, 2048), (2048, 6400)):  # a cyclic range and its complement
+            capi.planned_forward_keys(dev(Q), dev(K), dev(V), *st, plan, a, b)
+        assert_state_close(to_np(st), want, TOL_TILED, "long residual rows, cyclic key range")
 
 
 def test_stored_plan_matches_one_shot_calls(capi, orc, pkg):
