@@ -18,12 +18,16 @@
 //      original row offsets (row r: res_col[row_off[r] .. row_off[r] + res_cnt[r])); columns >= Lk are dropped
 //      (the ABI skips them); rows without any entry are NaN-filled here when use_nan is set
 // Steps 3 and 5 share one walk over the block's entries; the walk of step 5 is repeated only for a block that
-// had a tile demoted in step 3 or 4. The passes are latency bound: several independent column loads per
-// thread, and shared memory kept small enough for four CTAs per SM (the histogram of step 1 and the masks of
-// step 3 share one region; from step 3 on "is this key tile dense, and which slot" is answered by a bit per
-// key tile plus a per-word count).
-// Runs of equal keys inside a warp are combined before they touch a shared-memory counter or mask word:
-// the entries of a row are normally sorted, so whole warps would otherwise hit one address.
+// had a tile demoted in step 3 or 4. Shared memory is kept small enough for four CTAs per SM (the histogram of
+// step 1 and the masks of step 3 share one region; from step 3 on "is this key tile dense, and which slot" is
+// answered by a bit per key tile plus a per-word count).
+// The walks are bound by instruction issue, not by memory: a warp takes a row 128 entries at a time, every lane
+// FOUR CONSECUTIVE entries from one 16-byte load. Whatever concerns neighbouring entries (ascending order, runs of
+// equal mask words or key tiles -- the entries of a row are normally sorted, so a band puts dozens of entries into
+// one word) is settled inside the lane first; the lanes then meet only for the prefix sum that places the residual
+// entries (three ballots over the bits of the per-lane counts) and for one shuffle of the order check. Mask words
+// and counters are updated with one shared-memory atomic per lane-local run; lanes that hit the same word are
+// serialised by the memory pipe, which has the headroom.
 #pragma once
 #include "gather_kernels.cuh"
 #include "spfa_common.cuh"
@@ -40,8 +44,6 @@ constexpr int kListedRowSlots = 128;
 // about half a millisecond, which is a fixed tail once the rest of a launch is short (a rank's share of a multi-GPU split).
 constexpr int kSplitRowSlots = 1024;
 constexpr int kPlanThreads = 512;
-constexpr int kPlanUnroll = 4;  // independent column loads in flight per thread in the row walks
-constexpr int kPlanHistUnroll = 8;  // ... and in the histogram pass
 constexpr int kPlanSampleStride = 4;  // the histogram looks at every 4th row of a block
 constexpr int kPlanWarps = kPlanThreads / 32;
 constexpr int kPlanMaxSmem = 200 * 1024;
@@ -201,16 +203,31 @@ inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
   return (hist > masks ? hist : masks) + words * 4 + (words + 3) / 4 * 4;
 }
 
-// Runs of equal keys over the lanes of a warp. Returns the lane one past the end of the run this lane is in;
-// *lead says whether this lane starts its run (its length is then the return value minus the lane).
-// Inactive lanes pass a key no active lane has.
-__device__ __forceinline__ int run_end_of(uint32_t key, int lane, bool* lead) {
-  const uint32_t prev = __shfl_up_sync(kFullMask, key, 1);
-  *lead = (lane == 0) || (prev != key);
-  const uint32_t leaders = __ballot_sync(kFullMask, *lead);
-  const uint32_t later = (lane == 31) ? 0u : (leaders >> (lane + 1));
-  return later ? (lane + __ffs(later)) : 32;
+// Four consecutive entries e .. e+3 of the column array from one 16-byte load; `e` must put the address on a
+// 16-byte boundary. Positions outside [0, nnz) (only the array's first and last chunk can have some) read as `none`.
+__device__ __forceinline__ void load_four_columns(const uint32_t* __restrict__ col, int64_t e, int64_t nnz, uint32_t none,
+                                                  uint32_t (&c)[4]) {
+  if (e >= 0 && e + 4 <= nnz) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(col + e));
+    c[0] = v.x;
+    c[1] = v.y;
+    c[2] = v.z;
+    c[3] = v.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c[j] = (e + j >= 0 && e + j < nnz) ? __ldg(col + e + j) : none;
+  }
 }
+
+// A warp's walk over the entries [a, z) of one row, 128 per step: the step's first entry index (a multiple-of-16-byte
+// address at or below a) and, per step, the window [lo, hi) of positions 0..127 that belong to the row.
+struct RowSteps {
+  int64_t first;
+  __device__ __forceinline__ RowSteps(const uint32_t* col, int64_t a) {
+    const int mis = (int)((reinterpret_cast<uintptr_t>(col) >> 2) & 3u);  // entries between col and a 16-byte boundary
+    first = a - (int64_t)((a + mis) & 3);
+  }
+};
 
 template <int BN>
 __global__ void __launch_bounds__(kPlanThreads, 4)
@@ -265,23 +282,27 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   // ---- 1. histogram over key tiles, from every kPlanSampleStride-th row of the block ----
   // The counts only decide which tiles are CALLED dense (masks and residual lists are built from all entries
   // below), so a sample is enough: a tile is dense if the sampled rows hold their share of min_entries.
+  const uint32_t Lk32 = (Lk < 0xffffffffLL) ? (uint32_t)Lk : 0xffffffffu;  // kNoKey is never a valid column
   for (int rl = warp * kPlanSampleStride; rl < nr; rl += kPlanWarps * kPlanSampleStride) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
-    for (int64_t base = a; base < z; base += 32 * kPlanHistUnroll) {
-      uint32_t cu[kPlanHistUnroll];
+    for (int64_t base = (a < z) ? RowSteps(col, a).first : z; base < z; base += 128) {
+      const int lo = (a > base) ? (int)(a - base) : 0, hi = (z - base < 128) ? (int)(z - base) : 128;  // warp-uniform
+      uint32_t cu[4];
+      if (lane * 4 < hi) load_four_columns(col, base + lane * 4, nnz, kNoKey, cu);
+      uint32_t k_run = kNoKey, n_run = 0;  // a run of entries of one key tile inside this lane
 #pragma unroll
-      for (int u = 0; u < kPlanHistUnroll; ++u) {
-        const int64_t e = base + u * 32 + lane;
-        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+      for (int j = 0; j < 4; ++j) {
+        const int p = lane * 4 + j;
+        if (p < lo || p >= hi || cu[j] >= Lk32) continue;
+        const uint32_t kt = cu[j] / BN;
+        if (kt != k_run) {
+          if (n_run) atomicAdd(&hist[k_run >> 1], n_run << ((k_run & 1) * 16));
+          k_run = kt;
+          n_run = 0;
+        }
+        ++n_run;
       }
-#pragma unroll
-      for (int u = 0; u < kPlanHistUnroll; ++u) {
-        if (base + u * 32 >= z) break;  // warp-uniform
-        const uint32_t kt = ((int64_t)cu[u] < Lk) ? cu[u] / BN : kNoKey;  // kNoKey >= Lk
-        bool lead;
-        const int end = run_end_of(kt, lane, &lead);
-        if (lead && kt != kNoKey) atomicAdd(&hist[kt >> 1], (uint32_t)(end - lane) << ((kt & 1) * 16));
-      }
+      if (n_run) atomicAdd(&hist[k_run >> 1], n_run << ((k_run & 1) * 16));
     }
   }
   __syncthreads();
@@ -332,68 +353,66 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   // ---- 3. bit masks of the dense tiles (duplicates demote a tile) and, in the same walk, 5. the residual list ----
   for (int i = tid; i < nt * NC * 128; i += kPlanThreads) masks[i] = 0;
   __syncthreads();
+  // dense tiles lie in [kt_lo, kt_lo + kt_span] (s_sel ascends); a key tile outside is residual without a lookup
+  const uint32_t kt_lo = nt ? (uint32_t)s_sel[0] : 1u, kt_span = nt ? (uint32_t)s_sel[nt - 1] - kt_lo : 0u;
+  const uint32_t lanes_below = (1u << lane) - 1u;
   for (int rl = warp; rl < nr; rl += kPlanWarps) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
-    uint32_t last_col = kNoKey;  // column of the previous batch's last entry
+    uint32_t last_col = 0;  // column of the previous step's last entry
     bool row_unsorted = false;
-    for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
-      uint32_t cu[kPlanUnroll];
+    for (int64_t base = (a < z) ? RowSteps(col, a).first : z; base < z; base += 128) {
+      const int lo = (a > base) ? (int)(a - base) : 0, hi = (z - base < 128) ? (int)(z - base) : 128;  // warp-uniform
+      uint32_t cu[4] = {kNoKey, kNoKey, kNoKey, kNoKey};
+      if (lane * 4 < hi) load_four_columns(col, base + lane * 4, nnz, kNoKey, cu);
+      uint32_t keep_bits = 0;               // bit j: entry j of this lane stays on the gather path
+      uint32_t w_run = kNoKey, b_run = 0;   // a run of entries of one mask word inside this lane
+      auto flush_run = [&]() {
+        const uint32_t old = atomicOr(&masks[w_run], b_run);
+        if (old & b_run) s_dirty[w_run / (NC * 128)] = 1;  // the pair occurred in another lane or an earlier step
+      };
 #pragma unroll
-      for (int u = 0; u < kPlanUnroll; ++u) {
-        const int64_t e = base + u * 32 + lane;
-        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
-      }
-#pragma unroll
-      for (int u = 0; u < kPlanUnroll; ++u) {
-        if (base + u * 32 >= z) break;  // warp-uniform
-        const uint32_t c = cu[u];
-        uint32_t word = kNoKey, bit = 0;
-        bool keep = false;
-        if ((int64_t)c < Lk) {
-          const uint32_t kt = c / BN, slot1 = slot1_of(kt);
-          if (slot1) {
-            const uint32_t kk = c - kt * BN;
-            word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl;
-            bit = 1u << (kk & 31);
-          } else {
-            keep = true;
-          }
-        }
-        const uint32_t bal = __ballot_sync(kFullMask, keep);
-        if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
-        kept += __popc(bal);
-        {  // ascending order of the row's columns (all entries, so the kept ones as well)
-          const uint32_t before = __shfl_up_sync(kFullMask, c, 1);
-          const uint32_t prev = (lane == 0) ? last_col : before;
-          if (c != kNoKey && prev != kNoKey && c < prev) row_unsorted = true;
-          last_col = __shfl_sync(kFullMask, c, 31);  // kNoKey only in a row's last, ragged batch
-        }
-        if (bal == kFullMask) continue;  // warp-uniform: no entry of this batch lies in a dense tile
-        const uint32_t word0 = __shfl_sync(kFullMask, word, 0);
-        if (word0 != kNoKey && __all_sync(kFullMask, word == word0)) {
-          // the usual case of a sorted row inside a band: all 32 entries fall into one mask word
-          const uint32_t all = __reduce_or_sync(kFullMask, bit);
-          if (lane == 0) {
-            const uint32_t old = atomicOr(&masks[word0], all);
-            if ((old & all) != 0u || all != 0xffffffffu) s_dirty[word0 / (NC * 128)] = 1;
-          }
+      for (int j = 0; j < 4; ++j) {
+        const int p = lane * 4 + j;
+        // positions outside the row take the smallest / largest column, so they never break the ascending order
+        if (p < lo) cu[j] = 0u;
+        if (p >= hi) cu[j] = kNoKey;
+        const uint32_t c = cu[j];
+        if (p < lo || p >= hi || c >= Lk32) continue;
+        const uint32_t kt = c / BN;
+        const uint32_t slot1 = (kt - kt_lo <= kt_span) ? slot1_of(kt) : 0u;
+        if (!slot1) {
+          keep_bits |= 1u << j;
           continue;
         }
-        // OR of the bits of each run of equal words, at the run's first lane (suffix scan by doubling)
-        bool lead;
-        const int end = run_end_of(word, lane, &lead);
-        uint32_t acc = bit;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const uint32_t t = __shfl_down_sync(kFullMask, acc, o);
-          if (lane + o < end) acc |= t;
+        const uint32_t kk = c - kt * BN;
+        const uint32_t word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl, bit = 1u << (kk & 31);
+        if (word != w_run) {
+          if (w_run != kNoKey) flush_run();
+          w_run = word;
+          b_run = 0;
         }
-        if (lead && word != kNoKey) {
-          const uint32_t old = atomicOr(&masks[word], acc);
-          if ((old & acc) != 0u || __popc(acc) != end - lane) s_dirty[word / (NC * 128)] = 1;
-        }
+        if (b_run & bit) s_dirty[word / (NC * 128)] = 1;  // the pair occurs twice: a bit cannot say that
+        b_run |= bit;
       }
+      if (w_run != kNoKey) flush_run();
+      {  // ascending order of the row's columns (all entries, so the kept ones as well)
+        const uint32_t before = __shfl_up_sync(kFullMask, cu[3], 1);
+        const uint32_t prev = (lane == 0) ? last_col : before;
+        if (prev > cu[0] || cu[0] > cu[1] || cu[1] > cu[2] || cu[2] > cu[3]) row_unsorted = true;
+        last_col = __shfl_sync(kFullMask, cu[3], 31);
+      }
+      // residual entries in storage order: prefix sum of the per-lane counts (0..4) from ballots of their three bits
+      const uint32_t cnt = __popc(keep_bits);
+      const uint32_t b0 = __ballot_sync(kFullMask, cnt & 1u), b1 = __ballot_sync(kFullMask, cnt & 2u),
+                     b2 = __ballot_sync(kFullMask, cnt & 4u);
+      if ((b0 | b1 | b2) == 0u) continue;  // warp-uniform
+      uint32_t* dst = plan.res_col + a + kept + __popc(b0 & lanes_below) + 2 * __popc(b1 & lanes_below) +
+                      4 * __popc(b2 & lanes_below);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (keep_bits & (1u << j)) *dst++ = cu[j];
+      kept += __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2);
     }
     if (__any_sync(kFullMask, row_unsorted) && lane == 0) *plan.unsorted = 1u;  // benign race: every writer stores 1
     if (lane == 0) {
@@ -449,25 +468,28 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   for (int rl = warp; rl < nr; rl += kPlanWarps) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
-    for (int64_t base = a; base < z; base += 32 * kPlanUnroll) {
-      uint32_t cu[kPlanUnroll];
+    for (int64_t base = (a < z) ? RowSteps(col, a).first : z; base < z; base += 128) {
+      const int lo = (a > base) ? (int)(a - base) : 0, hi = (z - base < 128) ? (int)(z - base) : 128;  // warp-uniform
+      uint32_t cu[4] = {kNoKey, kNoKey, kNoKey, kNoKey};
+      if (lane * 4 < hi) load_four_columns(col, base + lane * 4, nnz, kNoKey, cu);
+      uint32_t keep_bits = 0;
 #pragma unroll
-      for (int u = 0; u < kPlanUnroll; ++u) {
-        const int64_t e = base + u * 32 + lane;
-        cu[u] = (e < z) ? __ldg(col + e) : kNoKey;
+      for (int j = 0; j < 4; ++j) {
+        const int p = lane * 4 + j;
+        const uint32_t c = cu[j];
+        if (p < lo || p >= hi || c >= Lk32) continue;
+        const uint32_t kt = c / BN;
+        if (((dense_bits[kt >> 5] >> (kt & 31)) & 1u) == 0u) keep_bits |= 1u << j;
       }
+      const uint32_t cnt = __popc(keep_bits);
+      const uint32_t b0 = __ballot_sync(kFullMask, cnt & 1u), b1 = __ballot_sync(kFullMask, cnt & 2u),
+                     b2 = __ballot_sync(kFullMask, cnt & 4u);
+      uint32_t* dst = plan.res_col + a + kept + __popc(b0 & lanes_below) + 2 * __popc(b1 & lanes_below) +
+                      4 * __popc(b2 & lanes_below);
 #pragma unroll
-      for (int u = 0; u < kPlanUnroll; ++u) {
-        const uint32_t c = cu[u];
-        bool keep = false;
-        if ((int64_t)c < Lk) {
-          const uint32_t kt = c / BN;
-          keep = ((dense_bits[kt >> 5] >> (kt & 31)) & 1u) == 0u;
-        }
-        const uint32_t bal = __ballot_sync(kFullMask, keep);
-        if (keep) plan.res_col[a + kept + __popc(bal & ((1u << lane) - 1u))] = c;
-        kept += __popc(bal);
-      }
+      for (int j = 0; j < 4; ++j)
+        if (keep_bits & (1u << j)) *dst++ = cu[j];
+      kept += __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2);
     }
     if (lane == 0) {
       const uint32_t before_cnt = plan.res_cnt[r0 + rl];  // listed already if it was long before the demotion

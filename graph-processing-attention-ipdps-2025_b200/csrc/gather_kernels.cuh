@@ -588,20 +588,38 @@ combine_partials_kernel(const float* __restrict__ partials, const int32_t* __res
 
 // ---- COO row pointers --------------------------------------------------------------------------
 // ptr[r] = first k with row_ind[k] >= row_begin + r, for r in [0, n_rows]. One pass over the sorted
-// row array: position k writes the pointers of all rows in (row_ind[k-1], row_ind[k]].
+// row array: position k writes the pointers of all rows in (row_ind[k-1], row_ind[k]]. The pass is a stream of
+// 8-byte (or 4-byte) loads bound by memory latency, so every thread keeps kRowPtrUnroll independent loads in
+// flight; the predecessor of a position comes from the neighbouring lane (lane 0 reads it, a cache hit).
+constexpr int kRowPtrUnroll = 4;
+constexpr int kRowPtrThreads = 256;
+
 template <class IdxT>  // uint64_t (the reference's layout) or int32_t (halves the bytes this pass reads)
-__global__ void coo_row_pointers_kernel(const IdxT* __restrict__ row_ind, int64_t nnz,
-                                        int64_t row_begin, int64_t n_rows, uint64_t* __restrict__ ptr) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k <= nnz; k += stride) {
-    // rows strictly above `prev` and up to `cur` start at k
-    int64_t prev = (k == 0) ? (row_begin - 1) : (int64_t)row_ind[k - 1];
-    int64_t cur = (k == nnz) ? (row_begin + n_rows) : (int64_t)row_ind[k];
-    if (cur == prev) continue;
-    int64_t a = prev + 1 - row_begin, b = cur - row_begin;
-    if (a < 0) a = 0;
-    if (b > n_rows) b = n_rows;
-    for (int64_t r = a; r <= b; ++r) ptr[r] = (uint64_t)k;
+__global__ void __launch_bounds__(kRowPtrThreads)
+coo_row_pointers_kernel(const IdxT* __restrict__ row_ind, int64_t nnz, int64_t row_begin, int64_t n_rows,
+                        uint64_t* __restrict__ ptr) {
+  constexpr int64_t span = (int64_t)kRowPtrThreads * kRowPtrUnroll;
+  const int lane = threadIdx.x & 31;
+  const int64_t end_row = row_begin + n_rows;
+  for (int64_t base = (int64_t)blockIdx.x * span; base <= nnz; base += (int64_t)gridDim.x * span) {  // uniform per CTA
+    int64_t cur[kRowPtrUnroll];
+#pragma unroll
+    for (int u = 0; u < kRowPtrUnroll; ++u) {
+      const int64_t k = base + u * kRowPtrThreads + threadIdx.x;
+      cur[u] = (k < nnz) ? (int64_t)__ldg(row_ind + k) : end_row;  // k == nnz closes the last rows
+    }
+#pragma unroll
+    for (int u = 0; u < kRowPtrUnroll; ++u) {
+      const int64_t k = base + u * kRowPtrThreads + threadIdx.x;
+      int64_t prev = __shfl_up_sync(kFullMask, cur[u], 1);
+      if (lane == 0 && k <= nnz) prev = (k == 0) ? (row_begin - 1) : (int64_t)__ldg(row_ind + k - 1);
+      if (k > nnz || cur[u] == prev) continue;
+      // rows strictly above `prev` and up to `cur` start at k
+      int64_t a = prev + 1 - row_begin, b = cur[u] - row_begin;
+      if (a < 0) a = 0;
+      if (b > n_rows) b = n_rows;
+      for (int64_t r = a; r <= b; ++r) ptr[r] = (uint64_t)k;
+    }
   }
 }
 

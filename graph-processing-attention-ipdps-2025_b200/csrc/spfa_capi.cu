@@ -452,9 +452,10 @@ inline int static_coo_scratch(unsigned long long** out) {
 template <class IdxT>
 int launch_row_pointers(const IdxT* row_ind, int64_t nnz, int64_t row_begin, int64_t n_rows, uint64_t* ptr,
                         cudaStream_t st) {
-  int64_t blocks = (nnz + 1 + 255) / 256;
-  if (blocks > 148 * 64) blocks = 148 * 64;
-  coo_row_pointers_kernel<IdxT><<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  constexpr int64_t span = (int64_t)kRowPtrThreads * kRowPtrUnroll;
+  int64_t blocks = (nnz + 1 + span - 1) / span;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  coo_row_pointers_kernel<IdxT><<<(unsigned)blocks, kRowPtrThreads, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
   g_launches.fetch_add(1);
   return launch_status();
 }

@@ -99,9 +99,10 @@ int spfa_coo_forward_16(int dtype, const void* Q, const void* K, const void* V, 
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   uint64_t* ptr = reinterpret_cast<uint64_t*>(workspace);
-  int64_t blocks = (nnz + 1 + 255) / 256;
-  if (blocks > 148 * 64) blocks = 148 * 64;
-  coo_row_pointers_kernel<uint64_t><<<(unsigned)blocks, 256, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
+  constexpr int64_t span = (int64_t)kRowPtrThreads * kRowPtrUnroll;
+  int64_t blocks = (nnz + 1 + span - 1) / span;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  coo_row_pointers_kernel<uint64_t><<<(unsigned)blocks, kRowPtrThreads, 0, st>>>(row_ind, nnz, row_begin, n_rows, ptr);
   g_launches.fetch_add(1);
   if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
   return with_dtype16(dtype, [&](auto* tag) {

@@ -646,6 +646,34 @@ def test_explicit_dense_tiles_vs_oracle(capi, orc, L, Lk, d, half, density):
     capi.set_path(capi.PATH_AUTO)
 
 
+@pytest.mark.parametrize("shift", [1, 2, 3])
+def test_explicit_column_array_on_any_four_byte_boundary(capi, orc, shift):
+    """The mask inspection reads the columns with 16-byte loads from the boundary at or below a row's first entry: the
+    column array may start on any 4-byte boundary, and the array's first and last chunk are read entry by entry."""
+    L, Lk, d = 390, 700, 64
+    Q, K, V = seeded_qkv(L, d, 91, Lk)
+    mask = _band_plus_random(L, Lk, 48, 0.01, 17, empty_rows=(0, 7, L - 1))
+    mask[1, :3] = True  # the first row with entries starts inside the array's first 16 bytes
+    for shuffle_seed in (None, 3):
+        row_off, col = _csr_of(mask, shuffle_seed=shuffle_seed)
+        rows = np.repeat(np.arange(L, dtype=np.int64), np.diff(row_off))
+        want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+        # no slack behind the last entry either: the view ends with the allocation
+        buf = torch.empty(shift + col.size, dtype=torch.int32, device="cuda")
+        col_dev = buf[shift:]
+        col_dev.copy_(torch.from_numpy(col.astype(np.int32)))
+        assert col_dev.data_ptr() % 16 == 4 * shift
+        capi.set_path(capi.PATH_TILED)
+        st = capi.new_state(L, d)
+        capi.csr_forward(dev(Q), dev(K), dev(V), dev(row_off), col_dev, *st, use_nan=True)
+        assert capi.last_path() == capi.PATH_TILED and capi.last_csr_dense_tiles() > 0
+        assert_state_close(to_np(st), want, TOL_TILED, f"csr, columns shifted by {shift} entries")
+        st = capi.new_state(L, d)
+        capi.coo_forward(dev(Q), dev(K), dev(V), dev(rows), col_dev, *st, use_nan=True)
+        assert_state_close(to_np(st), want, TOL_TILED, f"coo, columns shifted by {shift} entries")
+        capi.set_path(capi.PATH_AUTO)
+
+
 def test_explicit_dense_tiles_unsorted_duplicates_out_of_range_and_chaining(capi, orc):
     L, Lk, d = 600, 800, 64
     Q, K, V = seeded_qkv(L, d, 77, Lk)
