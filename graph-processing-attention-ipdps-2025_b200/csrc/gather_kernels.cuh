@@ -327,33 +327,44 @@ __device__ __forceinline__ void walk_slice_with_cta(const Cols& cols, const type
   __syncthreads();
 }
 
+constexpr int kMaxRowsPerCta = 32;
+
 struct RowCtaShared {
-  int heavy[kRowWarps];
+  int heavy[kMaxRowsPerCta];
   int n_heavy;
+  int next;  // next unclaimed row of the CTA's range
   float ml[kRowWarps][2];
 };
 
-// Rows [block*kRowWarps, (block+1)*kRowWarps) of the shard, by one CTA of kRowWarps warps.
+// Rows [block * rows_per_cta, (block + 1) * rows_per_cta) of the shard, by one CTA of kRowWarps warps.
+// A warp takes one row at a time and claims the next from a shared counter when it is done: with one fixed row per
+// warp a CTA lasts as long as its longest row while the other warps' slots sit idle, which on a mask with skewed row
+// lengths left a third of the resident warps waiting. rows_per_cta is at most kMaxRowsPerCta.
 template <int D, class Cols>
-__device__ __forceinline__ void gather_rows_cta(int64_t block, const float* __restrict__ Q, const float* __restrict__ K,
-                                                const float* __restrict__ V, float* __restrict__ m,
-                                                float* __restrict__ l, float* __restrict__ O, const Cols& cols,
-                                                int64_t row_begin, int64_t n_rows, int use_nan, float scale,
-                                                RowCtaShared& sh, float4 (*s_acc)[D / 4]) {
+__device__ __forceinline__ void gather_rows_cta(int64_t block, int rows_per_cta, const float* __restrict__ Q,
+                                                const float* __restrict__ K, const float* __restrict__ V,
+                                                float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
+                                                const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan,
+                                                float scale, RowCtaShared& sh, float4 (*s_acc)[D / 4]) {
   constexpr int LPK = D / 4;
   int* s_heavy = sh.heavy;
   int& s_n_heavy = sh.n_heavy;
   float (*s_ml)[2] = sh.ml;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) s_n_heavy = 0;
+  if (threadIdx.x == 0) {
+    s_n_heavy = 0;
+    sh.next = kRowWarps;
+  }
   __syncthreads();
-  const int64_t r = block * kRowWarps + warp;
-  if (r < n_rows) {
+  const int64_t first = block * rows_per_cta;
+  for (int i = warp; i < rows_per_cta;) {  // warp-uniform
+    const int64_t r = first + i;
+    if (r >= n_rows) break;
     const typename Cols::Row row = cols.open(r, row_begin + r);
     if (row.n <= 0) {
       if (Cols::kNanFillEmpty && use_nan) nan_fill_row<D>(O, r, lane);
     } else if (row.n > kHeavyRowSlots) {
-      if (lane == 0) s_heavy[atomicAdd(&s_n_heavy, 1)] = warp;
+      if (lane == 0) s_heavy[atomicAdd(&s_n_heavy, 1)] = i;
     } else {
       const float4 q = ldg4(Q + (size_t)r * D + (lane % LPK) * 4);
       RowAcc<D> st;
@@ -364,14 +375,29 @@ __device__ __forceinline__ void gather_rows_cta(int64_t block, const float* __re
       merge_groups<D>(st);
       if (st.l > 0.f) store_row<D>(st, m, l, O, r, lane);
     }
+    if (rows_per_cta <= kRowWarps) break;
+    int nxt = 0;
+    if (lane == 0) nxt = atomicAdd(&sh.next, 1);
+    i = __shfl_sync(kFullMask, nxt, 0);
   }
   __syncthreads();
   const int n_heavy = s_n_heavy;  // uniform over the CTA
   for (int h = 0; h < n_heavy; ++h) {
-    const int64_t rh = block * kRowWarps + s_heavy[h];
+    const int64_t rh = first + s_heavy[h];
     const typename Cols::Row row = cols.open(rh, row_begin + rh);
     walk_row_with_cta<D, Cols, kRowWarps>(cols, row, rh, Q, K, V, m, l, O, scale, warp, lane, s_ml, s_acc);
   }
+}
+
+// Rows per CTA for a launch over n_rows rows (times n_slices slices): as many as kMaxRowsPerCta once that still leaves
+// several waves of CTAs on the machine, down to one per warp for small shards.
+inline int rows_per_cta_for(int64_t n_rows, int64_t n_slices) {
+  const int64_t want_ctas = 148LL * 7 * 8;
+  int64_t r = n_rows * n_slices / want_ctas;
+  r = r / kRowWarps * kRowWarps;
+  if (r < kRowWarps) r = kRowWarps;
+  if (r > kMaxRowsPerCta) r = kMaxRowsPerCta;
+  return (int)r;
 }
 
 // Slices of a batched call (batch x heads, one mask for all) ride on blockIdx.y: Q, O advance by n_rows * D elements
@@ -380,12 +406,13 @@ template <int D, class Cols>
 __global__ void __launch_bounds__(kRowWarps * 32, 7)
 gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                    float* __restrict__ m, float* __restrict__ l, float* __restrict__ O,
-                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale, int64_t kv_slice) {
+                   const Cols cols, int64_t row_begin, int64_t n_rows, int use_nan, float scale, int64_t kv_slice,
+                   int rows_per_cta) {
   __shared__ RowCtaShared sh;
   __shared__ float4 s_acc[kRowWarps][D / 4];
   const size_t z = blockIdx.y;
-  gather_rows_cta<D, Cols>(blockIdx.x, Q + z * n_rows * D, K + z * kv_slice, V + z * kv_slice, m + z * n_rows, l + z * n_rows,
-                           O + z * n_rows * D, cols, row_begin, n_rows, use_nan, scale, sh, s_acc);
+  gather_rows_cta<D, Cols>(blockIdx.x, rows_per_cta, Q + z * n_rows * D, K + z * kv_slice, V + z * kv_slice, m + z * n_rows,
+                           l + z * n_rows, O + z * n_rows * D, cols, row_begin, n_rows, use_nan, scale, sh, s_acc);
 }
 
 // Same, for a shard whose long rows were listed beforehand (the explicit-mask plan lists the rows whose residual
@@ -403,7 +430,8 @@ gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __rest
                                 int64_t n_rows, int use_nan, float scale, const PlanHeader* __restrict__ hdr,
                                 const PlanHeader want, int* __restrict__ err, const int4* __restrict__ split_items,
                                 const unsigned int* __restrict__ n_split_items, long long cap_items,
-                                unsigned int* __restrict__ split_done, float* __restrict__ split_part) {
+                                unsigned int* __restrict__ split_done, float* __restrict__ split_part,
+                                int rows_per_cta) {
   __shared__ RowCtaShared sh;
   __shared__ float4 s_acc[kRowWarps][D / 4];
   __shared__ unsigned int s_last;
@@ -412,8 +440,8 @@ gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __rest
     return;
   }
   if ((int)blockIdx.x >= n_list_blocks) {
-    gather_rows_cta<D, Cols>((int64_t)blockIdx.x - n_list_blocks, Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan,
-                             scale, sh, s_acc);
+    gather_rows_cta<D, Cols>((int64_t)blockIdx.x - n_list_blocks, rows_per_cta, Q, K, V, m, l, O, cols, row_begin, n_rows,
+                             use_nan, scale, sh, s_acc);
     return;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -28,11 +28,12 @@ int launch_gather(const float* Q, const float* K, const float* V, float* m, floa
                   const Cols& cols, int64_t row_begin, int64_t n_rows, int use_nan, cudaStream_t st, int64_t n_slices = 1,
                   int64_t kv_slice = 0) {
   if (n_rows <= 0) return SPFA_OK;
-  const int64_t blocks = (n_rows + kRowWarps - 1) / kRowWarps;
+  const int per_cta = rows_per_cta_for(n_rows, n_slices);
+  const int64_t blocks = (n_rows + per_cta - 1) / per_cta;
   if (blocks > 0x7fffffffLL || n_slices > 65535) return SPFA_ERR_TOO_LARGE;
   const float scale = 1.0f / sqrtf((float)D);
   gather_rows_kernel<D, Cols><<<dim3((unsigned)blocks, (unsigned)n_slices), kRowWarps * 32, 0, st>>>(
-      Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, kv_slice);
+      Q, K, V, m, l, O, cols, row_begin, n_rows, use_nan, scale, kv_slice, per_cta);
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_GATHER);
   return launch_status();
@@ -378,7 +379,8 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   if (rc) return rc;
   // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
   const float scale = 1.0f / sqrtf((float)D);
-  const int64_t row_blocks = (n_rows + kRowWarps - 1) / kRowWarps;
+  const int per_cta = rows_per_cta_for(n_rows, 1);
+  const int64_t row_blocks = (n_rows + per_cta - 1) / per_cta;
   const int list_blocks = (int)(row_blocks < 512 ? row_blocks : 512);
   if (row_blocks + list_blocks > 0x7fffffffLL) return SPFA_ERR_TOO_LARGE;
   int* err = nullptr;
@@ -388,7 +390,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
     ResidualCols cols{row_off, plan.res_cnt, plan.res_col, (uint32_t)kListedRowSlots};
     gather_rows_listed_first_kernel<D, ResidualCols><<<(unsigned)(row_blocks + list_blocks), kRowWarps * 32, 0, st>>>(
         Q, K, V, m, l, O, cols, listed, plan.heavy_rows, plan.heavy_count, list_blocks, 0, n_rows, 0, scale, plan.header,
-        want, err, plan.split_items, plan.split_count, plan.cap_items, plan.split_done, plan.split_part);
+        want, err, plan.split_items, plan.split_count, plan.cap_items, plan.split_done, plan.split_part, per_cta);
   } else {
     const uint32_t klo = (uint32_t)key_begin, khi = (uint32_t)(key_end < Lk ? key_end : Lk);
     (void)cyclic;  // klo > khi is the cyclic range for the functor and for the tile filter alike
@@ -399,7 +401,7 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
                                                                         plan.heavy_count, list_blocks, 0, n_rows, 0, scale,
                                                                         plan.header, want, err, plan.split_items,
                                                                         plan.split_count, plan.cap_items, plan.split_done,
-                                                                        plan.split_part);
+                                                                        plan.split_part, per_cta);
   }
   g_launches.fetch_add(1);
   g_last_path.store(SPFA_PATH_TILED);
