@@ -197,7 +197,7 @@ struct ResidualRangeCols {
 };
 
 inline size_t explicit_plan_smem_bytes(int64_t n_key_tiles, int bn) {
-  const size_t hist = (size_t)(n_key_tiles + 1) / 2 * 4;  // 16-bit counters, two per word
+  const size_t hist = ((size_t)(n_key_tiles + 1) / 2 + 15) / 16 * 16 * 4;  // 16-bit counters, two per word, whole 64-byte groups
   const size_t masks = (size_t)tile::kMaxDenseTiles * (bn / 32) * 128 * 4;
   const size_t words = (size_t)(n_key_tiles + 31) / 32;
   return (hist > masks ? hist : masks) + words * 4 + (words + 3) / 4 * 4;
@@ -239,7 +239,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   constexpr uint32_t kNoKey = 0xffffffffu;
   extern __shared__ uint32_t plan_smem[];
   const int n_words = (n_key_tiles + 31) / 32;
-  const int n_hist_words = (n_key_tiles + 1) / 2;
+  const int n_hist_words = ((n_key_tiles + 1) / 2 + 15) / 16 * 16;  // the counters of 32 key tiles are four 16-byte loads
   const int region = (n_hist_words > MAXT * NC * 128) ? n_hist_words : MAXT * NC * 128;
   // Entry counts as 16-bit halves of 32-bit words. A count beyond 65535 (only possible with heavily duplicated
   // entries) carries into its neighbour: that can only change which tiles are CALLED dense, never the result,
@@ -254,7 +254,9 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   __shared__ int s_sel[MAXT];                    // key tile of slot t
   __shared__ int s_dirty[MAXT];
   __shared__ int s_map[MAXT];                    // slot -> position among the clean slots, or -1
+  __shared__ uint8_t s_tab[256];                 // slot + 1 of key tile kt_lo + i while the dense tiles span < 256 tiles
   __shared__ int s_nt, s_nclean, s_redo;
+  __shared__ int s_next_row[2];  // rows are claimed one at a time (row lengths differ widely): step 3, step 5 again
   __shared__ long long s_moff;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t b = blockIdx.x;
@@ -277,6 +279,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   for (int k = tid; k < n_hist_words; k += kPlanThreads) hist[k] = 0;
   for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
+  if (tid < 2) s_next_row[tid] = kPlanWarps;
   __syncthreads();
 
   // ---- 1. histogram over key tiles, from every kPlanSampleStride-th row of the block ----
@@ -308,41 +311,85 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   __syncthreads();
   min_entries = (min_entries + kPlanSampleStride - 1) / kPlanSampleStride;
 
-  // ---- 2. dense tiles, ascending: each warp scans a contiguous range of tiles, 32 at a time (lane <-> tile,
-  //         so the ballot of a step is the step's word of dense_bits and the shared-memory reads do not conflict) ----
-  const int per_w = ((n_key_tiles + kPlanWarps - 1) / kPlanWarps + 31) / 32 * 32;
-  const int w_lo = warp * per_w, w_hi = (w_lo + per_w < n_key_tiles) ? (w_lo + per_w) : n_key_tiles;
-  int mine = 0;  // dense tiles in this warp's range (warp-uniform)
-  for (int k0 = w_lo; k0 < w_hi; k0 += 32) {
-    const int k = k0 + lane;
-    mine += __popc(__ballot_sync(kFullMask, k < w_hi && count_of(k) >= (uint32_t)min_entries));
-  }
-  if (lane == 0) s_warp_cnt[warp] = mine;
-  __syncthreads();
-  int before = 0, total = 0;
-  for (int wv = 0; wv < kPlanWarps; ++wv) {
-    before += (wv < warp) ? s_warp_cnt[wv] : 0;
-    total += s_warp_cnt[wv];
-  }
-  if (tid == 0) s_nt = (total < MAXT) ? total : MAXT;
-  if (mine > 0 && before < MAXT)
-    for (int k0 = w_lo; k0 < w_hi; k0 += 32) {
-      const int k = k0 + lane;
-      const bool dense = k < w_hi && count_of(k) >= (uint32_t)min_entries;
-      const uint32_t bal = __ballot_sync(kFullMask, dense);
-      const int idx = before + __popc(bal & ((1u << lane) - 1u));
-      const bool keep = dense && idx < MAXT;
-      const uint32_t kept = __ballot_sync(kFullMask, keep);
-      if (keep) s_sel[idx] = k;
-      if (lane == 0 && kept) dense_bits[k0 >> 5] = kept;  // w_lo is a multiple of 32: one word per step
-      before += __popc(bal);
+  // ---- 2. dense tiles, ascending. A lane turns the 32 counters behind one word of dense_bits into that word (SIMD
+  //         compares on the 16-bit halves); each warp owns a contiguous range of words, so the ranges are in tile order ----
+  {
+    const uint32_t thr = (min_entries < 1) ? 1u : (min_entries > 0xffff ? 0xffffu : (uint32_t)min_entries);
+    const uint32_t thr2 = thr | (thr << 16);
+    auto dense_word = [&](int w) -> uint32_t {
+      const uint4* h4 = reinterpret_cast<const uint4*>(hist + (size_t)w * 16);
+      auto two = [&](uint32_t x) -> uint32_t {  // bit 0 / 1: low / high counter >= thr
+        const uint32_t r = __vcmpgeu2(x, thr2);
+        return (r & 1u) | ((r >> 15) & 2u);
+      };
+      uint32_t bits = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 v = h4[q];
+        bits |= (two(v.x) | (two(v.y) << 2) | (two(v.z) << 4) | (two(v.w) << 6)) << (8 * q);
+      }
+      return bits;
+    };
+    const int per_w = ((n_words + kPlanWarps - 1) / kPlanWarps + 31) / 32 * 32;
+    const int w_lo = warp * per_w, w_hi = (w_lo + per_w < n_words) ? (w_lo + per_w) : n_words;
+    int mine = 0;  // dense tiles in this warp's range
+    for (int w0 = w_lo; w0 < w_hi; w0 += 32) {
+      const int w = w0 + lane;
+      if (w < w_hi) {
+        const uint32_t dw = dense_word(w);
+        dense_bits[w] = dw;
+        mine += __popc(dw);
+      }
     }
+    mine = __reduce_add_sync(kFullMask, mine);
+    if (lane == 0) s_warp_cnt[warp] = mine;
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int wv = 0; wv < kPlanWarps; ++wv) {
+      before += (wv < warp) ? s_warp_cnt[wv] : 0;
+      total += s_warp_cnt[wv];
+    }
+    if (tid == 0) s_nt = (total < MAXT) ? total : MAXT;
+    if (mine > 0)  // number the warp's dense tiles; those beyond the MAXT-th lose their bit
+      for (int w0 = w_lo; w0 < w_hi; w0 += 32) {
+        const int w = w0 + lane;
+        uint32_t dw = (w < w_hi) ? dense_bits[w] : 0u;
+        const int cnt = __popc(dw);
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(kFullMask, incl, o);
+          if (lane >= o) incl += v;
+        }
+        int idx = before + incl - cnt;
+        if (cnt) {
+          uint32_t keep_w = dw;
+          for (uint32_t left = dw; left; left &= left - 1u) {
+            const int bit = __ffs(left) - 1;
+            if (idx < MAXT) s_sel[idx] = w * 32 + bit;
+            else keep_w &= ~(1u << bit);
+            ++idx;
+          }
+          if (keep_w != dw) dense_bits[w] = keep_w;
+        }
+        before += __shfl_sync(kFullMask, incl, 31);
+      }
+  }
   __syncthreads();  // the histogram is dead from here on: its storage becomes the masks
   const int nt = s_nt;
   for (int w = tid; w < n_words; w += kPlanThreads) {
     int c = 0;
     for (int t = 0; t < nt; ++t) c += ((s_sel[t] >> 5) < w);
     dense_before[w] = (uint8_t)c;
+  }
+  // dense tiles lie in [kt_lo, kt_lo + kt_span] (s_sel ascends); a key tile outside is residual without a lookup
+  const uint32_t kt_lo = nt ? (uint32_t)s_sel[0] : 1u, kt_span = nt ? (uint32_t)s_sel[nt - 1] - kt_lo : 0u;
+  const bool use_tab = kt_span < 256u;  // the usual case (a band, a few clusters): one byte load answers the lookup
+  if (tid < 256) {
+    uint32_t v = 0;
+    for (int t = 0; t < nt; ++t)
+      if ((uint32_t)s_sel[t] == kt_lo + (uint32_t)tid) v = (uint32_t)t + 1u;
+    s_tab[tid] = (uint8_t)v;
   }
   // slot + 1 of a dense key tile, 0 for any other
   auto slot1_of = [&](uint32_t kt) -> uint32_t {
@@ -353,10 +400,13 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   // ---- 3. bit masks of the dense tiles (duplicates demote a tile) and, in the same walk, 5. the residual list ----
   for (int i = tid; i < nt * NC * 128; i += kPlanThreads) masks[i] = 0;
   __syncthreads();
-  // dense tiles lie in [kt_lo, kt_lo + kt_span] (s_sel ascends); a key tile outside is residual without a lookup
-  const uint32_t kt_lo = nt ? (uint32_t)s_sel[0] : 1u, kt_span = nt ? (uint32_t)s_sel[nt - 1] - kt_lo : 0u;
   const uint32_t lanes_below = (1u << lane) - 1u;
-  for (int rl = warp; rl < nr; rl += kPlanWarps) {
+  auto claim_row = [&](int which) -> int {
+    int nxt = 0;
+    if (lane == 0) nxt = atomicAdd(&s_next_row[which], 1);
+    return __shfl_sync(kFullMask, nxt, 0);
+  };
+  for (int rl = warp; rl < nr; rl = claim_row(0)) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
     uint32_t last_col = 0;  // column of the previous step's last entry
@@ -365,37 +415,31 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
       const int lo = (a > base) ? (int)(a - base) : 0, hi = (z - base < 128) ? (int)(z - base) : 128;  // warp-uniform
       uint32_t cu[4] = {kNoKey, kNoKey, kNoKey, kNoKey};
       if (lane * 4 < hi) load_four_columns(col, base + lane * 4, nnz, kNoKey, cu);
-      uint32_t keep_bits = 0;               // bit j: entry j of this lane stays on the gather path
-      uint32_t w_run = kNoKey, b_run = 0;   // a run of entries of one mask word inside this lane
-      auto flush_run = [&]() {
-        const uint32_t old = atomicOr(&masks[w_run], b_run);
-        if (old & b_run) s_dirty[w_run / (NC * 128)] = 1;  // the pair occurred in another lane or an earlier step
-      };
+      // bit j: entry j of this lane belongs to the row
+      const int lo_l = min(max(lo - lane * 4, 0), 4), hi_l = min(max(hi - lane * 4, 0), 4);
+      const uint32_t in_row = ((1u << hi_l) - 1u) & ~((1u << lo_l) - 1u);
+      if (in_row != 0xfu) {  // positions outside the row take the smallest / largest column: they never break the order
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (!((in_row >> j) & 1u)) cu[j] = (j < lo_l) ? 0u : kNoKey;
+      }
+      uint32_t keep_bits = 0;  // bit j: entry j of this lane stays on the gather path
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int p = lane * 4 + j;
-        // positions outside the row take the smallest / largest column, so they never break the ascending order
-        if (p < lo) cu[j] = 0u;
-        if (p >= hi) cu[j] = kNoKey;
         const uint32_t c = cu[j];
-        if (p < lo || p >= hi || c >= Lk32) continue;
-        const uint32_t kt = c / BN;
-        const uint32_t slot1 = (kt - kt_lo <= kt_span) ? slot1_of(kt) : 0u;
+        if (!((in_row >> j) & 1u) || c >= Lk32) continue;
+        const uint32_t kt = c / BN, dk = kt - kt_lo;
+        uint32_t slot1 = 0;
+        if (dk <= kt_span) slot1 = use_tab ? (uint32_t)s_tab[dk] : slot1_of(kt);
         if (!slot1) {
           keep_bits |= 1u << j;
           continue;
         }
-        const uint32_t kk = c - kt * BN;
-        const uint32_t word = ((slot1 - 1) * NC + (kk >> 5)) * 128 + rl, bit = 1u << (kk & 31);
-        if (word != w_run) {
-          if (w_run != kNoKey) flush_run();
-          w_run = word;
-          b_run = 0;
-        }
-        if (b_run & bit) s_dirty[word / (NC * 128)] = 1;  // the pair occurs twice: a bit cannot say that
-        b_run |= bit;
+        // lanes that hit the same mask word are serialised by the memory pipe; `old` tells a pair that occurs twice
+        const uint32_t kk = c - kt * BN, bit = 1u << (kk & 31);
+        const uint32_t old = atomicOr(&masks[((slot1 - 1) * NC + (kk >> 5)) * 128 + rl], bit);
+        if (old & bit) s_dirty[slot1 - 1] = 1;  // a bit cannot say "twice"
       }
-      if (w_run != kNoKey) flush_run();
       {  // ascending order of the row's columns (all entries, so the kept ones as well)
         const uint32_t before = __shfl_up_sync(kFullMask, cu[3], 1);
         const uint32_t prev = (lane == 0) ? last_col : before;
@@ -465,7 +509,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
 
   // ---- 5 again, only if a tile was demoted: membership is all that is asked of the bits now ----
   if (!s_redo) return;
-  for (int rl = warp; rl < nr; rl += kPlanWarps) {
+  for (int rl = warp; rl < nr; rl = claim_row(1)) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
     uint32_t kept = 0;
     for (int64_t base = (a < z) ? RowSteps(col, a).first : z; base < z; base += 128) {
