@@ -280,7 +280,7 @@ def parse_args():
                     help="N>1, explicit masks: how K/V chunks travel (default: peer copies where CUDA IPC works, else NCCL)")
     ap.add_argument("--phase1-rounds", type=int, default=None,
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
-                         "(default: about 4/7 of the rounds; N-1 = a single pass after the exchange)")
+                         "(default N-1: a single pass after the exchange, with the mask inspection overlapping it)")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one process, one GPU: time only the first rank's share of an N-way strong-scaling split with K/V "
                          "resident (profiling the per-rank kernels without N GPUs); implies --no-e2e --no-cpu-baseline")
@@ -602,8 +602,7 @@ def run_ours(args, rank, world, dev):
             def step():
                 ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf,
                                                                            a, b), before, rounds_in_phase1=args.phase1_rounds)
-            p1, p2 = ex.two_phase_ranges(args.phase1_rounds if args.phase1_rounds is not None
-                                         else ((4 * (world - 1) + 6) // 7 if world > 2 else world - 1))
+            p1, p2 = ex.two_phase_ranges(args.phase1_rounds if args.phase1_rounds is not None else world - 1)
             exchange_note = ("%d rounds of %s; the mask inspection overlaps them, and the forward runs as %s" %
                              (world - 1, how, "one pass after the last round" if p2 is None else
                               "two passes: one over the keys of the own chunk and its nearest neighbours while the other "

@@ -295,11 +295,13 @@ class KeyChunkExchange:
     def run_two_phase(self, on_keys, before=None, own_ready=None, rounds_in_phase1=None):
         """Like run(), with the forward cut into at most two passes instead of one per chunk: pass 1 over the keys that
         have landed after `rounds_in_phase1` rounds, pass 2 over the rest once every round is done. Short per-row key
-        lists make a pass cost far more than its share of the keys (every pass revisits every row), so few large
-        passes beat many small ones; `rounds_in_phase1 = None` picks about 4/7 of the rounds, 0 rounds means "own
-        chunk first", world-1 or more a single pass after the whole exchange. on_keys(key_begin, key_end, i)."""
+        lists make a pass cost far more than its share of the keys (every pass revisits every row: its offsets, its Q
+        row, its running state), so few large passes beat many small ones, and on 4 GPUs one pass after the last round
+        (with the mask inspection overlapping the rounds) beat every two-pass split measured; that is what
+        `rounds_in_phase1 = None` picks. 0 rounds means "own chunk first", world-1 or more a single pass.
+        on_keys(key_begin, key_end, i)."""
         if rounds_in_phase1 is None:
-            rounds_in_phase1 = (4 * (self.world - 1) + 6) // 7 if self.world > 2 else self.world - 1
+            rounds_in_phase1 = self.world - 1
         p1, p2 = self.two_phase_ranges(rounds_in_phase1)
         k = min(rounds_in_phase1, self.world - 1) if p2 is not None else self.world - 1
         if not self.cuda:
