@@ -514,7 +514,7 @@ def roofline_of(job, workload, kernel_ms, tiled, peaks, peak_src, full_size):
     peak = peaks["hbm_gbs"]
     algorithmic = job.bytes / (kernel_ms * 1e-3) / 1e9
     traffic = recorded_traffic(f"gather_{workload}") if full_size else None
-    if job.kind in ("csr", "coo"):
+    if job.kind in ("csr", "coo", "bigbird"):
         real = (traffic / (kernel_ms * 1e-3) / 1e9) if traffic else None
         return {"bound": "hbm", "achieved": real, "peak": peak, "unit": "GB/s", "frac": (real / peak) if real else None,
                 "traffic": traffic, "effective_gbs": algorithmic,
@@ -638,7 +638,7 @@ def run_ours(args, rank, world, dev):
     if rank != 0:
         return None
     kernel_ms = statistics.mean(times_c)
-    full = WORKLOADS[args.workload]["L"] == FULL_SIZE_L[args.workload] and world == 1
+    full = WORKLOADS[args.workload]["L"] == FULL_SIZE_L[args.workload] and world == 1 and args.shard_of <= 1
     roof = roofline_of(job, args.workload, kernel_ms, tiled, peaks, peak_src, full)
     scaling = "weak" if job.weak else "strong"
     desc = job.w["desc"]
