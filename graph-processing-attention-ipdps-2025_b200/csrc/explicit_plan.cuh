@@ -256,6 +256,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   __shared__ int s_map[MAXT];                    // slot -> position among the clean slots, or -1
   __shared__ uint8_t s_tab[256];                 // slot + 1 of key tile kt_lo + i while the dense tiles span < 256 tiles
   __shared__ int s_nt, s_nclean, s_redo;
+  __shared__ int s_sampled, s_in_dense;  // sampled entries of the block / those that fell into its dense tiles
   __shared__ int s_next_row[2];  // rows are claimed one at a time (row lengths differ widely): step 3, step 5 again
   __shared__ long long s_moff;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -280,6 +281,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   for (int k = tid; k < n_words; k += kPlanThreads) dense_bits[k] = 0;
   if (tid < MAXT) s_dirty[tid] = 0;
   if (tid < 2) s_next_row[tid] = kPlanWarps;
+  if (tid == 0) s_sampled = s_in_dense = 0;
   __syncthreads();
 
   // ---- 1. histogram over key tiles, from every kPlanSampleStride-th row of the block ----
@@ -288,6 +290,7 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
   const uint32_t Lk32 = (Lk < 0xffffffffLL) ? (uint32_t)Lk : 0xffffffffu;  // kNoKey is never a valid column
   for (int rl = warp * kPlanSampleStride; rl < nr; rl += kPlanWarps * kPlanSampleStride) {
     const int64_t a = (int64_t)s_off[rl], z = (int64_t)s_off[rl + 1];
+    if (lane == 0 && z > a) atomicAdd(&s_sampled, (int)((z - a < (1 << 20)) ? (z - a) : (1 << 20)));
     for (int64_t base = (a < z) ? RowSteps(col, a).first : z; base < z; base += 128) {
       const int lo = (a > base) ? (int)(a - base) : 0, hi = (z - base < 128) ? (int)(z - base) : 128;  // warp-uniform
       uint32_t cu[4];
@@ -375,8 +378,13 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
         before += __shfl_sync(kFullMask, incl, 31);
       }
   }
-  __syncthreads();  // the histogram is dead from here on: its storage becomes the masks
+  __syncthreads();
   const int nt = s_nt;
+  if (tid < nt) atomicAdd(&s_in_dense, (int)count_of(s_sel[tid]));
+  __syncthreads();  // the histogram is dead from here on: its storage becomes the masks
+  // A block whose entries lie almost all in dense tiles (block-structured masks) is walked with a warp-level shortcut
+  // for runs of consecutive columns; elsewhere the test for it would only cost issue slots.
+  const bool dense_heavy = (long long)s_in_dense * 10 >= (long long)s_sampled * 9 && s_in_dense > 0;
   for (int w = tid; w < n_words; w += kPlanThreads) {
     int c = 0;
     for (int t = 0; t < nt; ++t) c += ((s_sel[t] >> 5) < w);
@@ -424,10 +432,28 @@ explicit_plan_kernel(const uint64_t* __restrict__ row_off, const uint32_t* __res
           if (!((in_row >> j) & 1u)) cu[j] = (j < lo_l) ? 0u : kNoKey;
       }
       uint32_t keep_bits = 0;  // bit j: entry j of this lane stays on the gather path
+      bool done = false;
+      if (dense_heavy) {  // every busy lane holds four consecutive columns of one 32-key group: one lookup, one atomic
+        const bool run4 = in_row == 0xfu && cu[3] < Lk32 && cu[1] == cu[0] + 1u && cu[2] == cu[0] + 2u &&
+                          cu[3] == cu[0] + 3u && ((cu[0] ^ cu[3]) >> 5) == 0u;
+        done = __all_sync(kFullMask, run4 || in_row == 0u);
+        if (done && run4) {
+          const uint32_t kt = cu[0] / BN, dk = kt - kt_lo;
+          uint32_t slot1 = 0;
+          if (dk <= kt_span) slot1 = use_tab ? (uint32_t)s_tab[dk] : slot1_of(kt);
+          if (slot1) {
+            const uint32_t kk = cu[0] - kt * BN, bits = 0xfu << (kk & 31);
+            const uint32_t old = atomicOr(&masks[((slot1 - 1) * NC + (kk >> 5)) * 128 + rl], bits);
+            if (old & bits) s_dirty[slot1 - 1] = 1;
+          } else {
+            keep_bits = 0xfu;
+          }
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t c = cu[j];
-        if (!((in_row >> j) & 1u) || c >= Lk32) continue;
+        if (done || !((in_row >> j) & 1u) || c >= Lk32) continue;
         const uint32_t kt = c / BN, dk = kt - kt_lo;
         uint32_t slot1 = 0;
         if (dk <= kt_span) slot1 = use_tab ? (uint32_t)s_tab[dk] : slot1_of(kt);
