@@ -421,8 +421,11 @@ gather_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, con
 // CTAs do the ordinary rows. Blocks are dispatched in index order, so the long rows start with the launch
 // instead of wherever their row number falls. The list length lives in device memory (it is produced there).
 // The lists come from a stored plan: its identity block is compared with the shape the caller passed first.
+// Eight CTAs per SM (64 registers, some spills) beat seven here: the residual rows of a split mask are short lists of
+// scattered keys, bound by load latency, so resident warps count for more than registers (2.89 -> 2.68 ms on the 1M-row
+// graph; nine CTAs: 2.90, ten: 3.45). The plain kernel above is closer to issue bound and loses 3-4 % at eight.
 template <int D, class Cols>
-__global__ void __launch_bounds__(kRowWarps * 32, 7)
+__global__ void __launch_bounds__(kRowWarps * 32, 8)
 gather_rows_listed_first_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                                 float* __restrict__ m, float* __restrict__ l, float* __restrict__ O, const Cols cols,
                                 const Cols listed, const int* __restrict__ row_list,
