@@ -280,7 +280,8 @@ def parse_args():
                     help="N>1, explicit masks: how K/V chunks travel (default: peer copies where CUDA IPC works, else NCCL)")
     ap.add_argument("--phase1-rounds", type=int, default=None,
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
-                         "(default N-1: a single pass after the exchange, with the mask inspection overlapping it)")
+                         "(default: not this schedule but run_tiles_first -- inspection and the own chunk's dense tiles overlap the "
+                         "exchange, everything else follows it; N-1 = a single pass after the exchange)")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one process, one GPU: time only the first rank's share of an N-way strong-scaling split with K/V "
                          "resident (profiling the per-rank kernels without N GPUs); implies --no-e2e --no-cpu-baseline")
@@ -599,14 +600,26 @@ def run_ours(args, rank, world, dev):
             plan_buf = job.plan if job.plan is not None else job.build_plan(capi)
             before = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
 
-            def step():
-                ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf,
-                                                                           a, b), before, rounds_in_phase1=args.phase1_rounds)
-            p1, p2 = ex.two_phase_ranges(args.phase1_rounds if args.phase1_rounds is not None else world - 1)
-            exchange_note = ("%d rounds of %s; the mask inspection overlaps them, and the forward runs as %s" %
-                             (world - 1, how, "one pass after the last round" if p2 is None else
-                              "two passes: one over the keys of the own chunk and its nearest neighbours while the other "
-                              "chunks travel, one over the rest after the last round"))
+            if args.phase1_rounds is None:  # default: dense tiles of the own chunk while the other chunks travel
+                def step():
+                    ex.run_tiles_first(
+                        lambda a, b: capi.planned_forward_parts(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b,
+                                                                capi.PLAN_DENSE_TILES),
+                        lambda: capi.planned_forward_parts(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf, 0, job.L,
+                                                           capi.PLAN_RESIDUAL), before)
+                exchange_note = ("%d rounds of %s; the mask inspection and the dense tiles of the own key chunk overlap them; "
+                                 "the other dense tiles and the residual entries of all keys follow the last round"
+                                 % (world - 1, how))
+            else:
+                def step():
+                    ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O,
+                                                                               plan_buf, a, b),
+                                     before, rounds_in_phase1=args.phase1_rounds)
+                p1, p2 = ex.two_phase_ranges(args.phase1_rounds)
+                exchange_note = ("%d rounds of %s; the mask inspection overlaps them, and the forward runs as %s" %
+                                 (world - 1, how, "one pass after the last round" if p2 is None else
+                                  "two passes: one over the keys that have landed after %d round(s) while the other chunks "
+                                  "travel, one over the rest after the last round" % args.phase1_rounds))
         elif explicit:
             def step():
                 ex.exchange_only()
@@ -806,12 +819,24 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
             q_up.record(s_in)
         job.reset_state()
         if overlap:
-            def on_chunk(a, b, i):
-                if i == 0:
-                    cur.wait_event(q_up)
-                capi.planned_forward_keys(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b)
-            ex.run_two_phase(on_chunk, None if args.planned else (lambda: job.build_plan(capi, out=plan_buf)),
-                             own_ready=kv_up, rounds_in_phase1=args.phase1_rounds)
+            inspect = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
+            if args.phase1_rounds is None:
+                first = [True]
+
+                def on_tiles(a, b):
+                    if first[0]:
+                        cur.wait_event(q_up)
+                        first[0] = False
+                    capi.planned_forward_parts(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b, capi.PLAN_DENSE_TILES)
+                ex.run_tiles_first(on_tiles, lambda: capi.planned_forward_parts(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf,
+                                                                                0, job.L, capi.PLAN_RESIDUAL),
+                                   inspect, own_ready=kv_up)
+            else:
+                def on_chunk(a, b, i):
+                    if i == 0:
+                        cur.wait_event(q_up)
+                    capi.planned_forward_keys(dQ, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b)
+                ex.run_two_phase(on_chunk, inspect, own_ready=kv_up, rounds_in_phase1=args.phase1_rounds)
         else:
             cur.wait_event(q_up)
             if explicit:
@@ -829,8 +854,9 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
     out["e2e"] = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                   "api": "per rank: K/V chunk and Q rows host->device on a copy stream, " +
-                         ("sharding.KeyChunkExchange.run_two_phase (exchange rounds start when the chunk is up; inspection, "
-                          "capi.planned_forward_keys over the arrived keys, then over the rest)" if overlap else
+                         ("sharding.KeyChunkExchange (exchange rounds start when the chunk is up; inspection and the own "
+                          "chunk's dense tiles meanwhile, the other tiles and the residual entries after the last round)"
+                          if overlap else
                           "K/V replication, capi.*_forward(row range)") + ", O rows device->host; bytes are the sum over ranks"}
     return out
 

@@ -28,7 +28,7 @@ EXPORTS = (
     "spfa_status_string", "spfa_abi_version", "spfa_set_path", "spfa_get_path", "spfa_last_path", "spfa_launch_count", "spfa_last_device_error",
     "spfa_csr_workspace_bytes", "spfa_csr_forward_f32",
     "spfa_coo_workspace_bytes", "spfa_coo_min_workspace_bytes", "spfa_coo_forward_f32",
-    "spfa_selftest_wait_limit", "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_planned_forward_keys_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
+    "spfa_selftest_wait_limit", "spfa_explicit_plan_bytes", "spfa_csr_plan_build", "spfa_coo_plan_build", "spfa_planned_forward_f32", "spfa_planned_forward_keys_f32", "spfa_planned_forward_parts_f32", "spfa_coo_static_max_rows", "spfa_coo_forward_f32_static",
     "spfa_local_workspace_bytes", "spfa_local_forward_f32",
     "spfa_local_1d_dilated_workspace_bytes", "spfa_local_1d_dilated_forward_f32",
     "spfa_local_2d_dilated_workspace_bytes", "spfa_local_2d_dilated_forward_f32",
@@ -132,6 +132,8 @@ def lib() -> ctypes.CDLL:
     L.spfa_planned_forward_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, vp]
     L.spfa_planned_forward_keys_f32.restype = i32
     L.spfa_planned_forward_keys_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, i64, i64, vp]
+    L.spfa_planned_forward_parts_f32.restype = i32
+    L.spfa_planned_forward_parts_f32.argtypes = [vp] * 6 + [i64, i64, i64, i32, i32, vp, sz, i64, i64, i32, vp]
     L.spfa_coo_static_max_rows.restype = i64
     L.spfa_coo_forward_f32_static.restype = i32
     L.spfa_coo_forward_f32_static.argtypes = [vp] * 5 + [i64] + [vp] * 3 + [i64, i64, i64, i32, i32, vp]
@@ -347,6 +349,21 @@ def planned_forward(Q, K, V, m, l, O, plan: ExplicitPlan, use_nan=False):
     with torch.cuda.device(dev):
         check(lib().spfa_planned_forward_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows, plan.nnz,
                                              plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes, _stream(dev)))
+    return O
+
+
+PLAN_DENSE_TILES, PLAN_RESIDUAL = 1, 2
+
+
+def planned_forward_parts(Q, K, V, m, l, O, plan: ExplicitPlan, key_begin: int, key_end: int, parts: int, use_nan=False):
+    """planned_forward_keys for the dense tiles (PLAN_DENSE_TILES), the residual entries (PLAN_RESIDUAL) or both."""
+    dev = _f32(Q, K, V, m, l, O)
+    if Q.shape[0] != plan.n_rows or K.shape[0] != plan.n_keys or Q.shape[1] != plan.d:
+        raise SpfaError(-1, "the plan was built for another shape")
+    with torch.cuda.device(dev):
+        check(lib().spfa_planned_forward_parts_f32(_ptr(Q), _ptr(K), _ptr(V), _ptr(m), _ptr(l), _ptr(O), plan.n_rows,
+                                                   plan.nnz, plan.n_keys, plan.d, int(use_nan), plan.ptr, plan.nbytes,
+                                                   int(key_begin), int(key_end), int(parts), _stream(dev)))
     return O
 
 

@@ -342,7 +342,7 @@ __global__ void nan_fill_empty_rows_kernel(const uint64_t* __restrict__ row_off,
 template <int D>
 int launch_from_plan(const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m, float* l,
                      float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, int64_t key_begin, int64_t key_end,
-                     cudaStream_t st) {
+                     cudaStream_t st, int parts = 3) {  // parts: bit 0 the dense tiles, bit 1 the residual entries
   constexpr int BN = TileCfg<D>::BN, kRows = TileCfg<D>::kRows;
   const HybridLayout h = hybrid_layout(n_rows, nnz, Lk, D);
   const ExplicitPlan plan = plan_view(h, ws);
@@ -375,8 +375,12 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, Lk, pitch, BN) ||
       !make_row_map(&tmV, V, D, Lk, pitch, BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
-  int rc = launch_band_raw<D, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
-  if (rc) return rc;
+  if (parts & 1) {
+    int rc = launch_band_raw<D, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
+    if (rc) return rc;
+    g_last_path.store(SPFA_PATH_TILED);
+  }
+  if (!(parts & 2)) return SPFA_OK;
   // everything else: one launch whose first CTAs take the long residual rows, the others the ordinary rows
   const float scale = 1.0f / sqrtf((float)D);
   const int per_cta = rows_per_cta_for(n_rows, 1);
@@ -410,11 +414,11 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
 
 inline int forward_from_plan(int d, const float* Q, const float* K, const float* V, const uint64_t* row_off, float* m,
                              float* l, float* O, int64_t n_rows, int64_t nnz, int64_t Lk, char* ws, cudaStream_t st,
-                             int64_t key_begin = 0, int64_t key_end = INT64_MAX) {
+                             int64_t key_begin = 0, int64_t key_end = INT64_MAX, int parts = 3) {
   switch (d) {
-    case 32: return launch_from_plan<32>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
-    case 64: return launch_from_plan<64>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
-    case 128: return launch_from_plan<128>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st);
+    case 32: return launch_from_plan<32>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st, parts);
+    case 64: return launch_from_plan<64>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st, parts);
+    case 128: return launch_from_plan<128>(Q, K, V, row_off, m, l, O, n_rows, nnz, Lk, ws, key_begin, key_end, st, parts);
   }
   return SPFA_ERR_EMBED_DIM;
 }
@@ -656,8 +660,16 @@ int spfa_planned_forward_f32(const float* Q, const float* K, const float* V, flo
 int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
                                   int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan, const void* plan,
                                   size_t plan_bytes, int64_t key_begin, int64_t key_end, void* stream) {
+  return spfa_planned_forward_parts_f32(Q, K, V, m, l, O, n_rows, nnz, Lk, d, use_nan, plan, plan_bytes, key_begin, key_end,
+                                        SPFA_PLAN_DENSE_TILES | SPFA_PLAN_RESIDUAL, stream);
+}
+
+int spfa_planned_forward_parts_f32(const float* Q, const float* K, const float* V, float* m, float* l, float* O,
+                                   int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan, const void* plan,
+                                   size_t plan_bytes, int64_t key_begin, int64_t key_end, int parts, void* stream) {
   int rc = check_common(Q, K, V, m, l, O, d);
   if (rc) return rc;
+  if (parts < 0 || parts > 3) return SPFA_ERR_BAD_ARG;
   if (n_rows <= 0 || nnz <= 0 || Lk <= 0 || Lk >= (1LL << 31)) return SPFA_ERR_BAD_ARG;
   if (key_begin < 0 || key_end < 0 || key_begin > Lk || (key_begin % 64) != 0) return SPFA_ERR_BAD_ARG;
   if (key_end > Lk) key_end = Lk;
@@ -674,9 +686,9 @@ int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V
     g_launches.fetch_add(1);
     if (launch_status() != SPFA_OK) return SPFA_ERR_LAUNCH;
   }
-  if (key_end == key_begin) return SPFA_OK;
+  if (key_end == key_begin || parts == 0) return SPFA_OK;
   return forward_from_plan(d, Q, K, V, offs, m, l, O, n_rows, nnz, Lk, base + spfa_coo_min_workspace_bytes(n_rows), st,
-                           key_begin, key_end);
+                           key_begin, key_end, parts);
 }
 
 int64_t spfa_coo_static_max_rows(void) { return kStaticCooMaxRows; }

@@ -292,6 +292,20 @@ class KeyChunkExchange:
             phase2 = (phase2[0], self.L)
         return phase1, phase2
 
+    def run_tiles_first(self, on_tiles, on_rest, before=None, own_ready=None):
+        """The schedule for a graph mask with a band: on_tiles(key_begin, key_end) for the own key chunk as soon as the
+        mask inspection (`before`) is done -- the dense tiles of a band read keys near the diagonal, i.e. mostly the own
+        chunk, and their pass costs nothing per row -- then, after the last round, on_tiles(the other keys: one cyclic
+        range) and on_rest() (everything that visits every row: the residual entries of ALL keys, once). With one rank
+        the three run back to back."""
+        p1, p2 = self.two_phase_ranges(0)
+
+        def on_keys(a, b, i):
+            on_tiles(a, b)
+            if p2 is None or i == 1:
+                on_rest()
+        self.run_two_phase(on_keys, before, own_ready, rounds_in_phase1=0)
+
     def run_two_phase(self, on_keys, before=None, own_ready=None, rounds_in_phase1=None):
         """Like run(), with the forward cut into at most two passes instead of one per chunk: pass 1 over the keys that
         have landed after `rounds_in_phase1` rounds, pass 2 over the rest once every round is done. Short per-row key

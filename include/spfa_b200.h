@@ -179,6 +179,17 @@ int spfa_planned_forward_keys_f32(const float* Q, const float* K, const float* V
                                   int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan,
                                   const void* plan, size_t plan_bytes,
                                   int64_t key_begin, int64_t key_end, void* stream);
+/* The same, for one part of the plan only: `parts` is SPFA_PLAN_DENSE_TILES, SPFA_PLAN_RESIDUAL or both. The dense
+ * tiles of a banded graph read keys near the diagonal only, i.e. mostly the K/V chunk a rank owns, and their pass
+ * costs nothing per row; the residual pass visits every row whatever the key range is. A multi-GPU caller therefore
+ * runs the dense tiles of its own key chunk while the other chunks travel, then the dense tiles of the other keys and
+ * the residual entries of all keys. No counterpart in the reference. */
+enum spfa_plan_parts { SPFA_PLAN_DENSE_TILES = 1, SPFA_PLAN_RESIDUAL = 2 };
+int spfa_planned_forward_parts_f32(const float* Q, const float* K, const float* V,
+                                   float* m, float* l, float* O,
+                                   int64_t n_rows, int64_t nnz, int64_t Lk, int d, int use_nan,
+                                   const void* plan, size_t plan_bytes,
+                                   int64_t key_begin, int64_t key_end, int parts, void* stream);
 
 /* ---- explicit COO mask, allocation-free variant ---------------------------------------------------
  * No counterpart in the reference (its COO kernel needs no scratch because it re-scans the row array

@@ -942,6 +942,27 @@ def test_planned_forward_split_along_the_key_axis(capi, orc, L, Lk, d, chunks, s
             assert_state_close(to_np(st), want, TOL_TILED, "cyclic key range and its complement")
 
 
+def test_planned_forward_by_parts(capi, orc):
+    """Dense tiles of one key range, dense tiles of its (cyclic) complement and the residual entries of all keys, as
+    three calls in any order, are the whole planned forward."""
+    L, Lk, d = 640, 1024, 64
+    mask = _band_plus_random(L, Lk, 48, 0.01, 12, empty_rows=(2,))
+    mask[9, ::2] = True
+    row_off, col = _csr_of(mask)
+    Q, K, V = seeded_qkv(L, d, 5, Lk)
+    want = orc.csr_forward(Q, K, V, row_off, col, use_nan=True)
+    plan = capi.csr_plan(dev(row_off), dev(col), Lk, d)
+    T, R = capi.PLAN_DENSE_TILES, capi.PLAN_RESIDUAL
+    for calls in (((256, 512, T), (512, 256, T), (0, Lk, R)), ((0, Lk, R), (704, 64, T), (64, 704, T)),
+                  ((0, 320, T | R), (320, Lk, T), (320, Lk, R))):
+        st = capi.new_state(L, d)
+        for n, (a, b, parts) in enumerate(calls):
+            capi.planned_forward_parts(dev(Q), dev(K), dev(V), *st, plan, a, b, parts, use_nan=(n == 0))
+        assert_state_close(to_np(st), want, TOL_TILED, f"parts {calls}")
+    with pytest.raises(capi.SpfaError):
+        capi.planned_forward_parts(dev(Q), dev(K), dev(V), *capi.new_state(L, d), plan, 0, Lk, 4)
+
+
 @pytest.mark.parametrize("L", [262144, 1048576])
 def test_full_size_coo_graph_split_vs_gather_and_oracle(capi, orc, L):
     """The benchmark's COO graph generator at a quarter of and at the benchmarked size (L=1048576: 1.6e8 entries, rows

@@ -167,6 +167,37 @@ def _exchange_worker(rank, world, port, tmp):
         ex.run_two_phase(on_keys, rounds_in_phase1=1 if world > 2 else 0)
         assert [c[2] for c in calls] == [0, 1]
         np.testing.assert_allclose(state2[2], state[2], rtol=0, atol=1e-12)
+        # dense tiles of the own chunk first, the other tiles and the residual pass after the last round
+        for t in (ex.K, ex.V):
+            t[:kb].fill_(float("nan"))
+            t[ke:].fill_(float("nan"))
+        order = []
+
+        def on_tiles(a, b):
+            inside = np.zeros(L, dtype=bool)
+            if a < b:
+                inside[a:b] = True
+            else:
+                inside[a:] = True
+                inside[:b] = True
+            assert not np.isnan(ex.K.numpy()[inside]).any()
+            order.append(("tiles", a, b, bool(np.isnan(ex.K.numpy()).any())))
+
+        def on_rest():
+            assert not np.isnan(ex.K.numpy()).any() and not np.isnan(ex.V.numpy()).any()
+            order.append(("rest",))
+
+        ex.run_tiles_first(on_tiles, on_rest, before=lambda: order.append(("before",)))
+        assert [o[0] for o in order] == ["before", "tiles", "tiles", "rest"]
+        assert (order[1][1], order[1][2]) == (kb, ke) and order[1][3]  # own chunk, while other chunks are still poison
+        covered = np.zeros(L, dtype=int)
+        for _, a, b, _ in order[1:3]:
+            if a < b:
+                covered[a:b] += 1
+            else:
+                covered[a:] += 1
+                covered[:b] += 1
+        assert (covered == 1).all()  # the two tile passes partition the keys
         np.savez(os.path.join(tmp, f"ex{rank}.npz"), rb=rb, re=re, O=state[2], l=state[1])
         dist.barrier()
     finally:
