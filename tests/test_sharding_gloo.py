@@ -90,6 +90,11 @@ def test_two_rank_row_sharding_matches_unsharded(pkg, orc, tmp_path):
         np.testing.assert_array_equal(got, want)
 
 
+def _exchange_case(world):
+    """(L, d): every rank owns at least one 64-key tile of K/V."""
+    return (192 if world <= 3 else 64 * world), 16
+
+
 def _exchange_worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)
@@ -98,7 +103,7 @@ def _exchange_worker(rank, world, port, tmp):
     pkg, orc = entry.load(), entry.load_oracle()
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        L, d = 192, 16
+        L, d = _exchange_case(world)
         Q, K, V = seeded_qkv(L, d, 31)
         _, row_off, col = random_csr(L, L, 0.15, 8, empty_rows=(7,))
         off_t, col_t = torch.from_numpy(row_off.astype(np.int64)), torch.from_numpy(col.astype(np.int32))
@@ -204,7 +209,7 @@ def _exchange_worker(rank, world, port, tmp):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 8])
 def test_key_chunk_exchange_orders_passes_behind_arrivals(pkg, orc, tmp_path, world):
     """The overlapped K/V replication: every pass runs only after its chunk has landed (the rest of the buffers is
     still poison), the own chunk comes first, all chunks are seen exactly once, and the passes chained through the
@@ -213,7 +218,7 @@ def test_key_chunk_exchange_orders_passes_behind_arrivals(pkg, orc, tmp_path, wo
     assert pkg.sharding.exchange_offsets(1) == [] and sorted(pkg.sharding.exchange_offsets(5)) == [1, 2, 3, 4]
     port = 31500 + (os.getpid() % 2000) + world
     mp.spawn(_exchange_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
-    L, d = 192, 16
+    L, d = _exchange_case(world)
     Q, K, V = seeded_qkv(L, d, 31)
     _, row_off, col = random_csr(L, L, 0.15, 8, empty_rows=(7,))
     want = orc.csr_forward(Q, K, V, row_off, col)
