@@ -283,7 +283,11 @@ class KeyChunkExchange:
         first = (self.rank - before) % self.world
         last = (self.rank + after) % self.world
         a, b = self.kv_ranges[first][0], self.kv_ranges[last][1]
-        if b == self.L and a == 0:
+        covered = sum(self.kv_ranges[(first + i) % self.world][1] - self.kv_ranges[(first + i) % self.world][0]
+                      for i in range(k + 1))
+        if covered == 0:  # empty chunks only (more ranks than key tiles): nothing in pass 1, everything in pass 2
+            return (a, a), (0, self.L)
+        if covered >= self.L or (b == self.L and a == 0):
             return (0, self.L), None
         b_wrapped = 0 if b == self.L else b
         phase1 = (a, b) if a < b else (a, b_wrapped)

@@ -225,3 +225,42 @@ def test_key_chunk_exchange_orders_passes_behind_arrivals(pkg, orc, tmp_path, wo
     parts = sorted((np.load(os.path.join(tmp_path, f"ex{r}.npz")) for r in range(world)), key=lambda p: int(p["rb"]))
     np.testing.assert_allclose(np.concatenate([p["O"] for p in parts]), want[2], rtol=0, atol=1e-12)
     np.testing.assert_allclose(np.concatenate([p["l"] for p in parts]), want[1], rtol=1e-12)
+
+
+def test_two_phase_ranges_partition_the_keys_even_with_empty_chunks(pkg):
+    """Whatever the chunks are (more ranks than key tiles leave some ranks an empty chunk), the two passes of every rank
+    cover every key exactly once, for every number of rounds in pass 1."""
+    Ex = pkg.sharding.KeyChunkExchange
+    for L, world in ((192, 8), (512, 8), (192, 3), (128, 2), (64, 4), (1024, 5)):
+        kv = pkg.sharding.equal_row_ranges(L, world, multiple=64)
+        for rank in range(world):
+            for rounds in range(world + 1):
+                ex = object.__new__(Ex)
+                ex.L, ex.world, ex.rank, ex.kv_ranges = L, world, rank, kv
+                p1, p2 = ex.two_phase_ranges(rounds)
+                covered = np.zeros(L, dtype=int)
+                for rng in (p1, p2):
+                    if rng is None or rng[0] == rng[1]:
+                        continue
+                    a, b = rng
+                    assert a % 64 == 0 and (b % 64 == 0 or b == L)
+                    if a < b:
+                        covered[a:b] += 1
+                    else:
+                        covered[a:] += 1
+                        covered[:b] += 1
+                assert (covered == 1).all(), (L, world, rank, rounds, p1, p2)
+                # pass 1 reads only chunks that have arrived after `rounds` rounds
+                offs = pkg.sharding.exchange_offsets(world)[:min(rounds, world - 1)]
+                have = np.zeros(L, dtype=bool)
+                for r in [rank] + [(rank - o) % world for o in offs]:
+                    have[kv[r][0]:kv[r][1]] = True
+                if p1[0] != p1[1]:
+                    a, b = p1
+                    inside = np.zeros(L, dtype=bool)
+                    if a < b:
+                        inside[a:b] = True
+                    else:
+                        inside[a:] = True
+                        inside[:b] = True
+                    assert have[inside].all(), (L, world, rank, rounds, p1)
