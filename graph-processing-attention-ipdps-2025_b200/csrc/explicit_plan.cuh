@@ -20,14 +20,17 @@
 // Steps 3 and 5 share one walk over the block's entries; the walk of step 5 is repeated only for a block that
 // had a tile demoted in step 3 or 4. Shared memory is kept small enough for four CTAs per SM (the histogram of
 // step 1 and the masks of step 3 share one region; from step 3 on "is this key tile dense, and which slot" is
-// answered by a bit per key tile plus a per-word count).
-// The walks are bound by instruction issue, not by memory: a warp takes a row 128 entries at a time, every lane
-// FOUR CONSECUTIVE entries from one 16-byte load. Whatever concerns neighbouring entries (ascending order, runs of
-// equal mask words or key tiles -- the entries of a row are normally sorted, so a band puts dozens of entries into
-// one word) is settled inside the lane first; the lanes then meet only for the prefix sum that places the residual
-// entries (three ballots over the bits of the per-lane counts) and for one shuffle of the order check. Mask words
-// and counters are updated with one shared-memory atomic per lane-local run; lanes that hit the same word are
-// serialised by the memory pipe, which has the headroom.
+// answered by a byte table over the span of the dense tiles, or by a bit per key tile plus a per-word count when
+// the dense tiles lie more than 255 tiles apart).
+// The walks are bound by instruction issue (the integer pipe), not by memory: a warp takes a row 128 entries at a
+// time, every lane FOUR CONSECUTIVE entries from one 16-byte load, so the ascending-order check and the per-lane
+// count of residual entries are settled inside the lane; the lanes meet only for the prefix sum that places the
+// residual entries (three ballots over the bits of the per-lane counts) and for one shuffle of the order check.
+// A dense entry sets its bit with one shared-memory atomic (entries of one warp instruction lie four apart in the
+// row, so a band puts about eight lanes on one word and the memory pipe, which has the headroom, serialises them);
+// the histogram merges runs of equal key tiles inside a lane first. In blocks whose entries are almost all dense
+// (block-structured masks) a step whose lanes each hold four consecutive columns of one 32-key group is settled
+// with one lookup and one atomic per lane.
 #pragma once
 #include "gather_kernels.cuh"
 #include "spfa_common.cuh"
