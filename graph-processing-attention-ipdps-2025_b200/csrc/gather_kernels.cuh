@@ -15,7 +15,7 @@
 
 namespace spfa {
 
-constexpr int kGatherWarps = 4;  // warps (rows) per CTA
+constexpr int kGatherWarps = 4;  // warps per CTA
 constexpr int kGatherUnroll = 4; // keys in flight per group per step
 
 template <int D>
@@ -207,8 +207,9 @@ __device__ __forceinline__ void nan_fill_row(float* __restrict__ O, int64_t r, i
   }
 }
 
-// One warp per row of the shard, four rows per CTA. Q/m/l/O are indexed by shard-local row; the generator
-// sees the absolute row (row_begin + r).
+// One warp per row of the shard at a time; a CTA of four warps owns up to kMaxRowsPerCta consecutive rows and its
+// warps claim them one by one (gather_rows_cta). Q/m/l/O are indexed by shard-local row; the generator sees the
+// absolute row (row_begin + r).
 //
 // Long rows: a single warp walking thousands of scattered keys is latency bound (one DRAM round trip per
 // step of eight keys), so the longest row of a power-law graph would set the duration of the whole launch.
