@@ -942,10 +942,41 @@ def test_planned_forward_split_along_the_key_axis(capi, orc, L, Lk, d, chunks, s
             assert_state_close(to_np(st), want, TOL_TILED, "cyclic key range and its complement")
 
 
-def test_planned_forward_by_parts(capi, orc):
+def test_batched_slices_with_a_generic_embedded_dimension(capi, orc):
+    """Batch x heads on the generic-d kernels (d = 48): every mask family, every slice against the oracle."""
+    S, L, d = 3, 300, 48
+    rng = np.random.default_rng(0)
+    Qs, Ks, Vs = (rng.standard_normal((S, L, d)).astype(np.float32) for _ in range(3))
+    _, ro, co = random_csr(L, L, 0.05, 3, empty_rows=(4,))
+    rows = np.repeat(np.arange(L, dtype=np.int64), np.diff(ro.astype(np.int64)))
+    G = np.array([5, 17, 200], dtype=np.int32)
+    cases = (
+        ("local", dict(p0=9), lambda q, k, v: orc.implicit_forward("local", q, k, v, 9)),
+        ("local_1d_dilated", dict(p0=5, p1=2), lambda q, k, v: orc.implicit_forward("local_1d_dilated", q, k, v, 5, 2)),
+        ("local_2d_dilated", dict(p0=20, p1=1, use_nan=True),
+         lambda q, k, v: orc.implicit_forward("local_2d_dilated", q, k, v, 20, 1, use_nan=True)),
+        ("global_no_local", dict(global_inds=dev(G), p0=3),
+         lambda q, k, v: orc.implicit_forward("global_no_local", q, k, v, 3, 0, G=G)),
+        ("csr", dict(row_off=dev(ro), col_ind=dev(co.astype(np.int32)), use_nan=True),
+         lambda q, k, v: orc.csr_forward(q, k, v, ro, co, use_nan=True)),
+        ("coo", dict(row_ind=dev(rows), col_ind=dev(co.astype(np.int32)), use_nan=True),
+         lambda q, k, v: orc.csr_forward(q, k, v, ro, co, use_nan=True)),
+    )
+    for kind, kw, want_of in cases:
+        m = torch.full((S, L), float("-inf"), device="cuda")
+        l = torch.zeros((S, L), device="cuda")
+        O = torch.zeros((S, L, d), device="cuda")
+        capi.forward_batched(kind, dev(Qs), dev(Ks), dev(Vs), m, l, O, **kw)
+        for sl in range(S):
+            assert_state_close(to_np((m[sl], l[sl], O[sl])), want_of(Qs[sl], Ks[sl], Vs[sl]), TOL_GATHER,
+                               f"batched d=48 {kind} slice {sl}")
+
+
+@pytest.mark.parametrize("d", [32, 64, 128])
+def test_planned_forward_by_parts(capi, orc, d):
     """Dense tiles of one key range, dense tiles of its (cyclic) complement and the residual entries of all keys, as
     three calls in any order, are the whole planned forward."""
-    L, Lk, d = 640, 1024, 64
+    L, Lk = 640, 1024
     mask = _band_plus_random(L, Lk, 48, 0.01, 12, empty_rows=(2,))
     mask[9, ::2] = True
     row_off, col = _csr_of(mask)
