@@ -905,12 +905,13 @@ def cpu_baseline(job, budget):
 
 def reference_step_fn(job, mods, dev):
     """(step function, note) running the reference's own kernel for this job's mask on the whole job.
-    COO above 65536 rows: the reference COO kernel scans the row-index array once per row (O(L*nnz)) and does not
-    complete; its CSR kernel on the identical mask (row offsets derived from the sorted row indices) stands in."""
+    COO above 32768 rows: the reference COO kernel scans the row-index array once per row (O(L*nnz): 12.4 s per call
+    at 16384 rows of this graph, 51.1 s at 32768, i.e. about 14 hours at 2^20) and does not complete; its CSR kernel on
+    the identical mask (row offsets derived from the sorted row indices) stands in."""
     w_val = torch.ones(1, device=dev)
     st = (job.m, job.l, job.O)
     k, note = job.kind, None
-    if k == "coo" and job.L > 65536:
+    if k == "coo" and job.L > 32768:
         row_off = torch.searchsorted(job.mask[0], torch.arange(job.L + 1, device=dev)).contiguous()
         mod = mods("csr")
         if mod is None:
