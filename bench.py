@@ -280,8 +280,10 @@ def parse_args():
                     help="N>1, explicit masks: how K/V chunks travel (default: peer copies where CUDA IPC works, else NCCL)")
     ap.add_argument("--phase1-rounds", type=int, default=None,
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
-                         "(default: not this schedule but run_tiles_first -- inspection and the own chunk's dense tiles overlap the "
-                         "exchange, everything else follows it; N-1 = a single pass after the exchange)")
+                         "(default N-1: a single pass after the exchange, with the mask inspection overlapping it)")
+    ap.add_argument("--tiles-first", action="store_true",
+                    help="N>1, explicit masks: also run the dense tiles of the own key chunk during the exchange "
+                         "(sharding.KeyChunkExchange.run_tiles_first); measured equal to or slightly behind the default")
     ap.add_argument("--shard-of", type=int, default=0,
                     help="one process, one GPU: time only the first rank's share of an N-way strong-scaling split with K/V "
                          "resident (profiling the per-rank kernels without N GPUs); implies --no-e2e --no-cpu-baseline")
@@ -600,7 +602,7 @@ def run_ours(args, rank, world, dev):
             plan_buf = job.plan if job.plan is not None else job.build_plan(capi)
             before = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
 
-            if args.phase1_rounds is None:  # default: dense tiles of the own chunk while the other chunks travel
+            if args.tiles_first:  # dense tiles of the own chunk while the other chunks travel
                 def step():
                     ex.run_tiles_first(
                         lambda a, b: capi.planned_forward_parts(job.Q, ex.K, ex.V, job.m, job.l, job.O, plan_buf, a, b,
@@ -611,15 +613,17 @@ def run_ours(args, rank, world, dev):
                                  "the other dense tiles and the residual entries of all keys follow the last round"
                                  % (world - 1, how))
             else:
+                rounds = world - 1 if args.phase1_rounds is None else args.phase1_rounds
+
                 def step():
                     ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O,
                                                                                plan_buf, a, b),
-                                     before, rounds_in_phase1=args.phase1_rounds)
-                p1, p2 = ex.two_phase_ranges(args.phase1_rounds)
+                                     before, rounds_in_phase1=rounds)
+                p1, p2 = ex.two_phase_ranges(rounds)
                 exchange_note = ("%d rounds of %s; the mask inspection overlaps them, and the forward runs as %s" %
                                  (world - 1, how, "one pass after the last round" if p2 is None else
                                   "two passes: one over the keys that have landed after %d round(s) while the other chunks "
-                                  "travel, one over the rest after the last round" % args.phase1_rounds))
+                                  "travel, one over the rest after the last round" % rounds))
         elif explicit:
             def step():
                 ex.exchange_only()
@@ -820,7 +824,7 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
         job.reset_state()
         if overlap:
             inspect = None if args.planned else (lambda: job.build_plan(capi, out=plan_buf))
-            if args.phase1_rounds is None:
+            if args.tiles_first:
                 first = [True]
 
                 def on_tiles(a, b):
@@ -854,8 +858,8 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
     out["e2e"] = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                   "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                   "api": "per rank: K/V chunk and Q rows host->device on a copy stream, " +
-                         ("sharding.KeyChunkExchange (exchange rounds start when the chunk is up; inspection and the own "
-                          "chunk's dense tiles meanwhile, the other tiles and the residual entries after the last round)"
+                         ("sharding.KeyChunkExchange (exchange rounds start when the chunk is up; the mask inspection "
+                          "meanwhile, the forward from the stored plan after the last round)"
                           if overlap else
                           "K/V replication, capi.*_forward(row range)") + ", O rows device->host; bytes are the sum over ranks"}
     return out
