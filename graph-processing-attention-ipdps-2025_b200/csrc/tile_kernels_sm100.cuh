@@ -692,15 +692,26 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int lo2_a = __shfl_sync(kFullMask, lo2_q, 0), lo2_b = __shfl_sync(kFullMask, lo2_q, 31);
     const int hi2_a = __shfl_sync(kFullMask, hi2_q, 0), hi2_b = __shfl_sync(kFullMask, hi2_q, 31);
     const int n_cols = (int)(kv_hi - kv_lo);  // real keys of this CTA's range
-    // The caller's state row is needed only in the epilogue; asking L2 for it now takes its DRAM latency
-    // off the end of the CTA.
+    // The caller's state row is needed only in the epilogue. Its (m, l) are read now, off the end of the CTA, and
+    // decide what the epilogue must fetch: a row whose l is 0 carries no information -- its old O row is multiplied by
+    // 0 -- so the D*4 bytes are neither prefetched nor read (a third of the traffic of a launch whose rows have few
+    // keys). The one exception the reference's arithmetic has, 0 * NaN = NaN for a row that an earlier use_nan call
+    // filled, is kept: the row's first element is looked at, and a row that does not start with a finite value is
+    // read in full like a row with l > 0. Other rows of the launch are never touched by this CTA, and launches that
+    // overlap (prm.overlap) write disjoint rows, so reading the state this early sees its final value.
+    float m_in0 = neg_inf(), l_in0 = 0.f;
+    bool fresh = false;
     if (row_valid && prm.mode != 2 && !listed) {
       const int64_t rl0 = prm.r + uq * prm.s - prm.row_begin;
-      const char* orow = reinterpret_cast<const char*>(O_out + (size_t)rl0 * D);
+      m_in0 = m_out[rl0];
+      l_in0 = l_out[rl0];
+      const float o_first = O_out[(size_t)rl0 * D];
+      fresh = (l_in0 == 0.f) && (fabsf(o_first) <= 3.402823466e38f);
+      if (!fresh) {
+        const char* orow = reinterpret_cast<const char*>(O_out + (size_t)rl0 * D);
 #pragma unroll
-      for (int b = 0; b < D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + b));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(m_out + rl0));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(l_out + rl0));
+        for (int b = 0; b < D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + b));
+      }
     }
     float m_true = neg_inf();   // running maximum of the scaled scores (log2 units)
     float shift = neg_inf();    // reference the exponentials and O are currently expressed against
@@ -877,7 +888,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float rel = fast_exp2(shift - m_true);
           const float l_loc = l_run * rel;
           const float m_loc = m_true * 0.6931471805599453f;
-          const float m_in = m_out[rl], l_in = l_out[rl];
+          const float m_in = m_in0, l_in = l_in0;  // read in the prologue
           const float m_o = fmaxf(m_in, m_loc);
           const float a = l_in * fast_exp2((m_in - m_o) * kLog2e);
           const float bt = fast_exp2((m_loc - m_o) * kLog2e);
@@ -906,6 +917,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr int LPR = D / 4;  // float4 chunks (= lanes) per row
         uint8_t* stage = smem + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
         const uint32_t store_mask = __ballot_sync(kFullMask, store);  // bit = row of this warp (lane <-> row)
+        const uint32_t read_mask = __ballot_sync(kFullMask, store && !fresh);  // rows whose old O row counts
         {
           uint32_t ob[32];
 #pragma unroll
@@ -942,7 +954,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int i = 0; i < NIT; ++i) {
             const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
             oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if ((store_mask >> rw) & 1u) {
+            if ((read_mask >> rw) & 1u) {
               const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
               oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
             }
