@@ -474,6 +474,36 @@ def test_nan_rows_propagate_like_the_reference(capi):
     assert np.isnan(O[dead]).all() and np.isfinite(O[~dead]).all() and np.isfinite(l).all()
 
 
+@pytest.mark.parametrize("d", [32, 64, 128])
+def test_tiled_path_and_an_empty_incoming_state(capi, orc, d):
+    """The tensor-core kernel does not read the old O row of a row whose incoming l is 0 -- unless the row starts with
+    a non-finite value, which is how a NaN-filled row keeps propagating (0 * NaN). Rows with l > 0 are merged as ever."""
+    L, w = 640, 40
+    Q, K, V = seeded_qkv(L, d, 21)
+    want_fresh = orc.implicit_forward("local", Q, K, V, w)
+    capi.set_path(capi.PATH_TILED)
+    # (a) l = 0, m = -inf, finite junk in O: the junk is multiplied by 0 either way
+    st = capi.new_state(L, d)
+    st[2].copy_(torch.randn(L, d, device="cuda") * 100)
+    capi.local_forward(dev(Q), dev(K), dev(V), *st, w)
+    assert capi.last_path() == capi.PATH_TILED
+    assert_state_close(to_np(st), want_fresh, TOL_TILED, "junk O under an empty state")
+    # (b) rows NaN-filled by an earlier use_nan call stay NaN; their neighbours in the same tile do not
+    st = capi.new_state(L, d)
+    capi.local_2d_dilated_forward(dev(Q), dev(K), dev(V), *st, 16, 1, use_nan=True)
+    first = to_np(st)
+    capi.set_path(capi.PATH_TILED)
+    capi.local_forward(dev(Q), dev(K), dev(V), *st, w)
+    assert capi.last_path() == capi.PATH_TILED
+    m, l, O = to_np(st)
+    dead = (np.arange(L) % 16) % 2 == 1
+    assert np.isnan(O[dead]).all() and np.isfinite(O[~dead]).all()
+    want = orc.implicit_forward("local", Q, K, V, w, state=tuple(x.copy() for x in first))
+    np.testing.assert_allclose(O[~dead], want[2][~dead], rtol=0, atol=TOL_TILED)
+    np.testing.assert_allclose(l, want[1], rtol=4e-3, atol=TOL_TILED)
+    capi.set_path(capi.PATH_AUTO)
+
+
 def test_duplicate_and_out_of_range_global_indices(capi, orc):
     L, d, w = 300, 64, 4
     Q, K, V = seeded_qkv(L, d, 12)
