@@ -698,20 +698,24 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // keys). The one exception the reference's arithmetic has, 0 * NaN = NaN for a row that an earlier use_nan call
     // filled, is kept: the row's first element is looked at, and a row that does not start with a finite value is
     // read in full like a row with l > 0. Other rows of the launch are never touched by this CTA, and launches that
-    // overlap (prm.overlap) write disjoint rows, so reading the state this early sees its final value.
-    float m_in0 = neg_inf(), l_in0 = 0.f;
-    bool fresh = false;
-    if (row_valid && prm.mode != 2 && !listed) {
-      const int64_t rl0 = prm.r + uq * prm.s - prm.row_begin;
-      m_in0 = m_out[rl0];
-      l_in0 = l_out[rl0];
-      const float o_first = O_out[(size_t)rl0 * D];
-      fresh = (l_in0 == 0.f) && (fabsf(o_first) <= 3.402823466e38f);
-      if (!fresh) {
-        const char* orow = reinterpret_cast<const char*>(O_out + (size_t)rl0 * D);
+    // overlap (prm.overlap) write disjoint rows, so reading the state this early sees its final value. A CTA with
+    // many key tiles looks at the three values right away (its softmax warps wait for the first S tile anyway); one with
+    // a handful of tiles only issues the loads here and looks at them after its first tile, so that their latency does
+    // not hold that tile up.
+    const bool has_state = row_valid && prm.mode != 2 && !listed;
+    float m_in0 = neg_inf(), l_in0 = 0.f, o_first = 0.f;
+    auto prefetch_old_row = [&]() {
+      if (has_state && !((l_in0 == 0.f) && (fabsf(o_first) <= 3.402823466e38f))) {
+        const char* orow = reinterpret_cast<const char*>(O_out + (size_t)(prm.r + uq * prm.s - prm.row_begin) * D);
 #pragma unroll
         for (int b = 0; b < D * 4; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(orow + b));
       }
+    };
+    if (has_state) {
+      const int64_t rl0 = prm.r + uq * prm.s - prm.row_begin;
+      m_in0 = m_out[rl0];
+      l_in0 = l_out[rl0];
+      o_first = O_out[(size_t)rl0 * D];
     }
     float m_true = neg_inf();   // running maximum of the scaled scores (log2 units)
     float shift = neg_inf();    // reference the exponentials and O are currently expressed against
@@ -721,6 +725,8 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int n_band = j1[x] - j0[x];
     const int nx = EXPL ? __popcll(act[x]) : (n_band + ((jl[x] != 0x7fffffff) ? (nT - nTb) : 0));
     const float sc = prm.scale_log2e;
+    const bool early_look = nx > 6;  // uniform over the softmax group
+    if (early_look) prefetch_old_row();
     uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
     const uint32_t* xm = nullptr;
     if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
@@ -854,7 +860,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       mbar_arrive(bar(B_PREADY + sb));
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      if (it == 0 && !early_look) prefetch_old_row();
     }
+    const bool fresh = (l_in0 == 0.f) && (fabsf(o_first) <= 3.402823466e38f);  // the incoming state of this row is empty
     // ---- epilogue: O row from TMEM, normalised and merged with the caller's (m, l, O) ----
     if (nx > 0) {  // uniform over the softmax group, so the group barriers below are safe
       // both tile parities: the PVs of the last two tiles
