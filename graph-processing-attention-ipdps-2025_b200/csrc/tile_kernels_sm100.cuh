@@ -422,13 +422,31 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (EXPL && warp == 1) {
+    // Merge the ascending dense-tile lists of the CTA's sub-tiles into one ascending list of key tiles. The lists are
+    // fetched by the whole warp first (one entry per lane, kMaxDenseTiles = 32) into the Q region, which stays free
+    // until the barrier below: a single thread walking them in global memory paid a round trip per entry.
+    static_assert(kMaxDenseTiles <= 32, "one list entry per lane");
+    int* s_list = reinterpret_cast<int*>(smem + P::kOffQ);
+    {
+      const int64_t n_blocks_w = (prm.n_q + 127) / 128;
+#pragma unroll
+      for (int x = 0; x < NSUB; ++x) {
+        const int64_t b = (int64_t)blockIdx.x * NSUB + x;
+        int nx_w = (b < n_blocks_w) ? prm.x_nt[b] : 0;
+        if (nx_w > kMaxDenseTiles) nx_w = kMaxDenseTiles;
+        s_list[x * 32 + lane] = (lane < nx_w) ? __ldg(prm.x_kt + b * kMaxDenseTiles + lane) : 0x7fffffff;
+      }
+    }
+    __syncwarp();
+  }
   if (EXPL && threadIdx.x == 32) {
-    // Merge the ascending dense-tile lists of the CTA's sub-tiles into one ascending list of key tiles.
     int* kt = reinterpret_cast<int*>(smem + P::kOffX + P::kXKt);
     uint64_t* s_act = reinterpret_cast<uint64_t*>(smem + P::kOffX + P::kXAct);
     const int64_t n_blocks = (prm.n_q + 127) / 128;
     int n[NSUB], pos[NSUB];
     const int* list[NSUB];
+    const int* s_list_ro = reinterpret_cast<const int*>(smem + P::kOffQ);
     uint64_t a[NSUB];
     uint8_t* s_pos = smem + P::kOffX + P::kXPos;
     // key tiles this launch works on: [lo, hi), or the cyclic range [lo, inf) + [0, hi) when lo > hi
@@ -439,7 +457,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int64_t b = (int64_t)blockIdx.x * NSUB + x;
       n[x] = (b < n_blocks) ? prm.x_nt[b] : 0;
       if (n[x] > kMaxDenseTiles) n[x] = kMaxDenseTiles;
-      list[x] = prm.x_kt + b * kMaxDenseTiles;
+      list[x] = s_list_ro + x * 32;
       pos[x] = 0;
       a[x] = 0;
       while (pos[x] < n[x] && !wanted(list[x][pos[x]])) ++pos[x];
@@ -731,11 +749,26 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t* xm = nullptr;
     if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
     const uint8_t* x_pos = smem + P::kOffX + P::kXPos + x * 64;  // explicit masks: tile j -> position in the block's list
+    // Explicit masks: the row's mask words of a tile come from global memory and decide the tile's chunk classes, so a
+    // load issued when the tile starts would put a DRAM round trip in front of every tile. They are loaded one tile
+    // ahead instead: the first tile's words travel while Q and the first S are on their way.
+    uint32_t vm_next[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) vm_next[c] = 0u;
+    auto load_masks = [&](int jj) {
+#pragma unroll
+      for (int c = 0; c < NC; ++c) vm_next[c] = __ldg(xm + (size_t)(x_pos[jj] * NC + c) * 128);
+    };
+    if (EXPL && nx > 0) load_masks(__ffsll((long long)rem) - 1);
     for (int it = 0; it < nx && ok; ++it) {
       int j;
+      uint32_t vm_cur[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) vm_cur[c] = vm_next[c];
       if (EXPL) {
         j = __ffsll((long long)rem) - 1;
         rem &= rem - 1;
+        if (rem) load_masks(__ffsll((long long)rem) - 1);
       } else {
         j = (it < n_band) ? (j0[x] + it) : (nTb + it - n_band);
       }
@@ -761,7 +794,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t m_hi = (b >= 31) ? 0xffffffffu : (b < 0 ? 0u : (0xffffffffu >> (31 - b)));
         const uint32_t m_in = m_lo & m_hi;
         if (EXPL) {  // valid = the pair's bit in the plan (masks are stored by the tile's position in the block's own list)
-          const uint32_t vm = __ldg(xm + (size_t)(x_pos[j] * NC + c) * 128);
+          const uint32_t vm = vm_cur[c];
           vmask[c] = vm;
           cls[c] = __all_sync(kFullMask, vm == 0xffffffffu) ? 2 : (__all_sync(kFullMask, vm == 0u) ? 0 : 1);
         } else if (tmode == 0) {  // valid = inside the interval
