@@ -328,6 +328,23 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::kOffMisc + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Explicit masks: the block's tile counts and mask offset are asked for together with the plan's identity block, one
+  // round trip instead of three. The host has checked that the plan region is at least as large as the layout of the
+  // shape the caller passed, so these reads stay inside it even when the identity block turns out to differ.
+  int nt_early[NSUB];
+  long long moff_early = 0;
+#pragma unroll
+  for (int x = 0; x < NSUB; ++x) nt_early[x] = 0;
+  if (EXPL) {
+    const int64_t n_blocks_e = (prm.n_q + 127) / 128;
+#pragma unroll
+    for (int x = 0; x < NSUB; ++x) {
+      const int64_t b = (int64_t)blockIdx.x * NSUB + x;
+      if (b < n_blocks_e) nt_early[x] = prm.x_nt[b];
+    }
+    const int64_t bq = (int64_t)blockIdx.x * NSUB + (((warp >> 2) < NSUB) ? (warp >> 2) : (NSUB - 1));
+    if (bq < n_blocks_e) moff_early = prm.x_moff[bq];
+  }
   if (EXPL) {  // uniform over the CTA: a plan of another shape is not walked at all
     if (!plan_header_matches(prm.x_hdr, prm.x_want)) {
       if (threadIdx.x == 0) atomicCAS(err, 0, kPlanMismatchCode);
@@ -433,8 +450,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int x = 0; x < NSUB; ++x) {
         const int64_t b = (int64_t)blockIdx.x * NSUB + x;
-        int nx_w = (b < n_blocks_w) ? prm.x_nt[b] : 0;
+        int nx_w = (b < n_blocks_w) ? nt_early[x] : 0;
         if (nx_w > kMaxDenseTiles) nx_w = kMaxDenseTiles;
+        if (nx_w < 0) nx_w = 0;
         s_list[x * 32 + lane] = (lane < nx_w) ? __ldg(prm.x_kt + b * kMaxDenseTiles + lane) : 0x7fffffff;
       }
     }
@@ -455,8 +473,9 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
     for (int x = 0; x < NSUB; ++x) {
       const int64_t b = (int64_t)blockIdx.x * NSUB + x;
-      n[x] = (b < n_blocks) ? prm.x_nt[b] : 0;
+      n[x] = (b < n_blocks) ? nt_early[x] : 0;
       if (n[x] > kMaxDenseTiles) n[x] = kMaxDenseTiles;
+      if (n[x] < 0) n[x] = 0;
       list[x] = s_list_ro + x * 32;
       pos[x] = 0;
       a[x] = 0;
@@ -747,7 +766,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (early_look) prefetch_old_row();
     uint64_t rem = act[x];  // explicit masks: tiles of this sub-tile not yet visited
     const uint32_t* xm = nullptr;
-    if (EXPL && nx > 0) xm = prm.x_masks + prm.x_moff[(int64_t)blockIdx.x * NSUB + x] + row;
+    if (EXPL && nx > 0) xm = prm.x_masks + moff_early + row;  // (warp >> 2 == x for the softmax warps)
     const uint8_t* x_pos = smem + P::kOffX + P::kXPos + x * 64;  // explicit masks: tile j -> position in the block's list
     // Explicit masks: the row's mask words of a tile come from global memory and decide the tile's chunk classes, so a
     // load issued when the tile starts would put a DRAM round trip in front of every tile. They are loaded one tile
