@@ -1009,29 +1009,37 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
           }
         } else {
-          float4 oin[NIT];
+          // Eight rows-per-instruction steps at a time: enough old rows in flight when they have to be read, and a loop
+          // body small enough to stay in the instruction cache (the epilogue runs once per CTA; fully unrolled it was
+          // a few thousand cold instructions, and instruction fetch showed among the stalls of short CTAs).
+          constexpr int NB = (NIT < 8) ? NIT : 8;
+#pragma unroll 1
+          for (int i0 = 0; i0 < NIT; i0 += NB) {
+            float4 oin[NB];
 #pragma unroll
-          for (int i = 0; i < NIT; ++i) {
-            const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
-            oin[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if ((read_mask >> rw) & 1u) {
-              const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
-              oin[i] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
+            for (int k = 0; k < NB; ++k) {
+              const int rw = (i0 + k) * RPI + lane / LPR, r = wrow0 + rw;
+              oin[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+              if ((read_mask >> rw) & 1u) {
+                const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+                oin[k] = *reinterpret_cast<const float4*>(O_out + (size_t)rl * D + sub * 4);
+              }
             }
-          }
 #pragma unroll
-          for (int i = 0; i < NIT; ++i) {
-            const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
-            const float car = __shfl_sync(kFullMask, ca, rw);  // the row's coefficient lives in the lane that owns the row
-            if ((store_mask >> rw) & 1u) {
-              const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
-              const float4 t = *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
-              float4 o;
-              o.x = fmaf(car, oin[i].x, t.x);
-              o.y = fmaf(car, oin[i].y, t.y);
-              o.z = fmaf(car, oin[i].z, t.z);
-              o.w = fmaf(car, oin[i].w, t.w);
-              *reinterpret_cast<float4*>(O_out + (size_t)rl * D + sub * 4) = o;
+            for (int k = 0; k < NB; ++k) {
+              const int rw = (i0 + k) * RPI + lane / LPR, r = wrow0 + rw;
+              const float car = __shfl_sync(kFullMask, ca, rw);  // the row's coefficient lives in the lane that owns the row
+              if ((store_mask >> rw) & 1u) {
+                const int64_t rl = prm.r + (uq0 + 128 * x + r) * prm.s - prm.row_begin;
+                const float4 t =
+                    *reinterpret_cast<const float4*>(stage + (size_t)r * (D * 4) + ((sub ^ (r & (LPR - 1))) << 4));
+                float4 o;
+                o.x = fmaf(car, oin[k].x, t.x);
+                o.y = fmaf(car, oin[k].y, t.y);
+                o.z = fmaf(car, oin[k].z, t.z);
+                o.w = fmaf(car, oin[k].w, t.w);
+                *reinterpret_cast<float4*>(O_out + (size_t)rl * D + sub * 4) = o;
+              }
             }
           }
         }
