@@ -999,7 +999,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         constexpr int NIT = 32 / RPI;    // instructions for this warp's 32 rows
         const int wrow0 = (warp & 3) * 32, sub = lane % LPR;
         if (partial_out) {
-#pragma unroll
+#pragma unroll 4
           for (int i = 0; i < NIT; ++i) {
             const int rw = i * RPI + lane / LPR, r = wrow0 + rw;
             if ((store_mask >> rw) & 1u) {
