@@ -370,13 +370,15 @@ int launch_from_plan(const float* Q, const float* K, const float* V, const uint6
   prm.x_want = want;
   prm.x_kt_lo = whole ? 0 : (int)(key_begin / BN);
   prm.x_kt_hi = whole ? 0x7fffffff : (int)((key_end + BN - 1) / BN);
-  CUtensorMap tmQ, tmK, tmV;
+  CUtensorMap tmQ, tmK, tmV, tmO;
   const int64_t pitch = D * (int64_t)sizeof(float);
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, Lk, pitch, BN) ||
-      !make_row_map(&tmV, V, D, Lk, pitch, BN, /*mn_major=*/true))
+      !make_row_map(&tmV, V, D, Lk, pitch, BN, /*mn_major=*/true) ||
+      !make_row_map(&tmO, O, D, n_rows, pitch, 128, false, 1, 0, true))
     return SPFA_ERR_LAUNCH;
   if (parts & 1) {
-    int rc = launch_band_raw<D, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st);
+    int rc = launch_band_raw<D, true>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + kRows - 1) / kRows)), st,
+                                      nullptr, nullptr, &tmO);
     if (rc) return rc;
     g_last_path.store(SPFA_PATH_TILED);
   }

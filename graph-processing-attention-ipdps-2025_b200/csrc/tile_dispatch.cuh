@@ -79,7 +79,7 @@ inline TensorMapEncodeTiledFn tensor_map_encoder() {
 // MN-major V operand). Rows outside [0, rows) read as zeros.
 // `slices` such matrices lie `slice_bytes` apart (a batch of heads); the third coordinate of a load picks one.
 inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows, int64_t pitch_bytes, int box_rows,
-                         bool mn_major = false, int64_t slices = 1, int64_t slice_bytes = 0) {
+                         bool mn_major = false, int64_t slices = 1, int64_t slice_bytes = 0, bool plain_f32 = false) {
   TensorMapEncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return false;
   if (slices <= 1 || slice_bytes <= 0) {
@@ -90,7 +90,9 @@ inline bool make_row_map(CUtensorMap* tm, const float* base, int d, int64_t rows
   cuuint64_t strides[2] = {(cuuint64_t)pitch_bytes, (cuuint64_t)slice_bytes};
   cuuint32_t box[3] = {32u, (cuuint32_t)box_rows, 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
-  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+  // plain_f32: the map of an output tensor (bulk stores of fp32 values); the operand maps are typed tf32
+  return enc(tm, plain_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3,
+             const_cast<float*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -124,10 +126,13 @@ bool band_kernel_usable() {
 // pair is handed to the kernel twice.
 template <int D, bool EXPL = false, class C = TileCfg<D>>
 int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, float* m, float* l, float* O,
-                    const tile::BandParams& prm, dim3 grid, cudaStream_t st, const CUtensorMap* tmK2p = nullptr,
-                    const CUtensorMap* tmV2p = nullptr) {
+                    const tile::BandParams& prm_in, dim3 grid, cudaStream_t st, const CUtensorMap* tmK2p = nullptr,
+                    const CUtensorMap* tmV2p = nullptr, const CUtensorMap* tmOp = nullptr) {
   const CUtensorMap& tmK2 = tmK2p ? *tmK2p : tmK;
   const CUtensorMap& tmV2 = tmV2p ? *tmV2p : tmV;
+  const CUtensorMap& tmO = tmOp ? *tmOp : tmQ;  // O's map (Q's geometry) enables the bulk store of finished tiles
+  tile::BandParams prm = prm_in;
+  prm.tma_store = tmOp ? 1 : 0;
   constexpr int NSUB = C::NSUB;
   using P = tile::Plan<D, C::BN, C::NS, NSUB, C::NSV>;
   using G = tile::Geo<NSUB>;
@@ -148,9 +153,10 @@ int launch_band_raw(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtens
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmK2, tmV2, m, l, O, prm, err) != cudaSuccess) return SPFA_ERR_LAUNCH;
+    if (cudaLaunchKernelEx(&cfg, kern, tmQ, tmK, tmV, tmK2, tmV2, tmO, m, l, O, prm, err) != cudaSuccess)
+      return SPFA_ERR_LAUNCH;
   } else {
-    kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, tmK2, tmV2, m, l, O, prm, err);
+    kern<<<grid, G::kThreads, P::kDynSmem, st>>>(tmQ, tmK, tmV, tmK2, tmV2, tmO, m, l, O, prm, err);
   }
   g_launches.fetch_add(1);
   return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
@@ -180,17 +186,19 @@ int launch_band(const float* Q, const float* K, const float* V, float* m, float*
     prm.scale_log2e = (1.0f / sqrtf((float)D)) * kLog2e;
     prm.slice_o = (row_end - row_begin) * D;
     prm.slice_ml = row_end - row_begin;
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmO;
     const int64_t pitch = s * D * (int64_t)sizeof(float);
     const int64_t q_slice = (row_end - row_begin) * D * (int64_t)sizeof(float), kv_slice = L * D * (int64_t)sizeof(float);
     if (!make_row_map(&tmQ, Q + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128, false, n_slices, q_slice) ||
+        !make_row_map(&tmO, O + (r + u_first * s - row_begin) * D, D, prm.n_q, pitch, 128, false, n_slices, q_slice, true) ||
         !make_row_map(&tmK, K + r * D, D, prm.n_keys, pitch, BN, false, n_slices, kv_slice) ||
         !make_row_map(&tmV, V + r * D, D, prm.n_keys, pitch, BN, /*mn_major=*/true, n_slices, kv_slice))
       return SPFA_ERR_LAUNCH;
     const int64_t grid = (prm.n_q + C::kRows - 1) / C::kRows;
     if (grid > 0x7fffffffLL || n_slices > 65535) return SPFA_ERR_TOO_LARGE;
     prm.overlap = ((r + 1 < s && r + 1 < L) ? 1 : 0) | (launched ? 2 : 0);
-    const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid, 1, (unsigned)n_slices), st);
+    const int rc = launch_band_raw<D>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)grid, 1, (unsigned)n_slices), st, nullptr,
+                                      nullptr, &tmO);
     if (rc) return rc;
     launched = true;
   }
@@ -345,15 +353,17 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   prm.n_listed = nG;
   prm.u_q_first = row_begin;
   prm.n_q = n_rows;
+  CUtensorMap tmO;
   if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, KG, D, nG, pitch, CR::BN) ||
-      !make_row_map(&tmV, VG, D, nG, pitch, CR::BN, /*mn_major=*/true))
+      !make_row_map(&tmV, VG, D, nG, pitch, CR::BN, /*mn_major=*/true) ||
+      !make_row_map(&tmO, O, D, n_rows, pitch, 128, false, 1, 0, true))
     return SPFA_ERR_LAUNCH;
   int rc = SPFA_OK;
   // the two launches write disjoint things (ordinary rows / partial states of the listed rows): they may overlap
   prm.overlap = 1;
   if (ordinary_rows_too)
     rc = launch_band_raw<D, false, CR>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + CR::kRows - 1) / CR::kRows)),
-                                       st);
+                                       st, nullptr, nullptr, &tmO);
   if (rc) return rc;
   // mode 2: the gathered global rows against every key, key range split over grid.y
   prm.mode = 2;
@@ -429,13 +439,14 @@ int launch_bigbird_tiled(const float* Q, const float* K, const float* V, float* 
   prm.sorted = sorted;
   prm.n_valid = n_valid;
   prm.overlap = 1;  // the strip launch below writes other things (partial states): it may start beside this one
-  CUtensorMap tmQ, tmK, tmV, tmK2, tmV2;
-  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmK, K, D, L, pitch, CB::BN) ||
+  CUtensorMap tmQ, tmK, tmV, tmK2, tmV2, tmO;
+  if (!make_row_map(&tmQ, Q, D, n_rows, pitch, 128) || !make_row_map(&tmO, O, D, n_rows, pitch, 128, false, 1, 0, true) ||
+      !make_row_map(&tmK, K, D, L, pitch, CB::BN) ||
       !make_row_map(&tmV, V, D, L, pitch, CB::BN, /*mn_major=*/true) || !make_row_map(&tmK2, KG, D, nG, pitch, CB::BN) ||
       !make_row_map(&tmV2, VG, D, nG, pitch, CB::BN, /*mn_major=*/true))
     return SPFA_ERR_LAUNCH;
   int rc = launch_band_raw<D, false, CB>(tmQ, tmK, tmV, m, l, O, prm, dim3((unsigned)((n_rows + CB::kRows - 1) / CB::kRows)),
-                                         st, &tmK2, &tmV2);
+                                         st, &tmK2, &tmV2, &tmO);
   if (rc) return rc;
   prm.mode = 2;
   prm.overlap = 2;

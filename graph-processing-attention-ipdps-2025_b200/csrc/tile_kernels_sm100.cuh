@@ -111,6 +111,8 @@ struct BandParams {
   // before touching the tables above), and the range of key tiles [x_kt_lo, x_kt_hi) this launch works on (a
   // forward split along the key axis runs one launch per range; the whole mask is [0, INT_MAX); x_kt_lo > x_kt_hi
   // names the cyclic range [x_kt_lo, INT_MAX) + [0, x_kt_hi))
+  // ---- bulk store of finished O tiles: set when the launch carries a tensor map of O with Q's geometry (tmO) ----
+  int tma_store;
   const PlanHeader* x_hdr;
   PlanHeader x_want;
   int x_kt_lo, x_kt_hi;
@@ -307,8 +309,9 @@ template <int D, int BN, int NS, int NSUB, bool EXPL = false, int NSV = NS>
 __global__ void __launch_bounds__(Geo<NSUB>::kThreads, Geo<NSUB>::kCtasPerSm)
 band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmK2,
-                    const __grid_constant__ CUtensorMap tmV2, float* __restrict__ m_base, float* __restrict__ l_base,
-                    float* __restrict__ O_base, const BandParams prm, int* __restrict__ err) {
+                    const __grid_constant__ CUtensorMap tmV2, const __grid_constant__ CUtensorMap tmO,
+                    float* __restrict__ m_base, float* __restrict__ l_base, float* __restrict__ O_base,
+                    const BandParams prm, int* __restrict__ err) {
   const int32_t zs = (int32_t)blockIdx.z;  // slice of a batched call
   float* __restrict__ m_out = m_base + (size_t)zs * prm.slice_ml;
   float* __restrict__ l_out = l_base + (size_t)zs * prm.slice_ml;
@@ -971,11 +974,56 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             part[D + 1] = 0.f;
           }
         }
+        constexpr int LPR = D / 4;  // float4 chunks (= lanes) per row
+        uint8_t* stage = smem + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
+        // A sub-tile whose rows all carry an empty incoming state (the usual first call on a state) needs no merge:
+        // cb * O_tmem IS the output. It is staged in the layout of the Q tile it replaces (32-column boxes of 128
+        // rows, 128-byte swizzle) and leaves as D/32 bulk tensor stores issued by one thread: the per-thread path below
+        // moves a 128 x D tile as 128 row-sized store instructions per warp, which the SM's store path takes at about
+        // 32 bytes per cycle -- a fifth of a short CTA's life. Rows past the end of the shard are clipped by the tensor
+        // map; a sub-tile with a row that must not be written (a listed row, a row without keys) or that has old state
+        // takes the per-thread path.
+        bool bulk = false;
+        if (prm.tma_store && !partial_out) {
+          uint32_t all_plain;
+          asm volatile(
+              "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, %2, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+              : "=r"(all_plain)
+              : "r"((uint32_t)(!row_valid || (store && fresh))), "r"(1 + x)
+              : "memory");
+          bulk = all_plain != 0;
+        }
+        if (bulk) {
+          uint32_t ob[32];
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            tmem_ld32(tO + c * 32, ob);
+            tc_wait_ld();
+            uint8_t* box = stage + c * P::kQChunkBytes + (size_t)row * 128;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float4 v4 = make_float4(cb * __uint_as_float(ob[4 * e + 0]), cb * __uint_as_float(ob[4 * e + 1]),
+                                      cb * __uint_as_float(ob[4 * e + 2]), cb * __uint_as_float(ob[4 * e + 3]));
+              *reinterpret_cast<float4*>(box + ((e ^ (row & 7)) << 4)) = v4;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stores above, to the bulk-copy engine
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+          if (row == 0) {
+            const int32_t yq = (int32_t)(uq0 - prm.u_q_first) + 128 * x;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c)
+              asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+                               reinterpret_cast<uint64_t>(&tmO)),
+                           "r"(c * 32), "r"(yq), "r"(zs), "r"(sbase + P::kOffQ + (x * P::kChunks + c) * P::kQChunkBytes)
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory is read out before the CTA ends
+          }
+        } else {
         // Stage cb * O_tmem in shared memory (this sub-tile's Q region is dead: all its S MMAs completed
         // before the last PV), 16-byte chunks XOR-swizzled by the row so that both the row-per-thread
         // writes here and the row-per-lane-group reads below spread over the banks.
-        constexpr int LPR = D / 4;  // float4 chunks (= lanes) per row
-        uint8_t* stage = smem + P::kOffQ + x * P::kChunks * P::kQChunkBytes;
         const uint32_t store_mask = __ballot_sync(kFullMask, store);  // bit = row of this warp (lane <-> row)
         const uint32_t read_mask = __ballot_sync(kFullMask, store && !fresh);  // rows whose old O row counts
         {
@@ -1043,6 +1091,7 @@ band_forward_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
           }
         }
+        }  // per-thread path
       }
     }
   }
