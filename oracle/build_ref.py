@@ -1,7 +1,7 @@
 """Compile the reference's own six CUDA extensions for sm_100a, from the sources where they lie.
 
 TEST INFRASTRUCTURE ONLY (side-by-side comparator and the benchmark's reference arm). Nothing is
-copied: nvcc/g++ read the reference tree directly (SPFA_REFERENCE_DIR, default /root/reference) and
+copied: nvcc/g++ read the reference tree directly (its location: environment variable SPFA_REFERENCE_DIR) and
 write only into oracle/_ref/ (git-ignored). The sources are compiled unmodified; ref_shim.h is
 force-included to make one dispatch macro accept the argument the reference passes.
 

@@ -2,7 +2,7 @@
 
 The reference ships no golden vectors; its only test is verification/verify.py, which needs a GPU and
 the six compiled modules. This generator runs that script unmodified (read from the reference tree,
-SPFA_REFERENCE_DIR, default /root/reference) on CPU tensors with:
+its location: environment variable SPFA_REFERENCE_DIR) on CPU tensors with:
 
   * torch/random seeded, so the run is reproducible;
   * stand-in modules spfa_csr/.../spfa_global_no_local whose forward() is the CPU oracle
