@@ -234,8 +234,34 @@ constexpr int kGnlTiledMaxGlobals = 1024;
 // see ~L keys each, go through the tiles).
 constexpr int kGnlTiledMinGlobalsForRows = 32;
 
+// One warp per sorted entry: copies the entry's K and V rows (always) and its Q row (if the row belongs to
+// this shard) into the contiguous scratch; entries that are invalid get zero rows. live[e] = 1 for the first
+// occurrence of a row that lies in the shard (the combine pass writes exactly those rows).
+struct GnlGatherArgs {
+  const float *Q, *K, *V;
+  int d;
+  int64_t row_begin, row_end;
+  float *QG, *KG, *VG;
+  uint8_t* live;
+};
+
+__device__ __forceinline__ void gnl_gather_entry(const int32_t* sorted, int e, int lane, const GnlGatherArgs& a) {
+  const int32_t g = sorted[e];
+  const bool valid = g != 0x7fffffff;
+  const bool mine = valid && g >= a.row_begin && g < a.row_end;
+  const bool first = (e == 0) || (sorted[e - 1] != g);
+  for (int c = lane * 4; c < a.d; c += 128) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(a.KG + (size_t)e * a.d + c) = valid ? ldg4(a.K + (size_t)g * a.d + c) : z;
+    *reinterpret_cast<float4*>(a.VG + (size_t)e * a.d + c) = valid ? ldg4(a.V + (size_t)g * a.d + c) : z;
+    *reinterpret_cast<float4*>(a.QG + (size_t)e * a.d + c) = mine ? ldg4(a.Q + (size_t)(g - a.row_begin) * a.d + c) : z;
+  }
+  if (lane == 0) a.live[e] = (mine && first) ? 1 : 0;
+}
+
+template <bool GATHER>
 __global__ void gnl_sort_globals_kernel(const int32_t* __restrict__ G, int nG, int64_t L, int32_t* __restrict__ sorted,
-                                        int32_t* __restrict__ n_valid) {
+                                        int32_t* __restrict__ n_valid, const GnlGatherArgs ga) {
   __shared__ int32_t g[kGnlTiledMaxGlobals];
   __shared__ int cnt;
   const int t = threadIdx.x;
@@ -255,28 +281,33 @@ __global__ void gnl_sort_globals_kernel(const int32_t* __restrict__ G, int nG, i
   }
   __syncthreads();
   if (t == 0) *n_valid = cnt;
+  if (GATHER)  // the order is complete (the barrier above orders this CTA's writes of `sorted`): copy the rows
+    for (int e = t >> 5; e < nG; e += kGnlTiledMaxGlobals / 32) gnl_gather_entry(sorted, e, t & 31, ga);
 }
 
-// One warp per sorted entry: copies the entry's K and V rows (always) and its Q row (if the row belongs to
-// this shard) into the contiguous scratch; entries that are invalid get zero rows. live[e] = 1 for the first
-// occurrence of a row that lies in the shard (the combine pass writes exactly those rows).
-__global__ void gnl_gather_globals_kernel(const int32_t* __restrict__ sorted, int nG, const float* __restrict__ Q,
-                                          const float* __restrict__ K, const float* __restrict__ V, int d,
-                                          int64_t row_begin, int64_t row_end, float* __restrict__ QG,
-                                          float* __restrict__ KG, float* __restrict__ VG, uint8_t* __restrict__ live) {
+__global__ void gnl_gather_globals_kernel(const int32_t* __restrict__ sorted, int nG, const GnlGatherArgs a) {
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (e >= nG) return;
-  const int32_t g = sorted[e];
-  const bool valid = g != 0x7fffffff;
-  const bool mine = valid && g >= row_begin && g < row_end;
-  const bool first = (e == 0) || (sorted[e - 1] != g);
-  for (int c = lane * 4; c < d; c += 128) {
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4*>(KG + (size_t)e * d + c) = valid ? ldg4(K + (size_t)g * d + c) : z;
-    *reinterpret_cast<float4*>(VG + (size_t)e * d + c) = valid ? ldg4(V + (size_t)g * d + c) : z;
-    *reinterpret_cast<float4*>(QG + (size_t)e * d + c) = mine ? ldg4(Q + (size_t)(g - row_begin) * d + c) : z;
+  gnl_gather_entry(sorted, e, lane, a);
+}
+
+// Short lists (the usual case: tens of global tokens) are sorted and gathered by ONE launch: the sorting CTA's 32 warps
+// copy the rows themselves once the order is known; a second tiny launch costs more than the copies.
+constexpr int kGnlFusedGatherMax = 128;
+
+// Sorts the listed rows and gathers their Q/K/V rows: one launch for short lists, two for long ones.
+inline int launch_gnl_sort_gather(const int32_t* G, int64_t nG, int64_t L, int32_t* sorted, int32_t* n_valid,
+                                  const GnlGatherArgs& ga, cudaStream_t st) {
+  if (nG <= kGnlFusedGatherMax) {
+    gnl_sort_globals_kernel<true><<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid, ga);
+    g_launches.fetch_add(1);
+  } else {
+    gnl_sort_globals_kernel<false><<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid, ga);
+    g_launches.fetch_add(1);
+    gnl_gather_globals_kernel<<<(unsigned)((nG + 3) / 4), 128, 0, st>>>(sorted, (int)nG, ga);
+    g_launches.fetch_add(1);
   }
-  if (lane == 0) live[e] = (mine && first) ? 1 : 0;
+  return cudaGetLastError() == cudaSuccess ? (int)SPFA_OK : (int)SPFA_ERR_LAUNCH;
 }
 
 struct GnlTiledPlan {
@@ -328,12 +359,8 @@ int launch_gnl_tiled(const float* Q, const float* K, const float* V, float* m, f
   float* KG = reinterpret_cast<float*>(ws + plan.off_kg);
   float* VG = reinterpret_cast<float*>(ws + plan.off_vg);
   float* partials = reinterpret_cast<float*>(ws + plan.off_part);
-  gnl_sort_globals_kernel<<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid);
-  g_launches.fetch_add(1);
-  gnl_gather_globals_kernel<<<(unsigned)((nG + 3) / 4), 128, 0, st>>>(sorted, (int)nG, Q, K, V, D, row_begin, row_end, QG,
-                                                                      KG, VG, live);
-  g_launches.fetch_add(1);
-  if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+  if (launch_gnl_sort_gather(G, nG, L, sorted, n_valid, GnlGatherArgs{Q, K, V, D, row_begin, row_end, QG, KG, VG, live}, st))
+    return SPFA_ERR_LAUNCH;
   using CR = typename GnlRowsCfg<D>::type;  // ordinary rows x listed keys
   using CK = typename GnlKeysCfg<D>::type;  // listed rows x all keys
   const int64_t pitch = D * (int64_t)sizeof(float);
@@ -415,12 +442,8 @@ int launch_bigbird_tiled(const float* Q, const float* K, const float* V, float* 
   float* KG = reinterpret_cast<float*>(ws + plan.off_kg);
   float* VG = reinterpret_cast<float*>(ws + plan.off_vg);
   float* partials = reinterpret_cast<float*>(ws + plan.off_part);
-  gnl_sort_globals_kernel<<<1, kGnlTiledMaxGlobals, 0, st>>>(G, (int)nG, L, sorted, n_valid);
-  g_launches.fetch_add(1);
-  gnl_gather_globals_kernel<<<(unsigned)((nG + 3) / 4), 128, 0, st>>>(sorted, (int)nG, Q, K, V, D, row_begin, row_end, QG,
-                                                                      KG, VG, live);
-  g_launches.fetch_add(1);
-  if (cudaGetLastError() != cudaSuccess) return SPFA_ERR_LAUNCH;
+  if (launch_gnl_sort_gather(G, nG, L, sorted, n_valid, GnlGatherArgs{Q, K, V, D, row_begin, row_end, QG, KG, VG, live}, st))
+    return SPFA_ERR_LAUNCH;
   using CB = TileCfg<D>;                    // band + listed keys, every row of the shard
   using CK = typename GnlKeysCfg<D>::type;  // listed rows x all keys
   const int64_t pitch = D * (int64_t)sizeof(float);
