@@ -280,7 +280,8 @@ def parse_args():
                     help="N>1, explicit masks: how K/V chunks travel (default: peer copies where CUDA IPC works, else NCCL)")
     ap.add_argument("--phase1-rounds", type=int, default=None,
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
-                         "(default N-1: a single pass after the exchange, with the mask inspection overlapping it)")
+                         "(default: N-1 up to 4 GPUs = a single pass after the exchange, with the mask inspection overlapping it; "
+                         "about 4/7 of the rounds from 8 GPUs on)")
     ap.add_argument("--tiles-first", action="store_true",
                     help="N>1, explicit masks: also run the dense tiles of the own key chunk during the exchange "
                          "(sharding.KeyChunkExchange.run_tiles_first); measured equal to or slightly behind the default")
@@ -613,7 +614,7 @@ def run_ours(args, rank, world, dev):
                                  "the other dense tiles and the residual entries of all keys follow the last round"
                                  % (world - 1, how))
             else:
-                rounds = world - 1 if args.phase1_rounds is None else args.phase1_rounds
+                rounds = sh.default_rounds_in_phase1(world) if args.phase1_rounds is None else args.phase1_rounds
 
                 def step():
                     ex.run_two_phase(lambda a, b, i: capi.planned_forward_keys(job.Q, ex.K, ex.V, job.m, job.l, job.O,

@@ -118,6 +118,14 @@ def exchange_offsets(world: int) -> list[int]:
     return out
 
 
+def default_rounds_in_phase1(world: int) -> int:
+    """Rounds of the K/V exchange before the first pass of a forward cut in two along the key axis. Up to 4 ranks: all of
+    them, i.e. ONE pass after the exchange (measured best on 2 and 4 GPUs: an extra pass revisits every row of a large
+    shard). From 8 ranks on a shard is small enough for two passes to pay: about 4/7 of the rounds, then the rest
+    (8 GPUs: 1.22 against 1.28 ms)."""
+    return world - 1 if world <= 4 else (4 * (world - 1) + 6) // 7
+
+
 class KeyChunkExchange:
     """K/V replication overlapped with the forward, for operators that can work on one range of keys at a time.
 
@@ -315,11 +323,12 @@ class KeyChunkExchange:
         have landed after `rounds_in_phase1` rounds, pass 2 over the rest once every round is done. Short per-row key
         lists make a pass cost far more than its share of the keys (every pass revisits every row: its offsets, its Q
         row, its running state), so few large passes beat many small ones, and on 4 GPUs one pass after the last round
-        (with the mask inspection overlapping the rounds) beat every two-pass split measured; that is what
-        `rounds_in_phase1 = None` picks. 0 rounds means "own chunk first", world-1 or more a single pass.
+        (with the mask inspection overlapping the rounds) beat every two-pass split measured, while on 8 GPUs four rounds
+        before the first pass won by 4 %; `rounds_in_phase1 = None` picks accordingly (default_rounds_in_phase1).
+        0 rounds means "own chunk first", world-1 or more a single pass.
         on_keys(key_begin, key_end, i)."""
         if rounds_in_phase1 is None:
-            rounds_in_phase1 = self.world - 1
+            rounds_in_phase1 = default_rounds_in_phase1(self.world)
         p1, p2 = self.two_phase_ranges(rounds_in_phase1)
         k = min(rounds_in_phase1, self.world - 1) if p2 is not None else self.world - 1
         if not self.cuda:
