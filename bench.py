@@ -282,6 +282,8 @@ def parse_args():
                     help="N>1, explicit masks: exchange rounds after which the first of the two forward passes starts "
                          "(default: N-1 up to 4 GPUs = a single pass after the exchange, with the mask inspection overlapping it; "
                          "about 4/7 of the rounds from 8 GPUs on)")
+    ap.add_argument("--e2e-chunks", type=int, default=8,
+                    help="row chunks of the host pipeline for masks whose rows may need any key (end-to-end leg, 1 GPU)")
     ap.add_argument("--tiles-first", action="store_true",
                     help="N>1, explicit masks: also run the dense tiles of the own key chunk during the exchange "
                          "(sharding.KeyChunkExchange.run_tiles_first); measured equal to or slightly behind the default")
@@ -722,7 +724,8 @@ def run_e2e(args, pkg, capi, job, ex, rank, world, dev, total_flops):
         if banded and big and not args.planned:
             pipe = pkg.hostio.BandedHostPipeline(job.kind, job.L, job.d, job.p0, job.p1, n_chunks=8, device=dev)
         elif not args.planned and ((banded and job.L * job.d * 4 >= (8 << 20)) or (not banded and big)):
-            full_pipe = pkg.hostio.FullKeyHostPipeline(job.L, job.L, job.d, n_chunks=3 if banded else 8, device=dev)
+            full_pipe = pkg.hostio.FullKeyHostPipeline(job.L, job.L, job.d, n_chunks=3 if banded else args.e2e_chunks,
+                                                       device=dev)
             if banded:
                 def chunk_call(a, b, q, k, v, m_, l_, o_):
                     if job.kind == "local":
