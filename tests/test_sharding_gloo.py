@@ -264,3 +264,10 @@ def test_two_phase_ranges_partition_the_keys_even_with_empty_chunks(pkg):
                         inside[a:] = True
                         inside[:b] = True
                     assert have[inside].all(), (L, world, rank, rounds, p1)
+
+
+def test_default_schedule_of_the_sharded_forward(pkg):
+    """One pass after the exchange up to four ranks; from eight ranks on a first pass after about 4/7 of the rounds."""
+    f = pkg.sharding.default_rounds_in_phase1
+    assert [f(w) for w in (1, 2, 3, 4)] == [0, 1, 2, 3]  # world - 1: everything in the first pass
+    assert f(8) == 4 and 0 < f(16) < 15
